@@ -1,0 +1,206 @@
+/*
+ * superl8_b200 -- C ABI of the B200 (sm_100a) INT8 attention engine.
+ *
+ * The library replaces, for one hot path only, the compiled operators that the
+ * reference binds into its `superl8._C` module (reference csrc/fni8_api.cpp:213-291):
+ * the per-row symmetric int8 quantiser, the int8-QK FlashAttention-2 forward and
+ * the split-KV int8-K / fp16-V decode.  Every entry point takes plain device
+ * pointers, sizes and a CUDA stream (passed as void*); none of them allocates
+ * device memory unless its comment says so: callers own inputs, outputs and the
+ * workspace.  All launches are asynchronous on the given stream.  Return value:
+ * SL8_OK or a negative SL8_ERR_* code; sl8_status_string() names it.
+ *
+ * Tensor layout everywhere: [B, H, S, D] contiguous, head dim innermost, exactly
+ * the reference layout (reference csrc/include/attn_int8_fwd.cuh:47-58).
+ */
+#ifndef SUPERL8_B200_H_
+#define SUPERL8_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SL8_ABI_VERSION 1
+
+/* ---- status codes ------------------------------------------------------- */
+#define SL8_OK 0
+#define SL8_ERR_BAD_HEAD_DIM (-1)   /* reference: "head dim must be 32/64/72/80/128/256" */
+#define SL8_ERR_BAD_DTYPE (-2)      /* reference: "v must be float16 or bfloat16" */
+#define SL8_ERR_MISALIGNED (-3)     /* pointer not 16-byte aligned (TMA / vector loads) */
+#define SL8_ERR_BAD_NUM_SPLITS (-4) /* reference: "num_splits must be 1..256" */
+#define SL8_ERR_WORKSPACE (-5)      /* workspace null or too small */
+#define SL8_ERR_BAD_SHAPE (-6)      /* negative size, Hq % Hkv != 0, ... */
+#define SL8_ERR_NULL (-7)           /* required pointer is null */
+#define SL8_ERR_CUDA (-8)           /* a CUDA runtime / driver call failed */
+#define SL8_ERR_DEVICE_TIMEOUT (-9) /* a bounded device-side wait expired */
+#define SL8_ERR_UNSUPPORTED (-10)   /* valid request this backend cannot serve */
+#define SL8_ERR_TOO_LARGE (-11)     /* request exceeds a fixed built-in capacity */
+
+/* element types of floating-point tensors */
+#define SL8_F16 0
+#define SL8_BF16 1
+#define SL8_F32 2
+
+/* prefill backends (sl8_fwd_params.backend) */
+#define SL8_BACKEND_AUTO 0
+#define SL8_BACKEND_TCGEN05 1 /* TMA + tcgen05 (D = 64, 128, 256) */
+#define SL8_BACKEND_MMA 2     /* warp-level mma.sync path (every supported D) */
+
+int sl8_abi_version(void);
+const char* sl8_status_string(int status);
+
+/* ---- quantiser ---------------------------------------------------------- */
+
+/*
+ * Per-row symmetric int8 quantisation of x[M, K] (row-major, contiguous).
+ * scale[r] = amax(|x[r,:]|) * float(1/127), 1.0 for an all-zero row;
+ * q[r,c] = clamp(rint(x[r,c] / scale[r]), -127, 127)  (never -128).
+ * Replaces `quantize_i8_rowwise` (reference csrc/kernel/quant_rowwise.cu:84-121,
+ * kernel csrc/include/quant_rowwise.cuh:42-92; binding csrc/fni8_api.cpp:286-291).
+ * M == 0 or K == 0 is a no-op (reference quant_rowwise.cu:96).
+ */
+int sl8_quantize_i8_rowwise(const void* x, int x_dtype, int64_t M, int64_t K,
+                            int8_t* q, float* scale, void* stream);
+
+/*
+ * Q prologue: quantise q[rows, D] like sl8_quantize_i8_rowwise and store the
+ * FOLDED scale  scale * fold  (fold = float(softmax_scale * log2 e)), which is
+ * what the attention kernels consume (reference superl8/quant/core.py:193-195).
+ * If outlier_flag != NULL the kernel also evaluates the reference's accuracy
+ * gate in the same pass (reference superl8/quant/core.py:113-145): a row is
+ * outlier-dominated when  max|q| / (median|q| + 1e-10) > ratio_threshold
+ * (median = lower middle element, as torch.median); *outlier_flag is OR-ed
+ * with 1 when any row is.  The caller zeroes the flag beforehand.
+ * plain_scale (nullable) receives the unfolded scale.
+ */
+int sl8_quant_q_prologue(const void* q, int dtype, int64_t rows, int64_t D, float fold,
+                         float ratio_threshold, int8_t* q_i8, float* q_scale_folded,
+                         float* plain_scale, int32_t* outlier_flag, void* stream);
+
+/*
+ * K prologue, step 1: per-(batch, kv-head) fp32 mean over the keys,
+ * k[BH, N, D] -> mean[BH, D]  (reference superl8/quant/core.py:29-44, 81-85).
+ * seqlens (nullable, int32[B], with heads_per_batch = Hkv) restricts sequence b
+ * to its first seqlens[b] keys.  The sum runs in a fixed order (bitwise
+ * repeatable).  workspace: sl8_k_mean_workspace() bytes.
+ */
+size_t sl8_k_mean_workspace(int64_t BH, int64_t N, int64_t D);
+int sl8_k_mean(const void* k, int dtype, int64_t BH, int64_t N, int64_t D,
+               const int32_t* seqlens, int32_t heads_per_batch, float* mean,
+               void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * K prologue, step 2: smooth and quantise in one pass:
+ * k_s = T(float(k) - mean[bh, :]) rounded to k's own dtype, then the row
+ * quantiser (reference superl8/quant/core.py:86-95 then :47-62).  k_smoothed
+ * (nullable) receives k_s.
+ */
+int sl8_smooth_quant_k(const void* k, int dtype, int64_t BH, int64_t N, int64_t D,
+                       const float* mean, int8_t* k_i8, float* k_scale, void* k_smoothed,
+                       void* stream);
+
+/* ---- prefill: int8-QK FlashAttention-2 forward -------------------------- */
+
+typedef struct sl8_fwd_params {
+  const int8_t* q;        /* [B, Hq, M, D] int8 */
+  const float* q_scale;   /* [B, Hq, M] folded: scale * softmax_scale * log2(e) */
+  const int8_t* k;        /* [B, Hkv, N, D] int8 (smoothed) */
+  const float* k_scale;   /* [B, Hkv, N] */
+  const void* v;          /* [B, Hkv, N, D] fp16 or bf16 */
+  void* out;              /* [B, Hq, M, D], dtype of v */
+  float* lse;             /* [B, Hq, M] natural-log LSE, or NULL */
+  const int32_t* seqlens_q; /* int32[B] or NULL: valid query rows per sequence  */
+  const int32_t* seqlens_k; /* int32[B] or NULL: valid keys per sequence        */
+  int32_t B, Hq, Hkv, M, N, D;
+  int32_t v_dtype;        /* SL8_F16 or SL8_BF16 */
+  int32_t causal;         /* bottom-right aligned: query i sees keys <= i + N - M */
+  int32_t window_left;    /* < 0: none; else keys in (pos - window_left, pos] */
+  int32_t backend;        /* SL8_BACKEND_* */
+} sl8_fwd_params;
+
+/*
+ * out = softmax2(int32(q k^T) * q_scale[m] * k_scale[n]) v, rows with no valid
+ * key give 0 (LSE -inf).  Replaces `attn_int8_fwd` / `attn_int8_fwd_train`
+ * (reference csrc/kernel/attn_int8_fwd.cu:101-200, kernels
+ * csrc/include/attn_int8_fwd.cuh:47-209 and :228-373; bindings
+ * csrc/fni8_api.cpp:225-233).  D in {32, 64, 72, 80, 128, 256}.
+ * workspace: sl8_attn_int8_fwd_workspace() bytes; its first int32 is a device
+ * status word the kernel sets non-zero when a bounded wait expires (read it
+ * with sl8_read_device_status after synchronising).
+ * With seqlens_*, sequence b is computed as if the reference had been called on
+ * its [:, :, :len] slices; padded output rows are written as zeros.
+ */
+size_t sl8_attn_int8_fwd_workspace(const sl8_fwd_params* p);
+int sl8_attn_int8_fwd(const sl8_fwd_params* p, void* workspace, size_t workspace_bytes,
+                      void* stream);
+
+/*
+ * Raw int32 logits of one (batch, head): s[M, N] = q[M, D] . k[N, D]^T computed
+ * by the same tcgen05 kind::i8 tile path as the forward kernel.  Exists so the
+ * integer contraction can be pinned bit-exactly; the reference has the same
+ * quantity only inside its kernel (csrc/include/attn_int8_fwd.cuh:129-138).
+ */
+int sl8_qk_logits_i32(const int8_t* q, const int8_t* k, int32_t M, int32_t N, int32_t D,
+                      int32_t* s, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Full-precision sibling used when the accuracy gate demotes a call
+ * (reference superl8/ops.py:120-130 -> csrc/kernel/attn_fp16_fwd.cu:105-207):
+ * q, k, v one dtype (fp16 or bf16), logits = (q . k) * softmax_scale.
+ */
+typedef struct sl8_fp16_fwd_params {
+  const void* q; const void* k; const void* v; void* out; float* lse;
+  const int32_t* seqlens_q; const int32_t* seqlens_k;
+  int32_t B, Hq, Hkv, M, N, D;
+  int32_t dtype; int32_t causal; int32_t window_left;
+  float softmax_scale;
+} sl8_fp16_fwd_params;
+size_t sl8_attn_fp16_fwd_workspace(const sl8_fp16_fwd_params* p);
+int sl8_attn_fp16_fwd(const sl8_fp16_fwd_params* p, void* workspace, size_t workspace_bytes,
+                      void* stream);
+
+/* ---- decode: split-KV, one query row per sequence ----------------------- */
+
+typedef struct sl8_decode_params {
+  const int8_t* q;        /* [B, Hq, 1, D] int8 */
+  const float* q_scale;   /* [B, Hq] folded */
+  const int8_t* k;        /* [B, Hkv, N, D] int8 cache */
+  const float* k_scale;   /* [B, Hkv, N] per-token scales */
+  const void* v;          /* [B, Hkv, N, D] fp16 cache */
+  void* out;              /* [B, Hq, 1, D] fp16 */
+  const int32_t* context_lens; /* int32[B] or NULL (every sequence uses N keys) */
+  int32_t B, Hq, Hkv, N, D;
+  int32_t num_splits;     /* 1..256, or -1 = choose (sl8_choose_n_splits) */
+} sl8_decode_params;
+
+/*
+ * Split count used when num_splits == -1.  The reference's heuristic
+ * (csrc/kernel/attn_decode.cu:33-53) sizes one-warp blocks for 80 SMs; this one
+ * sizes 128-thread blocks that each serve a whole GQA group for 148 SMs.
+ */
+int sl8_choose_n_splits(int64_t N, int64_t B_times_Hkv);
+
+/*
+ * Replaces `attn_int8_decode` (reference csrc/kernel/attn_decode.cu:163-240;
+ * kernels csrc/include/attn_decode.cuh:47-132 and :430-466; binding
+ * csrc/fni8_api.cpp:260-263).  Split s of a sequence owns keys
+ * [s*per, min(len, (s+1)*per)), per = ceil(N / num_splits); partials
+ * (O, m, l) go to the workspace and a second kernel merges them by
+ * log-sum-exp.  N == 0 writes zeros.  num_splits 0 or > 256 is rejected.
+ * workspace: sl8_attn_int8_decode_workspace() bytes (status word + partials).
+ */
+size_t sl8_attn_int8_decode_workspace(const sl8_decode_params* p);
+int sl8_attn_int8_decode(const sl8_decode_params* p, void* workspace, size_t workspace_bytes,
+                         void* stream);
+
+/* Synchronises the stream and returns the device status word of a workspace
+ * (SL8_OK or SL8_ERR_DEVICE_TIMEOUT); clears it. */
+int sl8_read_device_status(void* workspace, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SUPERL8_B200_H_ */

@@ -1,0 +1,248 @@
+"""Operator layer with the names and argument lists of the reference's compiled
+module ``superl8._C`` (reference csrc/fni8_api.cpp:225-291), implemented over the
+C ABI of ``libsuperl8_b200.so``.
+
+Each function validates like the reference's ``TORCH_CHECK``s (same key words in
+the messages), allocates outputs/workspaces with torch on the inputs' device and
+launches on torch's current stream.  Nothing here computes on the CPU.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from . import _lib
+
+_DTYPE = {torch.float16: _lib.SL8_F16, torch.bfloat16: _lib.SL8_BF16, torch.float32: _lib.SL8_F32}
+_status_ws: dict = {}
+_decode_ws: dict = {}
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _status_buffer(device) -> torch.Tensor:
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _status_ws.get(key)
+    if buf is None:
+        buf = torch.zeros(64, dtype=torch.int32, device=device)
+        _status_ws[key] = buf
+    return buf
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _check_cuda(*ts) -> None:
+    _check(all(t.is_cuda for t in ts), "superl8_b200: all inputs (incl. scales) must be CUDA tensors")
+    _check(all(t.device == ts[0].device for t in ts), "superl8_b200: all inputs must be on the same device")
+
+
+def device_status(device=None) -> int:
+    """Synchronises and returns the device status word of the current stream's
+    status buffer (0, or the DEVICE_TIMEOUT code when a bounded wait expired)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    buf = _status_buffer(device)
+    return _lib.load().sl8_read_device_status(_ptr(buf), _stream(device))
+
+
+def quantize_i8_rowwise(x: torch.Tensor):
+    """x [M, K] fp16/bf16/fp32 -> (q int8 [M, K], scale fp32 [M]).
+    Reference binding: csrc/fni8_api.cpp:286-291; op csrc/kernel/quant_rowwise.cu:84-121."""
+    _check(x.is_cuda, "superl8_b200 quantize_i8_rowwise: x must be a CUDA tensor")
+    _check(x.dim() == 2, "superl8_b200 quantize_i8_rowwise: expect [M, K]")
+    _check(x.dtype in _DTYPE, "superl8_b200 quantize_i8_rowwise: x must be float16, bfloat16 or float32")
+    x = x.contiguous()
+    M, K = x.shape
+    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    scale = torch.empty((M,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().sl8_quantize_i8_rowwise(_ptr(x), _DTYPE[x.dtype], M, K, _ptr(q), _ptr(scale), _stream(x.device))
+    _lib.check(rc, "quantize_i8_rowwise")
+    return q, scale
+
+
+def _fwd_checks(q, q_scale, k, k_scale, v, what):
+    _check_cuda(q, q_scale, k, k_scale, v)
+    _check(q.dtype == torch.int8 and k.dtype == torch.int8, f"{what}: q/k must be int8")
+    _check(q_scale.dtype == torch.float32 and k_scale.dtype == torch.float32, f"{what}: scales must be float32")
+    _check(q.dim() == 4 and k.dim() == 4 and v.dim() == 4, f"{what}: expect [B,H,S,D]")
+    _check(all(t.is_contiguous() for t in (q, q_scale, k, k_scale, v)), f"{what}: inputs must be contiguous")
+    B, H, M, D = q.shape
+    Hkv, N = k.shape[1], k.shape[2]
+    _check(k.shape[0] == B and v.shape[0] == B and v.shape[1] == Hkv, f"{what}: batch/head mismatch")
+    _check(Hkv > 0 and H % Hkv == 0, f"{what}: H_q must be divisible by H_kv (GQA)")
+    _check(k.shape[3] == D and v.shape[3] == D and v.shape[2] == N, f"{what}: K/V shape mismatch")
+    _check(q_scale.numel() == B * H * M and k_scale.numel() == B * Hkv * N, f"{what}: scale shape mismatch")
+    return B, H, Hkv, M, N, D
+
+
+def _run_fwd(q, q_scale, k, k_scale, v, causal, want_lse, window_left, seqlens_q=None, seqlens_k=None,
+             backend=_lib.SL8_BACKEND_AUTO):
+    what = "superl8_b200"
+    B, H, Hkv, M, N, D = _fwd_checks(q, q_scale, k, k_scale, v, what)
+    _check(v.dtype in (torch.float16, torch.bfloat16), f"{what}: v must be float16 or bfloat16")
+    _check(D in (32, 64, 72, 80, 128, 256), f"{what}: head dim must be 32/64/72/80/128/256, got {D}")
+    out = torch.empty((B, H, M, D), dtype=v.dtype, device=v.device)
+    lse = torch.empty((B, H, M) if want_lse else (0,), dtype=torch.float32, device=q.device)
+    if M == 0 or B == 0 or H == 0:
+        return out, lse
+    for s in (seqlens_q, seqlens_k):
+        if s is not None:
+            _check(s.is_cuda and s.dtype == torch.int32 and s.numel() == B and s.is_contiguous(),
+                   f"{what}: seqlens must be contiguous int32 [B] CUDA tensors")
+    p = _lib.FwdParams(
+        q=q.data_ptr(), q_scale=q_scale.data_ptr(), k=k.data_ptr(), k_scale=k_scale.data_ptr(), v=v.data_ptr(),
+        out=out.data_ptr(), lse=lse.data_ptr() if want_lse else None,
+        seqlens_q=None if seqlens_q is None else seqlens_q.data_ptr(),
+        seqlens_k=None if seqlens_k is None else seqlens_k.data_ptr(),
+        B=B, Hq=H, Hkv=Hkv, M=M, N=N, D=D, v_dtype=_DTYPE[v.dtype], causal=int(bool(causal)),
+        window_left=int(window_left), backend=int(backend))
+    with torch.cuda.device(q.device):
+        ws = _status_buffer(q.device)
+        rc = _lib.load().sl8_attn_int8_fwd(C.byref(p), _ptr(ws), ws.numel() * 4, _stream(q.device))
+    _lib.check(rc, "attn_int8_fwd")
+    return out, lse
+
+
+def attn_int8_fwd(q, q_scale, k, k_scale, v, causal=False, window_left=-1, *, seqlens_q=None, seqlens_k=None,
+                  backend=_lib.SL8_BACKEND_AUTO):
+    """Reference binding csrc/fni8_api.cpp:225-229 (op csrc/kernel/attn_int8_fwd.cu:185-190)."""
+    return _run_fwd(q, q_scale, k, k_scale, v, causal, False, window_left, seqlens_q, seqlens_k, backend)[0]
+
+
+def attn_int8_fwd_train(q, q_scale, k, k_scale, v, causal=False, *, backend=_lib.SL8_BACKEND_AUTO):
+    """Also returns the natural-log LSE.  Reference binding csrc/fni8_api.cpp:230-233."""
+    return _run_fwd(q, q_scale, k, k_scale, v, causal, True, -1, None, None, backend)
+
+
+def qk_logits_i32(q_i8: torch.Tensor, k_i8: torch.Tensor) -> torch.Tensor:
+    """int32 q[M,D] . k[N,D]^T on the tcgen05 kind::i8 tile path (no reference op; see the header)."""
+    _check(q_i8.is_cuda and k_i8.is_cuda and q_i8.dtype == torch.int8 and k_i8.dtype == torch.int8,
+           "superl8_b200 qk_logits_i32: q/k must be int8 CUDA tensors")
+    _check(q_i8.dim() == 2 and k_i8.dim() == 2 and q_i8.shape[1] == k_i8.shape[1], "superl8_b200 qk_logits_i32: expect [M,D],[N,D]")
+    q_i8, k_i8 = q_i8.contiguous(), k_i8.contiguous()
+    M, D = q_i8.shape
+    N = k_i8.shape[0]
+    _check(D in (64, 128, 256), f"superl8_b200 qk_logits_i32: head dim must be 64/128/256, got {D}")
+    s = torch.empty((M, N), dtype=torch.int32, device=q_i8.device)
+    with torch.cuda.device(q_i8.device):
+        ws = _status_buffer(q_i8.device)
+        rc = _lib.load().sl8_qk_logits_i32(_ptr(q_i8), _ptr(k_i8), M, N, D, _ptr(s), _ptr(ws), ws.numel() * 4,
+                                           _stream(q_i8.device))
+    _lib.check(rc, "qk_logits_i32")
+    return s
+
+
+def attn_fp16_fwd(q, k, v, causal=False, scale=None, window_left=-1, mask=None, *, seqlens_q=None, seqlens_k=None):
+    """Full-precision forward.  Reference binding csrc/fni8_api.cpp:234-244."""
+    what = "superl8_b200 fp16 fwd"
+    _check_cuda(q, k, v)
+    _check(q.dtype in (torch.float16, torch.bfloat16), f"{what}: q must be float16 or bfloat16")
+    _check(k.dtype == q.dtype and v.dtype == q.dtype, f"{what}: q, k, v must share one dtype")
+    _check(q.dim() == 4 and k.dim() == 4 and v.dim() == 4, f"{what}: expect [B,H,S,D]")
+    if mask is not None:
+        raise NotImplementedError("superl8_b200 attn_fp16_fwd: additive masks are not implemented")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    B, H, M, D = q.shape
+    Hkv, N = k.shape[1], k.shape[2]
+    _check(k.shape[0] == B and v.shape[0] == B and v.shape[1] == Hkv, f"{what}: batch/head mismatch")
+    _check(Hkv > 0 and H % Hkv == 0, f"{what}: H_q must be divisible by H_kv (GQA)")
+    _check(k.shape[3] == D and v.shape[3] == D and v.shape[2] == N, f"{what}: K/V shape mismatch")
+    _check(D in (32, 64, 72, 80, 128, 256), f"{what}: head dim must be 32/64/72/80/128/256, got {D}")
+    out = torch.empty((B, H, M, D), dtype=v.dtype, device=v.device)
+    if out.numel() == 0:
+        return out
+    sc = (1.0 / math.sqrt(D)) if scale is None else float(scale)
+    p = _lib.Fp16FwdParams(
+        q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), lse=None,
+        seqlens_q=None if seqlens_q is None else seqlens_q.data_ptr(),
+        seqlens_k=None if seqlens_k is None else seqlens_k.data_ptr(),
+        B=B, Hq=H, Hkv=Hkv, M=M, N=N, D=D, dtype=_DTYPE[q.dtype], causal=int(bool(causal)),
+        window_left=int(window_left), softmax_scale=sc)
+    with torch.cuda.device(q.device):
+        ws = _status_buffer(q.device)
+        rc = _lib.load().sl8_attn_fp16_fwd(C.byref(p), _ptr(ws), ws.numel() * 4, _stream(q.device))
+    _lib.check(rc, "attn_fp16_fwd")
+    return out
+
+
+def _decode_workspace(device, nbytes: int) -> torch.Tensor:
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _decode_ws.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        buf[:256].zero_()
+        _decode_ws[key] = buf
+    return buf
+
+
+def attn_int8_decode(q, q_scale, k, k_scale, v, num_splits=-1, *, context_lens=None):
+    """Reference binding csrc/fni8_api.cpp:260-263 (op csrc/kernel/attn_decode.cu:163-240)."""
+    what = "superl8_b200 decode"
+    B, H, Hkv, M, N, D = _fwd_checks(q, q_scale, k, k_scale, v, what)
+    _check(v.dtype == torch.float16, f"{what}: v must be float16")
+    _check(M == 1, f"{what}: query length M must be 1 (decode)")
+    _check(D in (32, 64, 128, 256), f"{what}: head dim must be 32/64/128/256, got {D}")
+    num_splits = int(num_splits)
+    _check(num_splits != 0, f"{what}: num_splits=0 is invalid; use -1 for auto or 1..256")
+    if num_splits < 0:
+        num_splits = -1
+    _check(num_splits <= 256, f"{what}: num_splits must be 1..256, got {num_splits}")
+    if context_lens is not None:
+        _check(context_lens.is_cuda and context_lens.dtype == torch.int32 and context_lens.numel() == B
+               and context_lens.is_contiguous(), f"{what}: context_lens must be a contiguous int32 [B] CUDA tensor")
+    out = torch.empty((B, H, 1, D), dtype=v.dtype, device=v.device)
+    if out.numel() == 0:
+        return out
+    p = _lib.DecodeParams(
+        q=q.data_ptr(), q_scale=q_scale.data_ptr(), k=k.data_ptr(), k_scale=k_scale.data_ptr(), v=v.data_ptr(),
+        out=out.data_ptr(), context_lens=None if context_lens is None else context_lens.data_ptr(),
+        B=B, Hq=H, Hkv=Hkv, N=N, D=D, num_splits=num_splits)
+    lib = _lib.load()
+    with torch.cuda.device(q.device):
+        ws = _decode_workspace(q.device, int(lib.sl8_attn_int8_decode_workspace(C.byref(p))))
+        rc = lib.sl8_attn_int8_decode(C.byref(p), _ptr(ws), ws.numel(), _stream(q.device))
+    _lib.check(rc, "attn_int8_decode")
+    return out
+
+
+def attn_bwd(q, k, v, o, do_, lse, scale, causal=False):
+    """Exact FlashAttention-2 gradient in fp32 torch ops on the tensors' device
+    (the reference's own first definition of the backward, superl8/autograd.py:30-45).
+    The reference later binds a CUDA kernel pair here (csrc/fni8_api.cpp:256-259);
+    a native kernel for this row is not written yet."""
+    qf, kf, vf, of, dof = (t.float() for t in (q, k, v, o, do_))
+    Hq, Hkv = qf.shape[1], kf.shape[1]
+    rep = Hq // Hkv
+    if rep > 1:
+        kf = kf.repeat_interleave(rep, dim=1)
+        vf = vf.repeat_interleave(rep, dim=1)
+    s = torch.einsum("bhmd,bhnd->bhmn", qf, kf) * scale
+    if causal:
+        m, n = s.shape[-2], s.shape[-1]
+        keep = torch.ones(m, n, device=s.device, dtype=torch.bool).tril(n - m)
+        s = s.masked_fill(~keep, float("-inf"))
+    p = torch.exp(s - lse.unsqueeze(-1)) if lse is not None and lse.numel() else torch.softmax(s, dim=-1)
+    p = torch.nan_to_num(p, nan=0.0)
+    dv = torch.einsum("bhmn,bhmd->bhnd", p, dof)
+    dp = torch.einsum("bhmd,bhnd->bhmn", dof, vf)
+    drow = (dof * of).sum(dim=-1, keepdim=True)
+    ds = p * (dp - drow)
+    dq = torch.einsum("bhmn,bhnd->bhmd", ds, kf) * scale
+    dk = torch.einsum("bhmn,bhmd->bhnd", ds, qf) * scale
+    if rep > 1:
+        B, _, N, D = dk.shape
+        dk = dk.view(B, Hkv, rep, N, D).sum(dim=2)
+        dv = dv.view(B, Hkv, rep, N, D).sum(dim=2)
+    return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)

@@ -1,0 +1,31 @@
+"""superl8_b200 -- the reference's int8 attention hot path on B200 (sm_100a).
+
+Public names follow the reference package (reference superl8/__init__.py):
+``attn_int8_fwd``, ``attn_int8_decode`` (alias ``attn_decode``), ``attn_fp16_fwd``,
+``quantize_i8_rowwise``, ``attn``, and the ``quant`` helpers.
+"""
+
+from . import _C, quant  # noqa: F401
+from .autograd import attn  # noqa: F401
+from .ops import (  # noqa: F401
+    attn_decode,
+    attn_decode_int8_cache,
+    attn_fp16_fwd,
+    attn_int8_decode,
+    attn_int8_fwd,
+    quantize_i8_rowwise,
+)
+from .quant import (  # noqa: F401
+    LOG2E,
+    Q_MAX,
+    detect_q_outlier_domination,
+    quantize_int8_rowwise,
+    quantize_qk,
+    smooth_k,
+)
+
+__all__ = [
+    "attn", "attn_decode", "attn_decode_int8_cache", "attn_fp16_fwd", "attn_int8_decode", "attn_int8_fwd",
+    "quantize_i8_rowwise", "quantize_int8_rowwise", "quantize_qk", "smooth_k", "detect_q_outlier_domination",
+    "LOG2E", "Q_MAX",
+]

@@ -1,0 +1,121 @@
+"""ctypes binding of ``libsuperl8_b200.so`` (declarations: ``include/superl8_b200.h``).
+
+The library is the product; there is no Python or CPU implementation behind
+it.  If it is missing, every kernel call raises (``Sl8LibraryMissing``), the
+same way the reference's ``_MissingC`` stand-in does (reference
+superl8/ops.py:12-31).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libsuperl8_b200.so"
+
+SL8_OK = 0
+SL8_F16, SL8_BF16, SL8_F32 = 0, 1, 2
+SL8_BACKEND_AUTO, SL8_BACKEND_TCGEN05, SL8_BACKEND_MMA = 0, 1, 2
+
+ERR_BAD_HEAD_DIM = -1
+ERR_BAD_DTYPE = -2
+ERR_MISALIGNED = -3
+ERR_BAD_NUM_SPLITS = -4
+ERR_WORKSPACE = -5
+ERR_BAD_SHAPE = -6
+ERR_NULL = -7
+ERR_CUDA = -8
+ERR_DEVICE_TIMEOUT = -9
+ERR_UNSUPPORTED = -10
+ERR_TOO_LARGE = -11
+
+
+class Sl8LibraryMissing(RuntimeError):
+    pass
+
+
+class FwdParams(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("q_scale", C.c_void_p), ("k", C.c_void_p), ("k_scale", C.c_void_p),
+        ("v", C.c_void_p), ("out", C.c_void_p), ("lse", C.c_void_p),
+        ("seqlens_q", C.c_void_p), ("seqlens_k", C.c_void_p),
+        ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("M", C.c_int32), ("N", C.c_int32),
+        ("D", C.c_int32), ("v_dtype", C.c_int32), ("causal", C.c_int32), ("window_left", C.c_int32),
+        ("backend", C.c_int32),
+    ]
+
+
+class Fp16FwdParams(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p), ("lse", C.c_void_p),
+        ("seqlens_q", C.c_void_p), ("seqlens_k", C.c_void_p),
+        ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("M", C.c_int32), ("N", C.c_int32),
+        ("D", C.c_int32), ("dtype", C.c_int32), ("causal", C.c_int32), ("window_left", C.c_int32),
+        ("softmax_scale", C.c_float),
+    ]
+
+
+class DecodeParams(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("q_scale", C.c_void_p), ("k", C.c_void_p), ("k_scale", C.c_void_p),
+        ("v", C.c_void_p), ("out", C.c_void_p), ("context_lens", C.c_void_p),
+        ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("N", C.c_int32), ("D", C.c_int32),
+        ("num_splits", C.c_int32),
+    ]
+
+
+# name -> (restype, argtypes); every symbol declared in include/superl8_b200.h
+SIGNATURES = {
+    "sl8_abi_version": (C.c_int, []),
+    "sl8_status_string": (C.c_char_p, [C.c_int]),
+    "sl8_quantize_i8_rowwise": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "sl8_quant_q_prologue": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_float, C.c_float,
+                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "sl8_k_mean_workspace": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64]),
+    "sl8_k_mean": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int32,
+                             C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "sl8_smooth_quant_k": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
+                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "sl8_attn_int8_fwd_workspace": (C.c_size_t, [C.POINTER(FwdParams)]),
+    "sl8_attn_int8_fwd": (C.c_int, [C.POINTER(FwdParams), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "sl8_qk_logits_i32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                    C.c_void_p, C.c_size_t, C.c_void_p]),
+    "sl8_attn_fp16_fwd_workspace": (C.c_size_t, [C.POINTER(Fp16FwdParams)]),
+    "sl8_attn_fp16_fwd": (C.c_int, [C.POINTER(Fp16FwdParams), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "sl8_choose_n_splits": (C.c_int, [C.c_int64, C.c_int64]),
+    "sl8_attn_int8_decode_workspace": (C.c_size_t, [C.POINTER(DecodeParams)]),
+    "sl8_attn_int8_decode": (C.c_int, [C.POINTER(DecodeParams), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "sl8_read_device_status": (C.c_int, [C.c_void_p, C.c_void_p]),
+}
+
+_lib = None
+
+
+def load():
+    """Returns the loaded library (loads it on first use)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise Sl8LibraryMissing(
+            f"{LIB_PATH} is not built, so no superl8_b200 kernel can run. "
+            "Build it with `python -m superl8_b200.build` (needs nvcc; cross-compiles for sm_100a). "
+            "There is no CPU fallback."
+        )
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def status_string(code: int) -> str:
+    return load().sl8_status_string(int(code)).decode()
+
+
+def check(code: int, what: str) -> None:
+    """Turns a non-zero status into the RuntimeError the reference's TORCH_CHECKs raise."""
+    if code != SL8_OK:
+        raise RuntimeError(f"superl8_b200 {what}: {status_string(code)} (status {code})")

@@ -1,0 +1,501 @@
+// Prefill forward on the Blackwell tensor-core path: TMA-staged int8 Q/K tiles,
+// S = Q.K^T as tcgen05.mma kind::i8 with an int32 accumulator in tensor memory,
+// fp32 online softmax on the CUDA cores, O += P.V as tcgen05.mma kind::f16 with P
+// read from tensor memory and V from shared memory.
+//
+// Mathematics are the reference's (csrc/include/attn_int8_fwd.cuh:107-208):
+//   s = float(int32 q.k) * q_scale[m] * k_scale[n]            (that multiply order)
+//   valid = n < N and (not causal or n <= m + N - M) and (window < 0 or n > pos - window)
+//   online softmax in the exp2 domain (fp32 m, l), out = O / l (0 if l == 0),
+//   lse = m * ln2 + ln l.
+// Differences a caller can observe only inside the tolerance: tiles are 128 x 128
+// (reference 64 x 64) and P is rounded to V's dtype before P.V (reference fp32).
+//
+// Block = one 128-row query tile of one (batch, query head).  Six warps:
+//   warps 0-3  softmax + correction + epilogue; warp w owns tensor-memory lanes
+//              [32w, 32w+32) = query rows, one row per thread (no shuffles);
+//   warp 4     producer: TMA loads of Q, K, V tiles (3-D tensor maps, 128-byte
+//              swizzle, zero fill past the end of a head) and the k_scale tile;
+//   warp 5     allocates tensor memory and issues every MMA from one thread.
+// Tensor memory: S (int32, later fp32 logits, then P as packed 16-bit pairs in its
+// first 64 columns) at columns [0,128), O (fp32) at [128, 128 + D).  Two blocks
+// share an SM, so one block's softmax overlaps the other's MMAs.
+// Every mbarrier wait is bounded (sl8_common.cuh); on expiry the block raises the
+// workspace status word, frees tensor memory and exits.
+#include "sl8_common.cuh"
+
+#include <type_traits>
+
+int sl8_fwd_mma_int8(const sl8_fwd_params* p, cudaStream_t s);  // fwd_mma.cu
+
+namespace sl8 {
+namespace {
+
+constexpr int kTM = 128, kTN = 128;
+constexpr int kTcThreads = 192;
+
+template <int D>
+struct TcCfg {
+  static constexpr int QROW = D < 128 ? D : 128;          // bytes per shared row of a Q/K sub-tile
+  static constexpr int QSUBS = D / QROW;
+  static constexpr uint32_t QK_SW = QROW == 128 ? kUmmaSw128 : kUmmaSw64;
+  static constexpr int QK_SUB_BYTES = 128 * QROW;
+  static constexpr int QK_TILE_BYTES = 128 * D;
+  static constexpr int VSUBS = 2 * D / 128;               // 64-channel sub-tiles of 128 keys x 128 B
+  static constexpr int V_SUB_BYTES = 128 * 128;
+  static constexpr int V_TILE_BYTES = 128 * 2 * D;
+  static constexpr int NKS = 2;
+  static constexpr int NVS = D == 64 ? 2 : 1;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + QK_TILE_BYTES;
+  static constexpr int OFF_V = OFF_K + NKS * QK_TILE_BYTES;
+  static constexpr int OFF_KS = OFF_V + NVS * V_TILE_BYTES;
+  static constexpr int OFF_BAR = OFF_KS + 2 * kTN * 4;
+  static constexpr int NEED = OFF_BAR + 256 + 1024;
+  // never more than two blocks per SM: each holds TMEM_COLS columns of the 512
+  static constexpr int SMEM = NEED < 78 * 1024 ? 78 * 1024 : NEED;
+  static constexpr uint32_t TMEM_COLS = D <= 128 ? 256 : 512;
+  static constexpr uint32_t COL_S = 0, COL_O = 128;
+};
+
+struct TcArgs {
+  const float* q_scale;
+  const float* k_scale;
+  void* out;
+  float* lse;
+  const int32_t* seqlens_q;
+  const int32_t* seqlens_k;
+  int* status;
+  int Hq, Hkv, M, N;
+  int causal, window_left;
+};
+
+enum Bar { Q_FULL = 0, S_FULL, P_FULL, O_DONE, K_FULL, K_EMPTY = K_FULL + 2, V_FULL = K_EMPTY + 2,
+           V_EMPTY = V_FULL + 2, KS_FULL = V_EMPTY + 2, KS_EMPTY = KS_FULL + 2, NUM_BARS = KS_EMPTY + 2 };
+
+template <int D, typename VT>
+__global__ void __launch_bounds__(kTcThreads) fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map,
+                                                            const __grid_constant__ CUtensorMap k_map,
+                                                            const __grid_constant__ CUtensorMap v_map, TcArgs a) {
+  using C = TcCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* ks_smem = reinterpret_cast<float*>(smem + C::OFF_KS);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t bh = blockIdx.y;
+  const int b = (int)(bh / a.Hq);
+  const int G = a.Hq / a.Hkv;
+  const int kv_bh = b * a.Hkv + (int)(bh % a.Hq) / G;
+  const int m_len = a.seqlens_q ? min(max(a.seqlens_q[b], 0), a.M) : a.M;
+  const int n_len = a.seqlens_k ? min(max(a.seqlens_k[b], 0), a.N) : a.N;
+  const int m_block = (a.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x) * kTM;
+  const int causal_diag = a.causal ? n_len - m_len : 0;
+  const int n_end = a.causal ? max(0, min(n_len, m_block + kTM + causal_diag)) : n_len;
+  int n_begin = 0;
+  if (a.window_left >= 0) n_begin = max(0, (m_block + causal_diag - a.window_left + 1)) / kTN * kTN;
+  const int ntiles = (m_block < m_len && n_end > n_begin) ? (n_end - n_begin + kTN - 1) / kTN : 0;
+  VT* out_bh = reinterpret_cast<VT*>(a.out) + bh * (int64_t)a.M * D;
+
+  if (ntiles == 0) {  // no visible key for any row of the tile (or padded rows): zeros
+    for (int idx = threadIdx.x; idx < kTM * (D / 8); idx += kTcThreads) {
+      const int r = idx / (D / 8), c = (idx % (D / 8)) * 8;
+      if (m_block + r < a.M) *reinterpret_cast<uint4*>(out_bh + (int64_t)(m_block + r) * D + c) = make_uint4(0, 0, 0, 0);
+    }
+    if (a.lse) for (int r = threadIdx.x; r < kTM; r += kTcThreads)
+        if (m_block + r < a.M) a.lse[bh * a.M + m_block + r] = -INFINITY;
+    return;
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars[Q_FULL], 1);
+    mbar_init(&bars[S_FULL], 1);
+    mbar_init(&bars[P_FULL], 4);
+    mbar_init(&bars[O_DONE], 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars[K_FULL + i], 1);
+      mbar_init(&bars[K_EMPTY + i], 1);
+      mbar_init(&bars[V_FULL + i], 1);
+      mbar_init(&bars[V_EMPTY + i], 1);
+      mbar_init(&bars[KS_FULL + i], 1);
+      mbar_init(&bars[KS_EMPTY + i], 4);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tc_alloc(tmem_slot, C::TMEM_COLS);
+    tc_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  bool ok = true;
+
+  if (warp == 4) {
+    // ======================= producer =======================
+    if (lane == 0) {
+      tma_prefetch_desc(&q_map);
+      tma_prefetch_desc(&k_map);
+      tma_prefetch_desc(&v_map);
+      mbar_expect_tx(&bars[Q_FULL], C::QK_TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < C::QSUBS; ++c)
+        tma_load_3d(smem + C::OFF_Q + c * C::QK_SUB_BYTES, &q_map, &bars[Q_FULL], c * C::QROW, m_block, (int)bh);
+    }
+    for (int j = 0; j < ntiles && ok; ++j) {
+      const int n_block = n_begin + j * kTN;
+      if (lane == 0) {
+        const int ks = j % C::NKS, vs = j % C::NVS;
+        if (j >= C::NKS) ok = mbar_wait(&bars[K_EMPTY + ks], ((j / C::NKS) - 1) & 1, a.status);
+        if (ok) {
+          mbar_expect_tx(&bars[K_FULL + ks], C::QK_TILE_BYTES);
+#pragma unroll
+          for (int c = 0; c < C::QSUBS; ++c)
+            tma_load_3d(smem + C::OFF_K + ks * C::QK_TILE_BYTES + c * C::QK_SUB_BYTES, &k_map, &bars[K_FULL + ks],
+                        c * C::QROW, n_block, kv_bh);
+          if (j >= C::NVS) ok = mbar_wait(&bars[V_EMPTY + vs], ((j / C::NVS) - 1) & 1, a.status);
+        }
+        if (ok) {
+          mbar_expect_tx(&bars[V_FULL + vs], C::V_TILE_BYTES);
+#pragma unroll
+          for (int c = 0; c < C::VSUBS; ++c)
+            tma_load_3d(smem + C::OFF_V + vs * C::V_TILE_BYTES + c * C::V_SUB_BYTES, &v_map, &bars[V_FULL + vs],
+                        c * 64, n_block, kv_bh);
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      // k_scale tile through the generic proxy (its start is not 16-byte aligned in general)
+      const int ss = j & 1;
+      if (j >= 2) ok = mbar_wait(&bars[KS_EMPTY + ss], ((j >> 1) - 1) & 1, a.status);
+      if (!ok) break;
+#pragma unroll
+      for (int i = 0; i < kTN / 32; ++i) {
+        const int n = n_block + lane + 32 * i;
+        ks_smem[ss * kTN + lane + 32 * i] = (n < n_len) ? __ldg(a.k_scale + (int64_t)kv_bh * a.N + n) : 0.f;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[KS_FULL + ss]);
+    }
+  } else if (warp == 5) {
+    // ======================= MMA issuer =======================
+    if (lane == 0) {
+      const uint32_t idesc_qk = umma_idesc(2, 1, 1, 0, 0, kTM, kTN);
+      constexpr uint32_t vfmt = std::is_same<VT, __nv_bfloat16>::value ? 1u : 0u;
+      const uint32_t idesc_pv = umma_idesc(1, vfmt, vfmt, 0, 1, kTM, D);
+      const uint32_t q_u = smem_u32(smem + C::OFF_Q);
+      ok = mbar_wait(&bars[Q_FULL], 0, a.status);
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int ks = j % C::NKS, vs = j % C::NVS;
+        ok = mbar_wait(&bars[K_FULL + ks], (j / C::NKS) & 1, a.status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t k_u = smem_u32(smem + C::OFF_K + ks * C::QK_TILE_BYTES);
+#pragma unroll
+        for (int s = 0; s < D / 32; ++s) {
+          const uint32_t off = (32 * s / C::QROW) * C::QK_SUB_BYTES + (32 * s % C::QROW);
+          tc_mma_i8_ss(tmem + C::COL_S, umma_smem_desc(q_u + off, 16, 8 * C::QROW, C::QK_SW),
+                       umma_smem_desc(k_u + off, 16, 8 * C::QROW, C::QK_SW), idesc_qk, s > 0 ? 1u : 0u);
+        }
+        tc_commit(&bars[K_EMPTY + ks]);
+        tc_commit(&bars[S_FULL]);
+        ok = mbar_wait(&bars[P_FULL], j & 1, a.status);
+        if (ok) ok = mbar_wait(&bars[V_FULL + vs], (j / C::NVS) & 1, a.status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t v_u = smem_u32(smem + C::OFF_V + vs * C::V_TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < kTN / 16; ++kk)
+          tc_mma_f16_ts(tmem + C::COL_O, tmem + C::COL_S + 8 * kk,
+                        umma_smem_desc(v_u + kk * 2048, C::V_SUB_BYTES, 1024, kUmmaSw128), idesc_pv,
+                        (j > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(&bars[V_EMPTY + vs]);
+        if (j == ntiles - 1) tc_commit(&bars[O_DONE]);
+      }
+    }
+  } else {
+    // ======================= softmax / correction / epilogue =======================
+    const int m = m_block + 32 * warp + lane;  // this thread's query row
+    const float qs = (m < m_len) ? __ldg(a.q_scale + bh * a.M + m) : 0.f;
+    const int qpos = m + causal_diag;
+    const uint32_t t_row = tmem + ((uint32_t)(32 * warp) << 16);
+    float m_run = -INFINITY, l_run = 0.f;
+
+    for (int j = 0; j < ntiles; ++j) {
+      const int n_block = n_begin + j * kTN;
+      const int ss = j & 1;
+      ok = mbar_wait(&bars[KS_FULL + ss], (j >> 1) & 1, a.status);
+      if (ok) ok = mbar_wait(&bars[S_FULL], j & 1, a.status);
+      if (!ok) break;
+      tc_fence_after();
+      const float* ksv = ks_smem + ss * kTN;
+      const bool need_mask = (n_block + kTN > n_len) || (a.causal && n_block + kTN - 1 > m_block + causal_diag) ||
+                             (a.window_left >= 0 && n_block <= m_block + kTM - 1 + causal_diag - a.window_left);
+      // ---- pass 1: int32 -> fp32 logits (kept in tensor memory), row max ----
+      float tmax = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < kTN / 32; ++c) {
+        uint32_t r[32];
+        tc_ld32(t_row + C::COL_S + 32 * c, r);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = (float)(int)r[i] * qs * ksv[32 * c + i];
+          if (need_mask) {
+            const int gn = n_block + 32 * c + i;
+            const bool valid = (gn < n_len) && (!a.causal || gn <= qpos) &&
+                               (a.window_left < 0 || gn > qpos - a.window_left);
+            s = valid ? s : -INFINITY;
+          }
+          tmax = fmaxf(tmax, s);
+          r[i] = __float_as_uint(s);
+        }
+        tc_st32(t_row + C::COL_S + 32 * c, r);
+      }
+      const float m_new = fmaxf(m_run, tmax);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float resc = exp2f(m_run - m_use);  // m_run = -inf -> 0
+      // ---- correction: O *= resc (the previous tile's P.V has completed: the
+      //      commit behind S_FULL covers every earlier MMA) ----
+      if (j > 0 && __any_sync(0xffffffffu, m_new > m_run)) {
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tc_ld32(t_row + C::COL_O + 32 * c, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * resc);
+          tc_st32(t_row + C::COL_O + 32 * c, r);
+        }
+      }
+      tc_wait_st();  // logits written in pass 1 are visible to the loads below
+      // ---- pass 2: P = exp2(s - m), row sum, P -> tensor memory (16-bit pairs) ----
+      float psum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < kTN / 32; ++c) {
+        uint32_t r[32];
+        tc_ld32(t_row + C::COL_S + 32 * c, r);
+        tc_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = exp2f(__uint_as_float(r[2 * i]) - m_use);
+          const float p1 = exp2f(__uint_as_float(r[2 * i + 1]) - m_use);
+          psum += p0 + p1;
+          pk[i] = pack2<VT>(p0, p1);
+        }
+        tc_st16(t_row + C::COL_S + 16 * c, pk);
+      }
+      l_run = l_run * resc + psum;
+      m_run = m_new;
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&bars[P_FULL]);
+        mbar_arrive(&bars[KS_EMPTY + ss]);
+      }
+    }
+    // ---- epilogue ----
+    if (ok) ok = mbar_wait(&bars[O_DONE], 0, a.status);
+    if (ok) {
+      tc_fence_after();
+      const bool live = m < m_len;
+      const float inv = (live && l_run > 0.f) ? 1.f / l_run : 0.f;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tc_ld32(t_row + C::COL_O + 32 * c, r);
+        tc_wait_ld();
+        if (m < a.M) {
+          uint4* dst = reinterpret_cast<uint4*>(out_bh + (int64_t)m * D + 32 * c);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 w;
+            w.x = pack2<VT>(__uint_as_float(r[8 * v + 0]) * inv, __uint_as_float(r[8 * v + 1]) * inv);
+            w.y = pack2<VT>(__uint_as_float(r[8 * v + 2]) * inv, __uint_as_float(r[8 * v + 3]) * inv);
+            w.z = pack2<VT>(__uint_as_float(r[8 * v + 4]) * inv, __uint_as_float(r[8 * v + 5]) * inv);
+            w.w = pack2<VT>(__uint_as_float(r[8 * v + 6]) * inv, __uint_as_float(r[8 * v + 7]) * inv);
+            dst[v] = w;
+          }
+        }
+      }
+      if (a.lse != nullptr && m < a.M)
+        a.lse[bh * a.M + m] = (live && l_run > 0.f) ? (m_run * 0.6931471805599453f + logf(l_run)) : -INFINITY;
+    }
+    tc_fence_before();
+  }
+
+  // ---- teardown: every role arrives here, on success and on a timed-out wait ----
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tc_dealloc(tmem, C::TMEM_COLS);
+  }
+}
+
+// ---- raw int32 logits through the same TMA + kind::i8 tile path ----------------
+template <int D>
+__global__ void __launch_bounds__(128) qk_logits_kernel(const __grid_constant__ CUtensorMap q_map,
+                                                        const __grid_constant__ CUtensorMap k_map, int32_t* s_out,
+                                                        int M, int N, int* status) {
+  using C = TcCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * C::QK_TILE_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_block = blockIdx.x * kTM, n_block = blockIdx.y * kTN;
+  if (threadIdx.x == 0) {
+    mbar_init(&bars[0], 1);
+    mbar_init(&bars[1], 1);
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tc_alloc(tmem_slot, 128);
+    tc_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  bool ok = true;
+  if (threadIdx.x == 0) {
+    mbar_expect_tx(&bars[0], 2 * C::QK_TILE_BYTES);
+#pragma unroll
+    for (int c = 0; c < C::QSUBS; ++c) {
+      tma_load_3d(smem + c * C::QK_SUB_BYTES, &q_map, &bars[0], c * C::QROW, m_block, 0);
+      tma_load_3d(smem + C::QK_TILE_BYTES + c * C::QK_SUB_BYTES, &k_map, &bars[0], c * C::QROW, n_block, 0);
+    }
+    ok = mbar_wait(&bars[0], 0, status);
+    if (ok) {
+      tc_fence_after();
+      const uint32_t idesc = umma_idesc(2, 1, 1, 0, 0, kTM, kTN);
+      const uint32_t q_u = smem_u32(smem), k_u = smem_u32(smem + C::QK_TILE_BYTES);
+#pragma unroll
+      for (int s = 0; s < D / 32; ++s) {
+        const uint32_t off = (32 * s / C::QROW) * C::QK_SUB_BYTES + (32 * s % C::QROW);
+        tc_mma_i8_ss(tmem, umma_smem_desc(q_u + off, 16, 8 * C::QROW, C::QK_SW),
+                     umma_smem_desc(k_u + off, 16, 8 * C::QROW, C::QK_SW), idesc, s > 0 ? 1u : 0u);
+      }
+      tc_commit(&bars[1]);
+    }
+  }
+  ok = mbar_wait(&bars[1], 0, status);
+  if (ok) {
+    tc_fence_after();
+    const int m = m_block + 32 * warp + lane;
+#pragma unroll 1
+    for (int c = 0; c < kTN / 32; ++c) {
+      uint32_t r[32];
+      tc_ld32(tmem + ((uint32_t)(32 * warp) << 16) + 32 * c, r);
+      tc_wait_ld();
+      if (m < M)
+        for (int i = 0; i < 32; ++i) {
+          const int n = n_block + 32 * c + i;
+          if (n < N) s_out[(int64_t)m * N + n] = (int)r[i];
+        }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tc_dealloc(tmem, 128);
+  }
+}
+
+template <int D, typename VT>
+int launch_tc(const sl8_fwd_params& p, int* status, cudaStream_t stream) {
+  using C = TcCfg<D>;
+  CUtensorMap q_map, k_map, v_map;
+  int rc = sl8_make_tmap_3d(&q_map, p.q, 1, D, p.M, (uint64_t)p.B * p.Hq, C::QROW, kTM, C::QROW);
+  if (rc == SL8_OK) rc = sl8_make_tmap_3d(&k_map, p.k, 1, D, p.N, (uint64_t)p.B * p.Hkv, C::QROW, kTN, C::QROW);
+  if (rc == SL8_OK) rc = sl8_make_tmap_3d(&v_map, p.v, 2, D, p.N, (uint64_t)p.B * p.Hkv, 64, kTN, 128);
+  if (rc != SL8_OK) return rc;
+  SL8_CUDA_TRY(cudaFuncSetAttribute(fwd_tc_kernel<D, VT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+  TcArgs a{};
+  a.q_scale = p.q_scale; a.k_scale = p.k_scale; a.out = p.out; a.lse = p.lse;
+  a.seqlens_q = p.seqlens_q; a.seqlens_k = p.seqlens_k; a.status = status;
+  a.Hq = p.Hq; a.Hkv = p.Hkv; a.M = p.M; a.N = p.N; a.causal = p.causal; a.window_left = p.window_left;
+  dim3 grid((p.M + kTM - 1) / kTM, (unsigned)((int64_t)p.B * p.Hq));
+  fwd_tc_kernel<D, VT><<<grid, kTcThreads, C::SMEM, stream>>>(q_map, k_map, v_map, a);
+  return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
+}
+
+template <typename VT>
+int launch_tc_d(const sl8_fwd_params& p, int* status, cudaStream_t s) {
+  switch (p.D) {
+    case 64: return launch_tc<64, VT>(p, status, s);
+    case 128: return launch_tc<128, VT>(p, status, s);
+    case 256: return launch_tc<256, VT>(p, status, s);
+  }
+  return SL8_ERR_UNSUPPORTED;
+}
+
+template <int D>
+int launch_logits(const int8_t* q, const int8_t* k, int M, int N, int32_t* s_out, int* status, cudaStream_t stream) {
+  using C = TcCfg<D>;
+  CUtensorMap q_map, k_map;
+  int rc = sl8_make_tmap_3d(&q_map, q, 1, D, M, 1, C::QROW, kTM, C::QROW);
+  if (rc == SL8_OK) rc = sl8_make_tmap_3d(&k_map, k, 1, D, N, 1, C::QROW, kTN, C::QROW);
+  if (rc != SL8_OK) return rc;
+  const int smem = 2 * C::QK_TILE_BYTES + 1024 + 64;
+  SL8_CUDA_TRY(cudaFuncSetAttribute(qk_logits_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  dim3 grid((M + kTM - 1) / kTM, (N + kTN - 1) / kTN);
+  qk_logits_kernel<D><<<grid, 128, smem, stream>>>(q_map, k_map, s_out, M, N, status);
+  return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
+}
+
+bool head_dim_ok(int D) { return D == 32 || D == 64 || D == 72 || D == 80 || D == 128 || D == 256; }
+bool tc_head_dim(int D) { return D == 64 || D == 128 || D == 256; }
+
+}  // namespace
+}  // namespace sl8
+
+using namespace sl8;
+
+extern "C" size_t sl8_attn_int8_fwd_workspace(const sl8_fwd_params*) { return 256; }
+
+extern "C" int sl8_attn_int8_fwd(const sl8_fwd_params* p, void* workspace, size_t workspace_bytes, void* stream) {
+  if (p == nullptr) return SL8_ERR_NULL;
+  if (p->B < 0 || p->Hq < 0 || p->Hkv < 0 || p->M < 0 || p->N < 0) return SL8_ERR_BAD_SHAPE;
+  if (!head_dim_ok(p->D)) return SL8_ERR_BAD_HEAD_DIM;
+  if (p->v_dtype != SL8_F16 && p->v_dtype != SL8_BF16) return SL8_ERR_BAD_DTYPE;
+  if (p->Hq > 0 && (p->Hkv <= 0 || p->Hq % p->Hkv != 0)) return SL8_ERR_BAD_SHAPE;
+  if ((int64_t)p->B * p->Hq * p->M == 0) return SL8_OK;  // empty output (reference attn_int8_fwd.cu:145)
+  if (!p->q || !p->q_scale || !p->out) return SL8_ERR_NULL;
+  if (p->N > 0 && (!p->k || !p->k_scale || !p->v)) return SL8_ERR_NULL;
+  if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->out)) return SL8_ERR_MISALIGNED;
+  if ((int64_t)p->B * p->Hq > 65535) return SL8_ERR_TOO_LARGE;
+  if (workspace == nullptr || workspace_bytes < 256) return SL8_ERR_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int backend = p->backend;
+  if (backend == SL8_BACKEND_AUTO) backend = (tc_head_dim(p->D) && p->N > 0) ? SL8_BACKEND_TCGEN05 : SL8_BACKEND_MMA;
+  if (backend == SL8_BACKEND_MMA) return sl8_fwd_mma_int8(p, s);
+  if (backend != SL8_BACKEND_TCGEN05) return SL8_ERR_UNSUPPORTED;
+  if (!tc_head_dim(p->D) || p->N == 0) return SL8_ERR_UNSUPPORTED;
+  int* status = reinterpret_cast<int*>(workspace);
+  return p->v_dtype == SL8_F16 ? launch_tc_d<__half>(*p, status, s) : launch_tc_d<__nv_bfloat16>(*p, status, s);
+}
+
+extern "C" int sl8_qk_logits_i32(const int8_t* q, const int8_t* k, int32_t M, int32_t N, int32_t D, int32_t* s_out,
+                                 void* workspace, size_t workspace_bytes, void* stream) {
+  if (M < 0 || N < 0) return SL8_ERR_BAD_SHAPE;
+  if (!tc_head_dim(D)) return SL8_ERR_BAD_HEAD_DIM;
+  if (M == 0 || N == 0) return SL8_OK;
+  if (!q || !k || !s_out) return SL8_ERR_NULL;
+  if (!aligned16(q) || !aligned16(k)) return SL8_ERR_MISALIGNED;
+  if (workspace == nullptr || workspace_bytes < 256) return SL8_ERR_WORKSPACE;
+  int* status = reinterpret_cast<int*>(workspace);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (D) {
+    case 64: return launch_logits<64>(q, k, M, N, s_out, status, s);
+    case 128: return launch_logits<128>(q, k, M, N, s_out, status, s);
+    case 256: return launch_logits<256>(q, k, M, N, s_out, status, s);
+  }
+  return SL8_ERR_BAD_HEAD_DIM;
+}

@@ -1,0 +1,404 @@
+// Per-row symmetric int8 quantiser and the Q / K prologues that wrap it.
+//
+// Arithmetic contract (bit-exact with the reference's CUDA path,
+// csrc/include/quant_rowwise.cuh:32-92): scale = amax * float(1/127) (a
+// reciprocal MULTIPLY, not a division), an all-zero row gets scale 1, element
+// = clamp(rint(x / scale), +-127) with an IEEE-rounded division.
+//
+// Mapping to the machine: the operation moves 3 bytes per element and is bound
+// by HBM bandwidth, so a row is owned by a sub-group of lanes that each load 16
+// bytes (8 two-byte elements) once, keep them in registers for both the amax and
+// the rounding pass, and store 8 bytes of codes.  One 256-thread block covers
+// 8 * (32 / lanes-per-row) rows per step and walks the rows grid-stride.
+#include "sl8_common.cuh"
+
+namespace sl8 {
+namespace {
+
+constexpr int kQuantThreads = 256;
+constexpr float kQMax = 127.0f;
+constexpr float kQMaxInv = 1.0f / 127.0f;
+
+enum QuantMode { kPlain = 0, kQueryFoldGate = 1, kKeySmooth = 2 };
+
+struct QuantArgs {
+  const void* x;
+  int8_t* q;
+  float* scale;         // plain: scale; query: folded scale; key: scale
+  float* plain_scale;   // query mode only (nullable)
+  const float* mean;    // key mode: [BH, K]
+  void* smoothed;       // key mode (nullable): k - mean in x's dtype
+  int32_t* flag;        // query mode (nullable): OR-ed with 1 if any row is outlier dominated
+  int64_t rows;
+  int64_t rows_per_head;
+  int K;
+  float fold;
+  float ratio_threshold;
+};
+
+__device__ __forceinline__ float quant_one(float x, float s) {
+  float v = rintf(__fdiv_rn(x, s));
+  return fminf(fmaxf(v, -kQMax), kQMax);
+}
+
+template <typename T> struct Vec8;  // 8 two-byte elements in a uint4
+template <> struct Vec8<__half> {
+  __device__ static void unpack(const uint4& u, float (&f)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 t = __half22float2(h[i]);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+};
+template <> struct Vec8<__nv_bfloat16> {
+  __device__ static void unpack(const uint4& u, float (&f)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 t = __bfloat1622float2(h[i]);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+};
+
+// LPR lanes own one row; each lane holds NV vectors of 8 elements.
+template <typename T, int LPR, int NV, int MODE>
+__global__ void __launch_bounds__(kQuantThreads) quant_rows_vec_kernel(QuantArgs a) {
+  constexpr int ROWS_PER_WARP = 32 / LPR;
+  constexpr unsigned FULL = 0xffffffffu;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / LPR;       // which row of the warp's group
+  const int sl = lane % LPR;        // lane within the row
+  const int warp = threadIdx.x >> 5;
+  const int kvec = a.K >> 3;
+  const int64_t rows_per_block = (int64_t)(kQuantThreads / 32) * ROWS_PER_WARP;
+  const int rank_need = ((a.K - 1) >> 1) + 1;  // elements <= lower median, counted from the bottom
+  int any_outlier = 0;
+
+  for (int64_t base = (int64_t)blockIdx.x * rows_per_block; base < a.rows;
+       base += (int64_t)gridDim.x * rows_per_block) {
+    const int64_t row = base + (int64_t)warp * ROWS_PER_WARP + sub;
+    const bool live = row < a.rows;
+    const T* xr = reinterpret_cast<const T*>(a.x) + row * a.K;
+    float f[NV][8];
+    bool has[NV];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int vi = sl + v * LPR;
+      has[v] = live && vi < kvec;
+      uint4 u = make_uint4(0, 0, 0, 0);
+      if (has[v]) u = __ldg(reinterpret_cast<const uint4*>(xr) + vi);
+      Vec8<T>::unpack(u, f[v]);
+    }
+    if (MODE == kKeySmooth) {
+      const int64_t bh = live ? row / a.rows_per_head : 0;
+      const float* mr = a.mean + bh * a.K;
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        if (!has[v]) continue;
+        const int c0 = (sl + v * LPR) * 8;
+        const float4 m0 = __ldg(reinterpret_cast<const float4*>(mr + c0));
+        const float4 m1 = __ldg(reinterpret_cast<const float4*>(mr + c0 + 4));
+        const float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+        T t[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          t[i] = from_f32<T>(f[v][i] - mm[i]);  // rounded to the storage dtype, as torch.sub(out=)
+          f[v][i] = to_f32<T>(t[i]);
+        }
+        if (a.smoothed != nullptr)
+          *reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.smoothed) + row * a.K + c0) =
+              *reinterpret_cast<const uint4*>(t);
+      }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[v][i]));
+#pragma unroll
+    for (int off = LPR / 2; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(FULL, amax, off));
+
+    float s = amax * kQMaxInv;
+    s = (s == 0.0f) ? 1.0f : s;
+
+    if (MODE == kQueryFoldGate && a.flag != nullptr) {
+      // max / (median + 1e-10) > thr  <=>  at least rank_need elements e satisfy
+      // max / (|e| + 1e-10) > thr, because the quotient is monotone in |e|.
+      int cnt = 0;
+#pragma unroll
+      for (int v = 0; v < NV; ++v)
+        if (has[v]) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            cnt += (__fdiv_rn(amax, fabsf(f[v][i]) + 1e-10f) > a.ratio_threshold) ? 1 : 0;
+        }
+#pragma unroll
+      for (int off = LPR / 2; off > 0; off >>= 1) cnt += __shfl_xor_sync(FULL, cnt, off);
+      if (live && cnt >= rank_need) any_outlier = 1;
+    }
+
+    int8_t* qr = a.q + row * a.K;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      if (!has[v]) continue;
+      uint32_t w[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t acc = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int qi = (int)quant_one(f[v][4 * h + i], s);
+          acc |= (uint32_t)(qi & 0xff) << (8 * i);
+        }
+        w[h] = acc;
+      }
+      *reinterpret_cast<uint2*>(qr + (sl + v * LPR) * 8) = make_uint2(w[0], w[1]);
+    }
+    if (live && sl == 0) {
+      if (MODE == kQueryFoldGate) {
+        a.scale[row] = s * a.fold;
+        if (a.plain_scale != nullptr) a.plain_scale[row] = s;
+      } else {
+        a.scale[row] = s;
+      }
+    }
+  }
+  if (MODE == kQueryFoldGate && a.flag != nullptr) {
+    any_outlier = __syncthreads_or(any_outlier);
+    if (threadIdx.x == 0 && any_outlier) atomicOr(a.flag, 1);
+  }
+}
+
+// One warp per row, scalar element access, two passes over the row (the second
+// comes from L1/L2): every dtype, every K.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(kQuantThreads) quant_rows_generic_kernel(QuantArgs a) {
+  constexpr unsigned FULL = 0xffffffffu;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int rank_need = ((a.K - 1) >> 1) + 1;
+  int any_outlier = 0;
+  for (int64_t row = (int64_t)blockIdx.x * (kQuantThreads / 32) + warp; row < a.rows;
+       row += (int64_t)gridDim.x * (kQuantThreads / 32)) {
+    const T* xr = reinterpret_cast<const T*>(a.x) + row * a.K;
+    const float* mr = (MODE == kKeySmooth) ? a.mean + (row / a.rows_per_head) * a.K : nullptr;
+    auto elem = [&](int c) -> float {
+      float v = to_f32<T>(xr[c]);
+      if (MODE == kKeySmooth) v = to_f32<T>(from_f32<T>(v - mr[c]));
+      return v;
+    };
+    float amax = 0.0f;
+    for (int c = lane; c < a.K; c += 32) amax = fmaxf(amax, fabsf(elem(c)));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(FULL, amax, off));
+    float s = amax * kQMaxInv;
+    s = (s == 0.0f) ? 1.0f : s;
+    if (MODE == kQueryFoldGate && a.flag != nullptr) {
+      int cnt = 0;
+      for (int c = lane; c < a.K; c += 32)
+        cnt += (__fdiv_rn(amax, fabsf(elem(c)) + 1e-10f) > a.ratio_threshold) ? 1 : 0;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) cnt += __shfl_xor_sync(FULL, cnt, off);
+      if (cnt >= rank_need) any_outlier = 1;
+    }
+    int8_t* qr = a.q + row * a.K;
+    for (int c = lane; c < a.K; c += 32) {
+      const float e = elem(c);
+      qr[c] = (int8_t)quant_one(e, s);
+      if (MODE == kKeySmooth && a.smoothed != nullptr)
+        reinterpret_cast<T*>(a.smoothed)[row * a.K + c] = from_f32<T>(e);
+    }
+    if (lane == 0) {
+      if (MODE == kQueryFoldGate) {
+        a.scale[row] = s * a.fold;
+        if (a.plain_scale != nullptr) a.plain_scale[row] = s;
+      } else {
+        a.scale[row] = s;
+      }
+    }
+  }
+  if (MODE == kQueryFoldGate && a.flag != nullptr) {
+    any_outlier = __syncthreads_or(any_outlier);
+    if (threadIdx.x == 0 && any_outlier) atomicOr(a.flag, 1);
+  }
+}
+
+int grid_for(int64_t rows, int64_t rows_per_block) {
+  int64_t need = (rows + rows_per_block - 1) / rows_per_block;
+  const int64_t cap = (int64_t)kNumSms * 16;  // 8 resident blocks per SM, two waves
+  if (need > cap) need = cap;
+  return (int)(need < 1 ? 1 : need);
+}
+
+template <typename T, int MODE, int LPR, int NV>
+void launch_vec(const QuantArgs& a, cudaStream_t s) {
+  const int64_t rpb = (int64_t)(kQuantThreads / 32) * (32 / LPR);
+  quant_rows_vec_kernel<T, LPR, NV, MODE><<<grid_for(a.rows, rpb), kQuantThreads, 0, s>>>(a);
+}
+
+template <typename T, int MODE>
+int launch_2byte(const QuantArgs& a, cudaStream_t s) {
+  const int kvec = a.K / 8;
+  const bool vec_ok = (a.K % 8 == 0) && aligned16(a.x) && (reinterpret_cast<uintptr_t>(a.q) % 8 == 0) &&
+                      (MODE != kKeySmooth || (aligned16(a.mean) && (a.smoothed == nullptr || aligned16(a.smoothed))));
+  if (vec_ok && kvec <= 4) launch_vec<T, MODE, 4, 1>(a, s);
+  else if (vec_ok && kvec <= 8) launch_vec<T, MODE, 8, 1>(a, s);
+  else if (vec_ok && kvec <= 16) launch_vec<T, MODE, 16, 1>(a, s);
+  else if (vec_ok && kvec <= 32) launch_vec<T, MODE, 32, 1>(a, s);
+  else if (vec_ok && kvec <= 64) launch_vec<T, MODE, 32, 2>(a, s);
+  else if (vec_ok && kvec <= 128) launch_vec<T, MODE, 32, 4>(a, s);
+  else
+    quant_rows_generic_kernel<T, MODE><<<grid_for(a.rows, kQuantThreads / 32), kQuantThreads, 0, s>>>(a);
+  return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
+}
+
+template <int MODE>
+int dispatch(const QuantArgs& a, int dtype, cudaStream_t s) {
+  if (a.rows < 0 || a.K < 0) return SL8_ERR_BAD_SHAPE;
+  if (a.rows == 0 || a.K == 0) return SL8_OK;
+  if (a.x == nullptr || a.q == nullptr || a.scale == nullptr) return SL8_ERR_NULL;
+  switch (dtype) {
+    case SL8_F16: return launch_2byte<__half, MODE>(a, s);
+    case SL8_BF16: return launch_2byte<__nv_bfloat16, MODE>(a, s);
+    case SL8_F32:
+      quant_rows_generic_kernel<float, MODE><<<grid_for(a.rows, kQuantThreads / 32), kQuantThreads, 0, s>>>(a);
+      return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
+    default: return SL8_ERR_BAD_DTYPE;
+  }
+}
+
+// ---- K mean -------------------------------------------------------------------
+constexpr int kMeanChunkRows = 1024;
+constexpr int kMeanThreads = 256;
+
+// grid (chunks, BH).  Thread (rl, cv) sums rows rl, rl + RL, ... of the chunk for
+// the 8 columns of vector cv; the RL row-lanes are then added in index order.
+template <typename T>
+__global__ void __launch_bounds__(kMeanThreads) k_mean_partial_kernel(
+    const T* __restrict__ k, int64_t N, int K, const int32_t* __restrict__ seqlens, int heads_per_batch,
+    float* __restrict__ partial, int nchunks) {
+  extern __shared__ float red[];  // [RL][K]
+  const int kvec = K >> 3;
+  int cvp = 1;
+  while (cvp < kvec) cvp <<= 1;   // column lanes, power of two <= 256
+  const int RL = kMeanThreads / cvp;
+  const int cv = threadIdx.x % cvp;
+  const int rl = threadIdx.x / cvp;
+  const int64_t bh = blockIdx.y;
+  const int64_t len = seqlens ? (int64_t)seqlens[bh / heads_per_batch] : N;
+  const int64_t r0 = (int64_t)blockIdx.x * kMeanChunkRows;
+  const int64_t r1 = min(len < N ? len : N, r0 + kMeanChunkRows);
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (cv < kvec) {
+    const T* kb = k + bh * N * K;
+    for (int64_t r = r0 + rl; r < r1; r += RL) {
+      const uint4 u = __ldg(reinterpret_cast<const uint4*>(kb + r * K) + cv);
+      float f[8];
+      Vec8<T>::unpack(u, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[rl * K + cv * 8 + i] = acc[i];
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < K; c += kMeanThreads) {
+    float s = 0.0f;
+    for (int r = 0; r < RL; ++r) s += red[r * K + c];
+    partial[(bh * nchunks + blockIdx.x) * K + c] = s;
+  }
+}
+
+__global__ void k_mean_finish_kernel(const float* __restrict__ partial, int nchunks, int K, int64_t N,
+                                     const int32_t* __restrict__ seqlens, int heads_per_batch,
+                                     float* __restrict__ mean) {
+  const int64_t bh = blockIdx.x;
+  int64_t len = seqlens ? (int64_t)seqlens[bh / heads_per_batch] : N;
+  if (len > N) len = N;
+  const float inv = len > 0 ? __fdiv_rn(1.0f, (float)len) : 0.0f;
+  for (int c = threadIdx.x; c < K; c += blockDim.x) {
+    float s = 0.0f;
+    for (int j = 0; j < nchunks; ++j) s += partial[(bh * nchunks + j) * K + c];
+    mean[bh * K + c] = s * inv;
+  }
+}
+
+}  // namespace
+}  // namespace sl8
+
+using namespace sl8;
+
+extern "C" int sl8_quantize_i8_rowwise(const void* x, int x_dtype, int64_t M, int64_t K, int8_t* q,
+                                       float* scale, void* stream) {
+  if (K > (1 << 30)) return SL8_ERR_TOO_LARGE;
+  QuantArgs a{};
+  a.x = x; a.q = q; a.scale = scale; a.rows = M; a.K = (int)K; a.rows_per_head = 1;
+  return dispatch<kPlain>(a, x_dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int sl8_quant_q_prologue(const void* q, int dtype, int64_t rows, int64_t D, float fold,
+                                    float ratio_threshold, int8_t* q_i8, float* q_scale_folded,
+                                    float* plain_scale, int32_t* outlier_flag, void* stream) {
+  if (D > (1 << 30)) return SL8_ERR_TOO_LARGE;
+  QuantArgs a{};
+  a.x = q; a.q = q_i8; a.scale = q_scale_folded; a.plain_scale = plain_scale; a.flag = outlier_flag;
+  a.rows = rows; a.K = (int)D; a.rows_per_head = 1; a.fold = fold; a.ratio_threshold = ratio_threshold;
+  return dispatch<kQueryFoldGate>(a, dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" size_t sl8_k_mean_workspace(int64_t BH, int64_t N, int64_t D) {
+  if (BH <= 0 || N <= 0 || D <= 0) return 16;
+  const int64_t nchunks = (N + kMeanChunkRows - 1) / kMeanChunkRows;
+  return (size_t)(BH * nchunks * D) * sizeof(float) + 16;
+}
+
+extern "C" int sl8_k_mean(const void* k, int dtype, int64_t BH, int64_t N, int64_t D,
+                          const int32_t* seqlens, int32_t heads_per_batch, float* mean, void* workspace,
+                          size_t workspace_bytes, void* stream) {
+  if (BH < 0 || N < 0 || D < 0) return SL8_ERR_BAD_SHAPE;
+  if (BH == 0 || D == 0) return SL8_OK;
+  if (k == nullptr || mean == nullptr) return SL8_ERR_NULL;
+  if (dtype != SL8_F16 && dtype != SL8_BF16) return SL8_ERR_BAD_DTYPE;
+  if (D % 8 != 0 || D > 2048) return SL8_ERR_BAD_HEAD_DIM;
+  if (!aligned16(k)) return SL8_ERR_MISALIGNED;
+  if (seqlens != nullptr && heads_per_batch <= 0) return SL8_ERR_BAD_SHAPE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (N == 0) {
+    SL8_CUDA_TRY(cudaMemsetAsync(mean, 0, (size_t)(BH * D) * sizeof(float), s));
+    return SL8_OK;
+  }
+  if (workspace == nullptr || workspace_bytes < sl8_k_mean_workspace(BH, N, D)) return SL8_ERR_WORKSPACE;
+  const int nchunks = (int)((N + kMeanChunkRows - 1) / kMeanChunkRows);
+  int cvp = 1;
+  while (cvp < D / 8) cvp <<= 1;
+  const size_t smem = (size_t)(kMeanThreads / cvp) * D * sizeof(float);
+  float* partial = reinterpret_cast<float*>(workspace);
+  dim3 grid(nchunks, (unsigned)BH);
+  if (BH > 65535) return SL8_ERR_TOO_LARGE;
+  if (dtype == SL8_F16)
+    k_mean_partial_kernel<__half><<<grid, kMeanThreads, smem, s>>>(
+        reinterpret_cast<const __half*>(k), N, (int)D, seqlens, heads_per_batch, partial, nchunks);
+  else
+    k_mean_partial_kernel<__nv_bfloat16><<<grid, kMeanThreads, smem, s>>>(
+        reinterpret_cast<const __nv_bfloat16*>(k), N, (int)D, seqlens, heads_per_batch, partial, nchunks);
+  k_mean_finish_kernel<<<(unsigned)BH, 128, 0, s>>>(partial, nchunks, (int)D, N, seqlens, heads_per_batch, mean);
+  return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
+}
+
+extern "C" int sl8_smooth_quant_k(const void* k, int dtype, int64_t BH, int64_t N, int64_t D,
+                                  const float* mean, int8_t* k_i8, float* k_scale, void* k_smoothed,
+                                  void* stream) {
+  if (BH < 0 || N < 0 || D < 0) return SL8_ERR_BAD_SHAPE;
+  if (D > (1 << 30)) return SL8_ERR_TOO_LARGE;
+  if (BH * N > 0 && mean == nullptr) return SL8_ERR_NULL;
+  if (dtype == SL8_F32) return SL8_ERR_BAD_DTYPE;
+  QuantArgs a{};
+  a.x = k; a.q = k_i8; a.scale = k_scale; a.mean = mean; a.smoothed = k_smoothed;
+  a.rows = BH * N; a.K = (int)D; a.rows_per_head = N > 0 ? N : 1;
+  return dispatch<kKeySmooth>(a, dtype, static_cast<cudaStream_t>(stream));
+}

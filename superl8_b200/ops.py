@@ -1,0 +1,94 @@
+"""Python entry points with the reference's signatures (reference superl8/ops.py:70-267)."""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _C, _lib
+from .quant import _capturing, quantize_q, quantize_qk, smooth_quantize_k, k_mean
+
+last_gate_decision: bool | None = None  # whether the most recent attn_int8_fwd call was demoted
+
+
+def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, int8_pv: bool = False,
+                  rotate: bool = False, window_left: int = -1, per_warp_quant: bool = True,
+                  internal_accuracy_gate: bool = True, seqlens_q=None, seqlens_k=None,
+                  backend: int = _lib.SL8_BACKEND_AUTO):
+    """INT8-QK FlashAttention-2 forward; q, k, v fp16/bf16 [B, H, S, D]; output in v's dtype.
+
+    Same contract as the reference entry (superl8/ops.py:70-175): per-row int8 Q and
+    smoothed K with exp2-ready folded scales, fp32 softmax, 16-bit P.V, bottom-right
+    aligned causal mask, optional left window.  The accuracy gate (any Q row with
+    max|q|/median|q| > 12) demotes the whole call to the full-precision kernel; it is
+    evaluated inside the Q quantisation pass and costs one 4-byte device->host read,
+    skipped during CUDA-graph capture like the reference's.
+    ``seqlens_q`` / ``seqlens_k`` (int32 [B], not in the reference) give per-sequence
+    lengths for padded ragged batches.
+    """
+    global last_gate_decision
+    if int8_pv:
+        raise NotImplementedError("superl8_b200: int8 P.V (int8_pv=True) is not implemented; P.V runs in v's dtype")
+    del per_warp_quant
+    s = (1.0 / math.sqrt(q.shape[-1])) if scale is None else scale
+    use_gate = internal_accuracy_gate and not _capturing()
+    if rotate:
+        if use_gate:
+            _qi, _qs, flag = quantize_q(q, s, want_gate=True)
+            if bool(flag.item()):
+                last_gate_decision = True
+                return _C.attn_fp16_fwd(q, k, v, causal, s, window_left, None, seqlens_q=seqlens_q, seqlens_k=seqlens_k)
+        q_i8, q_scale, k_i8, k_scale, _ = quantize_qk(q, k, softmax_scale=s, rotate=True, seqlens_k=seqlens_k)
+    else:
+        q_i8, q_scale, flag = quantize_q(q, s, want_gate=use_gate)
+        if use_gate and bool(flag.item()):
+            last_gate_decision = True
+            if v.dtype == q.dtype and k.dtype == q.dtype:
+                return _C.attn_fp16_fwd(q, k, v, causal, s, window_left, None, seqlens_q=seqlens_q, seqlens_k=seqlens_k)
+            return _C.attn_fp16_fwd(q.to(v.dtype), k.to(v.dtype), v, causal, s, window_left, None,
+                                    seqlens_q=seqlens_q, seqlens_k=seqlens_k)
+        k_i8, k_scale, _ = smooth_quantize_k(k, k_mean(k, seqlens_k))
+    last_gate_decision = False if use_gate else None
+    return _C.attn_int8_fwd(q_i8, q_scale.squeeze(-1).contiguous(), k_i8, k_scale.squeeze(-1).contiguous(),
+                            v.contiguous(), causal, window_left, seqlens_q=seqlens_q, seqlens_k=seqlens_k,
+                            backend=backend)
+
+
+def attn_fp16_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, mask=None, window_left: int = -1):
+    """Full-precision forward (reference superl8/ops.py:178-227)."""
+    return _C.attn_fp16_fwd(q.contiguous(), k.contiguous(), v.contiguous(), causal, scale, window_left, mask)
+
+
+def attn_int8_decode(q, k, v, *, scale: float | None = None, rotate: bool = False, num_splits: int | None = None):
+    """Decode (M = 1) via split-KV from fp16 q, k, v; quantises Q and the whole K first,
+    exactly like the reference entry (superl8/ops.py:230-267)."""
+    assert q.shape[-2] == 1, f"decode expects M=1, got M={q.shape[-2]}"
+    q_i8, q_scale, k_i8, k_scale, _ = quantize_qk(q, k, softmax_scale=scale, rotate=rotate)
+    ns = -1 if num_splits is None else int(num_splits)
+    return _C.attn_int8_decode(q_i8, q_scale.reshape(q.shape[0], q.shape[1], 1).contiguous(), k_i8,
+                               k_scale.squeeze(-1).contiguous(), v.contiguous(), ns)
+
+
+def attn_decode(q, k, v, **kw):
+    """Alias of :func:`attn_int8_decode`."""
+    return attn_int8_decode(q, k, v, **kw)
+
+
+def attn_decode_int8_cache(q, k_i8, k_scale, v, *, scale: float | None = None, num_splits: int | None = None,
+                           context_lens=None):
+    """Decode against an ALREADY quantised K cache (int8 [B,Hkv,N,D] + fp32 [B,Hkv,N]) and an
+    fp16 V cache: only the one-row Q is quantised per step.  This is the serving-time shape of
+    the path (the reference quantises its query the same way for cached decode,
+    superl8/ops.py:706-717); ``context_lens`` int32 [B] gives per-sequence lengths."""
+    assert q.shape[-2] == 1, f"decode expects M=1, got M={q.shape[-2]}"
+    s = (1.0 / math.sqrt(q.shape[-1])) if scale is None else scale
+    q_i8, q_scale, _ = quantize_q(q, s)
+    ns = -1 if num_splits is None else int(num_splits)
+    return _C.attn_int8_decode(q_i8, q_scale.reshape(q.shape[0], q.shape[1], 1).contiguous(), k_i8, k_scale, v, ns,
+                               context_lens=context_lens)
+
+
+def quantize_i8_rowwise(x: torch.Tensor):
+    """[M, K] -> (int8 [M, K], fp32 [M]) (reference superl8/ops.py:975-991; CUDA tensors only)."""
+    return _C.quantize_i8_rowwise(x)
