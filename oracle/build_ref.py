@@ -1,0 +1,35 @@
+"""Builds oracle/_ref/libref_kernels.so: the reference's OWN CUDA kernels (its header-only
+device code, compiled from the reference checkout where it lies) behind the extern "C"
+launchers of oracle/ref_kernels.cu, for sm_100a.  Checker only -- the product never loads
+it.  Needs the reference checkout; on a GPU box the prebuilt file is used.
+
+    python oracle/build_ref.py [/path/to/reference]
+"""
+
+import subprocess
+import sys
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+OUT_DIR = HERE / "_ref"
+LIB = OUT_DIR / "libref_kernels.so"
+
+
+def build_ref(reference_root="/root/reference", force=False):
+    inc = Path(reference_root) / "csrc" / "include"
+    if not inc.is_dir():
+        return None
+    src = HERE / "ref_kernels.cu"
+    if LIB.exists() and not force and LIB.stat().st_mtime > src.stat().st_mtime:
+        return LIB
+    OUT_DIR.mkdir(exist_ok=True)
+    cmd = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
+           "-Xcompiler", "-fPIC", "-shared", "-I", str(inc), str(src), "-o", str(LIB)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("reference kernel build failed:\n" + r.stdout + r.stderr)
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build_ref(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", force=True))

@@ -1,0 +1,300 @@
+"""CPU restatement of the reference's int8 attention path.  TEST INFRASTRUCTURE ONLY.
+
+Only ``tests/``, ``__graft_entry__.smoke()`` and ``bench.py``'s CPU-baseline legs may
+import this module; the product (``superl8_b200``) never does and has no CPU path.
+
+Parity status: PINNED.  ``tests/test_oracle_golden.py`` checks every function here
+against vectors produced by importing the reference's own Python code
+(``tests/golden/make_golden.py`` -> ``tests/golden/*.npz``), and on a GPU box
+``tests/test_ref_kernels.py`` checks the kernel restatements against the reference's
+own CUDA kernels compiled from its sources (``oracle/_ref``).
+
+Two scale rules exist in the reference and both are restated:
+  rule="cpu"   scale = amax / 127        (reference CPU branch, superl8/quant/core.py:58)
+  rule="cuda"  scale = amax * f32(1/127) (reference CUDA kernel,
+               csrc/include/quant_rowwise.cuh:33-38, 72) -- the parity target.
+Everything is torch-on-CPU / numpy in fp32 with the reference's operation order.
+"""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+LOG2E = math.log2(math.e)  # reference superl8/quant/core.py:24
+Q_MAX = 127.0              # reference superl8/quant/core.py:25
+K_MEAN_CHUNK = 1024        # reference superl8/quant/core.py:26
+DEC_NEG_INF = -1e30        # reference csrc/include/attn_decode.cuh:34
+
+
+# --------------------------------------------------------------------------- quantiser
+
+def quantize_rowwise(x: torch.Tensor, rule: str = "cuda"):
+    """Reference superl8/quant/core.py:47-62 and csrc/include/quant_rowwise.cuh:42-92.
+    Returns (q int8 [..., d], scale fp32 [..., 1])."""
+    xf = x.detach().cpu().float()
+    amax = xf.abs().amax(dim=-1, keepdim=True)
+    if rule == "cuda":
+        scale = amax * torch.tensor(np.float32(1.0) / np.float32(127.0))
+    elif rule == "cpu":
+        scale = amax / Q_MAX
+    else:
+        raise ValueError(rule)
+    safe = torch.where(scale == 0, torch.ones_like(scale), scale)
+    q = torch.round(xf / safe).clamp_(-Q_MAX, Q_MAX).to(torch.int8)
+    return q, safe
+
+
+def k_mean_fp32(k: torch.Tensor) -> torch.Tensor:
+    """Reference superl8/quant/core.py:29-44: fp32 mean over keys, 1024-row partial sums
+    when N > 1024.  (Summation order inside each partial is torch's own.)"""
+    k = k.detach().cpu()
+    n = k.shape[-2]
+    if n <= K_MEAN_CHUNK:
+        return torch.mean(k, dim=-2, keepdim=True, dtype=torch.float32)
+    mean = torch.zeros((*k.shape[:-2], 1, k.shape[-1]), dtype=torch.float32)
+    for start in range(0, n, K_MEAN_CHUNK):
+        mean.add_(torch.sum(k[..., start:start + K_MEAN_CHUNK, :], dim=-2, keepdim=True, dtype=torch.float32))
+    return mean.div_(n)
+
+
+def smooth_k(k: torch.Tensor, mean: torch.Tensor | None = None):
+    """Reference superl8/quant/core.py:70-95: k_s = dtype(fp32(k) - mean)."""
+    k = k.detach().cpu()
+    mean = k_mean_fp32(k) if mean is None else mean.detach().cpu().float()
+    k_s = (k.float() - mean).to(k.dtype)
+    return k_s, mean
+
+
+def detect_q_outlier_domination(q: torch.Tensor, ratio_threshold: float = 12.0) -> bool:
+    """Reference superl8/quant/core.py:113-145 (median = lower middle element)."""
+    q_abs = q.detach().cpu().float().abs()
+    row_max = q_abs.amax(dim=-1)
+    row_med = q_abs.median(dim=-1).values
+    return bool(((row_max / (row_med + 1e-10)) > ratio_threshold).any())
+
+
+def outlier_rows(q: torch.Tensor, ratio_threshold: float = 12.0) -> torch.Tensor:
+    q_abs = q.detach().cpu().float().abs()
+    return (q_abs.amax(dim=-1) / (q_abs.median(dim=-1).values + 1e-10)) > ratio_threshold
+
+
+def fold_scale(scale: torch.Tensor, softmax_scale: float) -> torch.Tensor:
+    """Reference superl8/quant/core.py:195: fp32 tensor times a Python scalar."""
+    return scale * (softmax_scale * LOG2E)
+
+
+def quantize_qk(q, k, softmax_scale=None, rule: str = "cuda", k_mean=None):
+    """Reference superl8/quant/core.py:164-196 (rotate=False)."""
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(q.shape[-1])
+    k_s, mean = smooth_k(k, k_mean)
+    q_i8, q_scale = quantize_rowwise(q, rule)
+    k_i8, k_scale = quantize_rowwise(k_s, rule)
+    return q_i8, fold_scale(q_scale, softmax_scale), k_i8, k_scale, mean
+
+
+# --------------------------------------------------------------------------- fp32 oracles
+
+def _expand_kv(kf, vf, h_q):
+    h_kv = kf.shape[1]
+    if h_q != h_kv:
+        assert h_q % h_kv == 0
+        rep = h_q // h_kv
+        kf = kf.repeat_interleave(rep, dim=1)
+        vf = vf.repeat_interleave(rep, dim=1)
+    return kf, vf
+
+
+def attention_fp32(q, k, v, causal: bool = False, scale: float | None = None, window_left: int = -1):
+    """Reference tests/reference.py:26-54 (and :57-86 for the window): naive fp32 attention,
+    GQA by repeat_interleave, bottom-right aligned causal mask."""
+    qf, kf, vf = (t.detach().cpu().float() for t in (q, k, v))
+    kf, vf = _expand_kv(kf, vf, qf.shape[1])
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    s = torch.einsum("bhmd,bhnd->bhmn", qf, kf) * scale
+    m_len, n_len = s.shape[-2], s.shape[-1]
+    if window_left >= 0:
+        row = torch.arange(m_len).view(-1, 1)
+        col = torch.arange(n_len).view(1, -1)
+        diff = (row + (n_len - m_len)) - col
+        s = s.masked_fill(~((diff >= 0) & (diff < window_left)), float("-inf"))
+    elif causal:
+        keep = torch.ones(m_len, n_len, dtype=torch.bool).tril(n_len - m_len)
+        s = s.masked_fill(~keep, float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    return torch.einsum("bhmn,bhnd->bhmd", p, vf)
+
+
+def attention_fp32_ragged(q, k, v, seqlens_q, seqlens_k, causal=False, scale=None):
+    """Per-sequence loop over [:, :, :len] slices (the pattern of reference
+    tests/reference.py:154-169); padded output rows are zero."""
+    out = torch.zeros(q.shape, dtype=torch.float32)
+    for b in range(q.shape[0]):
+        mq, nk = int(seqlens_q[b]), int(seqlens_k[b])
+        if mq and nk:
+            out[b:b + 1, :, :mq] = attention_fp32(q[b:b + 1, :, :mq], k[b:b + 1, :, :nk], v[b:b + 1, :, :nk], causal, scale)
+    return out
+
+
+# --------------------------------------------------------------------------- kernel restatements
+
+def int32_logits(q_i8: torch.Tensor, k_i8: torch.Tensor) -> torch.Tensor:
+    """int32 Q.K^T (reference csrc/include/attn_int8_fwd.cuh:129-133: __dp4a chain).
+    q [..., M, D], k [..., N, D] int8 -> int32 [..., M, N].  Exact: |acc| <= 127^2 * 256 < 2^31."""
+    a = q_i8.detach().cpu().numpy().astype(np.int32)
+    b = k_i8.detach().cpu().numpy().astype(np.int32)
+    return torch.from_numpy(np.matmul(a, np.swapaxes(b, -1, -2)).astype(np.int32))
+
+
+def attn_int8_fwd(q_i8, q_scale, k_i8, k_scale, v, causal=False, window_left=-1, want_lse=False):
+    """Kernel mathematics of reference csrc/include/attn_int8_fwd.cuh:126-208, whole rows at
+    once instead of 64-key tiles: s = float(acc) * q_scale[m] * k_scale[n]; masked -> -inf;
+    p = exp2(s - rowmax); out = (p @ v) / l cast to v's dtype, 0 where l == 0;
+    lse = m * ln2 + ln l.  q_scale [B,Hq,M], k_scale [B,Hkv,N]."""
+    q_i8, k_i8, v = q_i8.detach().cpu(), k_i8.detach().cpu(), v.detach().cpu()
+    qs, ks = q_scale.detach().cpu().float(), k_scale.detach().cpu().float()
+    B, Hq, M, D = q_i8.shape
+    Hkv, N = k_i8.shape[1], k_i8.shape[2]
+    g = Hq // Hkv
+    out = torch.zeros((B, Hq, M, D), dtype=v.dtype)
+    lse = torch.full((B, Hq, M), float("-inf"), dtype=torch.float32)
+    if N == 0 or M == 0:
+        return (out, lse) if want_lse else out
+    row = torch.arange(M).view(-1, 1)
+    col = torch.arange(N).view(1, -1)
+    pos = row + ((N - M) if causal else 0)
+    valid = torch.ones(M, N, dtype=torch.bool)
+    if causal:
+        valid &= col <= pos
+    if window_left >= 0:
+        valid &= col > pos - window_left
+    for b in range(B):
+        for h in range(Hq):
+            hk = h // g
+            acc = int32_logits(q_i8[b, h], k_i8[b, hk]).float()
+            s = acc * qs[b, h].view(-1, 1) * ks[b, hk].view(1, -1)
+            s = torch.where(valid, s, torch.full_like(s, float("-inf")))
+            m = s.amax(dim=-1, keepdim=True)
+            m_safe = torch.where(torch.isinf(m), torch.zeros_like(m), m)
+            p = torch.exp2(s - m_safe)
+            l = p.sum(dim=-1, keepdim=True)
+            o = p @ v[b, hk].float()
+            inv = torch.where(l > 0, 1.0 / l, torch.zeros_like(l))
+            out[b, h] = (o * inv).to(v.dtype)
+            lse[b, h] = torch.where(l.squeeze(-1) > 0, m.squeeze(-1) * 0.6931471805599453 + torch.log(l.squeeze(-1)),
+                                    torch.full_like(l.squeeze(-1), float("-inf")))
+    return (out, lse) if want_lse else out
+
+
+def choose_n_splits_reference(n_len: int, bhq: int) -> int:
+    """Reference csrc/kernel/attn_decode.cu:33-53."""
+    if n_len <= 0 or bhq <= 0:
+        return 1
+    s_occ = (2048 + bhq - 1) // bhq
+    s_lo = (n_len + 255) // 256
+    s_hi = max(1, (n_len + 47) // 48)
+    return max(1, min(min(max(s_occ, s_lo), s_hi), 256))
+
+
+def attn_int8_decode(q_i8, q_scale, k_i8, k_scale, v, n_splits: int = 1, context_lens=None):
+    """Reference csrc/include/attn_decode.cuh:68-131 (split) and :442-465 (combine): split s
+    owns keys [s*per, min(len, (s+1)*per)), per = ceil(N / n_splits); partial (o, m, l) in
+    the exp2 domain; merge o = sum o_s 2^(m_s - gm) / sum l_s 2^(m_s - gm) -> fp16.
+    q_i8 [B,Hq,1,D], q_scale [B,Hq(,1)], k_i8 [B,Hkv,N,D], k_scale [B,Hkv,N], v fp16."""
+    q_i8, k_i8, v = q_i8.detach().cpu(), k_i8.detach().cpu(), v.detach().cpu()
+    qs = q_scale.detach().cpu().float().reshape(q_i8.shape[0], q_i8.shape[1])
+    ks = k_scale.detach().cpu().float()
+    B, Hq, _, D = q_i8.shape
+    Hkv, N = k_i8.shape[1], k_i8.shape[2]
+    g = Hq // Hkv
+    out = torch.zeros((B, Hq, 1, D), dtype=torch.float16)
+    if N == 0:
+        return out
+    per = (N + n_splits - 1) // n_splits
+    for b in range(B):
+        n_b = N if context_lens is None else min(int(context_lens[b]), N)
+        for h in range(Hq):
+            hk = h // g
+            acc = int32_logits(q_i8[b, h], k_i8[b, hk, :n_b]).float().view(-1)
+            s = acc * qs[b, h] * ks[b, hk, :n_b]
+            ms, ls, os_ = [], [], []
+            for sp in range(n_splits):
+                n0, n1 = sp * per, min(n_b, (sp + 1) * per)
+                if n1 <= n0:
+                    continue
+                m = s[n0:n1].max()
+                p = torch.exp2(s[n0:n1] - m)
+                ms.append(m)
+                ls.append(p.sum())
+                os_.append(p @ v[b, hk, n0:n1].float())
+            if not ms:
+                continue
+            gm = torch.stack(ms).max()
+            w = torch.exp2(torch.stack(ms) - gm)
+            denom = (torch.stack(ls) * w).sum()
+            o = (torch.stack(os_) * w.view(-1, 1)).sum(dim=0)
+            out[b, h, 0] = (o / denom if denom > 0 else torch.zeros_like(o)).to(torch.float16)
+    return out
+
+
+# --------------------------------------------------------------------------- gates (reference tests/tolerances.py)
+
+def sqnr_db(out, ref) -> float:
+    ref_f, out_f = ref.detach().cpu().float(), out.detach().cpu().float()
+    noise = (out_f - ref_f).pow(2).mean()
+    signal = ref_f.pow(2).mean()
+    if noise == 0:
+        return float("inf")
+    return (10.0 * torch.log10(signal / noise)).item()
+
+
+def cos_sim(out, ref) -> float:
+    a, b = out.detach().cpu().float().flatten(), ref.detach().cpu().float().flatten()
+    return torch.nn.functional.cosine_similarity(a, b, dim=0).item()
+
+
+def rel_l1(out, ref) -> float:
+    ref_f = ref.detach().cpu().float()
+    return ((out.detach().cpu().float() - ref_f).abs().sum() / ref_f.abs().sum().clamp_min(1e-12)).item()
+
+
+def assert_int8_quality(out, ref, *, min_cos=0.999, max_rel_l1=0.02, min_sqnr_db=20.0, what="int8 output"):
+    """The reference's one int8 gate (tests/tolerances.py:74-88)."""
+    assert torch.isfinite(out.detach().cpu().float()).all(), f"{what} contains NaN/Inf"
+    c, l1, s = cos_sim(out, ref), rel_l1(out, ref), sqnr_db(out, ref)
+    assert c >= min_cos, f"{what}: cos-sim {c:.6f} < {min_cos}"
+    assert l1 <= max_rel_l1, f"{what}: rel-L1 {l1:.4f} > {max_rel_l1}"
+    assert s >= min_sqnr_db, f"{what}: SQNR {s:.1f} dB < {min_sqnr_db} dB"
+
+
+# --------------------------------------------------------------------------- synthetic inputs
+
+def make_qkv(seed: int, Hq: int, Hkv: int, S: int, D: int, Sk: int | None = None, dtype=torch.float16):
+    """One batch element: Q [Hq,S,D], K, V [Hkv,Sk,D] drawn in that order from a CPU
+    generator seeded with ``seed``, ~N(0,1), cast to ``dtype``."""
+    g = torch.Generator().manual_seed(seed)
+    Sk = S if Sk is None else Sk
+    q = torch.randn(Hq, S, D, generator=g).to(dtype)
+    k = torch.randn(Hkv, Sk, D, generator=g).to(dtype)
+    v = torch.randn(Hkv, Sk, D, generator=g).to(dtype)
+    return q, k, v
+
+
+def make_batch(cfg: int, B: int, Hq: int, Hkv: int, S: int, D: int, Sk: int | None = None, dtype=torch.float16,
+               first_b: int = 0):
+    """Batch elements first_b .. first_b + B - 1 of a configuration: seed = 1000 * cfg + b."""
+    qs, ks, vs = zip(*(make_qkv(1000 * cfg + first_b + b, Hq, Hkv, S, D, Sk, dtype) for b in range(B)))
+    return torch.stack(qs), torch.stack(ks), torch.stack(vs)
+
+
+def outlier_channels(H: int, D: int, seed: int, frac: float = 0.01) -> torch.Tensor:
+    """Mask [H, D] of the ceil(frac * H * D) channels that get scaled x20."""
+    n = math.ceil(frac * H * D)
+    idx = torch.randperm(H * D, generator=torch.Generator().manual_seed(seed))[:n]
+    mask = torch.zeros(H * D, dtype=torch.bool)
+    mask[idx] = True
+    return mask.view(H, D)

@@ -52,8 +52,12 @@ def device_status(device=None) -> int:
     """Synchronises and returns the device status word of the current stream's
     status buffer (0, or the DEVICE_TIMEOUT code when a bounded wait expired)."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    buf = _status_buffer(device)
-    return _lib.load().sl8_read_device_status(_ptr(buf), _stream(device))
+    lib = _lib.load()
+    rc = lib.sl8_read_device_status(_ptr(_status_buffer(device)), _stream(device))
+    ws = _decode_ws.get((device.index, torch.cuda.current_stream(device).cuda_stream))
+    if rc == 0 and ws is not None:
+        rc = lib.sl8_read_device_status(_ptr(ws), _stream(device))
+    return rc
 
 
 def quantize_i8_rowwise(x: torch.Tensor):

@@ -1,0 +1,143 @@
+"""Generates tests/golden/*.npz by running the REFERENCE's own Python code on CPU.
+
+Run in a container that has the reference checkout (it cannot travel to a GPU box):
+    python tests/golden/make_golden.py /path/to/reference
+Inputs are seeded; inputs and the reference's outputs are both stored so the tests
+never need the reference.  16-bit floats are stored as raw bit patterns.
+"""
+
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+sys.path.insert(0, str(ref_root))
+sys.path.insert(0, str(ref_root / "tests"))
+
+from superl8.quant.core import (  # noqa: E402
+    detect_q_outlier_domination,
+    quantize_int8_rowwise,
+    quantize_qk,
+    smooth_k,
+)
+import reference as ref_oracles  # noqa: E402  (reference tests/reference.py)
+import tolerances as ref_tol  # noqa: E402  (reference tests/tolerances.py)
+
+OUT = Path(__file__).resolve().parent
+
+
+def bits(t: torch.Tensor) -> np.ndarray:
+    if t.dtype in (torch.float16, torch.bfloat16):
+        return t.contiguous().view(torch.int16).numpy()
+    return t.contiguous().numpy()
+
+
+def gen(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def quant_cases():
+    out = {}
+    cases = {
+        "f16_128": (torch.randn(37, 128, generator=gen(1)).half(), "float16"),
+        "f16_64": (torch.randn(50, 64, generator=gen(2)).half() * 3.0, "float16"),
+        "bf16_128": (torch.randn(33, 128, generator=gen(3)).bfloat16(), "bfloat16"),
+        "f32_72": (torch.randn(21, 72, generator=gen(4)), "float32"),
+        "f16_odd33": (torch.randn(19, 33, generator=gen(5)).half(), "float16"),
+        "f16_256": (torch.randn(17, 256, generator=gen(6)).half() * 0.01, "float16"),
+    }
+    x = cases["f16_128"][0]
+    x[3] = 0                      # zero row -> scale 1
+    x[5, 7] = 1000.0              # outlier row
+    x[6] = 0
+    x[6, 0] = -65504.0            # fp16 max: saturates to -127
+    for name, (x, dt) in cases.items():
+        q, s = quantize_int8_rowwise(x)      # reference CPU branch
+        out[f"{name}__x"] = bits(x)
+        out[f"{name}__dtype"] = np.array(dt)
+        out[f"{name}__q"] = q.numpy()
+        out[f"{name}__scale"] = s.numpy()
+    np.savez_compressed(OUT / "quant_rowwise.npz", **out)
+
+
+def smooth_cases():
+    out = {}
+    cases = {
+        "short": torch.randn(2, 2, 300, 64, generator=gen(11)).half() + 0.5,
+        "chunked": torch.randn(1, 1, 2500, 64, generator=gen(12)).half() * 2.0 - 1.0,
+        "bf16": (torch.randn(1, 2, 130, 128, generator=gen(13)) + 2.0).bfloat16(),
+    }
+    for name, k in cases.items():
+        k_s, k_mean = smooth_k(k)
+        out[f"{name}__k"] = bits(k)
+        out[f"{name}__dtype"] = np.array(str(k.dtype).replace("torch.", ""))
+        out[f"{name}__k_s"] = bits(k_s)
+        out[f"{name}__k_mean"] = k_mean.numpy()
+    np.savez_compressed(OUT / "smooth_k.npz", **out)
+
+
+def gate_cases():
+    out = {}
+    base = torch.randn(2, 4, 64, 128, generator=gen(21)).half()
+    spike = base.clone()
+    spike[1, 2, 17, 5] = 60.0
+    chan = base.clone()
+    chan[:, :, :, 9] *= 20.0
+    d64 = torch.randn(1, 2, 512, 64, generator=gen(22)).half()
+    near = torch.ones(1, 1, 4, 8).half()
+    near[0, 0, 0, 0] = 12.0      # ratio exactly 12 -> not > 12
+    near[0, 0, 1, 0] = 12.01     # just above
+    near[0, 0, 1, 1:] = 1.0
+    for name, q in {"clean": base, "spike": spike, "chan20": chan, "d64": d64, "near": near}.items():
+        out[f"{name}__q"] = bits(q)
+        out[f"{name}__flag"] = np.array(detect_q_outlier_domination(q))
+        qa = q.float().abs()
+        out[f"{name}__ratio"] = (qa.amax(-1) / (qa.median(-1).values + 1e-10)).numpy()
+    np.savez_compressed(OUT / "outlier_gate.npz", **out)
+
+
+def qk_cases():
+    out = {}
+    q = torch.randn(1, 4, 96, 64, generator=gen(31)).half()
+    k = torch.randn(1, 2, 80, 64, generator=gen(32)).half() + 0.25
+    for name, sc in {"default": None, "scaled": 0.2}.items():
+        q_i8, q_scale, k_i8, k_scale, k_mean = quantize_qk(q, k, softmax_scale=sc)
+        out[f"{name}__q_i8"] = q_i8.numpy()
+        out[f"{name}__q_scale"] = q_scale.numpy()
+        out[f"{name}__k_i8"] = k_i8.numpy()
+        out[f"{name}__k_scale"] = k_scale.numpy()
+        out[f"{name}__k_mean"] = k_mean.numpy()
+    out["q"] = bits(q)
+    out["k"] = bits(k)
+    np.savez_compressed(OUT / "quantize_qk.npz", **out)
+
+
+def attention_cases():
+    out = {}
+    g = gen(41)
+    q = torch.randn(2, 4, 40, 32, generator=g).half()
+    k = torch.randn(2, 2, 56, 32, generator=g).half()
+    v = torch.randn(2, 2, 56, 32, generator=g).half()
+    out["q"], out["k"], out["v"] = bits(q), bits(k), bits(v)
+    out["noncausal"] = ref_oracles.attention_fp32_oracle(q, k, v).numpy()
+    out["causal_rect"] = ref_oracles.attention_fp32_oracle(q, k, v, causal=True).numpy()
+    out["scaled"] = ref_oracles.attention_fp32_oracle(q, k, v, causal=True, scale=0.3).numpy()
+    out["window9"] = ref_oracles.attention_fp32_window_oracle(q, k, v, window_left=9).numpy()
+    a = torch.randn(3, 50, generator=g)
+    b = a + 0.05 * torch.randn(3, 50, generator=g)
+    out["metric_a"], out["metric_b"] = a.numpy(), b.numpy()
+    out["metric_vals"] = np.array([ref_tol.cos_sim(b, a), ref_tol.rel_l1(b, a), ref_tol.sqnr_db(b, a)])
+    np.savez_compressed(OUT / "attention_fp32.npz", **out)
+
+
+if __name__ == "__main__":
+    torch.set_num_threads(1)
+    quant_cases()
+    smooth_cases()
+    gate_cases()
+    qk_cases()
+    attention_cases()
+    for f in sorted(OUT.glob("*.npz")):
+        print(f.name, f.stat().st_size)

@@ -1,0 +1,90 @@
+"""CPU-only checks of the C-ABI boundary: the library loads, exports every symbol the
+header declares, and rejects bad requests on the host before touching a device."""
+
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+
+from superl8_b200 import _lib
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = ROOT / "include" / "superl8_b200.h"
+
+
+def declared_symbols():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(sl8_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_all_exported_and_bound():
+    lib = _lib.load()
+    names = declared_symbols()
+    assert len(names) >= 16
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in the header but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    assert lib.sl8_abi_version() == 1
+
+
+def test_status_strings_carry_the_reference_key_words():
+    assert "num_splits" in _lib.status_string(_lib.ERR_BAD_NUM_SPLITS)
+    assert "float16 or bfloat16" in _lib.status_string(_lib.ERR_BAD_DTYPE)
+    assert "head dim" in _lib.status_string(_lib.ERR_BAD_HEAD_DIM)
+    assert _lib.status_string(0) == "ok"
+
+
+def test_host_side_validation_needs_no_device():
+    lib = _lib.load()
+    p = _lib.DecodeParams(B=1, Hq=8, Hkv=2, N=128, D=96, num_splits=-1)
+    assert lib.sl8_attn_int8_decode(C.byref(p), None, 0, None) == _lib.ERR_BAD_HEAD_DIM
+    for ns in (0, 257, -2):
+        p = _lib.DecodeParams(B=1, Hq=8, Hkv=2, N=128, D=128, num_splits=ns)
+        assert lib.sl8_attn_int8_decode(C.byref(p), None, 0, None) == _lib.ERR_BAD_NUM_SPLITS
+    p = _lib.DecodeParams(B=1, Hq=8, Hkv=3, N=128, D=128, num_splits=1)
+    assert lib.sl8_attn_int8_decode(C.byref(p), None, 0, None) == _lib.ERR_BAD_SHAPE
+    f = _lib.FwdParams(B=1, Hq=4, Hkv=2, M=64, N=64, D=96, v_dtype=0)
+    assert lib.sl8_attn_int8_fwd(C.byref(f), None, 0, None) == _lib.ERR_BAD_HEAD_DIM
+    f = _lib.FwdParams(B=1, Hq=4, Hkv=2, M=64, N=64, D=128, v_dtype=2)
+    assert lib.sl8_attn_int8_fwd(C.byref(f), None, 0, None) == _lib.ERR_BAD_DTYPE
+    f = _lib.FwdParams(B=1, Hq=4, Hkv=2, M=0, N=64, D=128, v_dtype=0)
+    assert lib.sl8_attn_int8_fwd(C.byref(f), None, 0, None) == 0          # empty output is a no-op
+    f = _lib.FwdParams(B=1, Hq=4, Hkv=2, M=64, N=64, D=128, v_dtype=0)
+    assert lib.sl8_attn_int8_fwd(C.byref(f), None, 0, None) == _lib.ERR_NULL
+    assert lib.sl8_quantize_i8_rowwise(None, 0, 0, 128, None, None, None) == 0
+    assert lib.sl8_quantize_i8_rowwise(None, 0, 4, 128, None, None, None) == _lib.ERR_NULL
+    assert lib.sl8_quantize_i8_rowwise(None, 7, 4, 128, C.c_void_p(16), C.c_void_p(16), None) == _lib.ERR_NULL
+
+
+def test_split_heuristic_properties():
+    lib = _lib.load()
+    assert lib.sl8_choose_n_splits(0, 8) == 1
+    for n, bh in ((1024, 1024), (32768, 1024), (777, 8), (64000, 24), (100, 1), (2000, 16)):
+        s = lib.sl8_choose_n_splits(n, bh)
+        assert 1 <= s <= 256
+        per = -(-n // s)
+        assert per <= 2048 or s == 256
+        assert s == 1 or per >= 128
+    assert lib.sl8_choose_n_splits(32768, 1024) == 16
+    p = _lib.DecodeParams(B=2, Hq=8, Hkv=2, N=4096, D=128, num_splits=4)
+    assert lib.sl8_attn_int8_decode_workspace(C.byref(p)) == 256 + 4 * 16 * (128 + 2) * 4
+
+
+def test_missing_library_raises_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "nope.so")
+    with pytest.raises(_lib.Sl8LibraryMissing, match="no CPU fallback"):
+        _lib.load()
+
+
+def test_python_layer_refuses_cpu_tensors():
+    import torch
+    import superl8_b200 as s8
+    x = torch.randn(4, 128).half()
+    with pytest.raises(RuntimeError, match="CUDA"):
+        s8.quantize_i8_rowwise(x)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        s8.quantize_int8_rowwise(x)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        s8.attn_int8_fwd(x.view(1, 1, 4, 128), x.view(1, 1, 4, 128), x.view(1, 1, 4, 128))

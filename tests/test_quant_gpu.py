@@ -1,0 +1,148 @@
+"""GPU parity of the quantiser and the Q/K prologues, through the C ABI.
+Bit-exact targets: the oracle's CUDA scale rule, the reference's own kernel (oracle/_ref)
+and the CUDA-eager torch formula the reference tests use (tests/test_quant_rowwise.py:42-52)."""
+
+import numpy as np
+import pytest
+import torch
+
+import superl8_b200 as s8
+from conftest import GOLDEN, from_bits
+from gpu_helpers import ref_lib, ref_quantize
+from oracle import oracle
+from superl8_b200 import quant
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(37, 128, torch.float16), (50, 64, torch.float16), (33, 128, torch.bfloat16), (21, 72, torch.float32),
+          (19, 33, torch.float16), (17, 256, torch.float16), (1000, 80, torch.float16), (64, 1024, torch.bfloat16),
+          (8, 4096, torch.float16), (3, 20000, torch.float16), (301, 32, torch.float16), (5, 7, torch.float32)]
+
+
+def eager_cuda_oracle(x):
+    """The reference tests' independent oracle, run by torch on the device."""
+    scale = x.float().abs().amax(dim=-1, keepdim=True) / 127.0
+    safe = torch.where(scale == 0, torch.ones_like(scale), scale)
+    return torch.round(x.float() / safe).clamp_(-127.0, 127.0).to(torch.int8), safe.squeeze(-1)
+
+
+@pytest.mark.parametrize("M,K,dtype", SHAPES)
+def test_rowwise_bit_exact(M, K, dtype, device):
+    x = (torch.randn(M, K, generator=torch.Generator().manual_seed(M * 7 + K)) * 2.5).to(dtype)
+    x[0] = 0
+    if M > 2:
+        x[1, K // 2] = 900.0
+        x[2] = x[2] * 1e-3
+    q, s = s8.quantize_i8_rowwise(x.to(device))
+    qo, so = oracle.quantize_rowwise(x, rule="cuda")
+    assert torch.equal(s.cpu(), so.squeeze(-1))
+    assert torch.equal(q.cpu(), qo)
+    qe, se = eager_cuda_oracle(x.to(device))
+    assert torch.equal(s, se) and torch.equal(q, qe)
+    assert int(q.min()) >= -127 and float(s[0]) == 1.0 and int(q[0].abs().max()) == 0
+    if ref_lib() is not None:
+        qr, sr = ref_quantize(x.to(device))
+        assert torch.equal(q, qr) and torch.equal(s, sr)
+    q2, s2 = s8.quantize_i8_rowwise(x.to(device))
+    assert torch.equal(q, q2) and torch.equal(s, s2)
+
+
+def test_rowwise_golden_inputs(device):
+    g = np.load(GOLDEN / "quant_rowwise.npz")
+    for n in sorted({k.split("__")[0] for k in g.files}):
+        x = from_bits(g[f"{n}__x"], str(g[f"{n}__dtype"]))
+        q, s = s8.quantize_i8_rowwise(x.to(device))
+        qo, so = oracle.quantize_rowwise(x, rule="cuda")
+        assert torch.equal(q.cpu(), qo) and torch.equal(s.cpu(), so.squeeze(-1)), n
+        # against the reference's CPU branch the scale may be 1 ulp off (amax/127 vs amax*(1/127))
+        assert np.abs(q.cpu().numpy().astype(int) - g[f"{n}__q"].astype(int)).max() <= 1
+
+
+def test_rowwise_empty_and_nd(device):
+    q, s = s8.quantize_i8_rowwise(torch.empty(0, 128, dtype=torch.float16, device=device))
+    assert q.shape == (0, 128) and s.shape == (0,)
+    x = torch.randn(2, 3, 5, 64, device=device).half()
+    q, s = s8.quantize_int8_rowwise(x)
+    assert q.shape == x.shape and s.shape == (2, 3, 5, 1)
+    with pytest.raises(RuntimeError, match="float16"):
+        s8.quantize_i8_rowwise(torch.zeros(4, 8, dtype=torch.float64, device=device))
+
+
+def test_full_size_config_rows_against_eager(device):
+    # cfg2 Q: 1 x 32 x 4096 x 128 (131072 rows), checked against the CUDA-eager formula
+    x = torch.randn(32 * 4096, 128, device=device).half()
+    q, s = s8.quantize_i8_rowwise(x)
+    qe, se = eager_cuda_oracle(x)
+    assert torch.equal(q, qe) and torch.equal(s, se)
+    # round trip property: |x - q*s| <= s/2 (+ fp rounding)
+    err = (x.float() - q.float() * s[:, None]).abs()
+    assert bool((err <= s[:, None] * 0.5001).all())
+    assert int(q.abs().amax(dim=-1).min()) == 127
+
+
+@pytest.mark.parametrize("D,dtype", [(128, torch.float16), (64, torch.float16), (256, torch.bfloat16), (80, torch.float16)])
+def test_q_prologue_fold_and_gate(D, dtype, device):
+    g = torch.Generator().manual_seed(D)
+    qf = torch.randn(2, 3, 70, D, generator=g).to(dtype)
+    sc = 0.11
+    q_i8, q_scale, flag = quant.quantize_q(qf.to(device), sc, want_gate=True)
+    qo, so = oracle.quantize_rowwise(qf, rule="cuda")
+    assert torch.equal(q_i8.cpu(), qo)
+    assert torch.equal(q_scale.cpu(), oracle.fold_scale(so, sc))
+    assert bool(flag.item()) == oracle.detect_q_outlier_domination(qf)
+    spiked = qf.clone()
+    spiked[1, 2, 33, D // 3] = 80.0
+    assert s8.detect_q_outlier_domination(spiked.to(device)) is True
+    assert oracle.detect_q_outlier_domination(spiked) is True
+
+
+def test_gate_on_golden_cases(device):
+    g = np.load(GOLDEN / "outlier_gate.npz")
+    for n in ("clean", "spike", "chan20", "d64", "near"):
+        q = from_bits(g[f"{n}__q"], "float16")
+        assert s8.detect_q_outlier_domination(q.to(device)) == bool(g[f"{n}__flag"]), n
+    near = from_bits(g["near__q"], "float16")
+    for r, want in enumerate([False, True, False, False]):
+        assert s8.detect_q_outlier_domination(near[:, :, r:r + 1].contiguous().to(device)) == want
+
+
+@pytest.mark.parametrize("shape,dtype", [((2, 2, 300, 64), torch.float16), ((1, 1, 2500, 64), torch.float16),
+                                         ((1, 2, 130, 128), torch.bfloat16), ((1, 3, 1025, 256), torch.float16)])
+def test_k_prologue(shape, dtype, device):
+    g = torch.Generator().manual_seed(shape[2])
+    k = (torch.randn(*shape, generator=g) * 1.5 + 0.4).to(dtype)
+    mean_o = oracle.k_mean_fp32(k)
+    mean = quant.k_mean(k.to(device))
+    assert torch.equal(mean, quant.k_mean(k.to(device)))           # fixed summation order
+    rel = ((mean.cpu() - mean_o).abs() / mean_o.abs().clamp_min(1e-3)).max().item()
+    assert rel <= 1e-5, rel                                          # reference's own bar is 1e-6 on sums of 1k rows
+    # given the SAME mean the smoothed values, codes and scales are bit-exact
+    k_i8, k_scale, k_s = quant.smooth_quantize_k(k.to(device), mean_o.to(device), want_smoothed=True)
+    ks_o, _ = oracle.smooth_k(k, mean_o)
+    qo, so = oracle.quantize_rowwise(ks_o, rule="cuda")
+    assert torch.equal(k_s.cpu(), ks_o)
+    assert torch.equal(k_i8.cpu(), qo) and torch.equal(k_scale.cpu(), so)
+    # fused mean: codes may differ where a 1-ulp mean change flips a rounding; must stay rare and +-1
+    k_i8_f, _ks_f, _ = quant.smooth_quantize_k(k.to(device), mean)
+    diff = (k_i8_f.cpu().int() - qo.int()).abs()
+    assert int(diff.max()) <= 1 and float((diff > 0).float().mean()) < 2e-3
+
+
+def test_k_mean_with_seqlens(device):
+    k = torch.randn(3, 2, 200, 64).half()
+    lens = torch.tensor([200, 57, 1], dtype=torch.int32)
+    mean = quant.k_mean(k.to(device), lens.to(device)).cpu()
+    for b in range(3):
+        ref = oracle.k_mean_fp32(k[b:b + 1, :, :int(lens[b])])
+        assert torch.allclose(mean[b:b + 1], ref, rtol=1e-5, atol=1e-6)
+
+
+def test_quantize_qk_matches_oracle_given_mean(device):
+    q, k, _ = oracle.make_batch(2, 1, 4, 2, 96, 64, Sk=80)
+    qo, qso, ko, kso, mo = oracle.quantize_qk(q, k, softmax_scale=0.2)
+    q_i8, q_scale, k_i8, k_scale, mean = s8.quantize_qk(q.to(device), k.to(device), softmax_scale=0.2,
+                                                        k_mean_override=mo.to(device))
+    assert torch.equal(q_i8.cpu(), qo) and torch.equal(q_scale.cpu(), qso)
+    assert torch.equal(k_i8.cpu(), ko) and torch.equal(k_scale.cpu(), kso)
+    k_s, mean2 = s8.smooth_k(k.to(device))
+    assert k_s.shape == k.shape and mean2.shape == (1, 2, 1, 64)
