@@ -1,0 +1,368 @@
+#!/usr/bin/env python
+"""Benchmark of the int8 attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--gate on|off]
+
+One JSON line on stdout (rank 0).  A step is one call of the public entry
+``superl8_b200.attn_int8_fwd(q, k, v, causal=True)`` -- accuracy gate, Q/K quantisation
+prologue and attention kernel -- on the 64-head causal S=8192 configuration ("cfg3":
+B16 Hq64 Hkv8 S8192 D128, fp16 ~N(0,1), a seeded 1 % of Q and K channels x20).  With the
+gate on (default, the reference's behaviour) those outlier channels demote the call to the
+full-precision kernel; the same line also carries the pure int8 path (gate off), the
+split-KV decode (cfg5) and the quantiser, each with its own roofline figures.
+Every rank owns a full cfg3 batch (weak scaling over (batch, kv-head) units, no collective
+in the timed region).  ``--impl reference`` times the CPU restatement of the reference's
+path (oracle/) on the host cores instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "attn_int8_fwd_tops"
+UNIT = "TOPS"
+NOMINAL_INT8_TOPS = 4500.0
+NOMINAL_HBM_GBS = 7700.0
+
+
+def load_peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        p = json.loads(f.read_text())
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def timed(fn, steps: int, warmup: int, world: int, before=None):
+    """W untimed steps, then exactly K steps between barrier + synchronize; CUDA events on the
+    launching stream; MAX over ranks.  Returns ms per step."""
+    import torch.distributed as dist
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    if before is not None:
+        before()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item()) / steps
+
+
+class KernelTimer:
+    """Wraps an operator of superl8_b200._C so that every call inside the timed region is
+    bracketed by CUDA events on the stream it launches on."""
+
+    def __init__(self, module, name):
+        self.module, self.name = module, name
+        self.orig = getattr(module, name)
+        self.events = []
+        self.enabled = False
+
+    def __enter__(self):
+        def wrapped(*a, **kw):
+            if not self.enabled:
+                return self.orig(*a, **kw)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = self.orig(*a, **kw)
+            e1.record()
+            self.events.append((e0, e1))
+            return r
+        setattr(self.module, self.name, wrapped)
+        return self
+
+    def __exit__(self, *exc):
+        setattr(self.module, self.name, self.orig)
+
+    def mean_ms(self):
+        if not self.events:
+            return None
+        return sum(a.elapsed_time(b) for a, b in self.events) / len(self.events)
+
+
+def cpu_reference_sample(cfg, heads_groups: int, threads=None):
+    """The reference's CPU path restated (oracle/): CPU quantiser + fp32 attention oracle on
+    batch element 0, `heads_groups` KV groups (each with its Hq/Hkv query heads).
+    Returns (seconds, ops of the sample)."""
+    from oracle import oracle
+    if threads:
+        torch.set_num_threads(threads)
+    g = cfg.Hq // cfg.Hkv
+    q, k, v = oracle.make_qkv(3000, g * heads_groups, heads_groups, cfg.S, cfg.D)
+    q, k, v = q[None], k[None], v[None]
+    t0 = time.perf_counter()
+    oracle.quantize_qk(q, k)
+    for h in range(heads_groups):  # one KV group at a time bounds the fp32 score matrix
+        oracle.attention_fp32(q[:, h * g:(h + 1) * g], k[:, h:h + 1], v[:, h:h + 1], causal=cfg.causal)
+    dt = time.perf_counter() - t0
+    ops = 4.0 * g * heads_groups * cfg.S * cfg.S * cfg.D * (0.5 if cfg.causal else 1.0)
+    return dt, ops
+
+
+def run_reference(args, cfg):
+    rank, world, _ = dist_setup(args.gpus)
+    if rank != 0:
+        return
+    cores = torch.get_num_threads()
+    groups = 1
+    for _ in range(args.warmup):
+        cpu_reference_sample(cfg, groups)
+    ts = []
+    ops = 0.0
+    for _ in range(args.steps):
+        dt, ops = cpu_reference_sample(cfg, groups)
+        ts.append(dt)
+    sec = sum(ts) / len(ts)
+    val = ops / sec / 1e12
+    sample = f"batch element 0, {groups} KV group ({cfg.Hq // cfg.Hkv} query heads) of {cfg.name} per step"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(cfg, args, 1),
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(cfg, args, world):
+    return {"workload": f"{cfg.name}: attn_int8_fwd causal B{cfg.B} Hq{cfg.Hq} Hkv{cfg.Hkv} S{cfg.S} D{cfg.D} fp16 "
+                        f"~N(0,1), 1% of Q/K channels x20, per GPU",
+            "gate": args.gate, "per_gpu_batch": cfg.B, "global_batch": cfg.B * world,
+            "sharding": f"{cfg.units} independent (batch, kv-head) units per GPU, no collective",
+            "l2": "inputs (2.7 GB per step) larger than L2"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--gate", default="on", choices=["on", "off"])
+    ap.add_argument("--workload", default="cfg3")
+    ap.add_argument("--skip-extras", action="store_true", help="only the headline workload")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    from superl8_b200 import workloads
+    cfg = workloads.PREFILL[args.workload]
+    if args.impl == "reference":
+        run_reference(args, cfg)
+        return
+
+    import torch.distributed as dist
+    import superl8_b200 as s8
+    from superl8_b200 import _C, _lib, quant
+
+    rank, world, local = dist_setup(args.gpus)
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
+    gate = args.gate == "on"
+
+    q, k, v = workloads.prefill_inputs(cfg, dev, first_unit_batch=rank * cfg.B)
+    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+    hout = torch.empty(q.shape, dtype=torch.float16).pin_memory()
+
+    def step():
+        return s8.attn_int8_fwd(q, k, v, causal=cfg.causal, internal_accuracy_gate=gate)
+
+    def step_e2e():
+        dq, dk, dv = hq.to(dev, non_blocking=True), hk.to(dev, non_blocking=True), hv.to(dev, non_blocking=True)
+        out = s8.attn_int8_fwd(dq, dk, dv, causal=cfg.causal, internal_accuracy_gate=gate)
+        hout.copy_(out, non_blocking=True)
+        return out
+
+    out = step()
+    demoted = s8.ops.last_gate_decision
+    dominant = "attn_fp16_fwd" if demoted else "attn_int8_fwd"
+    sampler = ClockSampler(local)
+    with KernelTimer(_C, dominant) as kt:
+        launches0 = [0]
+
+        def before():
+            kt.enabled = True
+            kt.events.clear()
+            launches0[0] = _lib.launches
+            if rank == 0:
+                sampler.start()
+        ms = timed(step, args.steps, args.warmup, world, before=before)
+        kt.enabled = False
+        gpu_launches = _lib.launches - launches0[0]
+        clocks = sampler.stop() if rank == 0 else {}
+        kern_ms = kt.mean_ms()
+    status = _C.device_status()
+    value = world * cfg.ops / (ms * 1e-3) / 1e12
+
+    ms_e2e = timed(step_e2e, args.steps, args.warmup, world)
+    e2e = {"value": world * cfg.ops / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
+           "h2d_bytes_per_step": sum(t.numel() * 2 for t in (hq, hk, hv)), "d2h_bytes_per_step": hout.numel() * 2 + 4}
+
+    def tensor_roofline(kernel_ms, note):
+        ach = cfg.ops / (kernel_ms * 1e-3) / 1e12
+        return {"bound": "tensor", "kernel": note, "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                "frac": ach / peaks["bf16_tflops"], "peak_source": peaks["source"] + " bf16 dense (burst)",
+                "frac_of_nominal_int8": ach / NOMINAL_INT8_TOPS, "traffic": None, "ms_per_launch": kernel_ms}
+
+    roofline = tensor_roofline(kern_ms, dominant + (" (gate demoted the call)" if demoted else ""))
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16" if demoted else "s8", "data": "synthetic", "config": workload_config(cfg, args, world),
+        "gate_demoted": bool(demoted), "device_status": status, "e2e": e2e, "gpu_launches": gpu_launches,
+        "clocks": clocks, "roofline": roofline,
+    }
+
+    if not args.skip_extras:
+        # ---- pure int8 path on the same inputs (gate off) ----
+        with KernelTimer(_C, "attn_int8_fwd") as kt8:
+            def before8():
+                kt8.enabled = True
+                kt8.events.clear()
+            ms8 = timed(lambda: s8.attn_int8_fwd(q, k, v, causal=cfg.causal, internal_accuracy_gate=False),
+                        args.steps, args.warmup, world, before=before8)
+            k8 = kt8.mean_ms()
+        r8 = tensor_roofline(k8, "attn_int8_fwd (tcgen05 kind::i8 QK, kind::f16 PV)")
+        r8["frac_of_mixed_ceiling_nominal"] = r8["achieved"] / (NOMINAL_INT8_TOPS * 2.0 / 3.0)
+        line["int8_path"] = {"value": world * cfg.ops / (ms8 * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms8,
+                             "gate": "off", "roofline": r8}
+        del out
+        # ---- quantiser (Q prologue with the gate statistic, on cfg3's Q) ----
+        qbytes = q.numel() * 3 + (q.numel() // cfg.D) * 4
+        msq = timed(lambda: quant.quantize_q(q, 0.0884, want_gate=True), args.steps, args.warmup, world)
+        gq = world * qbytes / (msq * 1e-3) / 1e9
+        line["quant"] = {"value": gq, "unit": "GB/s", "ms_per_step": msq, "what": "Q prologue (quantise + fold + gate) on cfg3 Q",
+                         "roofline": {"bound": "hbm", "achieved": gq / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                      "frac": gq / world / peaks["hbm_gbs"], "frac_of_nominal": gq / world / NOMINAL_HBM_GBS,
+                                      "traffic": None}}
+        # ---- decode (cfg5): every rank owns 128 sequences ----
+        del q, k, v
+        torch.cuda.empty_cache()
+        dcfg = workloads.DecodeCfg()
+        lens = workloads.decode_lengths(dcfg, first_seq=0, count=dcfg.B)
+        dq, dk8, dks, dv, dlens = workloads.decode_inputs(dcfg, lens, dev)
+        dbytes = workloads.decode_bytes(lens, dcfg.Hkv, dcfg.D)
+        launches1 = _lib.launches
+        msd = timed(lambda: s8.attn_decode_int8_cache(dq, dk8, dks, dv, context_lens=dlens), max(args.steps, 10),
+                    args.warmup, world)
+        per_step = (_lib.launches - launches1) // (max(args.steps, 10) + args.warmup)
+        gd = world * dbytes / (msd * 1e-3) / 1e9
+        line["decode"] = {"metric": "int8_kv_decode_hbm_gbs", "value": gd, "unit": "GB/s", "ms_per_step": msd,
+                          "gpu_launches_per_step": per_step,
+                          "config": {"workload": "cfg5: B128 Hq64 Hkv8 D128, context uniform in [1024, 32768], int8 K + "
+                                                 "fp32 per-token scales, fp16 V, per GPU",
+                                     "l2": "K/V caches (13 GB) larger than L2"},
+                          "roofline": {"bound": "hbm", "achieved": gd / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                       "frac": gd / world / peaks["hbm_gbs"], "frac_of_nominal": gd / world / NOMINAL_HBM_GBS,
+                                       "peak_source": peaks["source"] + " copy bandwidth", "traffic": None},
+                          "device_status": _C.device_status()}
+        del dq, dk8, dks, dv
+
+    if rank == 0 and world == 1:
+        try:
+            sec, ops = cpu_reference_sample(cfg, 16)
+            line["cpu_baseline"] = {"value": ops / sec / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                                    "sample": f"16 KV groups (128 query heads = 2 batch elements) of {cfg.name}: CPU quantiser + "
+                                              f"fp32 attention oracle, {sec:.1f} s"}
+        except Exception as e:  # the CPU leg must never take the GPU numbers down with it
+            line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                                    "sample": f"failed: {e!r}"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -72,7 +72,7 @@ def quantize_i8_rowwise(x: torch.Tensor):
     scale = torch.empty((M,), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
         rc = _lib.load().sl8_quantize_i8_rowwise(_ptr(x), _DTYPE[x.dtype], M, K, _ptr(q), _ptr(scale), _stream(x.device))
-    _lib.check(rc, "quantize_i8_rowwise")
+    _lib.check(rc, "quantize_i8_rowwise", 1)
     return q, scale
 
 
@@ -115,7 +115,7 @@ def _run_fwd(q, q_scale, k, k_scale, v, causal, want_lse, window_left, seqlens_q
     with torch.cuda.device(q.device):
         ws = _status_buffer(q.device)
         rc = _lib.load().sl8_attn_int8_fwd(C.byref(p), _ptr(ws), ws.numel() * 4, _stream(q.device))
-    _lib.check(rc, "attn_int8_fwd")
+    _lib.check(rc, "attn_int8_fwd", 1)
     return out, lse
 
 
@@ -144,7 +144,7 @@ def qk_logits_i32(q_i8: torch.Tensor, k_i8: torch.Tensor) -> torch.Tensor:
         ws = _status_buffer(q_i8.device)
         rc = _lib.load().sl8_qk_logits_i32(_ptr(q_i8), _ptr(k_i8), M, N, D, _ptr(s), _ptr(ws), ws.numel() * 4,
                                            _stream(q_i8.device))
-    _lib.check(rc, "qk_logits_i32")
+    _lib.check(rc, "qk_logits_i32", 1)
     return s
 
 
@@ -177,7 +177,7 @@ def attn_fp16_fwd(q, k, v, causal=False, scale=None, window_left=-1, mask=None, 
     with torch.cuda.device(q.device):
         ws = _status_buffer(q.device)
         rc = _lib.load().sl8_attn_fp16_fwd(C.byref(p), _ptr(ws), ws.numel() * 4, _stream(q.device))
-    _lib.check(rc, "attn_fp16_fwd")
+    _lib.check(rc, "attn_fp16_fwd", 1)
     return out
 
 
@@ -217,7 +217,7 @@ def attn_int8_decode(q, q_scale, k, k_scale, v, num_splits=-1, *, context_lens=N
     with torch.cuda.device(q.device):
         ws = _decode_workspace(q.device, int(lib.sl8_attn_int8_decode_workspace(C.byref(p))))
         rc = lib.sl8_attn_int8_decode(C.byref(p), _ptr(ws), ws.numel(), _stream(q.device))
-    _lib.check(rc, "attn_int8_decode")
+    _lib.check(rc, "attn_int8_decode", 2 if N > 0 else 0)
     return out
 
 

@@ -90,6 +90,9 @@ SIGNATURES = {
 
 _lib = None
 
+# number of kernels of this library launched so far (each wrapper adds its own launches)
+launches = 0
+
 
 def load():
     """Returns the loaded library (loads it on first use)."""
@@ -115,7 +118,10 @@ def status_string(code: int) -> str:
     return load().sl8_status_string(int(code)).decode()
 
 
-def check(code: int, what: str) -> None:
-    """Turns a non-zero status into the RuntimeError the reference's TORCH_CHECKs raise."""
+def check(code: int, what: str, kernels: int = 0) -> None:
+    """Turns a non-zero status into the RuntimeError the reference's TORCH_CHECKs raise;
+    on success books ``kernels`` launches."""
+    global launches
     if code != SL8_OK:
         raise RuntimeError(f"superl8_b200 {what}: {status_string(code)} (status {code})")
+    launches += kernels

@@ -58,7 +58,7 @@ def k_mean(k: torch.Tensor, seqlens_k: torch.Tensor | None = None) -> torch.Tens
         rc = lib.sl8_k_mean(k.data_ptr(), _C._DTYPE[k.dtype], BH, N, D,
                             None if seqlens_k is None else seqlens_k.data_ptr(), hpb,
                             mean.data_ptr(), ws.data_ptr(), ws_bytes, _C._stream(k.device))
-    _lib.check(rc, "k_mean")
+    _lib.check(rc, "k_mean", 2 if N > 0 else 0)
     return mean
 
 
@@ -88,7 +88,7 @@ def smooth_quantize_k(k: torch.Tensor, mean: torch.Tensor, want_smoothed: bool =
             rc = _lib.load().sl8_smooth_quant_k(k.data_ptr(), _C._DTYPE[k.dtype], BH, N, D, mean.data_ptr(),
                                                 k_i8.data_ptr(), k_scale.data_ptr(),
                                                 None if k_s is None else k_s.data_ptr(), _C._stream(k.device))
-        _lib.check(rc, "smooth_quant_k")
+        _lib.check(rc, "smooth_quant_k", 1)
     return k_i8, k_scale, k_s
 
 
@@ -110,7 +110,7 @@ def quantize_q(q: torch.Tensor, softmax_scale: float, want_gate: bool = False,
                                                   C.c_float(ratio_threshold), q_i8.data_ptr(), q_scale.data_ptr(),
                                                   None, None if flag is None else flag.data_ptr(),
                                                   _C._stream(q.device))
-        _lib.check(rc, "quant_q_prologue")
+        _lib.check(rc, "quant_q_prologue", 1)
     return q_i8, q_scale, flag
 
 
