@@ -196,6 +196,38 @@ size_t sl8_attn_int8_decode_workspace(const sl8_decode_params* p);
 int sl8_attn_int8_decode(const sl8_decode_params* p, void* workspace, size_t workspace_bytes,
                          void* stream);
 
+/*
+ * Decode for callers that cannot allocate device memory.  No counterpart in the
+ * reference (its op allocates its partials with at::empty on every call,
+ * csrc/kernel/attn_decode.cu:214-217).
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits -- a plugin handed a
+ * fixed memory budget by its host application, a real-time serving loop that must not
+ * take the allocator's locks or risk an out-of-memory in steady state, or a host that
+ * keeps every byte of the device under its own arena and gives a library none.  Such a
+ * caller passes inputs and the output exactly as for sl8_attn_int8_decode; the split
+ * partials (O, m, l) go to a fixed array of SL8_DECODE_STATIC_SCRATCH_BYTES inside the
+ * library image instead of a caller workspace.  Every GPU that loads the library holds
+ * that array until the process exits.
+ *
+ * Limits and rules:
+ *  - need = 256 + num_splits * B * Hq * (D + 2) * 4 bytes must fit the array.  With
+ *    num_splits == -1 the split count is lowered until it fits; an explicit num_splits
+ *    that does not fit, or a batch too large even for one split, returns
+ *    SL8_ERR_TOO_LARGE and launches nothing.
+ *  - This function calls no cudaMalloc / cudaFree and no allocating library routine.
+ *  - The first call on each device looks up the array's device address (once per
+ *    device, with that device current); make that first call before any stream capture.
+ *  - All calls on a device share the one array, and it keeps the previous call's
+ *    contents (every value a call reads it has written itself first, so nothing needs
+ *    clearing between calls).  Two calls that overlap on the GPU -- different streams,
+ *    or the same stream from two threads without ordering -- race on it: serialise them.
+ *  - device_status (nullable) is a caller-owned device int32, zeroed by the caller; it
+ *    is set to SL8_ERR_DEVICE_TIMEOUT if a bounded device-side wait expires.
+ */
+#define SL8_DECODE_STATIC_SCRATCH_BYTES (32u << 20)
+int sl8_attn_int8_decode_static(const sl8_decode_params* p, int32_t* device_status, void* stream);
+
 /* Synchronises the stream and returns the device status word of a workspace
  * (SL8_OK or SL8_ERR_DEVICE_TIMEOUT); clears it. */
 int sl8_read_device_status(void* workspace, void* stream);

@@ -85,8 +85,11 @@ SIGNATURES = {
     "sl8_choose_n_splits": (C.c_int, [C.c_int64, C.c_int64]),
     "sl8_attn_int8_decode_workspace": (C.c_size_t, [C.POINTER(DecodeParams)]),
     "sl8_attn_int8_decode": (C.c_int, [C.POINTER(DecodeParams), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "sl8_attn_int8_decode_static": (C.c_int, [C.POINTER(DecodeParams), C.c_void_p, C.c_void_p]),
     "sl8_read_device_status": (C.c_int, [C.c_void_p, C.c_void_p]),
 }
+
+DECODE_STATIC_SCRATCH_BYTES = 32 << 20
 
 _lib = None
 

@@ -427,3 +427,69 @@ extern "C" int sl8_attn_int8_decode(const sl8_decode_params* p, void* workspace,
   }
   return SL8_ERR_BAD_HEAD_DIM;
 }
+
+
+// ---- decode without any allocation ---------------------------------------------
+// Scratch for sl8_attn_int8_decode_static: lives in the library image, one copy per GPU
+// that loads the library, zero-initialised at load.  First 256 bytes: status word.
+static __device__ __align__(256) unsigned char g_decode_static_scratch[SL8_DECODE_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxStaticDevices = 64;
+void* g_static_scratch_ptr[kMaxStaticDevices] = {nullptr};
+
+// Device address of the static array on the CURRENT device.  In host code the array's name
+// is only a handle, never a device address, so the address is asked for once per device.
+int static_scratch_address(void** out) {
+  int dev = 0;
+  SL8_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxStaticDevices) return SL8_ERR_TOO_LARGE;
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    SL8_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_decode_static_scratch));
+    if (ptr == nullptr) return SL8_ERR_CUDA;
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return SL8_OK;
+}
+
+size_t static_need(int ns, const sl8_decode_params* p) {
+  return 256 + (size_t)ns * (size_t)p->B * (size_t)p->Hq * (size_t)(p->D + 2) * sizeof(float);
+}
+}  // namespace
+
+extern "C" int sl8_attn_int8_decode_static(const sl8_decode_params* p, int32_t* device_status, void* stream) {
+  int rc = validate(p);
+  if (rc != SL8_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t BHq = (int64_t)p->B * p->Hq;
+  if (BHq == 0) return SL8_OK;
+  if (p->out == nullptr) return SL8_ERR_NULL;
+  if (p->N == 0) {
+    SL8_CUDA_TRY(cudaMemsetAsync(p->out, 0, (size_t)BHq * p->D * sizeof(__half), s));
+    return SL8_OK;
+  }
+  if (!p->q || !p->q_scale || !p->k || !p->k_scale || !p->v) return SL8_ERR_NULL;
+  if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->out)) return SL8_ERR_MISALIGNED;
+  if ((int64_t)p->B * p->Hkv > 65535) return SL8_ERR_TOO_LARGE;
+  int ns = resolve_splits(p);
+  if (p->num_splits < 0) {
+    while (ns > 1 && static_need(ns, p) > SL8_DECODE_STATIC_SCRATCH_BYTES) --ns;  // auto: fewer splits until it fits
+  }
+  if (static_need(ns, p) > SL8_DECODE_STATIC_SCRATCH_BYTES) return SL8_ERR_TOO_LARGE;
+  void* base = nullptr;
+  rc = static_scratch_address(&base);
+  if (rc != SL8_OK) return rc;
+  int* status = device_status ? reinterpret_cast<int*>(device_status) : reinterpret_cast<int*>(base);
+  float* o_part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(base) + 256);
+  float* m_part = o_part + (size_t)ns * BHq * p->D;
+  float* l_part = m_part + (size_t)ns * BHq;
+  switch (p->D) {
+    case 32: return launch_decode<32>(*p, ns, status, o_part, m_part, l_part, s);
+    case 64: return launch_decode<64>(*p, ns, status, o_part, m_part, l_part, s);
+    case 128: return launch_decode<128>(*p, ns, status, o_part, m_part, l_part, s);
+    case 256: return launch_decode<256>(*p, ns, status, o_part, m_part, l_part, s);
+  }
+  return SL8_ERR_BAD_HEAD_DIM;
+}
