@@ -212,6 +212,41 @@ def run_reference(args, cfg):
     print(json.dumps(line), flush=True)
 
 
+def run_kernel_case(args):
+    """Small, profiler-friendly cases (inputs larger than L2, about 1 GB on the device)."""
+    import superl8_b200 as s8
+    from superl8_b200 import _C, quant, workloads
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    n = args.warmup + args.steps
+    if args.kernel_case in ("prefill_int8", "prefill_fp16", "quant_q", "quant_k"):
+        c = workloads.PrefillCfg("cfg3_b2", 2, 64, 8, 8192, 128, True)
+        q, k, v = workloads.prefill_inputs(c, dev, outliers=False)
+        if args.kernel_case == "prefill_fp16":
+            for _ in range(n):
+                _C.attn_fp16_fwd(q, k, v, True, None, -1, None)
+        elif args.kernel_case == "quant_q":
+            for _ in range(n):
+                quant.quantize_q(q, 0.0884, want_gate=True)
+        elif args.kernel_case == "quant_k":
+            kk = torch.cat([k] * 8, dim=0)
+            for _ in range(n):
+                quant.smooth_quantize_k(kk, quant.k_mean(kk))
+        else:
+            q_i8, q_scale, k_i8, k_scale, _ = s8.quantize_qk(q, k)
+            qs, ks = q_scale.squeeze(-1).contiguous(), k_scale.squeeze(-1).contiguous()
+            for _ in range(n):
+                _C.attn_int8_fwd(q_i8, qs, k_i8, ks, v, True, -1)
+    else:
+        dcfg = workloads.DecodeCfg(B=16)
+        lens = workloads.decode_lengths(dcfg, 0, 16)
+        dq, dk8, dks, dv, dlens = workloads.decode_inputs(dcfg, lens, dev)
+        for _ in range(n):
+            s8.attn_decode_int8_cache(dq, dk8, dks, dv, context_lens=dlens)
+    torch.cuda.synchronize()
+    print(f"kernel-case {args.kernel_case}: {n} launches, device status {_C.device_status()}", file=sys.stderr)
+
+
 def workload_config(cfg, args, world):
     return {"workload": f"{cfg.name}: attn_int8_fwd causal B{cfg.B} Hq{cfg.Hq} Hkv{cfg.Hkv} S{cfg.S} D{cfg.D} fp16 "
                         f"~N(0,1), 1% of Q/K channels x20, per GPU",
@@ -229,11 +264,16 @@ def main():
     ap.add_argument("--gate", default="on", choices=["on", "off"])
     ap.add_argument("--workload", default="cfg3")
     ap.add_argument("--skip-extras", action="store_true", help="only the headline workload")
+    ap.add_argument("--kernel-case", default="", choices=["", "prefill_int8", "prefill_fp16", "decode", "quant_q", "quant_k"],
+                    help="launch ONE kernel family on a small case (for profilers): W warm-up + K launches, no JSON")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     from superl8_b200 import workloads
     cfg = workloads.PREFILL[args.workload]
+    if args.kernel_case:
+        run_kernel_case(args)
+        return
     if args.impl == "reference":
         run_reference(args, cfg)
         return

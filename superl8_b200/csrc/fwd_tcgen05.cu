@@ -73,6 +73,82 @@ struct TcArgs {
 enum Bar { Q_FULL = 0, S_FULL, P_FULL, O_DONE, K_FULL, K_EMPTY = K_FULL + 2, V_FULL = K_EMPTY + 2,
            V_EMPTY = V_FULL + 2, KS_FULL = V_EMPTY + 2, KS_EMPTY = KS_FULL + 2, NUM_BARS = KS_EMPTY + 2 };
 
+constexpr float kLazyRescaleLog2 = 8.0f;
+constexpr uint32_t kMagicBits = 0x4B400000u;   // 1.5 * 2^23 as float bits
+constexpr float kMagic = 12582912.0f;
+
+// Pass 1 over one 128-column S row held by this thread's tensor-memory lane: int32
+// accumulators -> fp32 logits (float(acc) * qs) * ks[n], optional masking, row max; the
+// logits replace the integers in tensor memory.  The int -> float conversion is exact and
+// runs on the ALU/FMA pipes (bit pattern of 1.5 * 2^23 plus the integer, minus 1.5 * 2^23;
+// |acc| <= 127 * 127 * 256 < 2^22), leaving the special-function unit to the exponentials.
+template <bool MASK>
+__device__ __forceinline__ float logits_pass(uint32_t t_s, const float* __restrict__ ksv, float qs, int n_block,
+                                             int n_len, int causal, int qpos, int window_left) {
+  const uint64_t qs2 = f2_pack(qs, qs);
+  const uint64_t neg_magic2 = f2_pack(-kMagic, -kMagic);
+  float tmax = -INFINITY;
+  uint32_t r[2][32];
+  tc_ld32(t_s, r[0]);
+#pragma unroll
+  for (int c = 0; c < kTN / 32; ++c) {
+    uint32_t(&cur)[32] = r[c & 1];
+    tc_wait_ld();
+    tc_regs_ready(cur);
+    if (c + 1 < kTN / 32) tc_ld32(t_s + 32 * (c + 1), r[(c + 1) & 1]);
+    const uint64_t* ks2 = reinterpret_cast<const uint64_t*>(ksv + 32 * c);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      uint64_t p = f2_pack_bits(cur[2 * i] + kMagicBits, cur[2 * i + 1] + kMagicBits);
+      p = f2_mul(f2_mul(f2_add(p, neg_magic2), qs2), ks2[i]);
+      float s0, s1;
+      f2_unpack(p, s0, s1);
+      if (MASK) {
+        const int gn = n_block + 32 * c + 2 * i;
+        const bool v0 = (gn < n_len) && (!causal || gn <= qpos) && (window_left < 0 || gn > qpos - window_left);
+        const bool v1 = (gn + 1 < n_len) && (!causal || gn + 1 <= qpos) && (window_left < 0 || gn + 1 > qpos - window_left);
+        s0 = v0 ? s0 : -INFINITY;
+        s1 = v1 ? s1 : -INFINITY;
+      }
+      tmax = max3f(tmax, s0, s1);
+      cur[2 * i] = __float_as_uint(s0);
+      cur[2 * i + 1] = __float_as_uint(s1);
+    }
+    tc_st32(t_s + 32 * c, cur);
+  }
+  return tmax;
+}
+
+// Pass 2: P = 2^(s - m) from the fp32 logits in tensor memory, packed to VT pairs over the
+// first 64 columns of S; returns the row sum of the unrounded P.
+template <typename VT>
+__device__ __forceinline__ float probs_pass(uint32_t t_s, float m_use) {
+  const uint64_t neg_m2 = f2_pack(-m_use, -m_use);
+  uint64_t sum2 = f2_pack(0.f, 0.f);
+  uint32_t r[2][32];
+  tc_ld32(t_s, r[0]);
+#pragma unroll
+  for (int c = 0; c < kTN / 32; ++c) {
+    uint32_t(&cur)[32] = r[c & 1];
+    tc_wait_ld();
+    tc_regs_ready(cur);
+    if (c + 1 < kTN / 32) tc_ld32(t_s + 32 * (c + 1), r[(c + 1) & 1]);
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float x0, x1;
+      f2_unpack(f2_add(f2_pack_bits(cur[2 * i], cur[2 * i + 1]), neg_m2), x0, x1);
+      const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+      sum2 = f2_add(sum2, f2_pack(p0, p1));
+      pk[i] = pack2<VT>(p0, p1);
+    }
+    tc_st16(t_s + 16 * c, pk);
+  }
+  float a, b;
+  f2_unpack(sum2, a, b);
+  return a + b;
+}
+
 template <int D, typename VT>
 __global__ void __launch_bounds__(kTcThreads) fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                                                             const __grid_constant__ CUtensorMap k_map,
@@ -234,63 +310,41 @@ __global__ void __launch_bounds__(kTcThreads) fwd_tc_kernel(const __grid_constan
       const float* ksv = ks_smem + ss * kTN;
       const bool need_mask = (n_block + kTN > n_len) || (a.causal && n_block + kTN - 1 > m_block + causal_diag) ||
                              (a.window_left >= 0 && n_block <= m_block + kTM - 1 + causal_diag - a.window_left);
-      // ---- pass 1: int32 -> fp32 logits (kept in tensor memory), row max ----
-      float tmax = -INFINITY;
+      // ---- pass 1: int32 -> fp32 logits (written back to tensor memory), row max ----
+      const float tmax = need_mask
+                             ? logits_pass<true>(t_row + C::COL_S, ksv, qs, n_block, n_len, a.causal, qpos, a.window_left)
+                             : logits_pass<false>(t_row + C::COL_S, ksv, qs, n_block, n_len, a.causal, qpos, a.window_left);
+      // Lazy rescale: the running max moves only when some row of the warp outgrew it by
+      // more than 2^8 (P then stays <= 256, harmless in fp16/bf16 and in the fp32 sum);
+      // out = O / l does not depend on which reference max was used.
+      const bool grow = (m_run == -INFINITY) ? (tmax > -INFINITY) : (tmax > m_run + kLazyRescaleLog2);
+      float resc = 1.f;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = fmaxf(m_run, tmax);
+        resc = exp2f(m_run - ((m_new == -INFINITY) ? 0.f : m_new));  // m_run = -inf -> 0
+        m_run = m_new;
+        if (j > 0) {
+          // correction: O *= resc (the previous tile's P.V has completed: the commit behind
+          // S_FULL covers every earlier MMA)
+          const uint64_t resc2 = f2_pack(resc, resc);
 #pragma unroll 1
-      for (int c = 0; c < kTN / 32; ++c) {
-        uint32_t r[32];
-        tc_ld32(t_row + C::COL_S + 32 * c, r);
-        tc_wait_ld();
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            tc_ld32(t_row + C::COL_O + 32 * c, r);
+            tc_wait_ld();
+            tc_regs_ready(r);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = (float)(int)r[i] * qs * ksv[32 * c + i];
-          if (need_mask) {
-            const int gn = n_block + 32 * c + i;
-            const bool valid = (gn < n_len) && (!a.causal || gn <= qpos) &&
-                               (a.window_left < 0 || gn > qpos - a.window_left);
-            s = valid ? s : -INFINITY;
+            for (int i = 0; i < 16; ++i)
+              f2_unpack_bits(f2_mul(f2_pack_bits(r[2 * i], r[2 * i + 1]), resc2), r[2 * i], r[2 * i + 1]);
+            tc_st32(t_row + C::COL_O + 32 * c, r);
           }
-          tmax = fmaxf(tmax, s);
-          r[i] = __float_as_uint(s);
-        }
-        tc_st32(t_row + C::COL_S + 32 * c, r);
-      }
-      const float m_new = fmaxf(m_run, tmax);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float resc = exp2f(m_run - m_use);  // m_run = -inf -> 0
-      // ---- correction: O *= resc (the previous tile's P.V has completed: the
-      //      commit behind S_FULL covers every earlier MMA) ----
-      if (j > 0 && __any_sync(0xffffffffu, m_new > m_run)) {
-#pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tc_ld32(t_row + C::COL_O + 32 * c, r);
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * resc);
-          tc_st32(t_row + C::COL_O + 32 * c, r);
         }
       }
+      const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
       tc_wait_st();  // logits written in pass 1 are visible to the loads below
       // ---- pass 2: P = exp2(s - m), row sum, P -> tensor memory (16-bit pairs) ----
-      float psum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < kTN / 32; ++c) {
-        uint32_t r[32];
-        tc_ld32(t_row + C::COL_S + 32 * c, r);
-        tc_wait_ld();
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = exp2f(__uint_as_float(r[2 * i]) - m_use);
-          const float p1 = exp2f(__uint_as_float(r[2 * i + 1]) - m_use);
-          psum += p0 + p1;
-          pk[i] = pack2<VT>(p0, p1);
-        }
-        tc_st16(t_row + C::COL_S + 16 * c, pk);
-      }
+      const float psum = probs_pass<VT>(t_row + C::COL_S, m_use);
       l_run = l_run * resc + psum;
-      m_run = m_new;
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
