@@ -157,6 +157,7 @@ typedef struct sl8_fp16_fwd_params {
   int32_t B, Hq, Hkv, M, N, D;
   int32_t dtype; int32_t causal; int32_t window_left;
   float softmax_scale;
+  int32_t backend;        /* SL8_BACKEND_* (tcgen05 for D = 64/128/256, else mma.sync) */
 } sl8_fp16_fwd_params;
 size_t sl8_attn_fp16_fwd_workspace(const sl8_fp16_fwd_params* p);
 int sl8_attn_fp16_fwd(const sl8_fp16_fwd_params* p, void* workspace, size_t workspace_bytes,

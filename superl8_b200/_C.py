@@ -148,7 +148,8 @@ def qk_logits_i32(q_i8: torch.Tensor, k_i8: torch.Tensor) -> torch.Tensor:
     return s
 
 
-def attn_fp16_fwd(q, k, v, causal=False, scale=None, window_left=-1, mask=None, *, seqlens_q=None, seqlens_k=None):
+def attn_fp16_fwd(q, k, v, causal=False, scale=None, window_left=-1, mask=None, *, seqlens_q=None, seqlens_k=None,
+                  backend=_lib.SL8_BACKEND_AUTO):
     """Full-precision forward.  Reference binding csrc/fni8_api.cpp:234-244."""
     what = "superl8_b200 fp16 fwd"
     _check_cuda(q, k, v)
@@ -173,7 +174,7 @@ def attn_fp16_fwd(q, k, v, causal=False, scale=None, window_left=-1, mask=None, 
         seqlens_q=None if seqlens_q is None else seqlens_q.data_ptr(),
         seqlens_k=None if seqlens_k is None else seqlens_k.data_ptr(),
         B=B, Hq=H, Hkv=Hkv, M=M, N=N, D=D, dtype=_DTYPE[q.dtype], causal=int(bool(causal)),
-        window_left=int(window_left), softmax_scale=sc)
+        window_left=int(window_left), softmax_scale=sc, backend=int(backend))
     with torch.cuda.device(q.device):
         ws = _status_buffer(q.device)
         rc = _lib.load().sl8_attn_fp16_fwd(C.byref(p), _ptr(ws), ws.numel() * 4, _stream(q.device))

@@ -11,7 +11,9 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libsuperl8_b200.so"
+import os
+
+LIB_PATH = Path(os.environ.get("SUPERL8_B200_LIB") or (Path(__file__).resolve().parent / "libsuperl8_b200.so"))
 
 SL8_OK = 0
 SL8_F16, SL8_BF16, SL8_F32 = 0, 1, 2
@@ -51,7 +53,7 @@ class Fp16FwdParams(C.Structure):
         ("seqlens_q", C.c_void_p), ("seqlens_k", C.c_void_p),
         ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("M", C.c_int32), ("N", C.c_int32),
         ("D", C.c_int32), ("dtype", C.c_int32), ("causal", C.c_int32), ("window_left", C.c_int32),
-        ("softmax_scale", C.c_float),
+        ("softmax_scale", C.c_float), ("backend", C.c_int32),
     ]
 
 

@@ -299,11 +299,12 @@ int sl8_fwd_mma_int8(const sl8_fwd_params* p, cudaStream_t s) {
   return SL8_ERR_BAD_DTYPE;
 }
 
+int sl8_fwd_tc_fp16(const sl8_fp16_fwd_params* p, int* status, cudaStream_t s);  // fwd_tcgen05.cu
+
 extern "C" size_t sl8_attn_fp16_fwd_workspace(const sl8_fp16_fwd_params*) { return 256; }
 
 extern "C" int sl8_attn_fp16_fwd(const sl8_fp16_fwd_params* p, void* workspace, size_t workspace_bytes,
                                  void* stream) {
-  (void)workspace; (void)workspace_bytes;
   if (p == nullptr) return SL8_ERR_NULL;
   if (p->B < 0 || p->Hq < 0 || p->Hkv < 0 || p->M < 0 || p->N < 0) return SL8_ERR_BAD_SHAPE;
   if (p->D != 32 && p->D != 64 && p->D != 72 && p->D != 80 && p->D != 128 && p->D != 256) return SL8_ERR_BAD_HEAD_DIM;
@@ -313,6 +314,15 @@ extern "C" int sl8_attn_fp16_fwd(const sl8_fp16_fwd_params* p, void* workspace, 
   if (!p->q || !p->out || (p->N > 0 && (!p->k || !p->v))) return SL8_ERR_NULL;
   if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->out)) return SL8_ERR_MISALIGNED;
   if ((int64_t)p->B * p->Hq > 65535) return SL8_ERR_TOO_LARGE;
+  const bool tc_ok = (p->D == 64 || p->D == 128 || p->D == 256) && p->N > 0;
+  int backend = p->backend;
+  if (backend == SL8_BACKEND_AUTO) backend = tc_ok ? SL8_BACKEND_TCGEN05 : SL8_BACKEND_MMA;
+  if (backend == SL8_BACKEND_TCGEN05) {
+    if (!tc_ok) return SL8_ERR_UNSUPPORTED;
+    if (workspace == nullptr || workspace_bytes < 256) return SL8_ERR_WORKSPACE;
+    return sl8_fwd_tc_fp16(p, reinterpret_cast<int*>(workspace), static_cast<cudaStream_t>(stream));
+  }
+  if (backend != SL8_BACKEND_MMA) return SL8_ERR_UNSUPPORTED;
   FwdArgs a{};
   a.q = p->q; a.k = p->k; a.v = p->v; a.out = p->out; a.lse = p->lse;
   a.seqlens_q = p->seqlens_q; a.seqlens_k = p->seqlens_k;

@@ -32,24 +32,28 @@ namespace sl8 {
 namespace {
 
 constexpr int kTM = 128, kTN = 128;
-constexpr int kTcThreads = 192;
+constexpr int kSoftmaxWarps = 4;                       // one query row per thread, rows = tensor-memory lanes
+constexpr int kProducerWarp = 4, kMmaWarp = 5;
+constexpr int kTcThreads = 32 * (kSoftmaxWarps + 2);
 
-template <int D>
+template <int D, bool QK8>
 struct TcCfg {
-  static constexpr int QROW = D < 128 ? D : 128;          // bytes per shared row of a Q/K sub-tile
-  static constexpr int QSUBS = D / QROW;
+  static constexpr int QK_ROWB = D * (QK8 ? 1 : 2);      // bytes of one Q/K row
+  static constexpr int QROW = QK_ROWB < 128 ? QK_ROWB : 128;  // bytes per shared row of a Q/K sub-tile
+  static constexpr int QSUBS = QK_ROWB / QROW;
   static constexpr uint32_t QK_SW = QROW == 128 ? kUmmaSw128 : kUmmaSw64;
   static constexpr int QK_SUB_BYTES = 128 * QROW;
-  static constexpr int QK_TILE_BYTES = 128 * D;
+  static constexpr int QK_TILE_BYTES = 128 * QK_ROWB;
+  static constexpr int QK_STEPS = QK_ROWB / 32;           // MMA K steps of 32 bytes
   static constexpr int VSUBS = 2 * D / 128;               // 64-channel sub-tiles of 128 keys x 128 B
   static constexpr int V_SUB_BYTES = 128 * 128;
   static constexpr int V_TILE_BYTES = 128 * 2 * D;
-  static constexpr int NKS = 2;
+  static constexpr int NKS = (QK8 || D == 64) ? 2 : 1;
   static constexpr int NVS = D == 64 ? 2 : 1;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + QK_TILE_BYTES;
   static constexpr int OFF_V = OFF_K + NKS * QK_TILE_BYTES;
-  static constexpr int OFF_KS = OFF_V + NVS * V_TILE_BYTES;
+  static constexpr int OFF_KS = OFF_V + NVS * V_TILE_BYTES;   // 2 x 128 k_scale floats
   static constexpr int OFF_BAR = OFF_KS + 2 * kTN * 4;
   static constexpr int NEED = OFF_BAR + 256 + 1024;
   // never more than two blocks per SM: each holds TMEM_COLS columns of the 512
@@ -68,26 +72,40 @@ struct TcArgs {
   int* status;
   int Hq, Hkv, M, N;
   int causal, window_left;
+  float scale_log2;  // 16-bit Q/K mode: softmax_scale * log2(e)
 };
 
 enum Bar { Q_FULL = 0, S_FULL, P_FULL, O_DONE, K_FULL, K_EMPTY = K_FULL + 2, V_FULL = K_EMPTY + 2,
            V_EMPTY = V_FULL + 2, KS_FULL = V_EMPTY + 2, KS_EMPTY = KS_FULL + 2, NUM_BARS = KS_EMPTY + 2 };
 
+#ifdef SL8_TRACE
+__device__ long long g_trace[8192];
+#define TR(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0) g_trace[(slot)] = clock64(); } while (0)
+#else
+#define TR(slot) do {} while (0)
+#endif
+
 constexpr float kLazyRescaleLog2 = 8.0f;
 constexpr uint32_t kMagicBits = 0x4B400000u;   // 1.5 * 2^23 as float bits
 constexpr float kMagic = 12582912.0f;
 
-// Pass 1 over one 128-column S row held by this thread's tensor-memory lane: int32
-// accumulators -> fp32 logits (float(acc) * qs) * ks[n], optional masking, row max; the
-// logits replace the integers in tensor memory.  The int -> float conversion is exact and
-// runs on the ALU/FMA pipes (bit pattern of 1.5 * 2^23 plus the integer, minus 1.5 * 2^23;
-// |acc| <= 127 * 127 * 256 < 2^22), leaving the special-function unit to the exponentials.
-template <bool MASK>
+__device__ __forceinline__ float2 bits2(uint32_t a, uint32_t b) {
+  return make_float2(__uint_as_float(a), __uint_as_float(b));
+}
+
+// Pass 1 over the 128-column S row in this thread's tensor-memory lane: accumulators ->
+// fp32 logits, optional masking, row max; the logits replace the accumulators in tensor
+// memory.  int8 mode: (float(acc) * qs) * ks[n] in the reference's multiply order; the
+// int -> float conversion is exact and runs on the ALU/FMA pipes (bit pattern of 1.5 * 2^23
+// plus the integer, minus 1.5 * 2^23; |acc| <= 127 * 127 * 256 < 2^22), leaving the
+// special-function unit to the exponentials.  16-bit mode: acc * (softmax_scale * log2 e).
+// Loads of the next 32 columns are in flight while the current 32 are processed.
+template <bool QK8, bool MASK>
 __device__ __forceinline__ float logits_pass(uint32_t t_s, const float* __restrict__ ksv, float qs, int n_block,
                                              int n_len, int causal, int qpos, int window_left) {
-  const uint64_t qs2 = f2_pack(qs, qs);
-  const uint64_t neg_magic2 = f2_pack(-kMagic, -kMagic);
-  float tmax = -INFINITY;
+  const float2 qs2 = make_float2(qs, qs);
+  const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
+  float mx0 = -INFINITY, mx1 = -INFINITY;
   uint32_t r[2][32];
   tc_ld32(t_s, r[0]);
 #pragma unroll
@@ -96,35 +114,39 @@ __device__ __forceinline__ float logits_pass(uint32_t t_s, const float* __restri
     tc_wait_ld();
     tc_regs_ready(cur);
     if (c + 1 < kTN / 32) tc_ld32(t_s + 32 * (c + 1), r[(c + 1) & 1]);
-    const uint64_t* ks2 = reinterpret_cast<const uint64_t*>(ksv + 32 * c);
+    const float2* ks2 = reinterpret_cast<const float2*>(ksv + 32 * c);
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      uint64_t p = f2_pack_bits(cur[2 * i] + kMagicBits, cur[2 * i + 1] + kMagicBits);
-      p = f2_mul(f2_mul(f2_add(p, neg_magic2), qs2), ks2[i]);
-      float s0, s1;
-      f2_unpack(p, s0, s1);
+      float2 p;
+      if (QK8) {
+        p = bits2(cur[2 * i] + kMagicBits, cur[2 * i + 1] + kMagicBits);
+        p = __fmul2_rn(__fmul2_rn(__fadd2_rn(p, neg_magic2), qs2), ks2[i]);
+      } else {
+        p = __fmul2_rn(bits2(cur[2 * i], cur[2 * i + 1]), qs2);
+      }
       if (MASK) {
         const int gn = n_block + 32 * c + 2 * i;
         const bool v0 = (gn < n_len) && (!causal || gn <= qpos) && (window_left < 0 || gn > qpos - window_left);
         const bool v1 = (gn + 1 < n_len) && (!causal || gn + 1 <= qpos) && (window_left < 0 || gn + 1 > qpos - window_left);
-        s0 = v0 ? s0 : -INFINITY;
-        s1 = v1 ? s1 : -INFINITY;
+        p.x = v0 ? p.x : -INFINITY;
+        p.y = v1 ? p.y : -INFINITY;
       }
-      tmax = max3f(tmax, s0, s1);
-      cur[2 * i] = __float_as_uint(s0);
-      cur[2 * i + 1] = __float_as_uint(s1);
+      if (i & 1) mx1 = max3f(mx1, p.x, p.y);
+      else mx0 = max3f(mx0, p.x, p.y);
+      cur[2 * i] = __float_as_uint(p.x);
+      cur[2 * i + 1] = __float_as_uint(p.y);
     }
     tc_st32(t_s + 32 * c, cur);
   }
-  return tmax;
+  return fmaxf(mx0, mx1);
 }
 
 // Pass 2: P = 2^(s - m) from the fp32 logits in tensor memory, packed to VT pairs over the
 // first 64 columns of S; returns the row sum of the unrounded P.
 template <typename VT>
 __device__ __forceinline__ float probs_pass(uint32_t t_s, float m_use) {
-  const uint64_t neg_m2 = f2_pack(-m_use, -m_use);
-  uint64_t sum2 = f2_pack(0.f, 0.f);
+  const float2 neg_m2 = make_float2(-m_use, -m_use);
+  float2 sum_a = make_float2(0.f, 0.f), sum_b = sum_a;
   uint32_t r[2][32];
   tc_ld32(t_s, r[0]);
 #pragma unroll
@@ -136,24 +158,23 @@ __device__ __forceinline__ float probs_pass(uint32_t t_s, float m_use) {
     uint32_t pk[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      float x0, x1;
-      f2_unpack(f2_add(f2_pack_bits(cur[2 * i], cur[2 * i + 1]), neg_m2), x0, x1);
-      const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
-      sum2 = f2_add(sum2, f2_pack(p0, p1));
-      pk[i] = pack2<VT>(p0, p1);
+      const float2 x = __fadd2_rn(bits2(cur[2 * i], cur[2 * i + 1]), neg_m2);
+      const float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+      if (i & 1) sum_b = __fadd2_rn(sum_b, pr);
+      else sum_a = __fadd2_rn(sum_a, pr);
+      pk[i] = pack2<VT>(pr.x, pr.y);
     }
     tc_st16(t_s + 16 * c, pk);
   }
-  float a, b;
-  f2_unpack(sum2, a, b);
-  return a + b;
+  const float2 t = __fadd2_rn(sum_a, sum_b);
+  return t.x + t.y;
 }
 
-template <int D, typename VT>
-__global__ void __launch_bounds__(kTcThreads) fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map,
-                                                            const __grid_constant__ CUtensorMap k_map,
-                                                            const __grid_constant__ CUtensorMap v_map, TcArgs a) {
-  using C = TcCfg<D>;
+template <int D, typename VT, bool QK8>
+__global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map,
+                                                               const __grid_constant__ CUtensorMap k_map,
+                                                               const __grid_constant__ CUtensorMap v_map, TcArgs a) {
+  using C = TcCfg<D, QK8>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* ks_smem = reinterpret_cast<float*>(smem + C::OFF_KS);
@@ -188,7 +209,7 @@ __global__ void __launch_bounds__(kTcThreads) fwd_tc_kernel(const __grid_constan
   if (threadIdx.x == 0) {
     mbar_init(&bars[Q_FULL], 1);
     mbar_init(&bars[S_FULL], 1);
-    mbar_init(&bars[P_FULL], 4);
+    mbar_init(&bars[P_FULL], kSoftmaxWarps);
     mbar_init(&bars[O_DONE], 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[K_FULL + i], 1);
@@ -196,11 +217,11 @@ __global__ void __launch_bounds__(kTcThreads) fwd_tc_kernel(const __grid_constan
       mbar_init(&bars[V_FULL + i], 1);
       mbar_init(&bars[V_EMPTY + i], 1);
       mbar_init(&bars[KS_FULL + i], 1);
-      mbar_init(&bars[KS_EMPTY + i], 4);
+      mbar_init(&bars[KS_EMPTY + i], kSoftmaxWarps);
     }
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tc_alloc(tmem_slot, C::TMEM_COLS);
     tc_relinquish();
     tc_fence_before();
@@ -210,7 +231,7 @@ __global__ void __launch_bounds__(kTcThreads) fwd_tc_kernel(const __grid_constan
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   bool ok = true;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ======================= producer =======================
     if (lane == 0) {
       tma_prefetch_desc(&q_map);
@@ -219,7 +240,8 @@ __global__ void __launch_bounds__(kTcThreads) fwd_tc_kernel(const __grid_constan
       mbar_expect_tx(&bars[Q_FULL], C::QK_TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < C::QSUBS; ++c)
-        tma_load_3d(smem + C::OFF_Q + c * C::QK_SUB_BYTES, &q_map, &bars[Q_FULL], c * C::QROW, m_block, (int)bh);
+        tma_load_3d(smem + C::OFF_Q + c * C::QK_SUB_BYTES, &q_map, &bars[Q_FULL], c * (C::QROW / (QK8 ? 1 : 2)),
+                    m_block, (int)bh);
     }
     for (int j = 0; j < ntiles && ok; ++j) {
       const int n_block = n_begin + j * kTN;
@@ -231,7 +253,7 @@ __global__ void __launch_bounds__(kTcThreads) fwd_tc_kernel(const __grid_constan
 #pragma unroll
           for (int c = 0; c < C::QSUBS; ++c)
             tma_load_3d(smem + C::OFF_K + ks * C::QK_TILE_BYTES + c * C::QK_SUB_BYTES, &k_map, &bars[K_FULL + ks],
-                        c * C::QROW, n_block, kv_bh);
+                        c * (C::QROW / (QK8 ? 1 : 2)), n_block, kv_bh);
           if (j >= C::NVS) ok = mbar_wait(&bars[V_EMPTY + vs], ((j / C::NVS) - 1) & 1, a.status);
         }
         if (ok) {
@@ -244,23 +266,25 @@ __global__ void __launch_bounds__(kTcThreads) fwd_tc_kernel(const __grid_constan
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
-      // k_scale tile through the generic proxy (its start is not 16-byte aligned in general)
-      const int ss = j & 1;
-      if (j >= 2) ok = mbar_wait(&bars[KS_EMPTY + ss], ((j >> 1) - 1) & 1, a.status);
-      if (!ok) break;
+      if (QK8) {
+        // k_scale tile through the generic proxy (its start is not 16-byte aligned in general)
+        const int ss = j & 1;
+        if (j >= 2) ok = mbar_wait(&bars[KS_EMPTY + ss], ((j >> 1) - 1) & 1, a.status);
+        if (!ok) break;
 #pragma unroll
-      for (int i = 0; i < kTN / 32; ++i) {
-        const int n = n_block + lane + 32 * i;
-        ks_smem[ss * kTN + lane + 32 * i] = (n < n_len) ? __ldg(a.k_scale + (int64_t)kv_bh * a.N + n) : 0.f;
+        for (int i = 0; i < kTN / 32; ++i) {
+          const int n = n_block + lane + 32 * i;
+          ks_smem[ss * kTN + lane + 32 * i] = (n < n_len) ? __ldg(a.k_scale + (int64_t)kv_bh * a.N + n) : 0.f;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[KS_FULL + ss]);
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[KS_FULL + ss]);
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ======================= MMA issuer =======================
     if (lane == 0) {
-      const uint32_t idesc_qk = umma_idesc(2, 1, 1, 0, 0, kTM, kTN);
       constexpr uint32_t vfmt = std::is_same<VT, __nv_bfloat16>::value ? 1u : 0u;
+      const uint32_t idesc_qk = QK8 ? umma_idesc(2, 1, 1, 0, 0, kTM, kTN) : umma_idesc(1, vfmt, vfmt, 0, 0, kTM, kTN);
       const uint32_t idesc_pv = umma_idesc(1, vfmt, vfmt, 0, 1, kTM, D);
       const uint32_t q_u = smem_u32(smem + C::OFF_Q);
       ok = mbar_wait(&bars[Q_FULL], 0, a.status);
@@ -269,19 +293,25 @@ __global__ void __launch_bounds__(kTcThreads) fwd_tc_kernel(const __grid_constan
         ok = mbar_wait(&bars[K_FULL + ks], (j / C::NKS) & 1, a.status);
         if (!ok) break;
         tc_fence_after();
+        TR(4096 + 8 * j + 0);
         const uint32_t k_u = smem_u32(smem + C::OFF_K + ks * C::QK_TILE_BYTES);
 #pragma unroll
-        for (int s = 0; s < D / 32; ++s) {
+        for (int s = 0; s < C::QK_STEPS; ++s) {
           const uint32_t off = (32 * s / C::QROW) * C::QK_SUB_BYTES + (32 * s % C::QROW);
-          tc_mma_i8_ss(tmem + C::COL_S, umma_smem_desc(q_u + off, 16, 8 * C::QROW, C::QK_SW),
-                       umma_smem_desc(k_u + off, 16, 8 * C::QROW, C::QK_SW), idesc_qk, s > 0 ? 1u : 0u);
+          const uint64_t da = umma_smem_desc(q_u + off, 16, 8 * C::QROW, C::QK_SW);
+          const uint64_t db = umma_smem_desc(k_u + off, 16, 8 * C::QROW, C::QK_SW);
+          if (QK8) tc_mma_i8_ss(tmem + C::COL_S, da, db, idesc_qk, s > 0 ? 1u : 0u);
+          else tc_mma_f16_ss(tmem + C::COL_S, da, db, idesc_qk, s > 0 ? 1u : 0u);
         }
         tc_commit(&bars[K_EMPTY + ks]);
         tc_commit(&bars[S_FULL]);
+        TR(4096 + 8 * j + 1);
         ok = mbar_wait(&bars[P_FULL], j & 1, a.status);
+        TR(4096 + 8 * j + 2);
         if (ok) ok = mbar_wait(&bars[V_FULL + vs], (j / C::NVS) & 1, a.status);
         if (!ok) break;
         tc_fence_after();
+        TR(4096 + 8 * j + 3);
         const uint32_t v_u = smem_u32(smem + C::OFF_V + vs * C::V_TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < kTN / 16; ++kk)
@@ -289,13 +319,14 @@ __global__ void __launch_bounds__(kTcThreads) fwd_tc_kernel(const __grid_constan
                         umma_smem_desc(v_u + kk * 2048, C::V_SUB_BYTES, 1024, kUmmaSw128), idesc_pv,
                         (j > 0 || kk > 0) ? 1u : 0u);
         tc_commit(&bars[V_EMPTY + vs]);
+        TR(4096 + 8 * j + 4);
         if (j == ntiles - 1) tc_commit(&bars[O_DONE]);
       }
     }
   } else {
     // ======================= softmax / correction / epilogue =======================
     const int m = m_block + 32 * warp + lane;  // this thread's query row
-    const float qs = (m < m_len) ? __ldg(a.q_scale + bh * a.M + m) : 0.f;
+    const float qs = QK8 ? ((m < m_len) ? __ldg(a.q_scale + bh * a.M + m) : 0.f) : a.scale_log2;
     const int qpos = m + causal_diag;
     const uint32_t t_row = tmem + ((uint32_t)(32 * warp) << 16);
     float m_run = -INFINITY, l_run = 0.f;
@@ -303,17 +334,20 @@ __global__ void __launch_bounds__(kTcThreads) fwd_tc_kernel(const __grid_constan
     for (int j = 0; j < ntiles; ++j) {
       const int n_block = n_begin + j * kTN;
       const int ss = j & 1;
-      ok = mbar_wait(&bars[KS_FULL + ss], (j >> 1) & 1, a.status);
+      if (warp == 0 && lane == 0) TR(8 * j + 0);
+      if (QK8) ok = mbar_wait(&bars[KS_FULL + ss], (j >> 1) & 1, a.status);
       if (ok) ok = mbar_wait(&bars[S_FULL], j & 1, a.status);
       if (!ok) break;
       tc_fence_after();
+      if (warp == 0 && lane == 0) TR(8 * j + 1);
       const float* ksv = ks_smem + ss * kTN;
       const bool need_mask = (n_block + kTN > n_len) || (a.causal && n_block + kTN - 1 > m_block + causal_diag) ||
                              (a.window_left >= 0 && n_block <= m_block + kTM - 1 + causal_diag - a.window_left);
-      // ---- pass 1: int32 -> fp32 logits (written back to tensor memory), row max ----
-      const float tmax = need_mask
-                             ? logits_pass<true>(t_row + C::COL_S, ksv, qs, n_block, n_len, a.causal, qpos, a.window_left)
-                             : logits_pass<false>(t_row + C::COL_S, ksv, qs, n_block, n_len, a.causal, qpos, a.window_left);
+      // ---- pass 1: accumulators -> fp32 logits (written back to tensor memory), row max ----
+      const float tmax =
+          need_mask ? logits_pass<QK8, true>(t_row + C::COL_S, ksv, qs, n_block, n_len, a.causal, qpos, a.window_left)
+                    : logits_pass<QK8, false>(t_row + C::COL_S, ksv, qs, n_block, n_len, a.causal, qpos, a.window_left);
+      if (warp == 0 && lane == 0) TR(8 * j + 2);
       // Lazy rescale: the running max moves only when some row of the warp outgrew it by
       // more than 2^8 (P then stays <= 256, harmless in fp16/bf16 and in the fp32 sum);
       // out = O / l does not depend on which reference max was used.
@@ -326,32 +360,38 @@ __global__ void __launch_bounds__(kTcThreads) fwd_tc_kernel(const __grid_constan
         if (j > 0) {
           // correction: O *= resc (the previous tile's P.V has completed: the commit behind
           // S_FULL covers every earlier MMA)
-          const uint64_t resc2 = f2_pack(resc, resc);
+          const float2 resc2 = make_float2(resc, resc);
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
-            uint32_t r[32];
-            tc_ld32(t_row + C::COL_O + 32 * c, r);
+            uint32_t o[32];
+            tc_ld32(t_row + C::COL_O + 32 * c, o);
             tc_wait_ld();
-            tc_regs_ready(r);
+            tc_regs_ready(o);
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-              f2_unpack_bits(f2_mul(f2_pack_bits(r[2 * i], r[2 * i + 1]), resc2), r[2 * i], r[2 * i + 1]);
-            tc_st32(t_row + C::COL_O + 32 * c, r);
+            for (int i = 0; i < 16; ++i) {
+              const float2 t = __fmul2_rn(bits2(o[2 * i], o[2 * i + 1]), resc2);
+              o[2 * i] = __float_as_uint(t.x);
+              o[2 * i + 1] = __float_as_uint(t.y);
+            }
+            tc_st32(t_row + C::COL_O + 32 * c, o);
           }
         }
       }
       const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
       tc_wait_st();  // logits written in pass 1 are visible to the loads below
+      if (warp == 0 && lane == 0) TR(8 * j + 3);
       // ---- pass 2: P = exp2(s - m), row sum, P -> tensor memory (16-bit pairs) ----
       const float psum = probs_pass<VT>(t_row + C::COL_S, m_use);
       l_run = l_run * resc + psum;
+      if (warp == 0 && lane == 0) TR(8 * j + 4);
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&bars[P_FULL]);
-        mbar_arrive(&bars[KS_EMPTY + ss]);
+        if (QK8) mbar_arrive(&bars[KS_EMPTY + ss]);
       }
+      if (warp == 0 && lane == 0) TR(8 * j + 5);
     }
     // ---- epilogue ----
     if (ok) ok = mbar_wait(&bars[O_DONE], 0, a.status);
@@ -361,18 +401,19 @@ __global__ void __launch_bounds__(kTcThreads) fwd_tc_kernel(const __grid_constan
       const float inv = (live && l_run > 0.f) ? 1.f / l_run : 0.f;
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tc_ld32(t_row + C::COL_O + 32 * c, r);
+        uint32_t o[32];
+        tc_ld32(t_row + C::COL_O + 32 * c, o);
         tc_wait_ld();
+        tc_regs_ready(o);
         if (m < a.M) {
           uint4* dst = reinterpret_cast<uint4*>(out_bh + (int64_t)m * D + 32 * c);
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             uint4 w;
-            w.x = pack2<VT>(__uint_as_float(r[8 * v + 0]) * inv, __uint_as_float(r[8 * v + 1]) * inv);
-            w.y = pack2<VT>(__uint_as_float(r[8 * v + 2]) * inv, __uint_as_float(r[8 * v + 3]) * inv);
-            w.z = pack2<VT>(__uint_as_float(r[8 * v + 4]) * inv, __uint_as_float(r[8 * v + 5]) * inv);
-            w.w = pack2<VT>(__uint_as_float(r[8 * v + 6]) * inv, __uint_as_float(r[8 * v + 7]) * inv);
+            w.x = pack2<VT>(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
+            w.y = pack2<VT>(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
+            w.z = pack2<VT>(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
+            w.w = pack2<VT>(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
             dst[v] = w;
           }
         }
@@ -385,7 +426,7 @@ __global__ void __launch_bounds__(kTcThreads) fwd_tc_kernel(const __grid_constan
 
   // ---- teardown: every role arrives here, on success and on a timed-out wait ----
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tc_dealloc(tmem, C::TMEM_COLS);
   }
@@ -396,7 +437,7 @@ template <int D>
 __global__ void __launch_bounds__(128) qk_logits_kernel(const __grid_constant__ CUtensorMap q_map,
                                                         const __grid_constant__ CUtensorMap k_map, int32_t* s_out,
                                                         int M, int N, int* status) {
-  using C = TcCfg<D>;
+  using C = TcCfg<D, true>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * C::QK_TILE_BYTES);
@@ -462,37 +503,36 @@ __global__ void __launch_bounds__(128) qk_logits_kernel(const __grid_constant__ 
   }
 }
 
-template <int D, typename VT>
-int launch_tc(const sl8_fwd_params& p, int* status, cudaStream_t stream) {
-  using C = TcCfg<D>;
+template <int D, typename VT, bool QK8>
+int launch_tc_impl(const void* q, const void* k, const void* v, int B, int Hq, int Hkv, int M, int N, const TcArgs& a,
+                   cudaStream_t stream) {
+  using C = TcCfg<D, QK8>;
+  constexpr int es = QK8 ? 1 : 2;
   CUtensorMap q_map, k_map, v_map;
-  int rc = sl8_make_tmap_3d(&q_map, p.q, 1, D, p.M, (uint64_t)p.B * p.Hq, C::QROW, kTM, C::QROW);
-  if (rc == SL8_OK) rc = sl8_make_tmap_3d(&k_map, p.k, 1, D, p.N, (uint64_t)p.B * p.Hkv, C::QROW, kTN, C::QROW);
-  if (rc == SL8_OK) rc = sl8_make_tmap_3d(&v_map, p.v, 2, D, p.N, (uint64_t)p.B * p.Hkv, 64, kTN, 128);
+  int rc = sl8_make_tmap_3d(&q_map, q, es, D, M, (uint64_t)B * Hq, C::QROW / es, kTM, C::QROW);
+  if (rc == SL8_OK) rc = sl8_make_tmap_3d(&k_map, k, es, D, N, (uint64_t)B * Hkv, C::QROW / es, kTN, C::QROW);
+  if (rc == SL8_OK) rc = sl8_make_tmap_3d(&v_map, v, 2, D, N, (uint64_t)B * Hkv, 64, kTN, 128);
   if (rc != SL8_OK) return rc;
-  SL8_CUDA_TRY(cudaFuncSetAttribute(fwd_tc_kernel<D, VT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-  TcArgs a{};
-  a.q_scale = p.q_scale; a.k_scale = p.k_scale; a.out = p.out; a.lse = p.lse;
-  a.seqlens_q = p.seqlens_q; a.seqlens_k = p.seqlens_k; a.status = status;
-  a.Hq = p.Hq; a.Hkv = p.Hkv; a.M = p.M; a.N = p.N; a.causal = p.causal; a.window_left = p.window_left;
-  dim3 grid((p.M + kTM - 1) / kTM, (unsigned)((int64_t)p.B * p.Hq));
-  fwd_tc_kernel<D, VT><<<grid, kTcThreads, C::SMEM, stream>>>(q_map, k_map, v_map, a);
+  SL8_CUDA_TRY(cudaFuncSetAttribute(fwd_tc_kernel<D, VT, QK8>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+  dim3 grid((M + kTM - 1) / kTM, (unsigned)((int64_t)B * Hq));
+  fwd_tc_kernel<D, VT, QK8><<<grid, kTcThreads, C::SMEM, stream>>>(q_map, k_map, v_map, a);
   return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
 }
 
-template <typename VT>
-int launch_tc_d(const sl8_fwd_params& p, int* status, cudaStream_t s) {
-  switch (p.D) {
-    case 64: return launch_tc<64, VT>(p, status, s);
-    case 128: return launch_tc<128, VT>(p, status, s);
-    case 256: return launch_tc<256, VT>(p, status, s);
+template <typename VT, bool QK8>
+int launch_tc_d(int D, const void* q, const void* k, const void* v, int B, int Hq, int Hkv, int M, int N,
+                const TcArgs& a, cudaStream_t s) {
+  switch (D) {
+    case 64: return launch_tc_impl<64, VT, QK8>(q, k, v, B, Hq, Hkv, M, N, a, s);
+    case 128: return launch_tc_impl<128, VT, QK8>(q, k, v, B, Hq, Hkv, M, N, a, s);
+    case 256: return launch_tc_impl<256, VT, QK8>(q, k, v, B, Hq, Hkv, M, N, a, s);
   }
   return SL8_ERR_UNSUPPORTED;
 }
 
 template <int D>
 int launch_logits(const int8_t* q, const int8_t* k, int M, int N, int32_t* s_out, int* status, cudaStream_t stream) {
-  using C = TcCfg<D>;
+  using C = TcCfg<D, true>;
   CUtensorMap q_map, k_map;
   int rc = sl8_make_tmap_3d(&q_map, q, 1, D, M, 1, C::QROW, kTM, C::QROW);
   if (rc == SL8_OK) rc = sl8_make_tmap_3d(&k_map, k, 1, D, N, 1, C::QROW, kTN, C::QROW);
@@ -532,8 +572,26 @@ extern "C" int sl8_attn_int8_fwd(const sl8_fwd_params* p, void* workspace, size_
   if (backend == SL8_BACKEND_MMA) return sl8_fwd_mma_int8(p, s);
   if (backend != SL8_BACKEND_TCGEN05) return SL8_ERR_UNSUPPORTED;
   if (!tc_head_dim(p->D) || p->N == 0) return SL8_ERR_UNSUPPORTED;
-  int* status = reinterpret_cast<int*>(workspace);
-  return p->v_dtype == SL8_F16 ? launch_tc_d<__half>(*p, status, s) : launch_tc_d<__nv_bfloat16>(*p, status, s);
+  TcArgs a{};
+  a.q_scale = p->q_scale; a.k_scale = p->k_scale; a.out = p->out; a.lse = p->lse;
+  a.seqlens_q = p->seqlens_q; a.seqlens_k = p->seqlens_k; a.status = reinterpret_cast<int*>(workspace);
+  a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N; a.causal = p->causal; a.window_left = p->window_left;
+  return p->v_dtype == SL8_F16
+             ? launch_tc_d<__half, true>(p->D, p->q, p->k, p->v, p->B, p->Hq, p->Hkv, p->M, p->N, a, s)
+             : launch_tc_d<__nv_bfloat16, true>(p->D, p->q, p->k, p->v, p->B, p->Hq, p->Hkv, p->M, p->N, a, s);
+}
+
+// 16-bit Q/K forward on the tcgen05 path (D = 64, 128, 256, N > 0); parameters were validated
+// by sl8_attn_fp16_fwd (fwd_mma.cu).
+int sl8_fwd_tc_fp16(const sl8_fp16_fwd_params* p, int* status, cudaStream_t s) {
+  if (!tc_head_dim(p->D) || p->N == 0) return SL8_ERR_UNSUPPORTED;
+  TcArgs a{};
+  a.out = p->out; a.lse = p->lse; a.seqlens_q = p->seqlens_q; a.seqlens_k = p->seqlens_k; a.status = status;
+  a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N; a.causal = p->causal; a.window_left = p->window_left;
+  a.scale_log2 = p->softmax_scale * 1.4426950408889634f;
+  return p->dtype == SL8_F16
+             ? launch_tc_d<__half, false>(p->D, p->q, p->k, p->v, p->B, p->Hq, p->Hkv, p->M, p->N, a, s)
+             : launch_tc_d<__nv_bfloat16, false>(p->D, p->q, p->k, p->v, p->B, p->Hq, p->Hkv, p->M, p->N, a, s);
 }
 
 extern "C" int sl8_qk_logits_i32(const int8_t* q, const int8_t* k, int32_t M, int32_t N, int32_t D, int32_t* s_out,
@@ -553,3 +611,9 @@ extern "C" int sl8_qk_logits_i32(const int8_t* q, const int8_t* k, int32_t M, in
   }
   return SL8_ERR_BAD_HEAD_DIM;
 }
+
+#ifdef SL8_TRACE
+extern "C" int sl8_dbg_read_trace(long long* host_out, int n) {
+  return (int)cudaMemcpyFromSymbol(host_out, sl8::g_trace, sizeof(long long) * n);
+}
+#endif

@@ -128,34 +128,54 @@ __global__ void __launch_bounds__(kQuantThreads) quant_rows_vec_kernel(QuantArgs
 
     if (MODE == kQueryFoldGate && a.flag != nullptr) {
       // max / (median + 1e-10) > thr  <=>  at least rank_need elements e satisfy
-      // max / (|e| + 1e-10) > thr, because the quotient is monotone in |e|.
+      // max / (|e| + 1e-10) > thr, because the quotient is monotone in |e|.  Elements whose
+      // y = |e| + 1e-10 is clearly below / above max / thr are decided by a comparison; only
+      // the few inside a 1e-6 relative band take the exactly rounded division.
+      const float t0 = __fdiv_rn(amax, a.ratio_threshold);
+      const float t_lo = t0 * 0.999999f, t_hi = t0 * 1.000001f;
       int cnt = 0;
 #pragma unroll
       for (int v = 0; v < NV; ++v)
         if (has[v]) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            cnt += (__fdiv_rn(amax, fabsf(f[v][i]) + 1e-10f) > a.ratio_threshold) ? 1 : 0;
+          for (int i = 0; i < 8; ++i) {
+            const float y = fabsf(f[v][i]) + 1e-10f;
+            if (y < t_lo) {
+              ++cnt;
+            } else if (y <= t_hi) {
+              cnt += (__fdiv_rn(amax, y) > a.ratio_threshold) ? 1 : 0;
+            }
+          }
         }
 #pragma unroll
       for (int off = LPR / 2; off > 0; off >>= 1) cnt += __shfl_xor_sync(FULL, cnt, off);
       if (live && cnt >= rank_need) any_outlier = 1;
     }
 
+    // Codes.  Fast path: t = x * (1/s) + 1.5 * 2^23 rounds x / s to the nearest integer in one
+    // fused operation (its low byte is the code).  1/s carries a 2^-24 relative error, so the
+    // result can differ from rint(fl(x / s)) only when x / s lies within ~1.5e-5 of a
+    // half-integer; those elements (|residual| >= 0.49996, also NaN / inf rows) are redone
+    // with the IEEE division, rint and clamp of the reference.
+    const float rcp = __frcp_rn(s);
     int8_t* qr = a.q + row * a.K;
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
       if (!has[v]) continue;
+      uint32_t tb[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float t = fmaf(f[v][i], rcp, 12582912.0f);
+        const float e = fmaf(f[v][i], rcp, -(t - 12582912.0f));
+        tb[i] = __float_as_uint(t);
+        if (!(fabsf(e) < 0.49996f)) tb[i] = (uint32_t)(int)quant_one(f[v][i], s);
+      }
       uint32_t w[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        uint32_t acc = 0;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int qi = (int)quant_one(f[v][4 * h + i], s);
-          acc |= (uint32_t)(qi & 0xff) << (8 * i);
-        }
-        w[h] = acc;
+        const uint32_t lo = __byte_perm(tb[4 * h], tb[4 * h + 1], 0x0040);
+        const uint32_t hi = __byte_perm(tb[4 * h + 2], tb[4 * h + 3], 0x0040);
+        w[h] = __byte_perm(lo, hi, 0x5410);
       }
       *reinterpret_cast<uint2*>(qr + (sl + v * LPR) * 8) = make_uint2(w[0], w[1]);
     }

@@ -190,14 +190,28 @@ def test_python_entry_with_gate_and_smoothing(device):
     assert s8.ops.last_gate_decision is None and torch.isfinite(out3.float()).all()
 
 
-@pytest.mark.parametrize("D,dtype", [(64, torch.float16), (128, torch.bfloat16), (80, torch.float16), (256, torch.float16)])
-def test_fp16_fwd(D, dtype, device):
-    q, k, v = oracle.make_batch(40 + D, 1, 4, 2, 300, D, Sk=333, dtype=dtype)
-    for causal in (False, True):
-        out = s8.attn_fp16_fwd(q.to(device), k.to(device), v.to(device), causal=causal)
-        ref = oracle.attention_fp32(q, k, v, causal=causal)
-        tol = 5e-3 if dtype == torch.float16 else 2e-2
-        assert oracle.cos_sim(out, ref) >= 0.9999 and oracle.rel_l1(out, ref) <= tol
+@pytest.mark.parametrize("D,dtype,backend", [(64, torch.float16, TC), (128, torch.bfloat16, TC), (128, torch.float16, TC),
+                                             (256, torch.float16, TC), (80, torch.float16, MMA), (128, torch.float16, MMA),
+                                             (64, torch.bfloat16, MMA), (256, torch.float16, MMA)])
+def test_fp16_fwd(D, dtype, backend, device):
+    q, k, v = oracle.make_batch(40 + D, 2, 4, 2, 300, D, Sk=333, dtype=dtype)
+    tol = 5e-3 if dtype == torch.float16 else 2e-2
+    for causal, window in ((False, -1), (True, -1), (True, 50)):
+        out = _C.attn_fp16_fwd(q.to(device), k.to(device), v.to(device), causal, None, window, None, backend=backend)
+        ref = oracle.attention_fp32(q, k, v, causal=causal, window_left=window)
+        assert oracle.cos_sim(out, ref) >= 0.9999 and oracle.rel_l1(out, ref) <= tol, (causal, window)
+        assert torch.equal(out, _C.attn_fp16_fwd(q.to(device), k.to(device), v.to(device), causal, None, window, None,
+                                                 backend=backend))
+    assert _C.device_status() == 0
+    lens = torch.tensor([300, 77], dtype=torch.int32)
+    out = _C.attn_fp16_fwd(q.to(device), k[:, :, :300].contiguous().to(device), v[:, :, :300].contiguous().to(device),
+                           True, None, -1, None, seqlens_q=lens.to(device), seqlens_k=lens.to(device), backend=backend)
+    ref = oracle.attention_fp32_ragged(q, k[:, :, :300], v[:, :, :300], lens, lens, causal=True)
+    assert oracle.cos_sim(out, ref) >= 0.9999 and float(out[1, :, 77:].abs().max()) == 0.0
+    if backend == TC:
+        with pytest.raises(RuntimeError, match="not supported"):
+            qq = torch.zeros(1, 2, 64, 80, dtype=dtype, device=device)
+            _C.attn_fp16_fwd(qq, qq, qq, False, None, -1, None, backend=TC)
 
 
 def test_autograd_wrapper(device):
