@@ -31,10 +31,12 @@ int sl8_fwd_mma_int8(const sl8_fwd_params* p, cudaStream_t s);  // fwd_mma.cu
 namespace sl8 {
 namespace {
 
-constexpr int kTM = 128, kTN = 128;
+constexpr int kTM = 128;                               // query rows per block
+constexpr int kTN = 64;                                // keys per tile
 constexpr int kSoftmaxWarps = 4;                       // one query row per thread, rows = tensor-memory lanes
 constexpr int kProducerWarp = 4, kMmaWarp = 5;
 constexpr int kTcThreads = 32 * (kSoftmaxWarps + 2);
+constexpr int kScaleStages = 4;                        // ring of k_scale tiles
 
 template <int D, bool QK8>
 struct TcCfg {
@@ -42,24 +44,26 @@ struct TcCfg {
   static constexpr int QROW = QK_ROWB < 128 ? QK_ROWB : 128;  // bytes per shared row of a Q/K sub-tile
   static constexpr int QSUBS = QK_ROWB / QROW;
   static constexpr uint32_t QK_SW = QROW == 128 ? kUmmaSw128 : kUmmaSw64;
-  static constexpr int QK_SUB_BYTES = 128 * QROW;
-  static constexpr int QK_TILE_BYTES = 128 * QK_ROWB;
+  static constexpr int Q_SUB_BYTES = kTM * QROW;
+  static constexpr int Q_TILE_BYTES = kTM * QK_ROWB;
+  static constexpr int K_SUB_BYTES = kTN * QROW;
+  static constexpr int K_TILE_BYTES = kTN * QK_ROWB;
   static constexpr int QK_STEPS = QK_ROWB / 32;           // MMA K steps of 32 bytes
-  static constexpr int VSUBS = 2 * D / 128;               // 64-channel sub-tiles of 128 keys x 128 B
-  static constexpr int V_SUB_BYTES = 128 * 128;
-  static constexpr int V_TILE_BYTES = 128 * 2 * D;
-  static constexpr int NKS = (QK8 || D == 64) ? 2 : 1;
-  static constexpr int NVS = D == 64 ? 2 : 1;
+  static constexpr int VSUBS = 2 * D / 128;               // 64-channel sub-tiles of kTN keys x 128 B
+  static constexpr int V_SUB_BYTES = kTN * 128;
+  static constexpr int V_TILE_BYTES = kTN * 2 * D;
+  static constexpr int NKS = QK8 ? 3 : 2;
+  static constexpr int NVS = 2;
   static constexpr int OFF_Q = 0;
-  static constexpr int OFF_K = OFF_Q + QK_TILE_BYTES;
-  static constexpr int OFF_V = OFF_K + NKS * QK_TILE_BYTES;
-  static constexpr int OFF_KS = OFF_V + NVS * V_TILE_BYTES;   // 2 x 128 k_scale floats
-  static constexpr int OFF_BAR = OFF_KS + 2 * kTN * 4;
-  static constexpr int NEED = OFF_BAR + 256 + 1024;
+  static constexpr int OFF_K = OFF_Q + Q_TILE_BYTES;
+  static constexpr int OFF_V = OFF_K + NKS * K_TILE_BYTES;
+  static constexpr int OFF_KS = OFF_V + NVS * V_TILE_BYTES;   // kScaleStages x kTN floats
+  static constexpr int OFF_BAR = OFF_KS + kScaleStages * kTN * 4;
+  static constexpr int NEED = OFF_BAR + 512 + 1024;
   // never more than two blocks per SM: each holds TMEM_COLS columns of the 512
   static constexpr int SMEM = NEED < 78 * 1024 ? 78 * 1024 : NEED;
   static constexpr uint32_t TMEM_COLS = D <= 128 ? 256 : 512;
-  static constexpr uint32_t COL_S = 0, COL_O = 128;
+  static constexpr uint32_t COL_S = 0, COL_O = 128;        // S: two buffers of kTN columns
 };
 
 struct TcArgs {
@@ -75,8 +79,11 @@ struct TcArgs {
   float scale_log2;  // 16-bit Q/K mode: softmax_scale * log2(e)
 };
 
-enum Bar { Q_FULL = 0, S_FULL, P_FULL, O_DONE, K_FULL, K_EMPTY = K_FULL + 2, V_FULL = K_EMPTY + 2,
-           V_EMPTY = V_FULL + 2, KS_FULL = V_EMPTY + 2, KS_EMPTY = KS_FULL + 2, NUM_BARS = KS_EMPTY + 2 };
+enum Bar {
+  Q_FULL = 0, O_DONE, PV_DONE, S_FULL, P_FULL = S_FULL + 2, K_FULL = P_FULL + 2, K_EMPTY = K_FULL + 3,
+  V_FULL = K_EMPTY + 3, V_EMPTY = V_FULL + 2, KS_FULL = V_EMPTY + 2, KS_EMPTY = KS_FULL + kScaleStages,
+  NUM_BARS = KS_EMPTY + kScaleStages
+};
 
 #ifdef SL8_TRACE
 __device__ long long g_trace[8192];
@@ -93,81 +100,40 @@ __device__ __forceinline__ float2 bits2(uint32_t a, uint32_t b) {
   return make_float2(__uint_as_float(a), __uint_as_float(b));
 }
 
-// Pass 1 over the 128-column S row in this thread's tensor-memory lane: accumulators ->
-// fp32 logits, optional masking, row max; the logits replace the accumulators in tensor
-// memory.  int8 mode: (float(acc) * qs) * ks[n] in the reference's multiply order; the
-// int -> float conversion is exact and runs on the ALU/FMA pipes (bit pattern of 1.5 * 2^23
-// plus the integer, minus 1.5 * 2^23; |acc| <= 127 * 127 * 256 < 2^22), leaving the
-// special-function unit to the exponentials.  16-bit mode: acc * (softmax_scale * log2 e).
-// Loads of the next 32 columns are in flight while the current 32 are processed.
+// The kTN accumulator columns of this thread's row -> fp32 logits in place; returns the max.
+// int8 mode: (float(acc) * qs) * ks[n] in the reference's multiply order; the int -> float
+// conversion is exact and runs on the ALU/FMA pipes (bit pattern of 1.5 * 2^23 plus the
+// integer, minus 1.5 * 2^23; |acc| <= 127 * 127 * 256 < 2^22), leaving the special-function
+// unit to the exponentials.  16-bit mode: acc * (softmax_scale * log2 e).
 template <bool QK8, bool MASK>
-__device__ __forceinline__ float logits_pass(uint32_t t_s, const float* __restrict__ ksv, float qs, int n_block,
-                                             int n_len, int causal, int qpos, int window_left) {
+__device__ __forceinline__ float logits_inplace(uint32_t (&r)[kTN], const float* __restrict__ ksv, float qs,
+                                                int n_block, int n_len, int causal, int qpos, int window_left) {
   const float2 qs2 = make_float2(qs, qs);
   const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
   float mx0 = -INFINITY, mx1 = -INFINITY;
-  uint32_t r[2][32];
-  tc_ld32(t_s, r[0]);
+  const float2* ks2 = reinterpret_cast<const float2*>(ksv);
 #pragma unroll
-  for (int c = 0; c < kTN / 32; ++c) {
-    uint32_t(&cur)[32] = r[c & 1];
-    tc_wait_ld();
-    tc_regs_ready(cur);
-    if (c + 1 < kTN / 32) tc_ld32(t_s + 32 * (c + 1), r[(c + 1) & 1]);
-    const float2* ks2 = reinterpret_cast<const float2*>(ksv + 32 * c);
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float2 p;
-      if (QK8) {
-        p = bits2(cur[2 * i] + kMagicBits, cur[2 * i + 1] + kMagicBits);
-        p = __fmul2_rn(__fmul2_rn(__fadd2_rn(p, neg_magic2), qs2), ks2[i]);
-      } else {
-        p = __fmul2_rn(bits2(cur[2 * i], cur[2 * i + 1]), qs2);
-      }
-      if (MASK) {
-        const int gn = n_block + 32 * c + 2 * i;
-        const bool v0 = (gn < n_len) && (!causal || gn <= qpos) && (window_left < 0 || gn > qpos - window_left);
-        const bool v1 = (gn + 1 < n_len) && (!causal || gn + 1 <= qpos) && (window_left < 0 || gn + 1 > qpos - window_left);
-        p.x = v0 ? p.x : -INFINITY;
-        p.y = v1 ? p.y : -INFINITY;
-      }
-      if (i & 1) mx1 = max3f(mx1, p.x, p.y);
-      else mx0 = max3f(mx0, p.x, p.y);
-      cur[2 * i] = __float_as_uint(p.x);
-      cur[2 * i + 1] = __float_as_uint(p.y);
+  for (int i = 0; i < kTN / 2; ++i) {
+    float2 p;
+    if (QK8) {
+      p = bits2(r[2 * i] + kMagicBits, r[2 * i + 1] + kMagicBits);
+      p = __fmul2_rn(__fmul2_rn(__fadd2_rn(p, neg_magic2), qs2), ks2[i]);
+    } else {
+      p = __fmul2_rn(bits2(r[2 * i], r[2 * i + 1]), qs2);
     }
-    tc_st32(t_s + 32 * c, cur);
+    if (MASK) {
+      const int gn = n_block + 2 * i;
+      const bool v0 = (gn < n_len) && (!causal || gn <= qpos) && (window_left < 0 || gn > qpos - window_left);
+      const bool v1 = (gn + 1 < n_len) && (!causal || gn + 1 <= qpos) && (window_left < 0 || gn + 1 > qpos - window_left);
+      p.x = v0 ? p.x : -INFINITY;
+      p.y = v1 ? p.y : -INFINITY;
+    }
+    if (i & 1) mx1 = max3f(mx1, p.x, p.y);
+    else mx0 = max3f(mx0, p.x, p.y);
+    r[2 * i] = __float_as_uint(p.x);
+    r[2 * i + 1] = __float_as_uint(p.y);
   }
   return fmaxf(mx0, mx1);
-}
-
-// Pass 2: P = 2^(s - m) from the fp32 logits in tensor memory, packed to VT pairs over the
-// first 64 columns of S; returns the row sum of the unrounded P.
-template <typename VT>
-__device__ __forceinline__ float probs_pass(uint32_t t_s, float m_use) {
-  const float2 neg_m2 = make_float2(-m_use, -m_use);
-  float2 sum_a = make_float2(0.f, 0.f), sum_b = sum_a;
-  uint32_t r[2][32];
-  tc_ld32(t_s, r[0]);
-#pragma unroll
-  for (int c = 0; c < kTN / 32; ++c) {
-    uint32_t(&cur)[32] = r[c & 1];
-    tc_wait_ld();
-    tc_regs_ready(cur);
-    if (c + 1 < kTN / 32) tc_ld32(t_s + 32 * (c + 1), r[(c + 1) & 1]);
-    uint32_t pk[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float2 x = __fadd2_rn(bits2(cur[2 * i], cur[2 * i + 1]), neg_m2);
-      const float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
-      if (i & 1) sum_b = __fadd2_rn(sum_b, pr);
-      else sum_a = __fadd2_rn(sum_a, pr);
-      pk[i] = pack2<VT>(pr.x, pr.y);
-    }
-    tc_st16(t_s + 16 * c, pk);
-  }
-  const float2 t = __fadd2_rn(sum_a, sum_b);
-  return t.x + t.y;
 }
 
 template <int D, typename VT, bool QK8>
@@ -208,14 +174,19 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(&bars[Q_FULL], 1);
-    mbar_init(&bars[S_FULL], 1);
-    mbar_init(&bars[P_FULL], kSoftmaxWarps);
     mbar_init(&bars[O_DONE], 1);
+    mbar_init(&bars[PV_DONE], 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars[K_FULL + i], 1);
-      mbar_init(&bars[K_EMPTY + i], 1);
+      mbar_init(&bars[S_FULL + i], 1);
+      mbar_init(&bars[P_FULL + i], kSoftmaxWarps);
       mbar_init(&bars[V_FULL + i], 1);
       mbar_init(&bars[V_EMPTY + i], 1);
+    }
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(&bars[K_FULL + i], 1);
+      mbar_init(&bars[K_EMPTY + i], 1);
+    }
+    for (int i = 0; i < kScaleStages; ++i) {
       mbar_init(&bars[KS_FULL + i], 1);
       mbar_init(&bars[KS_EMPTY + i], kSoftmaxWarps);
     }
@@ -237,10 +208,10 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
       tma_prefetch_desc(&q_map);
       tma_prefetch_desc(&k_map);
       tma_prefetch_desc(&v_map);
-      mbar_expect_tx(&bars[Q_FULL], C::QK_TILE_BYTES);
+      mbar_expect_tx(&bars[Q_FULL], C::Q_TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < C::QSUBS; ++c)
-        tma_load_3d(smem + C::OFF_Q + c * C::QK_SUB_BYTES, &q_map, &bars[Q_FULL], c * (C::QROW / (QK8 ? 1 : 2)),
+        tma_load_3d(smem + C::OFF_Q + c * C::Q_SUB_BYTES, &q_map, &bars[Q_FULL], c * (C::QROW / (QK8 ? 1 : 2)),
                     m_block, (int)bh);
     }
     for (int j = 0; j < ntiles && ok; ++j) {
@@ -249,10 +220,10 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
         const int ks = j % C::NKS, vs = j % C::NVS;
         if (j >= C::NKS) ok = mbar_wait(&bars[K_EMPTY + ks], ((j / C::NKS) - 1) & 1, a.status);
         if (ok) {
-          mbar_expect_tx(&bars[K_FULL + ks], C::QK_TILE_BYTES);
+          mbar_expect_tx(&bars[K_FULL + ks], C::K_TILE_BYTES);
 #pragma unroll
           for (int c = 0; c < C::QSUBS; ++c)
-            tma_load_3d(smem + C::OFF_K + ks * C::QK_TILE_BYTES + c * C::QK_SUB_BYTES, &k_map, &bars[K_FULL + ks],
+            tma_load_3d(smem + C::OFF_K + ks * C::K_TILE_BYTES + c * C::K_SUB_BYTES, &k_map, &bars[K_FULL + ks],
                         c * (C::QROW / (QK8 ? 1 : 2)), n_block, kv_bh);
           if (j >= C::NVS) ok = mbar_wait(&bars[V_EMPTY + vs], ((j / C::NVS) - 1) & 1, a.status);
         }
@@ -268,8 +239,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
       if (!ok) break;
       if (QK8) {
         // k_scale tile through the generic proxy (its start is not 16-byte aligned in general)
-        const int ss = j & 1;
-        if (j >= 2) ok = mbar_wait(&bars[KS_EMPTY + ss], ((j >> 1) - 1) & 1, a.status);
+        const int ss = j % kScaleStages;
+        if (j >= kScaleStages) ok = mbar_wait(&bars[KS_EMPTY + ss], ((j / kScaleStages) - 1) & 1, a.status);
         if (!ok) break;
 #pragma unroll
         for (int i = 0; i < kTN / 32; ++i) {
@@ -282,44 +253,53 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
     }
   } else if (warp == kMmaWarp) {
     // ======================= MMA issuer =======================
+    // Order of issue: QK_0, QK_1, then for every tile j: P.V_j, QK_{j+2}.  S has two buffers, so
+    // the next tile's logits are already in tensor memory while the softmax warps work on
+    // this one; QK_{j+2} reuses the buffer whose P the (earlier issued) P.V_j reads.
     if (lane == 0) {
       constexpr uint32_t vfmt = std::is_same<VT, __nv_bfloat16>::value ? 1u : 0u;
       const uint32_t idesc_qk = QK8 ? umma_idesc(2, 1, 1, 0, 0, kTM, kTN) : umma_idesc(1, vfmt, vfmt, 0, 0, kTM, kTN);
       const uint32_t idesc_pv = umma_idesc(1, vfmt, vfmt, 0, 1, kTM, D);
       const uint32_t q_u = smem_u32(smem + C::OFF_Q);
-      ok = mbar_wait(&bars[Q_FULL], 0, a.status);
-      for (int j = 0; j < ntiles && ok; ++j) {
-        const int ks = j % C::NKS, vs = j % C::NVS;
-        ok = mbar_wait(&bars[K_FULL + ks], (j / C::NKS) & 1, a.status);
-        if (!ok) break;
+      auto issue_qk = [&](int t) -> bool {
+        const int ks = t % C::NKS;
+        if (!mbar_wait(&bars[K_FULL + ks], (t / C::NKS) & 1, a.status)) return false;
         tc_fence_after();
-        TR(4096 + 8 * j + 0);
-        const uint32_t k_u = smem_u32(smem + C::OFF_K + ks * C::QK_TILE_BYTES);
+        const uint32_t k_u = smem_u32(smem + C::OFF_K + ks * C::K_TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < C::QK_STEPS; ++s) {
-          const uint32_t off = (32 * s / C::QROW) * C::QK_SUB_BYTES + (32 * s % C::QROW);
-          const uint64_t da = umma_smem_desc(q_u + off, 16, 8 * C::QROW, C::QK_SW);
-          const uint64_t db = umma_smem_desc(k_u + off, 16, 8 * C::QROW, C::QK_SW);
-          if (QK8) tc_mma_i8_ss(tmem + C::COL_S, da, db, idesc_qk, s > 0 ? 1u : 0u);
-          else tc_mma_f16_ss(tmem + C::COL_S, da, db, idesc_qk, s > 0 ? 1u : 0u);
+          const uint32_t sub = 32 * s / C::QROW, within = 32 * s % C::QROW;
+          const uint64_t da = umma_smem_desc(q_u + sub * C::Q_SUB_BYTES + within, 16, 8 * C::QROW, C::QK_SW);
+          const uint64_t db = umma_smem_desc(k_u + sub * C::K_SUB_BYTES + within, 16, 8 * C::QROW, C::QK_SW);
+          if (QK8) tc_mma_i8_ss(tmem + C::COL_S + kTN * (t & 1), da, db, idesc_qk, s > 0 ? 1u : 0u);
+          else tc_mma_f16_ss(tmem + C::COL_S + kTN * (t & 1), da, db, idesc_qk, s > 0 ? 1u : 0u);
         }
         tc_commit(&bars[K_EMPTY + ks]);
-        tc_commit(&bars[S_FULL]);
+        tc_commit(&bars[S_FULL + (t & 1)]);
+        return true;
+      };
+      ok = mbar_wait(&bars[Q_FULL], 0, a.status);
+      if (ok) ok = issue_qk(0);
+      if (ok && ntiles > 1) ok = issue_qk(1);
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int vs = j % C::NVS;
+        TR(4096 + 8 * j + 0);
+        ok = mbar_wait(&bars[P_FULL + (j & 1)], (j >> 1) & 1, a.status);
         TR(4096 + 8 * j + 1);
-        ok = mbar_wait(&bars[P_FULL], j & 1, a.status);
-        TR(4096 + 8 * j + 2);
         if (ok) ok = mbar_wait(&bars[V_FULL + vs], (j / C::NVS) & 1, a.status);
         if (!ok) break;
         tc_fence_after();
-        TR(4096 + 8 * j + 3);
         const uint32_t v_u = smem_u32(smem + C::OFF_V + vs * C::V_TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < kTN / 16; ++kk)
-          tc_mma_f16_ts(tmem + C::COL_O, tmem + C::COL_S + 8 * kk,
+          tc_mma_f16_ts(tmem + C::COL_O, tmem + C::COL_S + kTN * (j & 1) + 8 * kk,
                         umma_smem_desc(v_u + kk * 2048, C::V_SUB_BYTES, 1024, kUmmaSw128), idesc_pv,
                         (j > 0 || kk > 0) ? 1u : 0u);
         tc_commit(&bars[V_EMPTY + vs]);
-        TR(4096 + 8 * j + 4);
+        tc_commit(&bars[PV_DONE]);
+        TR(4096 + 8 * j + 2);
+        if (j + 2 < ntiles) ok = issue_qk(j + 2);
+        TR(4096 + 8 * j + 3);
         if (j == ntiles - 1) tc_commit(&bars[O_DONE]);
       }
     }
@@ -333,21 +313,27 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
 
     for (int j = 0; j < ntiles; ++j) {
       const int n_block = n_begin + j * kTN;
-      const int ss = j & 1;
+      const int ss = j % kScaleStages;
+      const uint32_t t_s = t_row + C::COL_S + kTN * (j & 1);
       if (warp == 0 && lane == 0) TR(8 * j + 0);
-      if (QK8) ok = mbar_wait(&bars[KS_FULL + ss], (j >> 1) & 1, a.status);
-      if (ok) ok = mbar_wait(&bars[S_FULL], j & 1, a.status);
+      if (QK8) ok = mbar_wait(&bars[KS_FULL + ss], (j / kScaleStages) & 1, a.status);
+      if (ok) ok = mbar_wait(&bars[S_FULL + (j & 1)], (j >> 1) & 1, a.status);
       if (!ok) break;
       tc_fence_after();
       if (warp == 0 && lane == 0) TR(8 * j + 1);
+      uint32_t r[kTN];
+      tc_ld32(t_s, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+      tc_ld32(t_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+      tc_wait_ld();
+      tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+      tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+      if (warp == 0 && lane == 0) TR(8 * j + 2);
       const float* ksv = ks_smem + ss * kTN;
       const bool need_mask = (n_block + kTN > n_len) || (a.causal && n_block + kTN - 1 > m_block + causal_diag) ||
                              (a.window_left >= 0 && n_block <= m_block + kTM - 1 + causal_diag - a.window_left);
-      // ---- pass 1: accumulators -> fp32 logits (written back to tensor memory), row max ----
-      const float tmax =
-          need_mask ? logits_pass<QK8, true>(t_row + C::COL_S, ksv, qs, n_block, n_len, a.causal, qpos, a.window_left)
-                    : logits_pass<QK8, false>(t_row + C::COL_S, ksv, qs, n_block, n_len, a.causal, qpos, a.window_left);
-      if (warp == 0 && lane == 0) TR(8 * j + 2);
+      const float tmax = need_mask ? logits_inplace<QK8, true>(r, ksv, qs, n_block, n_len, a.causal, qpos, a.window_left)
+                                   : logits_inplace<QK8, false>(r, ksv, qs, n_block, n_len, a.causal, qpos, a.window_left);
+      if (warp == 0 && lane == 0) TR(8 * j + 3);
       // Lazy rescale: the running max moves only when some row of the warp outgrew it by
       // more than 2^8 (P then stays <= 256, harmless in fp16/bf16 and in the fp32 sum);
       // out = O / l does not depend on which reference max was used.
@@ -358,8 +344,10 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
         resc = exp2f(m_run - ((m_new == -INFINITY) ? 0.f : m_new));  // m_run = -inf -> 0
         m_run = m_new;
         if (j > 0) {
-          // correction: O *= resc (the previous tile's P.V has completed: the commit behind
-          // S_FULL covers every earlier MMA)
+          // correction: O *= resc once the previous tile's P.V has landed in O
+          ok = mbar_wait(&bars[PV_DONE], (j - 1) & 1, a.status);
+          if (!ok) break;
+          tc_fence_after();
           const float2 resc2 = make_float2(resc, resc);
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
@@ -377,18 +365,31 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
           }
         }
       }
+      // ---- P = 2^(s - m), row sum, P -> tensor memory as 16-bit pairs over S's own columns ----
       const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-      tc_wait_st();  // logits written in pass 1 are visible to the loads below
-      if (warp == 0 && lane == 0) TR(8 * j + 3);
-      // ---- pass 2: P = exp2(s - m), row sum, P -> tensor memory (16-bit pairs) ----
-      const float psum = probs_pass<VT>(t_row + C::COL_S, m_use);
-      l_run = l_run * resc + psum;
+      const float2 neg_m2 = make_float2(-m_use, -m_use);
+      float2 sum_a = make_float2(0.f, 0.f), sum_b = sum_a;
+#pragma unroll
+      for (int c = 0; c < kTN / 32; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float2 x = __fadd2_rn(bits2(r[32 * c + 2 * i], r[32 * c + 2 * i + 1]), neg_m2);
+          const float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+          if (i & 1) sum_b = __fadd2_rn(sum_b, pr);
+          else sum_a = __fadd2_rn(sum_a, pr);
+          pk[i] = pack2<VT>(pr.x, pr.y);
+        }
+        tc_st16(t_s + 16 * c, pk);
+      }
+      const float2 st = __fadd2_rn(sum_a, sum_b);
+      l_run = l_run * resc + (st.x + st.y);
       if (warp == 0 && lane == 0) TR(8 * j + 4);
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&bars[P_FULL]);
+        mbar_arrive(&bars[P_FULL + (j & 1)]);
         if (QK8) mbar_arrive(&bars[KS_EMPTY + ss]);
       }
       if (warp == 0 && lane == 0) TR(8 * j + 5);
@@ -433,17 +434,20 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
 }
 
 // ---- raw int32 logits through the same TMA + kind::i8 tile path ----------------
+constexpr int kLN = 128;  // keys per tile of the logits kernel
+
 template <int D>
 __global__ void __launch_bounds__(128) qk_logits_kernel(const __grid_constant__ CUtensorMap q_map,
                                                         const __grid_constant__ CUtensorMap k_map, int32_t* s_out,
                                                         int M, int N, int* status) {
   using C = TcCfg<D, true>;
+  constexpr int SUB = 128 * C::QROW, TILE = 128 * D;   // 128-row tiles of Q and of K
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * C::QK_TILE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * TILE);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m_block = blockIdx.x * kTM, n_block = blockIdx.y * kTN;
+  const int m_block = blockIdx.x * kTM, n_block = blockIdx.y * kLN;
   if (threadIdx.x == 0) {
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
@@ -459,20 +463,20 @@ __global__ void __launch_bounds__(128) qk_logits_kernel(const __grid_constant__ 
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   bool ok = true;
   if (threadIdx.x == 0) {
-    mbar_expect_tx(&bars[0], 2 * C::QK_TILE_BYTES);
+    mbar_expect_tx(&bars[0], 2 * TILE);
 #pragma unroll
     for (int c = 0; c < C::QSUBS; ++c) {
-      tma_load_3d(smem + c * C::QK_SUB_BYTES, &q_map, &bars[0], c * C::QROW, m_block, 0);
-      tma_load_3d(smem + C::QK_TILE_BYTES + c * C::QK_SUB_BYTES, &k_map, &bars[0], c * C::QROW, n_block, 0);
+      tma_load_3d(smem + c * SUB, &q_map, &bars[0], c * C::QROW, m_block, 0);
+      tma_load_3d(smem + TILE + c * SUB, &k_map, &bars[0], c * C::QROW, n_block, 0);
     }
     ok = mbar_wait(&bars[0], 0, status);
     if (ok) {
       tc_fence_after();
-      const uint32_t idesc = umma_idesc(2, 1, 1, 0, 0, kTM, kTN);
-      const uint32_t q_u = smem_u32(smem), k_u = smem_u32(smem + C::QK_TILE_BYTES);
+      const uint32_t idesc = umma_idesc(2, 1, 1, 0, 0, kTM, kLN);
+      const uint32_t q_u = smem_u32(smem), k_u = smem_u32(smem + TILE);
 #pragma unroll
       for (int s = 0; s < D / 32; ++s) {
-        const uint32_t off = (32 * s / C::QROW) * C::QK_SUB_BYTES + (32 * s % C::QROW);
+        const uint32_t off = (32 * s / C::QROW) * SUB + (32 * s % C::QROW);
         tc_mma_i8_ss(tmem, umma_smem_desc(q_u + off, 16, 8 * C::QROW, C::QK_SW),
                      umma_smem_desc(k_u + off, 16, 8 * C::QROW, C::QK_SW), idesc, s > 0 ? 1u : 0u);
       }
@@ -484,10 +488,11 @@ __global__ void __launch_bounds__(128) qk_logits_kernel(const __grid_constant__ 
     tc_fence_after();
     const int m = m_block + 32 * warp + lane;
 #pragma unroll 1
-    for (int c = 0; c < kTN / 32; ++c) {
+    for (int c = 0; c < kLN / 32; ++c) {
       uint32_t r[32];
       tc_ld32(tmem + ((uint32_t)(32 * warp) << 16) + 32 * c, r);
       tc_wait_ld();
+      tc_regs_ready(r);
       if (m < M)
         for (int i = 0; i < 32; ++i) {
           const int n = n_block + 32 * c + i;
@@ -535,11 +540,11 @@ int launch_logits(const int8_t* q, const int8_t* k, int M, int N, int32_t* s_out
   using C = TcCfg<D, true>;
   CUtensorMap q_map, k_map;
   int rc = sl8_make_tmap_3d(&q_map, q, 1, D, M, 1, C::QROW, kTM, C::QROW);
-  if (rc == SL8_OK) rc = sl8_make_tmap_3d(&k_map, k, 1, D, N, 1, C::QROW, kTN, C::QROW);
+  if (rc == SL8_OK) rc = sl8_make_tmap_3d(&k_map, k, 1, D, N, 1, C::QROW, kLN, C::QROW);
   if (rc != SL8_OK) return rc;
-  const int smem = 2 * C::QK_TILE_BYTES + 1024 + 64;
+  const int smem = 2 * 128 * D + 1024 + 64;
   SL8_CUDA_TRY(cudaFuncSetAttribute(qk_logits_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  dim3 grid((M + kTM - 1) / kTM, (N + kTN - 1) / kTN);
+  dim3 grid((M + kTM - 1) / kTM, (N + kLN - 1) / kLN);
   qk_logits_kernel<D><<<grid, 128, smem, stream>>>(q_map, k_map, s_out, M, N, status);
   return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
 }
