@@ -214,19 +214,37 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
         tma_load_3d(smem + C::OFF_Q + c * C::Q_SUB_BYTES, &q_map, &bars[Q_FULL], c * (C::QROW / (QK8 ? 1 : 2)),
                     m_block, (int)bh);
     }
+    auto load_k = [&](int t) -> bool {   // lane 0 only
+      const int ks = t % C::NKS;
+      if (t >= C::NKS && !mbar_wait(&bars[K_EMPTY + ks], ((t / C::NKS) - 1) & 1, a.status)) return false;
+      mbar_expect_tx(&bars[K_FULL + ks], C::K_TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < C::QSUBS; ++c)
+        tma_load_3d(smem + C::OFF_K + ks * C::K_TILE_BYTES + c * C::K_SUB_BYTES, &k_map, &bars[K_FULL + ks],
+                    c * (C::QROW / (QK8 ? 1 : 2)), n_begin + t * kTN, kv_bh);
+      return true;
+    };
+    // K runs two tiles ahead of V: the issuer asks for K_{j+2} as soon as P.V_j is queued.
+    if (lane == 0) {
+      ok = load_k(0);
+      if (ok && ntiles > 1) ok = load_k(1);
+    }
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     for (int j = 0; j < ntiles && ok; ++j) {
       const int n_block = n_begin + j * kTN;
-      if (lane == 0) {
-        const int ks = j % C::NKS, vs = j % C::NVS;
-        if (j >= C::NKS) ok = mbar_wait(&bars[K_EMPTY + ks], ((j / C::NKS) - 1) & 1, a.status);
-        if (ok) {
-          mbar_expect_tx(&bars[K_FULL + ks], C::K_TILE_BYTES);
+      float ksv[kTN / 32];
+      if (QK8) {
+        // fetched first so that the latency of these loads overlaps the barrier waits below
 #pragma unroll
-          for (int c = 0; c < C::QSUBS; ++c)
-            tma_load_3d(smem + C::OFF_K + ks * C::K_TILE_BYTES + c * C::K_SUB_BYTES, &k_map, &bars[K_FULL + ks],
-                        c * (C::QROW / (QK8 ? 1 : 2)), n_block, kv_bh);
-          if (j >= C::NVS) ok = mbar_wait(&bars[V_EMPTY + vs], ((j / C::NVS) - 1) & 1, a.status);
+        for (int i = 0; i < kTN / 32; ++i) {
+          const int n = n_block + lane + 32 * i;
+          ksv[i] = (n < n_len) ? __ldg(a.k_scale + (int64_t)kv_bh * a.N + n) : 0.f;
         }
+      }
+      if (lane == 0) {
+        const int vs = j % C::NVS;
+        if (j + 2 < ntiles) ok = load_k(j + 2);
+        if (ok && j >= C::NVS) ok = mbar_wait(&bars[V_EMPTY + vs], ((j / C::NVS) - 1) & 1, a.status);
         if (ok) {
           mbar_expect_tx(&bars[V_FULL + vs], C::V_TILE_BYTES);
 #pragma unroll
@@ -243,10 +261,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
         if (j >= kScaleStages) ok = mbar_wait(&bars[KS_EMPTY + ss], ((j / kScaleStages) - 1) & 1, a.status);
         if (!ok) break;
 #pragma unroll
-        for (int i = 0; i < kTN / 32; ++i) {
-          const int n = n_block + lane + 32 * i;
-          ks_smem[ss * kTN + lane + 32 * i] = (n < n_len) ? __ldg(a.k_scale + (int64_t)kv_bh * a.N + n) : 0.f;
-        }
+        for (int i = 0; i < kTN / 32; ++i) ks_smem[ss * kTN + lane + 32 * i] = ksv[i];
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[KS_FULL + ss]);
       }
