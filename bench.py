@@ -128,10 +128,8 @@ def timed(fn, steps: int, warmup: int, world: int, before=None):
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    return float(ms.item()) / steps
+    from superl8_b200 import shard
+    return shard.max_over_ranks(e0.elapsed_time(e1), device="cuda") / steps
 
 
 class KernelTimer:
@@ -264,6 +262,8 @@ def main():
     ap.add_argument("--gate", default="on", choices=["on", "off"])
     ap.add_argument("--workload", default="cfg3")
     ap.add_argument("--skip-extras", action="store_true", help="only the headline workload")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: every GPU owns a full batch; strong: the batch's units are split across the GPUs")
     ap.add_argument("--kernel-case", default="", choices=["", "prefill_int8", "prefill_fp16", "decode", "quant_q", "quant_k"],
                     help="launch ONE kernel family on a small case (for profilers): W warm-up + K launches, no JSON")
     args = ap.parse_args()
@@ -290,7 +290,15 @@ def main():
     peaks = load_peaks()
     gate = args.gate == "on"
 
-    q, k, v = workloads.prefill_inputs(cfg, dev, first_unit_batch=rank * cfg.B)
+    from superl8_b200 import shard
+    total_ops = world * cfg.ops
+    if args.scaling == "strong":   # this rank's slice of the ONE global batch
+        b_rng, _h = shard.batch_range(cfg.B, 1, min(world, cfg.B), rank % min(world, cfg.B))
+        total_ops = cfg.ops
+        cfg = workloads.PrefillCfg(cfg.name, len(b_rng), cfg.Hq, cfg.Hkv, cfg.S, cfg.D, cfg.causal, cfg.outliers)
+        q, k, v = workloads.prefill_inputs(cfg, dev, first_unit_batch=b_rng.start)
+    else:
+        q, k, v = workloads.prefill_inputs(cfg, dev, first_unit_batch=rank * cfg.B)
     hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
     hout = torch.empty(q.shape, dtype=torch.float16).pin_memory()
 
@@ -322,10 +330,10 @@ def main():
         clocks = sampler.stop() if rank == 0 else {}
         kern_ms = kt.mean_ms()
     status = _C.device_status()
-    value = world * cfg.ops / (ms * 1e-3) / 1e12
+    value = total_ops / (ms * 1e-3) / 1e12
 
     ms_e2e = timed(step_e2e, args.steps, args.warmup, world)
-    e2e = {"value": world * cfg.ops / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
+    e2e = {"value": total_ops / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
            "h2d_bytes_per_step": sum(t.numel() * 2 for t in (hq, hk, hv)), "d2h_bytes_per_step": hout.numel() * 2 + 4}
 
     def tensor_roofline(kernel_ms, note):
@@ -337,7 +345,7 @@ def main():
     roofline = tensor_roofline(kern_ms, dominant + (" (gate demoted the call)" if demoted else ""))
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
         "dtype": "f16" if demoted else "s8", "data": "synthetic", "config": workload_config(cfg, args, world),
         "gate_demoted": bool(demoted), "device_status": status, "e2e": e2e, "gpu_launches": gpu_launches,
         "clocks": clocks, "roofline": roofline,
@@ -354,7 +362,7 @@ def main():
             k8 = kt8.mean_ms()
         r8 = tensor_roofline(k8, "attn_int8_fwd (tcgen05 kind::i8 QK, kind::f16 PV)")
         r8["frac_of_mixed_ceiling_nominal"] = r8["achieved"] / (NOMINAL_INT8_TOPS * 2.0 / 3.0)
-        line["int8_path"] = {"value": world * cfg.ops / (ms8 * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms8,
+        line["int8_path"] = {"value": total_ops / (ms8 * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms8,
                              "gate": "off", "roofline": r8}
         del out
         # ---- quantiser (Q prologue with the gate statistic, on cfg3's Q) ----

@@ -154,9 +154,25 @@ __global__ void __launch_bounds__(kDecThreads) decode_split_kernel(const __grid_
     }
     const float* ks_row = a.k_scale + (int64_t)bkv * a.N;
     const int mi = lane >> 3, mr = lane & 7;
+    // k_scale of this thread's four keys, fetched one tile ahead so that the global-load
+    // latency is hidden behind the previous tile's work
+    float ks_cur[2][2], ks_nxt[2][2];
+    auto fetch_scales = [&](int tile, float (&dst)[2][2]) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int key = n0 + tile * kDecTile + 16 * warp + 8 * j + 2 * t + e;
+          dst[j][e] = (key < n1) ? __ldg(ks_row + key) : 0.f;
+        }
+    };
+    fetch_scales(0, ks_nxt);
 
     for (int i = 0; i < ntiles; ++i) {
       const int st = i % C::STAGES;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) { ks_cur[j][0] = ks_nxt[j][0]; ks_cur[j][1] = ks_nxt[j][1]; }
+      if (i + 1 < ntiles) fetch_scales(i + 1, ks_nxt);
       ok = mbar_wait(&full_bar[st], (i / C::STAGES) & 1, a.status);
       if (!ok) break;
       const uint32_t kbase = smem_u32(smem + st * C::STAGE_BYTES);
@@ -187,7 +203,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_split_kernel(const __grid_
           for (int e = 0; e < 2; ++e) {
             const int key = key0 + 8 * j + 2 * t + e;
             const bool valid = key < n1;
-            const float ks = valid ? __ldg(ks_row + key) : 0.f;
+            const float ks = ks_cur[j][e];
             sv[j][e] = valid ? (float)acc[j][e] * qs[0] * ks : -INFINITY;
             sv[j][2 + e] = valid ? (float)acc[j][2 + e] * qs[1] * ks : -INFINITY;
             tmax[0] = fmaxf(tmax[0], sv[j][e]);
