@@ -134,19 +134,24 @@ __global__ void __launch_bounds__(kQuantThreads) quant_rows_vec_kernel(QuantArgs
       const float t0 = __fdiv_rn(amax, a.ratio_threshold);
       const float t_lo = t0 * 0.999999f, t_hi = t0 * 1.000001f;
       int cnt = 0;
+      bool ambiguous = false;
 #pragma unroll
-      for (int v = 0; v < NV; ++v)
-        if (has[v]) {
+      for (int v = 0; v < NV; ++v) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float y = fabsf(f[v][i]) + 1e-10f;
-            if (y < t_lo) {
-              ++cnt;
-            } else if (y <= t_hi) {
-              cnt += (__fdiv_rn(amax, y) > a.ratio_threshold) ? 1 : 0;
-            }
-          }
+        for (int i = 0; i < 8; ++i) {
+          const float y = fabsf(f[v][i]) + 1e-10f;
+          cnt += (has[v] && y < t_lo) ? 1 : 0;
+          ambiguous |= has[v] && (y >= t_lo) && (y <= t_hi);
         }
+      }
+      if (ambiguous) {  // rare: redo this lane's count with the exact quotient
+        cnt = 0;
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            cnt += (has[v] && __fdiv_rn(amax, fabsf(f[v][i]) + 1e-10f) > a.ratio_threshold) ? 1 : 0;
+      }
 #pragma unroll
       for (int off = LPR / 2; off > 0; off >>= 1) cnt += __shfl_xor_sync(FULL, cnt, off);
       if (live && cnt >= rank_need) any_outlier = 1;
@@ -163,12 +168,17 @@ __global__ void __launch_bounds__(kQuantThreads) quant_rows_vec_kernel(QuantArgs
     for (int v = 0; v < NV; ++v) {
       if (!has[v]) continue;
       uint32_t tb[8];
+      bool redo = false;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const float t = fmaf(f[v][i], rcp, 12582912.0f);
         const float e = fmaf(f[v][i], rcp, -(t - 12582912.0f));
         tb[i] = __float_as_uint(t);
-        if (!(fabsf(e) < 0.49996f)) tb[i] = (uint32_t)(int)quant_one(f[v][i], s);
+        redo |= !(fabsf(e) < 0.49996f);
+      }
+      if (redo) {  // rare: some element sits next to a rounding boundary (or is NaN / inf)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) tb[i] = (uint32_t)(int)quant_one(f[v][i], s);
       }
       uint32_t w[2];
 #pragma unroll
