@@ -33,8 +33,13 @@ namespace {
 
 constexpr int kTM = 128;                               // query rows per block
 constexpr int kTN = 64;                                // keys per tile
-constexpr int kSoftmaxWarps = 4;                       // one query row per thread, rows = tensor-memory lanes
-constexpr int kProducerWarp = 4, kMmaWarp = 5;
+#ifndef SL8_HALVES
+#define SL8_HALVES 2
+#endif
+constexpr int kHalves = SL8_HALVES;                    // threads per query row (each owns kTN / kHalves columns)
+constexpr int kCT = kTN / kHalves;                     // S columns per softmax thread and tile
+constexpr int kSoftmaxWarps = 4 * kHalves;             // warps w and w + 4 share tensor-memory lanes [32 (w & 3), +32)
+constexpr int kProducerWarp = kSoftmaxWarps, kMmaWarp = kSoftmaxWarps + 1;
 constexpr int kTcThreads = 32 * (kSoftmaxWarps + 2);
 constexpr int kScaleStages = 4;                        // ring of k_scale tiles
 
@@ -58,7 +63,8 @@ struct TcCfg {
   static constexpr int OFF_K = OFF_Q + Q_TILE_BYTES;
   static constexpr int OFF_V = OFF_K + NKS * K_TILE_BYTES;
   static constexpr int OFF_KS = OFF_V + NVS * V_TILE_BYTES;   // kScaleStages x kTN floats
-  static constexpr int OFF_BAR = OFF_KS + kScaleStages * kTN * 4;
+  static constexpr int OFF_XCH = OFF_KS + kScaleStages * kTN * 4;   // 2 parities x kHalves x kTM floats
+  static constexpr int OFF_BAR = OFF_XCH + 2 * kHalves * kTM * 4;
   static constexpr int NEED = OFF_BAR + 512 + 1024;
   // never more than two blocks per SM: each holds TMEM_COLS columns of the 512
   static constexpr int SMEM = NEED < 78 * 1024 ? 78 * 1024 : NEED;
@@ -99,27 +105,38 @@ constexpr float kMagic = 12582912.0f;
 __device__ __forceinline__ float2 bits2(uint32_t a, uint32_t b) {
   return make_float2(__uint_as_float(a), __uint_as_float(b));
 }
+#ifdef SL8_SCALAR_MATH
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return make_float2(a.x * b.x, a.y * b.y); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
+#else
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+#endif
 
-// The kTN accumulator columns of this thread's row -> fp32 logits in place; returns the max.
+// NC accumulator columns of this thread's row -> fp32 logits in place; returns their max.
 // int8 mode: (float(acc) * qs) * ks[n] in the reference's multiply order; the int -> float
 // conversion is exact and runs on the ALU/FMA pipes (bit pattern of 1.5 * 2^23 plus the
 // integer, minus 1.5 * 2^23; |acc| <= 127 * 127 * 256 < 2^22), leaving the special-function
 // unit to the exponentials.  16-bit mode: acc * (softmax_scale * log2 e).
-template <bool QK8, bool MASK>
-__device__ __forceinline__ float logits_inplace(uint32_t (&r)[kTN], const float* __restrict__ ksv, float qs,
+template <bool QK8, bool MASK, int NC>
+__device__ __forceinline__ float logits_inplace(uint32_t (&r)[NC], const float* __restrict__ ksv, float qs,
                                                 int n_block, int n_len, int causal, int qpos, int window_left) {
   const float2 qs2 = make_float2(qs, qs);
   const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
   float mx0 = -INFINITY, mx1 = -INFINITY;
   const float2* ks2 = reinterpret_cast<const float2*>(ksv);
 #pragma unroll
-  for (int i = 0; i < kTN / 2; ++i) {
+  for (int i = 0; i < NC / 2; ++i) {
     float2 p;
     if (QK8) {
+#ifdef SL8_I2F
+      p = mul2(mul2(make_float2((float)(int)r[2 * i], (float)(int)r[2 * i + 1]), qs2), ks2[i]);
+#else
       p = bits2(r[2 * i] + kMagicBits, r[2 * i + 1] + kMagicBits);
-      p = __fmul2_rn(__fmul2_rn(__fadd2_rn(p, neg_magic2), qs2), ks2[i]);
+      p = mul2(mul2(add2(p, neg_magic2), qs2), ks2[i]);
+#endif
     } else {
-      p = __fmul2_rn(bits2(r[2 * i], r[2 * i + 1]), qs2);
+      p = mul2(bits2(r[2 * i], r[2 * i + 1]), qs2);
     }
     if (MASK) {
       const int gn = n_block + 2 * i;
@@ -144,6 +161,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* ks_smem = reinterpret_cast<float*>(smem + C::OFF_KS);
+  float* xch = reinterpret_cast<float*>(smem + C::OFF_XCH);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
 
@@ -230,16 +248,35 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
       if (ok && ntiles > 1) ok = load_k(1);
     }
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    // k_scale values travel three tiles ahead in registers, so the latency of their global
+    // loads never sits on the path of a tile.
+    auto fetch_ks = [&](int t, float (&dst)[kTN / 32]) {
+#pragma unroll
+      for (int i = 0; i < kTN / 32; ++i) {
+        const int n = n_begin + t * kTN + lane + 32 * i;
+        dst[i] = (QK8 && t < ntiles && n < n_len) ? __ldg(a.k_scale + (int64_t)kv_bh * a.N + n) : 0.f;
+      }
+    };
+    float ks0[kTN / 32], ks1[kTN / 32], ks2[kTN / 32];
+    fetch_ks(0, ks0);
+    fetch_ks(1, ks1);
+    fetch_ks(2, ks2);
     for (int j = 0; j < ntiles && ok; ++j) {
       const int n_block = n_begin + j * kTN;
-      float ksv[kTN / 32];
       if (QK8) {
-        // fetched first so that the latency of these loads overlaps the barrier waits below
+        // k_scale tile through the generic proxy (its start is not 16-byte aligned in general)
+        const int ss = j % kScaleStages;
+        if (j >= kScaleStages) ok = mbar_wait(&bars[KS_EMPTY + ss], ((j / kScaleStages) - 1) & 1, a.status);
+        if (!ok) break;
 #pragma unroll
         for (int i = 0; i < kTN / 32; ++i) {
-          const int n = n_block + lane + 32 * i;
-          ksv[i] = (n < n_len) ? __ldg(a.k_scale + (int64_t)kv_bh * a.N + n) : 0.f;
+          ks_smem[ss * kTN + lane + 32 * i] = ks0[i];
+          ks0[i] = ks1[i];
+          ks1[i] = ks2[i];
         }
+        fetch_ks(j + 3, ks2);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[KS_FULL + ss]);
       }
       if (lane == 0) {
         const int vs = j % C::NVS;
@@ -254,17 +291,6 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
         }
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) break;
-      if (QK8) {
-        // k_scale tile through the generic proxy (its start is not 16-byte aligned in general)
-        const int ss = j % kScaleStages;
-        if (j >= kScaleStages) ok = mbar_wait(&bars[KS_EMPTY + ss], ((j / kScaleStages) - 1) & 1, a.status);
-        if (!ok) break;
-#pragma unroll
-        for (int i = 0; i < kTN / 32; ++i) ks_smem[ss * kTN + lane + 32 * i] = ksv[i];
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[KS_FULL + ss]);
-      }
     }
   } else if (warp == kMmaWarp) {
     // ======================= MMA issuer =======================
@@ -286,8 +312,12 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
           const uint32_t sub = 32 * s / C::QROW, within = 32 * s % C::QROW;
           const uint64_t da = umma_smem_desc(q_u + sub * C::Q_SUB_BYTES + within, 16, 8 * C::QROW, C::QK_SW);
           const uint64_t db = umma_smem_desc(k_u + sub * C::K_SUB_BYTES + within, 16, 8 * C::QROW, C::QK_SW);
+#ifndef SL8_NOMMA
           if (QK8) tc_mma_i8_ss(tmem + C::COL_S + kTN * (t & 1), da, db, idesc_qk, s > 0 ? 1u : 0u);
           else tc_mma_f16_ss(tmem + C::COL_S + kTN * (t & 1), da, db, idesc_qk, s > 0 ? 1u : 0u);
+#else
+          (void)da; (void)db;
+#endif
         }
         tc_commit(&bars[K_EMPTY + ks]);
         tc_commit(&bars[S_FULL + (t & 1)]);
@@ -307,9 +337,13 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
         const uint32_t v_u = smem_u32(smem + C::OFF_V + vs * C::V_TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < kTN / 16; ++kk)
+#ifdef SL8_NOMMA
+          (void)v_u;
+#else
           tc_mma_f16_ts(tmem + C::COL_O, tmem + C::COL_S + kTN * (j & 1) + 8 * kk,
                         umma_smem_desc(v_u + kk * 2048, C::V_SUB_BYTES, 1024, kUmmaSw128), idesc_pv,
                         (j > 0 || kk > 0) ? 1u : 0u);
+#endif
         tc_commit(&bars[V_EMPTY + vs]);
         tc_commit(&bars[PV_DONE]);
         TR(4096 + 8 * j + 2);
@@ -320,10 +354,17 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
     }
   } else {
     // ======================= softmax / correction / epilogue =======================
-    const int m = m_block + 32 * warp + lane;  // this thread's query row
+    // Thread = (query row, column part): part h = warp >> 2 owns S columns [h kCT, (h + 1) kCT) of
+    // every tile and O columns [h D / kHalves, ...).  With two parts the row maxima and the final
+    // row sums cross between the two warps of a lane group through shared memory.
+    const int lg = warp & 3, h = warp >> 2;
+    const int row = 32 * lg + lane;
+    const int m = m_block + row;                // this thread's query row
     const float qs = QK8 ? ((m < m_len) ? __ldg(a.q_scale + bh * a.M + m) : 0.f) : a.scale_log2;
     const int qpos = m + causal_diag;
-    const uint32_t t_row = tmem + ((uint32_t)(32 * warp) << 16);
+    const uint32_t t_row = tmem + ((uint32_t)(32 * lg) << 16);
+    constexpr int OC = D / kHalves;             // O columns owned by this thread
+    const uint32_t t_o = t_row + C::COL_O + OC * h;
     float m_run = -INFINITY, l_run = 0.f;
 
     for (int j = 0; j < ntiles; ++j) {
@@ -336,22 +377,35 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
       if (!ok) break;
       tc_fence_after();
       if (warp == 0 && lane == 0) TR(8 * j + 1);
-      uint32_t r[kTN];
-      tc_ld32(t_s, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-      tc_ld32(t_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+      uint32_t r[kCT];
+#pragma unroll
+      for (int c = 0; c < kCT / 32; ++c) tc_ld32(t_s + kCT * h + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
       tc_wait_ld();
-      tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-      tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+#pragma unroll
+      for (int c = 0; c < kCT / 32; ++c) tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
       if (warp == 0 && lane == 0) TR(8 * j + 2);
-      const float* ksv = ks_smem + ss * kTN;
+      const float* ksv = ks_smem + ss * kTN + kCT * h;
       const bool need_mask = (n_block + kTN > n_len) || (a.causal && n_block + kTN - 1 > m_block + causal_diag) ||
                              (a.window_left >= 0 && n_block <= m_block + kTM - 1 + causal_diag - a.window_left);
-      const float tmax = need_mask ? logits_inplace<QK8, true>(r, ksv, qs, n_block, n_len, a.causal, qpos, a.window_left)
-                                   : logits_inplace<QK8, false>(r, ksv, qs, n_block, n_len, a.causal, qpos, a.window_left);
+#ifdef SL8_NOSOFTMAX
+      float tmax = 0.f; (void)need_mask; (void)ksv;
+#else
+      float tmax = need_mask ? logits_inplace<QK8, true, kCT>(r, ksv, qs, n_block + kCT * h, n_len, a.causal, qpos, a.window_left)
+                             : logits_inplace<QK8, false, kCT>(r, ksv, qs, n_block + kCT * h, n_len, a.causal, qpos, a.window_left);
+#endif
+      if (kHalves == 2) {
+        // full-row max: both parts have loaded their S columns before this barrier, so the P
+        // stores below (which overwrite S columns of the other part) cannot race with them
+        float* xm = xch + (j & 1) * (kHalves * kTM);
+        xm[h * kTM + row] = tmax;
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + lg) : "memory");
+        tmax = fmaxf(tmax, xm[(h ^ 1) * kTM + row]);
+      }
       if (warp == 0 && lane == 0) TR(8 * j + 3);
       // Lazy rescale: the running max moves only when some row of the warp outgrew it by
       // more than 2^8 (P then stays <= 256, harmless in fp16/bf16 and in the fp32 sum);
-      // out = O / l does not depend on which reference max was used.
+      // out = O / l does not depend on which reference max was used.  Both parts of a row see
+      // the same maxima and take the same decision.
       const bool grow = (m_run == -INFINITY) ? (tmax > -INFINITY) : (tmax > m_run + kLazyRescaleLog2);
       float resc = 1.f;
       if (__any_sync(0xffffffffu, grow)) {
@@ -365,9 +419,9 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
           tc_fence_after();
           const float2 resc2 = make_float2(resc, resc);
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
+          for (int c = 0; c < OC / 32; ++c) {
             uint32_t o[32];
-            tc_ld32(t_row + C::COL_O + 32 * c, o);
+            tc_ld32(t_o + 32 * c, o);
             tc_wait_ld();
             tc_regs_ready(o);
 #pragma unroll
@@ -376,28 +430,32 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
               o[2 * i] = __float_as_uint(t.x);
               o[2 * i + 1] = __float_as_uint(t.y);
             }
-            tc_st32(t_row + C::COL_O + 32 * c, o);
+            tc_st32(t_o + 32 * c, o);
           }
         }
       }
-      // ---- P = 2^(s - m), row sum, P -> tensor memory as 16-bit pairs over S's own columns ----
+      // ---- P = 2^(s - m), row sum, P -> tensor memory as 16-bit pairs over the buffer's first columns ----
       const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
       const float2 neg_m2 = make_float2(-m_use, -m_use);
       float2 sum_a = make_float2(0.f, 0.f), sum_b = sum_a;
 #pragma unroll
-      for (int c = 0; c < kTN / 32; ++c) {
+      for (int c = 0; c < kCT / 32; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float2 x = __fadd2_rn(bits2(r[32 * c + 2 * i], r[32 * c + 2 * i + 1]), neg_m2);
+          const float2 x = add2(bits2(r[32 * c + 2 * i], r[32 * c + 2 * i + 1]), neg_m2);
+#ifdef SL8_NOSOFTMAX
+          const float2 pr = x;
+#else
           const float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
-          if (i & 1) sum_b = __fadd2_rn(sum_b, pr);
-          else sum_a = __fadd2_rn(sum_a, pr);
+#endif
+          if (i & 1) sum_b = add2(sum_b, pr);
+          else sum_a = add2(sum_a, pr);
           pk[i] = pack2<VT>(pr.x, pr.y);
         }
-        tc_st16(t_s + 16 * c, pk);
+        tc_st16(t_s + (kCT / 2) * h + 16 * c, pk);
       }
-      const float2 st = __fadd2_rn(sum_a, sum_b);
+      const float2 st = add2(sum_a, sum_b);
       l_run = l_run * resc + (st.x + st.y);
       if (warp == 0 && lane == 0) TR(8 * j + 4);
       tc_wait_st();
@@ -413,16 +471,23 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
     if (ok) ok = mbar_wait(&bars[O_DONE], 0, a.status);
     if (ok) {
       tc_fence_after();
+      float l_tot = l_run;
+      if (kHalves == 2) {
+        float* xl = xch + (ntiles & 1) * (kHalves * kTM);
+        xl[h * kTM + row] = l_run;
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + lg) : "memory");
+        l_tot += xl[(h ^ 1) * kTM + row];
+      }
       const bool live = m < m_len;
-      const float inv = (live && l_run > 0.f) ? 1.f / l_run : 0.f;
+      const float inv = (live && l_tot > 0.f) ? 1.f / l_tot : 0.f;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < OC / 32; ++c) {
         uint32_t o[32];
-        tc_ld32(t_row + C::COL_O + 32 * c, o);
+        tc_ld32(t_o + 32 * c, o);
         tc_wait_ld();
         tc_regs_ready(o);
         if (m < a.M) {
-          uint4* dst = reinterpret_cast<uint4*>(out_bh + (int64_t)m * D + 32 * c);
+          uint4* dst = reinterpret_cast<uint4*>(out_bh + (int64_t)m * D + OC * h + 32 * c);
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             uint4 w;
@@ -434,8 +499,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
           }
         }
       }
-      if (a.lse != nullptr && m < a.M)
-        a.lse[bh * a.M + m] = (live && l_run > 0.f) ? (m_run * 0.6931471805599453f + logf(l_run)) : -INFINITY;
+      if (a.lse != nullptr && m < a.M && h == 0)
+        a.lse[bh * a.M + m] = (live && l_tot > 0.f) ? (m_run * 0.6931471805599453f + logf(l_tot)) : -INFINITY;
     }
     tc_fence_before();
   }
