@@ -34,7 +34,7 @@ namespace {
 constexpr int kTM = 128;                               // query rows per block
 constexpr int kTN = 64;                                // keys per tile
 #ifndef SL8_HALVES
-#define SL8_HALVES 2
+#define SL8_HALVES 1
 #endif
 constexpr int kHalves = SL8_HALVES;                    // threads per query row (each owns kTN / kHalves columns)
 constexpr int kCT = kTN / kHalves;                     // S columns per softmax thread and tile
@@ -99,56 +99,57 @@ __device__ long long g_trace[8192];
 #endif
 
 constexpr float kLazyRescaleLog2 = 8.0f;
-constexpr uint32_t kMagicBits = 0x4B400000u;   // 1.5 * 2^23 as float bits
-constexpr float kMagic = 12582912.0f;
 
 __device__ __forceinline__ float2 bits2(uint32_t a, uint32_t b) {
   return make_float2(__uint_as_float(a), __uint_as_float(b));
 }
-#ifdef SL8_SCALAR_MATH
-__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return make_float2(a.x * b.x, a.y * b.y); }
-__device__ __forceinline__ float2 add2(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
-#else
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
 __device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
-#endif
 
 // NC accumulator columns of this thread's row -> fp32 logits in place; returns their max.
-// int8 mode: (float(acc) * qs) * ks[n] in the reference's multiply order; the int -> float
-// conversion is exact and runs on the ALU/FMA pipes (bit pattern of 1.5 * 2^23 plus the
-// integer, minus 1.5 * 2^23; |acc| <= 127 * 127 * 256 < 2^22), leaving the special-function
-// unit to the exponentials.  16-bit mode: acc * (softmax_scale * log2 e).
+// int8 mode: (float(acc) * qs) * ks[n], the reference's conversion and multiply order
+// (csrc/include/attn_int8_fwd.cuh:137).  16-bit mode: acc * (softmax_scale * log2 e).
 template <bool QK8, bool MASK, int NC>
 __device__ __forceinline__ float logits_inplace(uint32_t (&r)[NC], const float* __restrict__ ksv, float qs,
                                                 int n_block, int n_len, int causal, int qpos, int window_left) {
   const float2 qs2 = make_float2(qs, qs);
-  const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
   float mx0 = -INFINITY, mx1 = -INFINITY;
   const float2* ks2 = reinterpret_cast<const float2*>(ksv);
+  constexpr int G = 8;   // pairs per software stage: independent work laid side by side
 #pragma unroll
-  for (int i = 0; i < NC / 2; ++i) {
-    float2 p;
+  for (int g0 = 0; g0 < NC / 2; g0 += G) {
+    float2 p[G];
+#pragma unroll
+    for (int u = 0; u < G; ++u) {
+      const int i = g0 + u;
+      p[u] = QK8 ? make_float2((float)(int)r[2 * i], (float)(int)r[2 * i + 1]) : bits2(r[2 * i], r[2 * i + 1]);
+    }
+#pragma unroll
+    for (int u = 0; u < G; ++u) p[u] = mul2(p[u], qs2);
     if (QK8) {
-#ifdef SL8_I2F
-      p = mul2(mul2(make_float2((float)(int)r[2 * i], (float)(int)r[2 * i + 1]), qs2), ks2[i]);
-#else
-      p = bits2(r[2 * i] + kMagicBits, r[2 * i + 1] + kMagicBits);
-      p = mul2(mul2(add2(p, neg_magic2), qs2), ks2[i]);
-#endif
-    } else {
-      p = mul2(bits2(r[2 * i], r[2 * i + 1]), qs2);
+#pragma unroll
+      for (int u = 0; u < G; ++u) p[u] = mul2(p[u], ks2[g0 + u]);
     }
     if (MASK) {
-      const int gn = n_block + 2 * i;
-      const bool v0 = (gn < n_len) && (!causal || gn <= qpos) && (window_left < 0 || gn > qpos - window_left);
-      const bool v1 = (gn + 1 < n_len) && (!causal || gn + 1 <= qpos) && (window_left < 0 || gn + 1 > qpos - window_left);
-      p.x = v0 ? p.x : -INFINITY;
-      p.y = v1 ? p.y : -INFINITY;
+#pragma unroll
+      for (int u = 0; u < G; ++u) {
+        const int gn = n_block + 2 * (g0 + u);
+        const bool v0 = (gn < n_len) && (!causal || gn <= qpos) && (window_left < 0 || gn > qpos - window_left);
+        const bool v1 = (gn + 1 < n_len) && (!causal || gn + 1 <= qpos) && (window_left < 0 || gn + 1 > qpos - window_left);
+        p[u].x = v0 ? p[u].x : -INFINITY;
+        p[u].y = v1 ? p[u].y : -INFINITY;
+      }
     }
-    if (i & 1) mx1 = max3f(mx1, p.x, p.y);
-    else mx0 = max3f(mx0, p.x, p.y);
-    r[2 * i] = __float_as_uint(p.x);
-    r[2 * i + 1] = __float_as_uint(p.y);
+#pragma unroll
+    for (int u = 0; u < G; u += 2) {
+      mx0 = max3f(mx0, p[u].x, p[u].y);
+      mx1 = max3f(mx1, p[u + 1].x, p[u + 1].y);
+    }
+#pragma unroll
+    for (int u = 0; u < G; ++u) {
+      r[2 * (g0 + u)] = __float_as_uint(p[u].x);
+      r[2 * (g0 + u) + 1] = __float_as_uint(p[u].y);
+    }
   }
   return fmaxf(mx0, mx1);
 }
@@ -312,12 +313,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
           const uint32_t sub = 32 * s / C::QROW, within = 32 * s % C::QROW;
           const uint64_t da = umma_smem_desc(q_u + sub * C::Q_SUB_BYTES + within, 16, 8 * C::QROW, C::QK_SW);
           const uint64_t db = umma_smem_desc(k_u + sub * C::K_SUB_BYTES + within, 16, 8 * C::QROW, C::QK_SW);
-#ifndef SL8_NOMMA
           if (QK8) tc_mma_i8_ss(tmem + C::COL_S + kTN * (t & 1), da, db, idesc_qk, s > 0 ? 1u : 0u);
           else tc_mma_f16_ss(tmem + C::COL_S + kTN * (t & 1), da, db, idesc_qk, s > 0 ? 1u : 0u);
-#else
-          (void)da; (void)db;
-#endif
         }
         tc_commit(&bars[K_EMPTY + ks]);
         tc_commit(&bars[S_FULL + (t & 1)]);
@@ -337,13 +334,9 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
         const uint32_t v_u = smem_u32(smem + C::OFF_V + vs * C::V_TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < kTN / 16; ++kk)
-#ifdef SL8_NOMMA
-          (void)v_u;
-#else
           tc_mma_f16_ts(tmem + C::COL_O, tmem + C::COL_S + kTN * (j & 1) + 8 * kk,
                         umma_smem_desc(v_u + kk * 2048, C::V_SUB_BYTES, 1024, kUmmaSw128), idesc_pv,
                         (j > 0 || kk > 0) ? 1u : 0u);
-#endif
         tc_commit(&bars[V_EMPTY + vs]);
         tc_commit(&bars[PV_DONE]);
         TR(4096 + 8 * j + 2);
@@ -387,12 +380,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
       const float* ksv = ks_smem + ss * kTN + kCT * h;
       const bool need_mask = (n_block + kTN > n_len) || (a.causal && n_block + kTN - 1 > m_block + causal_diag) ||
                              (a.window_left >= 0 && n_block <= m_block + kTM - 1 + causal_diag - a.window_left);
-#ifdef SL8_NOSOFTMAX
-      float tmax = 0.f; (void)need_mask; (void)ksv;
-#else
       float tmax = need_mask ? logits_inplace<QK8, true, kCT>(r, ksv, qs, n_block + kCT * h, n_len, a.causal, qpos, a.window_left)
                              : logits_inplace<QK8, false, kCT>(r, ksv, qs, n_block + kCT * h, n_len, a.causal, qpos, a.window_left);
-#endif
       if (kHalves == 2) {
         // full-row max: both parts have loaded their S columns before this barrier, so the P
         // stores below (which overwrite S columns of the other part) cannot race with them
@@ -442,16 +431,19 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
       for (int c = 0; c < kCT / 32; ++c) {
         uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float2 x = add2(bits2(r[32 * c + 2 * i], r[32 * c + 2 * i + 1]), neg_m2);
-#ifdef SL8_NOSOFTMAX
-          const float2 pr = x;
-#else
-          const float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
-#endif
-          if (i & 1) sum_b = add2(sum_b, pr);
-          else sum_a = add2(sum_a, pr);
-          pk[i] = pack2<VT>(pr.x, pr.y);
+        for (int g0 = 0; g0 < 16; g0 += 8) {
+          float2 x[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) x[u] = add2(bits2(r[32 * c + 2 * (g0 + u)], r[32 * c + 2 * (g0 + u) + 1]), neg_m2);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) x[u] = make_float2(ex2_approx(x[u].x), ex2_approx(x[u].y));
+#pragma unroll
+          for (int u = 0; u < 8; u += 2) {
+            sum_a = add2(sum_a, x[u]);
+            sum_b = add2(sum_b, x[u + 1]);
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) pk[g0 + u] = pack2<VT>(x[u].x, x[u].y);
         }
         tc_st16(t_s + (kCT / 2) * h + 16 * c, pk);
       }
