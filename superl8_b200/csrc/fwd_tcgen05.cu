@@ -1,25 +1,33 @@
-// Prefill forward on the Blackwell tensor-core path: TMA-staged int8 Q/K tiles,
-// S = Q.K^T as tcgen05.mma kind::i8 with an int32 accumulator in tensor memory,
-// fp32 online softmax on the CUDA cores, O += P.V as tcgen05.mma kind::f16 with P
-// read from tensor memory and V from shared memory.
+// Prefill forward on the Blackwell tensor-core path: TMA-staged Q/K/V tiles,
+// S = Q.K^T as tcgen05.mma (kind::i8 with an int32 accumulator for the int8 path,
+// kind::f16 for the full-precision sibling the accuracy gate demotes to) into tensor
+// memory, fp32 online softmax on the CUDA cores, O += P.V as tcgen05.mma kind::f16
+// with P read from tensor memory and V from shared memory.
 //
-// Mathematics are the reference's (csrc/include/attn_int8_fwd.cuh:107-208):
-//   s = float(int32 q.k) * q_scale[m] * k_scale[n]            (that multiply order)
+// Mathematics are the reference's (csrc/include/attn_int8_fwd.cuh:107-208 and
+// csrc/include/attn_fp16_fwd.cuh:89-230):
+//   int8:   s = float(int32 q.k) * q_scale[m] * k_scale[n]     (that multiply order)
+//   16-bit: s = (q.k) * softmax_scale * log2(e)
 //   valid = n < N and (not causal or n <= m + N - M) and (window < 0 or n > pos - window)
 //   online softmax in the exp2 domain (fp32 m, l), out = O / l (0 if l == 0),
 //   lse = m * ln2 + ln l.
-// Differences a caller can observe only inside the tolerance: tiles are 128 x 128
-// (reference 64 x 64) and P is rounded to V's dtype before P.V (reference fp32).
+// Differences a caller can observe only inside the tolerance: tiles are 128 x 64
+// (reference 64 x 64), the running max moves lazily (only when a row outgrows it by
+// more than 2^8; out = O / l does not depend on it), and P is rounded to V's dtype
+// before P.V (reference fp32).
 //
 // Block = one 128-row query tile of one (batch, query head).  Six warps:
 //   warps 0-3  softmax + correction + epilogue; warp w owns tensor-memory lanes
 //              [32w, 32w+32) = query rows, one row per thread (no shuffles);
-//   warp 4     producer: TMA loads of Q, K, V tiles (3-D tensor maps, 128-byte
-//              swizzle, zero fill past the end of a head) and the k_scale tile;
-//   warp 5     allocates tensor memory and issues every MMA from one thread.
-// Tensor memory: S (int32, later fp32 logits, then P as packed 16-bit pairs in its
-// first 64 columns) at columns [0,128), O (fp32) at [128, 128 + D).  Two blocks
-// share an SM, so one block's softmax overlaps the other's MMAs.
+//   warp 4     producer: TMA loads of Q, K (three stages, two tiles ahead), V (two
+//              stages) -- 3-D tensor maps, 128-byte swizzle, zero fill past the end
+//              of a head -- and the k_scale tiles (ring of four, three tiles ahead);
+//   warp 5     allocates tensor memory and issues every MMA from one thread, in the
+//              order QK_0, QK_1, then for each tile j: P.V_j, QK_{j+2}.
+// Tensor memory (256 columns): S in two buffers of 64 columns (the logits of the next
+// tile are ready while the softmax warps work on this one); P overwrites the first 32
+// columns of its own S buffer as packed 16-bit pairs; O (fp32) at [128, 128 + D).
+// Two blocks share an SM, so one block's softmax overlaps the other's MMAs.
 // Every mbarrier wait is bounded (sl8_common.cuh); on expiry the block raises the
 // workspace status word, frees tensor memory and exits.
 #include "sl8_common.cuh"
@@ -33,6 +41,8 @@ namespace {
 
 constexpr int kTM = 128;                               // query rows per block
 constexpr int kTN = 64;                                // keys per tile
+// Threads per query row.  2 puts eight softmax warps on a block (two column halves that
+// exchange row maxima through shared memory); measured 5 % slower than 1 on B200.
 #ifndef SL8_HALVES
 #define SL8_HALVES 1
 #endif
