@@ -333,6 +333,9 @@ def main():
         hout.copy_(out, non_blocking=True)
         return out
 
+    # measured tensor-pipe peaks (back-to-back tcgen05.mma on constant operands, burst clocks)
+    probe_i8, probe_f16 = _C.tensor_peak(True, 8192), _C.tensor_peak(False, 8192)
+
     out = step()
     demoted = s8.ops.last_gate_decision
     dominant = "attn_fp16_fwd" if demoted else "attn_int8_fwd"
@@ -369,6 +372,8 @@ def main():
         return {"bound": "tensor", "kernel": note, "achieved": ach, "peak": peak, "unit": "TFLOP/s",
                 "frac": ach / peak, "peak_source": peaks["source"] + " bf16 dense (sustained)",
                 "frac_of_burst_bf16": ach / peaks["bf16_tflops"], "frac_of_nominal_int8": ach / NOMINAL_INT8_TOPS,
+                "frac_of_probed_int8": ach / probe_i8, "frac_of_probed_f16": ach / probe_f16,
+                "frac_of_probed_mixed_ceiling": ach / (1.0 / (0.5 / probe_i8 + 0.5 / probe_f16)),
                 "traffic": NCU_TRAFFIC[key] * cfg.B, "ms_per_launch": kernel_ms}
 
     roofline = tensor_roofline(kern_ms, dominant + (" (gate demoted the call)" if demoted else ""), dominant)
@@ -378,6 +383,8 @@ def main():
         "dtype": "f16" if demoted else "s8", "data": "synthetic", "config": workload_config(cfg, args, world),
         "gate_demoted": bool(demoted), "device_status": status, "e2e": e2e, "gpu_launches": gpu_launches,
         "clocks": clocks, "roofline": roofline,
+        "tensor_peak_probe": {"int8_tops": probe_i8, "f16_tflops": probe_f16,
+                              "how": "sl8_tensor_peak_probe: 148 blocks x 8192 x 4 tcgen05.mma M128 N256, constant operands"},
     }
 
     if not args.skip_extras:

@@ -229,6 +229,16 @@ int sl8_attn_int8_decode(const sl8_decode_params* p, void* workspace, size_t wor
 #define SL8_DECODE_STATIC_SCRATCH_BYTES (32u << 20)
 int sl8_attn_int8_decode_static(const sl8_decode_params* p, int32_t* device_status, void* stream);
 
+/*
+ * Tensor-pipe peak probe: one block per SM issues `iters` x 4 back-to-back tcgen05.mma
+ * (M128 N256, 32-byte K step; kind::i8 if kind_i8 != 0, else kind::f16 on fp16) on constant
+ * shared-memory operands.  *ops_per_launch (host, nullable) receives the operation count
+ * (2 x MACs) of the launch; time the launch with events to get the sustained peak that
+ * "fraction of INT8 peak" is quoted against.  No counterpart in the reference.
+ */
+int sl8_tensor_peak_probe(int kind_i8, int iters, double* ops_per_launch, void* workspace,
+                          size_t workspace_bytes, void* stream);
+
 /* Synchronises the stream and returns the device status word of a workspace
  * (SL8_OK or SL8_ERR_DEVICE_TIMEOUT); clears it. */
 int sl8_read_device_status(void* workspace, void* stream);

@@ -148,6 +148,26 @@ def qk_logits_i32(q_i8: torch.Tensor, k_i8: torch.Tensor) -> torch.Tensor:
     return s
 
 
+def tensor_peak(kind_i8: bool, iters: int = 4096, device=None) -> float:
+    """Measured tensor-pipe peak in T(FL)OP/s for kind::i8 (or kind::f16): times the probe launch
+    with CUDA events after one warm-up launch."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    lib = _lib.load()
+    ops = C.c_double(0.0)
+    with torch.cuda.device(device):
+        ws = _status_buffer(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for i in range(2):
+            if i == 1:
+                e0.record()
+            rc = lib.sl8_tensor_peak_probe(int(bool(kind_i8)), int(iters), C.byref(ops), _ptr(ws), ws.numel() * 4,
+                                           _stream(device))
+            _lib.check(rc, "tensor_peak_probe", 1)
+        e1.record()
+        torch.cuda.synchronize(device)
+    return ops.value / (e0.elapsed_time(e1) * 1e-3) / 1e12
+
+
 def attn_fp16_fwd(q, k, v, causal=False, scale=None, window_left=-1, mask=None, *, seqlens_q=None, seqlens_k=None,
                   backend=_lib.SL8_BACKEND_AUTO):
     """Full-precision forward.  Reference binding csrc/fni8_api.cpp:234-244."""

@@ -704,3 +704,75 @@ extern "C" int sl8_dbg_read_trace(long long* host_out, int n) {
   return (int)cudaMemcpyFromSymbol(host_out, sl8::g_trace, sizeof(long long) * n);
 }
 #endif
+
+// ---- tensor-pipe peak probe ---------------------------------------------------------------
+// Back-to-back tcgen05.mma (M128 N256, K = 32 bytes) on shared-memory operands that never
+// change: no softmax, no loads in the loop.  Measures what the tensor pipe sustains for
+// kind::i8 and kind::f16 on this GPU, the denominator for "fraction of INT8 peak".
+namespace sl8 {
+namespace {
+template <bool I8>
+__global__ void __launch_bounds__(128) tensor_peak_kernel(int iters, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int A_BYTES = 128 * 128, B_BYTES = 256 * 128;
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem + A_BYTES + B_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+  for (int i = threadIdx.x; i < (A_BYTES + B_BYTES) / 4; i += 128)
+    reinterpret_cast<uint32_t*>(smem)[i] = I8 ? (0x01fe02ffu * (i + 1)) : 0x3c003c00u;  // small ints / fp16 ones
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    mbar_fence_init();
+  }
+  fence_proxy_async_smem();
+  if (threadIdx.x < 32) {
+    tc_alloc(tmem_slot, 512);
+    tc_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  if (threadIdx.x == 0) {
+    const uint32_t idesc = I8 ? umma_idesc(2, 1, 1, 0, 0, 128, 256) : umma_idesc(1, 0, 0, 0, 0, 128, 256);
+    const uint32_t a_u = smem_u32(smem), b_u = smem_u32(smem + A_BYTES);
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const uint64_t da = umma_smem_desc(a_u + 32 * s, 16, 1024, kUmmaSw128);
+        const uint64_t db = umma_smem_desc(b_u + 32 * s, 16, 1024, kUmmaSw128);
+        if (I8) tc_mma_i8_ss(tmem + 256 * (it & 1), da, db, idesc, s > 0 ? 1u : 0u);
+        else tc_mma_f16_ss(tmem + 256 * (it & 1), da, db, idesc, s > 0 ? 1u : 0u);
+      }
+    }
+    tc_commit(bar);
+  }
+  mbar_wait(bar, 0, status);
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    tc_fence_after();
+    tc_dealloc(tmem, 512);
+  }
+}
+}  // namespace
+}  // namespace sl8
+
+extern "C" int sl8_tensor_peak_probe(int kind_i8, int iters, double* ops_per_launch, void* workspace,
+                                     size_t workspace_bytes, void* stream) {
+  if (iters <= 0 || iters > (1 << 20)) return SL8_ERR_BAD_SHAPE;
+  if (workspace == nullptr || workspace_bytes < 256) return SL8_ERR_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int smem = 128 * 128 + 256 * 128 + 1024 + 64;
+  const int grid = kNumSms;
+  // K per instruction: 32 int8 or 16 halves (both 32 bytes)
+  if (ops_per_launch) *ops_per_launch = 2.0 * 128 * 256 * (kind_i8 ? 32 : 16) * 4.0 * iters * grid;
+  if (kind_i8) {
+    SL8_CUDA_TRY(cudaFuncSetAttribute(tensor_peak_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    tensor_peak_kernel<true><<<grid, 128, smem, s>>>(iters, reinterpret_cast<int*>(workspace));
+  } else {
+    SL8_CUDA_TRY(cudaFuncSetAttribute(tensor_peak_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    tensor_peak_kernel<false><<<grid, 128, smem, s>>>(iters, reinterpret_cast<int*>(workspace));
+  }
+  return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
+}

@@ -247,3 +247,10 @@ def test_full_size_properties_cfg2(device):
     # first query row attends only key 0 -> equals v[0]
     assert torch.allclose(oa[:, :, 0].cpu(), v1.float().repeat_interleave(4, 1)[:, :, 0].cpu(), atol=2e-3)
     assert _C.device_status() == 0
+
+
+def test_tensor_peak_probe_runs(device):
+    i8 = _C.tensor_peak(True, 512)
+    f16 = _C.tensor_peak(False, 512)
+    assert _C.device_status() == 0
+    assert i8 > f16 > 100.0          # int8 issues at twice the fp16 rate; both far above any CUDA-core figure
