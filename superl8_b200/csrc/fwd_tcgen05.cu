@@ -19,9 +19,10 @@
 // Block = one 128-row query tile of one (batch, query head).  Six warps:
 //   warps 0-3  softmax + correction + epilogue; warp w owns tensor-memory lanes
 //              [32w, 32w+32) = query rows, one row per thread (no shuffles);
-//   warp 4     producer: TMA loads of Q, K (three stages, two tiles ahead), V (two
-//              stages) -- 3-D tensor maps, 128-byte swizzle, zero fill past the end
-//              of a head -- and the k_scale tiles (ring of four, three tiles ahead);
+//   warp 4     producer: TMA loads of Q, K and V (two stages each, K two tiles ahead;
+//              the barriers the issuer commits behind QK_t and P.V_j also free the K
+//              and V stages) -- 3-D tensor maps, 128-byte swizzle, zero fill past the
+//              end of a head -- and the k_scale tiles (ring of four, three tiles ahead);
 //   warp 5     allocates tensor memory and issues every MMA from one thread, in the
 //              order QK_0, QK_1, then for each tile j: P.V_j, QK_{j+2}.
 // Tensor memory (256 columns): S in two buffers of 64 columns (the logits of the next
@@ -67,7 +68,7 @@ struct TcCfg {
   static constexpr int VSUBS = 2 * D / 128;               // 64-channel sub-tiles of kTN keys x 128 B
   static constexpr int V_SUB_BYTES = kTN * 128;
   static constexpr int V_TILE_BYTES = kTN * 2 * D;
-  static constexpr int NKS = QK8 ? 3 : 2;
+  static constexpr int NKS = 2;                            // K stages = S buffers (one barrier frees both)
   static constexpr int NVS = 2;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_TILE_BYTES;
@@ -96,8 +97,10 @@ struct TcArgs {
 };
 
 enum Bar {
-  Q_FULL = 0, O_DONE, PV_DONE, S_FULL, P_FULL = S_FULL + 2, K_FULL = P_FULL + 2, K_EMPTY = K_FULL + 3,
-  V_FULL = K_EMPTY + 3, V_EMPTY = V_FULL + 2, KS_FULL = V_EMPTY + 2, KS_EMPTY = KS_FULL + kScaleStages,
+  // S_FULL[b] (commit behind QK_t, b = t & 1) also tells the producer that K stage b is free;
+  // PV_DONE[b] (commit behind P.V_j, b = j & 1) also tells it that V stage b is free.
+  Q_FULL = 0, O_DONE, PV_DONE, S_FULL = PV_DONE + 2, P_FULL = S_FULL + 2, K_FULL = P_FULL + 2,
+  V_FULL = K_FULL + 2, KS_FULL = V_FULL + 2, KS_EMPTY = KS_FULL + kScaleStages,
   NUM_BARS = KS_EMPTY + kScaleStages
 };
 
@@ -125,7 +128,10 @@ __device__ __forceinline__ float logits_inplace(uint32_t (&r)[NC], const float* 
   const float2 qs2 = make_float2(qs, qs);
   float mx0 = -INFINITY, mx1 = -INFINITY;
   const float2* ks2 = reinterpret_cast<const float2*>(ksv);
-  constexpr int G = 8;   // pairs per software stage: independent work laid side by side
+#ifndef SL8_STAGE
+#define SL8_STAGE 8
+#endif
+  constexpr int G = SL8_STAGE < NC / 2 ? SL8_STAGE : NC / 2;   // pairs per software stage: independent work side by side
 #pragma unroll
   for (int g0 = 0; g0 < NC / 2; g0 += G) {
     float2 p[G];
@@ -204,16 +210,12 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
   if (threadIdx.x == 0) {
     mbar_init(&bars[Q_FULL], 1);
     mbar_init(&bars[O_DONE], 1);
-    mbar_init(&bars[PV_DONE], 1);
     for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars[PV_DONE + i], 1);
       mbar_init(&bars[S_FULL + i], 1);
       mbar_init(&bars[P_FULL + i], kSoftmaxWarps);
       mbar_init(&bars[V_FULL + i], 1);
-      mbar_init(&bars[V_EMPTY + i], 1);
-    }
-    for (int i = 0; i < 3; ++i) {
       mbar_init(&bars[K_FULL + i], 1);
-      mbar_init(&bars[K_EMPTY + i], 1);
     }
     for (int i = 0; i < kScaleStages; ++i) {
       mbar_init(&bars[KS_FULL + i], 1);
@@ -245,7 +247,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
     }
     auto load_k = [&](int t) -> bool {   // lane 0 only
       const int ks = t % C::NKS;
-      if (t >= C::NKS && !mbar_wait(&bars[K_EMPTY + ks], ((t / C::NKS) - 1) & 1, a.status)) return false;
+      if (t >= C::NKS && !mbar_wait(&bars[S_FULL + ks], ((t / C::NKS) - 1) & 1, a.status)) return false;
       mbar_expect_tx(&bars[K_FULL + ks], C::K_TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < C::QSUBS; ++c)
@@ -292,7 +294,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
       if (lane == 0) {
         const int vs = j % C::NVS;
         if (j + 2 < ntiles) ok = load_k(j + 2);
-        if (ok && j >= C::NVS) ok = mbar_wait(&bars[V_EMPTY + vs], ((j / C::NVS) - 1) & 1, a.status);
+        if (ok && j >= C::NVS) ok = mbar_wait(&bars[PV_DONE + vs], ((j / C::NVS) - 1) & 1, a.status);
         if (ok) {
           mbar_expect_tx(&bars[V_FULL + vs], C::V_TILE_BYTES);
 #pragma unroll
@@ -326,7 +328,6 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
           if (QK8) tc_mma_i8_ss(tmem + C::COL_S + kTN * (t & 1), da, db, idesc_qk, s > 0 ? 1u : 0u);
           else tc_mma_f16_ss(tmem + C::COL_S + kTN * (t & 1), da, db, idesc_qk, s > 0 ? 1u : 0u);
         }
-        tc_commit(&bars[K_EMPTY + ks]);
         tc_commit(&bars[S_FULL + (t & 1)]);
         return true;
       };
@@ -347,8 +348,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
           tc_mma_f16_ts(tmem + C::COL_O, tmem + C::COL_S + kTN * (j & 1) + 8 * kk,
                         umma_smem_desc(v_u + kk * 2048, C::V_SUB_BYTES, 1024, kUmmaSw128), idesc_pv,
                         (j > 0 || kk > 0) ? 1u : 0u);
-        tc_commit(&bars[V_EMPTY + vs]);
-        tc_commit(&bars[PV_DONE]);
+        tc_commit(&bars[PV_DONE + (j & 1)]);
         TR(4096 + 8 * j + 2);
         if (j + 2 < ntiles) ok = issue_qk(j + 2);
         TR(4096 + 8 * j + 3);
@@ -413,7 +413,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
         m_run = m_new;
         if (j > 0) {
           // correction: O *= resc once the previous tile's P.V has landed in O
-          ok = mbar_wait(&bars[PV_DONE], (j - 1) & 1, a.status);
+          ok = mbar_wait(&bars[PV_DONE + ((j - 1) & 1)], ((j - 1) >> 1) & 1, a.status);
           if (!ok) break;
           tc_fence_after();
           const float2 resc2 = make_float2(resc, resc);
@@ -440,20 +440,24 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
 #pragma unroll
       for (int c = 0; c < kCT / 32; ++c) {
         uint32_t pk[16];
+#ifndef SL8_STAGE2
+#define SL8_STAGE2 8
+#endif
+        constexpr int G2 = SL8_STAGE2;
 #pragma unroll
-        for (int g0 = 0; g0 < 16; g0 += 8) {
-          float2 x[8];
+        for (int g0 = 0; g0 < 16; g0 += G2) {
+          float2 x[G2];
 #pragma unroll
-          for (int u = 0; u < 8; ++u) x[u] = add2(bits2(r[32 * c + 2 * (g0 + u)], r[32 * c + 2 * (g0 + u) + 1]), neg_m2);
+          for (int u = 0; u < G2; ++u) x[u] = add2(bits2(r[32 * c + 2 * (g0 + u)], r[32 * c + 2 * (g0 + u) + 1]), neg_m2);
 #pragma unroll
-          for (int u = 0; u < 8; ++u) x[u] = make_float2(ex2_approx(x[u].x), ex2_approx(x[u].y));
+          for (int u = 0; u < G2; ++u) x[u] = make_float2(ex2_approx(x[u].x), ex2_approx(x[u].y));
 #pragma unroll
-          for (int u = 0; u < 8; u += 2) {
+          for (int u = 0; u < G2; u += 2) {
             sum_a = add2(sum_a, x[u]);
             sum_b = add2(sum_b, x[u + 1]);
           }
 #pragma unroll
-          for (int u = 0; u < 8; ++u) pk[g0 + u] = pack2<VT>(x[u].x, x[u].y);
+          for (int u = 0; u < G2; ++u) pk[g0 + u] = pack2<VT>(x[u].x, x[u].y);
         }
         tc_st16(t_s + (kCT / 2) * h + 16 * c, pk);
       }
