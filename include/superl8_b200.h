@@ -158,6 +158,11 @@ typedef struct sl8_fp16_fwd_params {
   int32_t dtype; int32_t causal; int32_t window_left;
   float softmax_scale;
   int32_t backend;        /* SL8_BACKEND_* (tcgen05 for D = 64/128/256, else mma.sync) */
+  /* optional additive bias [B|1, H|1, M, N] in natural-log units, element type = dtype, indexed in
+   * place through element strides (0 on broadcast axes); served by the mma.sync kernel
+   * (reference csrc/kernel/attn_fp16_fwd.cu:146-168) */
+  const void* mask;
+  int64_t mask_stride_b, mask_stride_h, mask_stride_m, mask_stride_n;
 } sl8_fp16_fwd_params;
 size_t sl8_attn_fp16_fwd_workspace(const sl8_fp16_fwd_params* p);
 int sl8_attn_fp16_fwd(const sl8_fp16_fwd_params* p, void* workspace, size_t workspace_bytes,

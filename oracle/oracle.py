@@ -5,9 +5,9 @@ import this module; the product (``superl8_b200``) never does and has no CPU pat
 
 Parity status: PINNED.  ``tests/test_oracle_golden.py`` checks every function here
 against vectors produced by importing the reference's own Python code
-(``tests/golden/make_golden.py`` -> ``tests/golden/*.npz``), and on a GPU box
-``tests/test_ref_kernels.py`` checks the kernel restatements against the reference's
-own CUDA kernels compiled from its sources (``oracle/_ref``).
+(``tests/golden/make_golden.py`` -> ``tests/golden/*.npz``), and on a GPU box the
+``-m gpu`` tests compare this repository's kernels with the reference's own CUDA kernels
+compiled from its sources (``oracle/_ref``, helpers in ``tests/gpu_helpers.py``).
 
 Two scale rules exist in the reference and both are restated:
   rule="cpu"   scale = amax / 127        (reference CPU branch, superl8/quant/core.py:58)
@@ -108,14 +108,18 @@ def _expand_kv(kf, vf, h_q):
     return kf, vf
 
 
-def attention_fp32(q, k, v, causal: bool = False, scale: float | None = None, window_left: int = -1):
+def attention_fp32(q, k, v, causal: bool = False, scale: float | None = None, window_left: int = -1, mask=None):
     """Reference tests/reference.py:26-54 (and :57-86 for the window): naive fp32 attention,
-    GQA by repeat_interleave, bottom-right aligned causal mask."""
+    GQA by repeat_interleave, bottom-right aligned causal mask.  ``mask``: additive natural-log
+    bias broadcastable to [B, H, M, N], added to the scaled logits (the semantics of the
+    reference's attn_fp16_fwd, csrc/include/attn_fp16_fwd.cuh:176-178)."""
     qf, kf, vf = (t.detach().cpu().float() for t in (q, k, v))
     kf, vf = _expand_kv(kf, vf, qf.shape[1])
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     s = torch.einsum("bhmd,bhnd->bhmn", qf, kf) * scale
+    if mask is not None:
+        s = s + mask.detach().cpu().float()
     m_len, n_len = s.shape[-2], s.shape[-1]
     if window_left >= 0:
         row = torch.arange(m_len).view(-1, 1)

@@ -176,11 +176,20 @@ def attn_fp16_fwd(q, k, v, causal=False, scale=None, window_left=-1, mask=None, 
     _check(q.dtype in (torch.float16, torch.bfloat16), f"{what}: q must be float16 or bfloat16")
     _check(k.dtype == q.dtype and v.dtype == q.dtype, f"{what}: q, k, v must share one dtype")
     _check(q.dim() == 4 and k.dim() == 4 and v.dim() == 4, f"{what}: expect [B,H,S,D]")
-    if mask is not None:
-        raise NotImplementedError("superl8_b200 attn_fp16_fwd: additive masks are not implemented")
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     B, H, M, D = q.shape
     Hkv, N = k.shape[1], k.shape[2]
+    mk = dict(mask=None, mask_stride_b=0, mask_stride_h=0, mask_stride_m=0, mask_stride_n=0)
+    if mask is not None:
+        _check(mask.is_cuda and mask.device == q.device, f"{what}: mask must be a CUDA tensor on q's device")
+        _check(mask.dtype == q.dtype, f"{what}: mask dtype must match q/k/v")
+        _check(mask.dim() == 4, f"{what}: mask must be 4-D [B|1, H|1, M, N]")
+        _check(mask.shape[2] == M and mask.shape[3] == N, f"{what}: mask trailing dims must be [M,N]")
+        _check(mask.shape[0] in (B, 1) and mask.shape[1] in (H, 1), f"{what}: mask leading dims must broadcast to [B,H]")
+        # indexed in place: a broadcast [B,1,M,N] view is never expanded (zero stride on size-1 axes)
+        mk = dict(mask=mask.data_ptr(), mask_stride_b=0 if mask.shape[0] == 1 else mask.stride(0),
+                  mask_stride_h=0 if mask.shape[1] == 1 else mask.stride(1),
+                  mask_stride_m=mask.stride(2), mask_stride_n=mask.stride(3))
     _check(k.shape[0] == B and v.shape[0] == B and v.shape[1] == Hkv, f"{what}: batch/head mismatch")
     _check(Hkv > 0 and H % Hkv == 0, f"{what}: H_q must be divisible by H_kv (GQA)")
     _check(k.shape[3] == D and v.shape[3] == D and v.shape[2] == N, f"{what}: K/V shape mismatch")
@@ -194,7 +203,7 @@ def attn_fp16_fwd(q, k, v, causal=False, scale=None, window_left=-1, mask=None, 
         seqlens_q=None if seqlens_q is None else seqlens_q.data_ptr(),
         seqlens_k=None if seqlens_k is None else seqlens_k.data_ptr(),
         B=B, Hq=H, Hkv=Hkv, M=M, N=N, D=D, dtype=_DTYPE[q.dtype], causal=int(bool(causal)),
-        window_left=int(window_left), softmax_scale=sc, backend=int(backend))
+        window_left=int(window_left), softmax_scale=sc, backend=int(backend), **mk)
     with torch.cuda.device(q.device):
         ws = _status_buffer(q.device)
         rc = _lib.load().sl8_attn_fp16_fwd(C.byref(p), _ptr(ws), ws.numel() * 4, _stream(q.device))

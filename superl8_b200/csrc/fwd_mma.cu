@@ -32,6 +32,8 @@ struct FwdArgs {
   int Hq, Hkv, M, N;
   int causal, window_left;
   float scale_log2;     // 16-bit mode
+  const void* mask;     // 16-bit mode: additive bias (natural log), element type of q, or null
+  int64_t mask_sb, mask_sh, mask_sm, mask_sn;   // strides in elements, 0 on broadcast axes
 };
 
 template <int D, bool I8>
@@ -190,6 +192,12 @@ __global__ void __launch_bounds__(kThreads) fwd_mma_kernel(FwdArgs a) {
           const bool valid = (gn < n_len) && (!a.causal || gn <= qpos[h]) &&
                              (a.window_left < 0 || gn > qpos[h] - a.window_left);
           float& x = sv_f[j][2 * h + e];
+          if (!I8 && a.mask != nullptr && valid && row0 + 8 * h < m_len) {
+            // reference csrc/include/attn_fp16_fwd.cuh:176-178: natural-log bias, log2(e) folded in
+            const int64_t mi_ = (int64_t)b * a.mask_sb + (bh % a.Hq) * a.mask_sh + (int64_t)(row0 + 8 * h) * a.mask_sm +
+                                (int64_t)gn * a.mask_sn;
+            x += to_f32<VT>(reinterpret_cast<const VT*>(a.mask)[mi_]) * 1.4426950408889634f;
+          }
           x = valid ? x : -INFINITY;
           tmax[h] = fmaxf(tmax[h], x);
         }
@@ -314,7 +322,7 @@ extern "C" int sl8_attn_fp16_fwd(const sl8_fp16_fwd_params* p, void* workspace, 
   if (!p->q || !p->out || (p->N > 0 && (!p->k || !p->v))) return SL8_ERR_NULL;
   if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->out)) return SL8_ERR_MISALIGNED;
   if ((int64_t)p->B * p->Hq > 65535) return SL8_ERR_TOO_LARGE;
-  const bool tc_ok = (p->D == 64 || p->D == 128 || p->D == 256) && p->N > 0;
+  const bool tc_ok = (p->D == 64 || p->D == 128 || p->D == 256) && p->N > 0 && p->mask == nullptr;
   int backend = p->backend;
   if (backend == SL8_BACKEND_AUTO) backend = tc_ok ? SL8_BACKEND_TCGEN05 : SL8_BACKEND_MMA;
   if (backend == SL8_BACKEND_TCGEN05) {
@@ -328,6 +336,8 @@ extern "C" int sl8_attn_fp16_fwd(const sl8_fp16_fwd_params* p, void* workspace, 
   a.seqlens_q = p->seqlens_q; a.seqlens_k = p->seqlens_k;
   a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N; a.causal = p->causal; a.window_left = p->window_left;
   a.scale_log2 = p->softmax_scale * 1.4426950408889634f;
+  a.mask = p->mask; a.mask_sb = p->mask_stride_b; a.mask_sh = p->mask_stride_h;
+  a.mask_sm = p->mask_stride_m; a.mask_sn = p->mask_stride_n;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (p->dtype == SL8_F16) return launch_d<__half, false>(a, p->B, p->D, s);
   return launch_d<__nv_bfloat16, false>(a, p->B, p->D, s);

@@ -254,3 +254,26 @@ def test_tensor_peak_probe_runs(device):
     f16 = _C.tensor_peak(False, 512)
     assert _C.device_status() == 0
     assert i8 > f16 > 100.0          # int8 issues at twice the fp16 rate; both far above any CUDA-core figure
+
+
+@pytest.mark.parametrize("D,dtype", [(128, torch.float16), (64, torch.bfloat16), (80, torch.float16)])
+def test_fp16_fwd_additive_mask(D, dtype, device):
+    B, Hq, Hkv, M, N = 2, 4, 2, 150, 200
+    q, k, v = oracle.make_batch(48, B, Hq, Hkv, M, D, Sk=N, dtype=dtype)
+    g = torch.Generator().manual_seed(9)
+    tol = 5e-3 if dtype == torch.float16 else 2e-2
+    for shape in ((B, 1, M, N), (1, Hq, M, N), (1, 1, M, N), (B, Hq, M, N)):
+        bias = (torch.randn(*shape, generator=g) * 2.0).to(dtype)
+        bias[..., ::7, 3::11] = float("-inf")                # some keys hidden from some rows
+        for causal in (False, True):
+            out = _C.attn_fp16_fwd(q.to(device), k.to(device), v.to(device), causal, None, -1, bias.to(device))
+            ref = oracle.attention_fp32(q, k, v, causal=causal, mask=bias)
+            assert oracle.cos_sim(out, ref) >= 0.9999 and oracle.rel_l1(out, ref) <= tol, (shape, causal)
+    # a broadcast VIEW is indexed in place through its strides
+    base = (torch.randn(B, 1, M, N, generator=g)).to(dtype).to(device)
+    view = base.expand(B, Hq, M, N)
+    out = s8.attn_fp16_fwd(q.to(device), k.to(device), v.to(device), mask=view)
+    ref = oracle.attention_fp32(q, k, v, mask=base.cpu())
+    assert oracle.cos_sim(out, ref) >= 0.9999
+    with pytest.raises(RuntimeError, match="mask"):
+        _C.attn_fp16_fwd(q.to(device), k.to(device), v.to(device), False, None, -1, base[:, :, :, :5])
