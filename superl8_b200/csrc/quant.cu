@@ -65,6 +65,28 @@ template <> struct Vec8<__nv_bfloat16> {
   }
 };
 
+// Packed fp16 evaluation of the outlier statistic (see the call site for the argument).
+template <typename T> __device__ __forceinline__ bool half_gate_ok(float, float) { return false; }
+template <> __device__ __forceinline__ bool half_gate_ok<__half>(float t0, float amax) {
+  return t0 >= 0.0078125f && amax <= 65504.0f;   // 2^-7 <= max / thr, finite row
+}
+template <int NV>
+__device__ __forceinline__ int half_gate_count(const uint4 (&raw)[NV], const bool (&has)[NV], float t0, float amax,
+                                               float thr) {
+  __half h = __float2half_rd(t0);
+  if (!(__fdiv_rn(amax, __half2float(h) + 1e-10f) > thr)) h = __ushort_as_half((unsigned short)(__half_as_ushort(h) - 1));
+  const __half2 hstar = __half2half2(h);
+  __half2 cnt2 = __float2half2_rn(0.f);
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    if (!has[v]) continue;
+    const __half2* x2 = reinterpret_cast<const __half2*>(&raw[v]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) cnt2 = __hadd2(cnt2, __hle2(__habs2(x2[i]), hstar));
+  }
+  return (int)(__low2float(cnt2) + __high2float(cnt2));
+}
+
 // LPR lanes own one row; each lane holds NV vectors of 8 elements.
 template <typename T, int LPR, int NV, int MODE>
 __global__ void __launch_bounds__(kQuantThreads) quant_rows_vec_kernel(QuantArgs a) {
@@ -85,14 +107,15 @@ __global__ void __launch_bounds__(kQuantThreads) quant_rows_vec_kernel(QuantArgs
     const bool live = row < a.rows;
     const T* xr = reinterpret_cast<const T*>(a.x) + row * a.K;
     float f[NV][8];
+    uint4 raw[NV];
     bool has[NV];
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
       const int vi = sl + v * LPR;
       has[v] = live && vi < kvec;
-      uint4 u = make_uint4(0, 0, 0, 0);
-      if (has[v]) u = __ldg(reinterpret_cast<const uint4*>(xr) + vi);
-      Vec8<T>::unpack(u, f[v]);
+      raw[v] = make_uint4(0, 0, 0, 0);
+      if (has[v]) raw[v] = __ldg(reinterpret_cast<const uint4*>(xr) + vi);
+      Vec8<T>::unpack(raw[v], f[v]);
     }
     if (MODE == kKeySmooth) {
       const int64_t bh = live ? row / a.rows_per_head : 0;
@@ -132,8 +155,18 @@ __global__ void __launch_bounds__(kQuantThreads) quant_rows_vec_kernel(QuantArgs
       // y = |e| + 1e-10 is clearly below / above max / thr are decided by a comparison; only
       // the few inside a 1e-6 relative band take the exactly rounded division.
       const float t0 = __fdiv_rn(amax, a.ratio_threshold);
-      const float t_lo = t0 * 0.999999f, t_hi = t0 * 1.000001f;
       int cnt = 0;
+      if (half_gate_ok<T>(t0, amax)) {
+        // fp16 input: every element is an fp16 number, so the condition is |e| <= h*, with h* the
+        // largest fp16 value that still satisfies it.  h* is RD_fp16(max / thr) or its fp16
+        // predecessor: fp16 neighbours are 2^13 fp32 ulps apart, so every fp16 value below
+        // RD_fp16(t0) satisfies the condition, every one above t0 fails it, and only RD_fp16(t0)
+        // itself needs the exactly rounded quotient.  (|e| + 1e-10 == |e| in fp32 for
+        // |e| >= 2^-9, and smaller elements satisfy the condition either way because
+        // t0 >= 2^-7.)  Two divisions per row, then three packed instructions per element pair.
+        cnt = half_gate_count<NV>(raw, has, t0, amax, a.ratio_threshold);
+      } else {
+      const float t_lo = t0 * 0.999999f, t_hi = t0 * 1.000001f;
       bool ambiguous = false;
 #pragma unroll
       for (int v = 0; v < NV; ++v) {
@@ -151,6 +184,7 @@ __global__ void __launch_bounds__(kQuantThreads) quant_rows_vec_kernel(QuantArgs
 #pragma unroll
           for (int i = 0; i < 8; ++i)
             cnt += (has[v] && __fdiv_rn(amax, fabsf(f[v][i]) + 1e-10f) > a.ratio_threshold) ? 1 : 0;
+      }
       }
 #pragma unroll
       for (int off = LPR / 2; off > 0; off >>= 1) cnt += __shfl_xor_sync(FULL, cnt, off);
@@ -276,11 +310,14 @@ int launch_2byte(const QuantArgs& a, cudaStream_t s) {
   const int kvec = a.K / 8;
   const bool vec_ok = (a.K % 8 == 0) && aligned16(a.x) && (reinterpret_cast<uintptr_t>(a.q) % 8 == 0) &&
                       (MODE != kKeySmooth || (aligned16(a.mean) && (a.smoothed == nullptr || aligned16(a.smoothed))));
-  if (vec_ok && kvec <= 4) launch_vec<T, MODE, 4, 1>(a, s);
-  else if (vec_ok && kvec <= 8) launch_vec<T, MODE, 8, 1>(a, s);
-  else if (vec_ok && kvec <= 16) launch_vec<T, MODE, 16, 1>(a, s);
-  else if (vec_ok && kvec <= 32) launch_vec<T, MODE, 32, 1>(a, s);
-  else if (vec_ok && kvec <= 64) launch_vec<T, MODE, 32, 2>(a, s);
+  // lanes per row x vectors per lane: four 16-byte vectors per lane amortise the per-row work
+  // (reductions, scale, reciprocal, threshold) over 32 elements
+  if (vec_ok && kvec <= 4) launch_vec<T, MODE, 2, 2>(a, s);
+  else if (vec_ok && kvec <= 8) launch_vec<T, MODE, 2, 4>(a, s);
+  else if (vec_ok && kvec <= 12) launch_vec<T, MODE, 4, 3>(a, s);
+  else if (vec_ok && kvec <= 16) launch_vec<T, MODE, 4, 4>(a, s);
+  else if (vec_ok && kvec <= 32) launch_vec<T, MODE, 8, 4>(a, s);
+  else if (vec_ok && kvec <= 64) launch_vec<T, MODE, 16, 4>(a, s);
   else if (vec_ok && kvec <= 128) launch_vec<T, MODE, 32, 4>(a, s);
   else
     quant_rows_generic_kernel<T, MODE><<<grid_for(a.rows, kQuantThreads / 32), kQuantThreads, 0, s>>>(a);

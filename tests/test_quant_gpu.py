@@ -146,3 +146,39 @@ def test_quantize_qk_matches_oracle_given_mean(device):
     assert torch.equal(k_i8.cpu(), ko) and torch.equal(k_scale.cpu(), kso)
     k_s, mean2 = s8.smooth_k(k.to(device))
     assert k_s.shape == k.shape and mean2.shape == (1, 2, 1, 64)
+
+
+def test_gate_exact_at_the_threshold_boundary(device):
+    """Rows whose lower median sits on fp16 neighbours of max/12: the fused statistic (packed
+    fp16 path for max/12 >= 2^-7, fp32 path below) must agree with the reference formula row by row."""
+    g = torch.Generator().manual_seed(123)
+    rows = []
+    for amax in [1.0, 3.0, 12.0, 0.75, 100.0, 0.05, 0.011, 6.0e-4, 65504.0, 7.3, 0.0947, 0.0937]:
+        a16 = torch.tensor(amax).half()
+        c0 = (a16.float() / 12.0).half()
+        for step in range(-4, 5):
+            c = torch.tensor(c0.view(torch.int16).item() + step, dtype=torch.int16).view(torch.float16)
+            row = torch.empty(128, dtype=torch.float16)
+            row[:64] = c                       # 64 smallest -> the lower median is c
+            row[64:127] = (a16.float() * 0.5).half()
+            row[127] = a16
+            sign = torch.where(torch.rand(128, generator=g) < 0.5, -1.0, 1.0).half()
+            rows.append((row * sign)[torch.randperm(128, generator=g)])
+    q = torch.stack(rows)
+    expect = oracle.outlier_rows(q)
+    assert bool(expect.any()) and not bool(expect.all())
+    neg = q[~expect]
+    assert s8.detect_q_outlier_domination(neg.view(1, 1, -1, 128).contiguous().to(device)) is False
+    for r in q[expect]:
+        assert s8.detect_q_outlier_domination(r.view(1, 1, 1, 128).contiguous().to(device)) is True
+    # one positive row hidden among many negative ones still trips the any-row flag
+    mixed = torch.cat([neg, q[expect][:1], neg])
+    assert s8.detect_q_outlier_domination(mixed.view(1, 1, -1, 128).contiguous().to(device)) is True
+    # other head dims use other lane layouts
+    for D in (64, 256, 80):
+        x = torch.randn(3000, D, generator=g).half()
+        x[::97, 0] *= 9.0
+        e = oracle.outlier_rows(x)
+        for lo in range(0, 3000, 500):
+            blk = x[lo:lo + 500]
+            assert s8.detect_q_outlier_domination(blk.view(1, 1, -1, D).contiguous().to(device)) == bool(e[lo:lo + 500].any())
