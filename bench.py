@@ -49,9 +49,15 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs.
 
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    nvidia-smi needs a few hundred ms before its first sample, so it is started before the warm-up
+    (start() returns once the first sample is on disk) and every sample carries its timestamp;
+    stop() keeps the samples that fall inside the wall-clock window of the timed region.  When
+    that window is shorter than the sampling can resolve, the samples of warm-up + timed region
+    (the same kernels, back to back) are used and the record says so."""
+
+    FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -59,6 +65,7 @@ class ClockSampler:
         self.gpu = gpu_index
         self.proc = None
         self.path = None
+        self.t_begin = self.t_end = None
 
     def start(self):
         try:
@@ -67,37 +74,66 @@ class ClockSampler:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+            deadline = time.time() + 5.0
+            while time.time() < deadline and os.path.getsize(self.path) == 0:
+                time.sleep(0.02)
         except Exception:
             self.proc = None
+
+    def mark_begin(self):
+        self.t_begin = time.time()
+
+    def mark_end(self):
+        self.t_end = time.time()
+
+    @staticmethod
+    def _epoch(stamp: str):
+        import datetime
+        try:
+            return datetime.datetime.strptime(stamp, "%Y/%m/%d %H:%M:%S.%f").timestamp()
+        except ValueError:
+            return None
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
             return out
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        rows = []
         try:
             for line in open(self.path):
                 f = [x.strip() for x in line.split(",")]
-                if len(f) < 9:
+                if len(f) < 10:
                     continue
                 try:
-                    sm.append(float(f[1]))
-                    mx.append(float(f[2]))
+                    rows.append((self._epoch(f[0]), float(f[2]), float(f[3]), float(f[4]), f[6:10]))
                 except ValueError:
                     continue
-                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
             os.unlink(self.path)
         except Exception:
             pass
-        if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        inside = [r for r in rows if r[0] is not None and self.t_begin is not None and self.t_end is not None
+                  and self.t_begin <= r[0] <= self.t_end]
+        window = "timed region"
+        if len(inside) < 3:
+            # the region is shorter than three sampling periods: use warm-up + timed region, and of
+            # those only the samples taken under load (power well above idle)
+            inside = [r for r in rows if r[3] > 400.0] or rows
+            window = "warm-up + timed region (timed region shorter than three samples)"
+        if inside:
+            reasons = set()
+            for r in inside:
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            out.update(sm_mhz=statistics.median([r[1] for r in inside]), sm_max_mhz=max(r[2] for r in inside),
+                       power_w=statistics.median([r[3] for r in inside]), reasons=sorted(reasons),
+                       samples=len(inside), window=window)
         return out
 
 
@@ -108,7 +144,7 @@ def dist_setup(n_gpus: int):
     return rank, world, local
 
 
-def timed(fn, steps: int, warmup: int, world: int, before=None):
+def timed(fn, steps: int, warmup: int, world: int, before=None, after=None):
     """W untimed steps, then exactly K steps between barrier + synchronize; CUDA events on the
     launching stream; MAX over ranks.  Returns ms per step."""
     import torch.distributed as dist
@@ -126,6 +162,8 @@ def timed(fn, steps: int, warmup: int, world: int, before=None):
         fn()
     e1.record()
     torch.cuda.synchronize()
+    if after is not None:
+        after()
     if world > 1:
         dist.barrier()
     from superl8_b200 import shard
@@ -340,6 +378,8 @@ def main():
     demoted = s8.ops.last_gate_decision
     dominant = "attn_fp16_fwd" if demoted else "attn_int8_fwd"
     sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     with KernelTimer(_C, dominant) as kt:
         launches0 = [0]
 
@@ -347,9 +387,8 @@ def main():
             kt.enabled = True
             kt.events.clear()
             launches0[0] = _lib.launches
-            if rank == 0:
-                sampler.start()
-        ms = timed(step, args.steps, args.warmup, world, before=before)
+            sampler.mark_begin()
+        ms = timed(step, args.steps, args.warmup, world, before=before, after=sampler.mark_end)
         kt.enabled = False
         gpu_launches = _lib.launches - launches0[0]
         clocks = sampler.stop() if rank == 0 else {}

@@ -322,7 +322,9 @@ extern "C" int sl8_attn_fp16_fwd(const sl8_fp16_fwd_params* p, void* workspace, 
   if (!p->q || !p->out || (p->N > 0 && (!p->k || !p->v))) return SL8_ERR_NULL;
   if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->out)) return SL8_ERR_MISALIGNED;
   if ((int64_t)p->B * p->Hq > 65535) return SL8_ERR_TOO_LARGE;
-  const bool tc_ok = (p->D == 64 || p->D == 128 || p->D == 256) && p->N > 0 && p->mask == nullptr;
+  // the tensor-memory kernel takes the row maximum before scaling, so it wants a scale >= 0
+  const bool tc_ok = (p->D == 64 || p->D == 128 || p->D == 256) && p->N > 0 && p->mask == nullptr &&
+                     p->softmax_scale >= 0.f;
   int backend = p->backend;
   if (backend == SL8_BACKEND_AUTO) backend = tc_ok ? SL8_BACKEND_TCGEN05 : SL8_BACKEND_MMA;
   if (backend == SL8_BACKEND_TCGEN05) {

@@ -12,19 +12,28 @@
 //   online softmax in the exp2 domain (fp32 m, l), out = O / l (0 if l == 0),
 //   lse = m * ln2 + ln l.
 // Differences a caller can observe only inside the tolerance: tiles are 128 x 64
-// (reference 64 x 64), the running max moves lazily (only when a row outgrows it by
-// more than 2^8; out = O / l does not depend on it), and P is rounded to V's dtype
-// before P.V (reference fp32).
+// (reference 64 x 64); the running max moves lazily (only when a row outgrows it by
+// more than 2^8; out = O / l does not depend on it); P is rounded to V's dtype before
+// P.V (reference fp32); the int8 logit is (float(acc) * k_scale) * q_scale (reference:
+// q_scale first), so that scale and max subtraction are one fused multiply-add.
 //
 // Block = one 128-row query tile of one (batch, query head).  Six warps:
 //   warps 0-3  softmax + correction + epilogue; warp w owns tensor-memory lanes
-//              [32w, 32w+32) = query rows, one row per thread (no shuffles);
+//              [32w, 32w+32) = query rows, one row per thread (no shuffles).  A tile is
+//              one sweep over its 64 columns (softmax_pass): conversion, max, exponent
+//              and 2^x of neighbouring column groups are interleaved by hand, P is formed
+//              against the running max while the tile's own max is still being collected,
+//              and only when the max has to move (first tile, rarely later) is O corrected
+//              and P formed again;
 //   warp 4     producer: TMA loads of Q, K and V (two stages each, K two tiles ahead;
 //              the barriers the issuer commits behind QK_t and P.V_j also free the K
 //              and V stages) -- 3-D tensor maps, 128-byte swizzle, zero fill past the
 //              end of a head -- and the k_scale tiles (ring of four, three tiles ahead);
-//   warp 5     allocates tensor memory and issues every MMA from one thread, in the
-//              order QK_0, QK_1, then for each tile j: P.V_j, QK_{j+2}.
+//              its arrival for a k_scale tile goes to the same barrier as the commit of
+//              that tile's QK, so the softmax warps wait once per tile;
+//   warp 5     allocates tensor memory; the whole warp walks the issue loop and polls the
+//              barriers, one elected lane issues the MMAs and commits, in the order
+//              QK_0, QK_1, then for each tile j: P.V_j, QK_{j+2}.
 // Tensor memory (256 columns): S in two buffers of 64 columns (the logits of the next
 // tile are ready while the softmax warps work on this one); P overwrites the first 32
 // columns of its own S buffer as packed 16-bit pairs; O (fp32) at [128, 128 + D).
@@ -42,14 +51,7 @@ namespace {
 
 constexpr int kTM = 128;                               // query rows per block
 constexpr int kTN = 64;                                // keys per tile
-// Threads per query row.  2 puts eight softmax warps on a block (two column halves that
-// exchange row maxima through shared memory); measured 5 % slower than 1 on B200.
-#ifndef SL8_HALVES
-#define SL8_HALVES 1
-#endif
-constexpr int kHalves = SL8_HALVES;                    // threads per query row (each owns kTN / kHalves columns)
-constexpr int kCT = kTN / kHalves;                     // S columns per softmax thread and tile
-constexpr int kSoftmaxWarps = 4 * kHalves;             // warps w and w + 4 share tensor-memory lanes [32 (w & 3), +32)
+constexpr int kSoftmaxWarps = 4;                       // warp w owns tensor-memory lanes [32 w, 32 w + 32)
 constexpr int kProducerWarp = kSoftmaxWarps, kMmaWarp = kSoftmaxWarps + 1;
 constexpr int kTcThreads = 32 * (kSoftmaxWarps + 2);
 constexpr int kScaleStages = 4;                        // ring of k_scale tiles
@@ -74,8 +76,7 @@ struct TcCfg {
   static constexpr int OFF_K = OFF_Q + Q_TILE_BYTES;
   static constexpr int OFF_V = OFF_K + NKS * K_TILE_BYTES;
   static constexpr int OFF_KS = OFF_V + NVS * V_TILE_BYTES;   // kScaleStages x kTN floats
-  static constexpr int OFF_XCH = OFF_KS + kScaleStages * kTN * 4;   // 2 parities x kHalves x kTM floats
-  static constexpr int OFF_BAR = OFF_XCH + 2 * kHalves * kTM * 4;
+  static constexpr int OFF_BAR = OFF_KS + kScaleStages * kTN * 4;
   static constexpr int NEED = OFF_BAR + 512 + 1024;
   // never more than two blocks per SM: each holds TMEM_COLS columns of the 512
   static constexpr int SMEM = NEED < 78 * 1024 ? 78 * 1024 : NEED;
@@ -97,11 +98,11 @@ struct TcArgs {
 };
 
 enum Bar {
-  // S_FULL[b] (commit behind QK_t, b = t & 1) also tells the producer that K stage b is free;
+  // S_FULL[b] (commit behind QK_t, b = t & 1; in int8 mode a second arrival says that the tile's
+  // k_scale values are in shared memory) also tells the producer that K stage b is free;
   // PV_DONE[b] (commit behind P.V_j, b = j & 1) also tells it that V stage b is free.
   Q_FULL = 0, O_DONE, PV_DONE, S_FULL = PV_DONE + 2, P_FULL = S_FULL + 2, K_FULL = P_FULL + 2,
-  V_FULL = K_FULL + 2, KS_FULL = V_FULL + 2, KS_EMPTY = KS_FULL + kScaleStages,
-  NUM_BARS = KS_EMPTY + kScaleStages
+  V_FULL = K_FULL + 2, KS_EMPTY = V_FULL + 2, NUM_BARS = KS_EMPTY + kScaleStages
 };
 
 #ifdef SL8_TRACE
@@ -113,61 +114,95 @@ __device__ long long g_trace[8192];
 
 constexpr float kLazyRescaleLog2 = 8.0f;
 
+
 __device__ __forceinline__ float2 bits2(uint32_t a, uint32_t b) {
   return make_float2(__uint_as_float(a), __uint_as_float(b));
 }
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
 __device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
 
-// NC accumulator columns of this thread's row -> fp32 logits in place; returns their max.
-// int8 mode: (float(acc) * qs) * ks[n], the reference's conversion and multiply order
-// (csrc/include/attn_int8_fwd.cuh:137).  16-bit mode: acc * (softmax_scale * log2 e).
-template <bool QK8, bool MASK, int NC>
-__device__ __forceinline__ float logits_inplace(uint32_t (&r)[NC], const float* __restrict__ ksv, float qs,
-                                                int n_block, int n_len, int causal, int qpos, int window_left) {
-  const float2 qs2 = make_float2(qs, qs);
-  float mx0 = -INFINITY, mx1 = -INFINITY;
+// One streaming pass over the kTN columns of this thread's row:
+//   FIRST: r holds the accumulators.  int8 mode: t = float(acc) * k_scale[n]; 16-bit mode: t = acc.
+//          MASK = false leaves t in r (the exponent is then fma(t, qs, -m): scale and max
+//          subtraction in one instruction per pair); MASK = true (tiles on the diagonal, the
+//          window edge or the tail) leaves the finished logits t * qs, -inf where masked (xs = 1).
+//          The maximum of what is left in r is tracked (the caller scales it by qs >= 0).
+//          The reference multiplies (float(acc) * q_scale) * k_scale
+//          (csrc/include/attn_int8_fwd.cuh:137); the two orders differ by fp32 rounding only.
+//   both:  P = 2^(r * xs - m) goes to tensor memory as 16-bit pairs over the first kTN / 2 columns
+//          of the S buffer, and its fp32 row sum is returned.
+// The sweep is software-pipelined by hand, in groups of G pairs: the ex2 of group g are issued,
+// then the conversion / scaling / max of group g + 1 (work for the FMA and ALU pipes that does
+// not depend on them), and only then the sums and the packing of group g.  A warp issues in
+// order, so this is what lets the special-function unit run while the other pipes work.
+template <bool QK8, bool MASK, bool FIRST, typename VT>
+__device__ __forceinline__ void softmax_pass(uint32_t (&r)[kTN], const float* __restrict__ ksv, float qs, float xs,
+                                             float neg_m, int n_block, int n_len, int causal, int qpos,
+                                             int window_left, uint32_t t_p, float& mx, float& sum) {
+  const float2 qs2 = make_float2(qs, qs), xs2 = make_float2(xs, xs), neg_m2 = make_float2(neg_m, neg_m);
   const float2* ks2 = reinterpret_cast<const float2*>(ksv);
-#ifndef SL8_STAGE
-#define SL8_STAGE 8
-#endif
-  constexpr int G = SL8_STAGE < NC / 2 ? SL8_STAGE : NC / 2;   // pairs per software stage: independent work side by side
-#pragma unroll
-  for (int g0 = 0; g0 < NC / 2; g0 += G) {
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+  float2 sum_a = make_float2(0.f, 0.f), sum_b = sum_a;
+  constexpr int G = 4;                 // pairs per group
+  constexpr int NG = kTN / 2 / G;      // groups per row
+  float2 x[2][G];
+  uint32_t pk[16];
+  // exponent arguments of group g -> x[g & 1]
+  auto prep = [&](int g, float2 (&xo)[G]) {
     float2 p[G];
 #pragma unroll
     for (int u = 0; u < G; ++u) {
-      const int i = g0 + u;
-      p[u] = QK8 ? make_float2((float)(int)r[2 * i], (float)(int)r[2 * i + 1]) : bits2(r[2 * i], r[2 * i + 1]);
+      const int i = g * G + u;
+      if (FIRST && QK8) p[u] = mul2(make_float2((float)(int)r[2 * i], (float)(int)r[2 * i + 1]), ks2[i]);
+      else p[u] = bits2(r[2 * i], r[2 * i + 1]);
     }
-#pragma unroll
-    for (int u = 0; u < G; ++u) p[u] = mul2(p[u], qs2);
-    if (QK8) {
-#pragma unroll
-      for (int u = 0; u < G; ++u) p[u] = mul2(p[u], ks2[g0 + u]);
-    }
-    if (MASK) {
+    if (FIRST && MASK) {
 #pragma unroll
       for (int u = 0; u < G; ++u) {
-        const int gn = n_block + 2 * (g0 + u);
+        p[u] = mul2(p[u], qs2);
+        const int gn = n_block + 2 * (g * G + u);
         const bool v0 = (gn < n_len) && (!causal || gn <= qpos) && (window_left < 0 || gn > qpos - window_left);
         const bool v1 = (gn + 1 < n_len) && (!causal || gn + 1 <= qpos) && (window_left < 0 || gn + 1 > qpos - window_left);
         p[u].x = v0 ? p[u].x : -INFINITY;
         p[u].y = v1 ? p[u].y : -INFINITY;
       }
     }
+    if (FIRST) {
+#pragma unroll
+      for (int u = 0; u < G; u += 2) {
+        mx0 = max3f(mx0, p[u].x, p[u].y);
+        mx1 = max3f(mx1, p[u + 1].x, p[u + 1].y);
+      }
+      if (QK8 || MASK) {
+#pragma unroll
+        for (int u = 0; u < G; ++u) {
+          r[2 * (g * G + u)] = __float_as_uint(p[u].x);
+          r[2 * (g * G + u) + 1] = __float_as_uint(p[u].y);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < G; ++u) xo[u] = __ffma2_rn(p[u], xs2, neg_m2);
+  };
+  prep(0, x[0]);
+#pragma unroll
+  for (int g = 0; g < NG; ++g) {
+    float2(&xc)[G] = x[g & 1];
+#pragma unroll
+    for (int u = 0; u < G; ++u) xc[u] = make_float2(ex2_issue(xc[u].x), ex2_issue(xc[u].y));
+    if (g + 1 < NG) prep(g + 1, x[(g + 1) & 1]);
 #pragma unroll
     for (int u = 0; u < G; u += 2) {
-      mx0 = max3f(mx0, p[u].x, p[u].y);
-      mx1 = max3f(mx1, p[u + 1].x, p[u + 1].y);
+      sum_a = add2(sum_a, xc[u]);
+      sum_b = add2(sum_b, xc[u + 1]);
     }
 #pragma unroll
-    for (int u = 0; u < G; ++u) {
-      r[2 * (g0 + u)] = __float_as_uint(p[u].x);
-      r[2 * (g0 + u) + 1] = __float_as_uint(p[u].y);
-    }
+    for (int u = 0; u < G; ++u) pk[(g * G + u) & 15] = pack2<VT>(xc[u].x, xc[u].y);
+    if (((g + 1) * G) % 16 == 0) tc_st16(t_p + 16 * (((g + 1) * G) / 16 - 1), pk);
   }
-  return fmaxf(mx0, mx1);
+  const float2 st = add2(sum_a, sum_b);
+  sum = st.x + st.y;
+  mx = fmaxf(mx0, mx1);
 }
 
 template <int D, typename VT, bool QK8>
@@ -178,7 +213,6 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* ks_smem = reinterpret_cast<float*>(smem + C::OFF_KS);
-  float* xch = reinterpret_cast<float*>(smem + C::OFF_XCH);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
 
@@ -212,13 +246,12 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
     mbar_init(&bars[O_DONE], 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[PV_DONE + i], 1);
-      mbar_init(&bars[S_FULL + i], 1);
+      mbar_init(&bars[S_FULL + i], QK8 ? 2 : 1);   // int8: the MMA commit and the k_scale tile
       mbar_init(&bars[P_FULL + i], kSoftmaxWarps);
       mbar_init(&bars[V_FULL + i], 1);
       mbar_init(&bars[K_FULL + i], 1);
     }
     for (int i = 0; i < kScaleStages; ++i) {
-      mbar_init(&bars[KS_FULL + i], 1);
       mbar_init(&bars[KS_EMPTY + i], kSoftmaxWarps);
     }
     mbar_fence_init();
@@ -289,7 +322,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
         }
         fetch_ks(j + 3, ks2);
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[KS_FULL + ss]);
+        if (lane == 0) mbar_arrive(&bars[S_FULL + (j & 1)]);
       }
       if (lane == 0) {
         const int vs = j % C::NVS;
@@ -310,64 +343,74 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
     // Order of issue: QK_0, QK_1, then for every tile j: P.V_j, QK_{j+2}.  S has two buffers, so
     // the next tile's logits are already in tensor memory while the softmax warps work on
     // this one; QK_{j+2} reuses the buffer whose P the (earlier issued) P.V_j reads.
-    if (lane == 0) {
-      constexpr uint32_t vfmt = std::is_same<VT, __nv_bfloat16>::value ? 1u : 0u;
-      const uint32_t idesc_qk = QK8 ? umma_idesc(2, 1, 1, 0, 0, kTM, kTN) : umma_idesc(1, vfmt, vfmt, 0, 0, kTM, kTN);
-      const uint32_t idesc_pv = umma_idesc(1, vfmt, vfmt, 0, 1, kTM, D);
-      const uint32_t q_u = smem_u32(smem + C::OFF_Q);
-      auto issue_qk = [&](int t) -> bool {
-        const int ks = t % C::NKS;
-        if (!mbar_wait(&bars[K_FULL + ks], (t / C::NKS) & 1, a.status)) return false;
-        tc_fence_after();
-        const uint32_t k_u = smem_u32(smem + C::OFF_K + ks * C::K_TILE_BYTES);
+    // The whole warp walks the loop and polls the barriers (warp-uniform control flow and
+    // addresses); one elected lane issues the MMAs and commits.  Descriptors are built once:
+    // per MMA only the start-address field of a descriptor moves.
+    constexpr uint32_t vfmt = std::is_same<VT, __nv_bfloat16>::value ? 1u : 0u;
+    const uint32_t idesc_qk = QK8 ? umma_idesc(2, 1, 1, 0, 0, kTM, kTN) : umma_idesc(1, vfmt, vfmt, 0, 0, kTM, kTN);
+    const uint32_t idesc_pv = umma_idesc(1, vfmt, vfmt, 0, 1, kTM, D);
+    const uint64_t dq = umma_smem_desc(smem_u32(smem + C::OFF_Q), 16, 8 * C::QROW, C::QK_SW);
+    const uint64_t dk = umma_smem_desc(smem_u32(smem + C::OFF_K), 16, 8 * C::QROW, C::QK_SW);
+    const uint64_t dv = umma_smem_desc(smem_u32(smem + C::OFF_V), C::V_SUB_BYTES, 1024, kUmmaSw128);
+    auto issue_qk = [&](int t, int buf) -> bool {   // buf = t & 1 = K stage = S buffer
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars[K_FULL + buf], (t >> 1) & 1, a.status))) return false;
+      tc_fence_after();
+      if (elect_one()) {
 #pragma unroll
         for (int s = 0; s < C::QK_STEPS; ++s) {
           const uint32_t sub = 32 * s / C::QROW, within = 32 * s % C::QROW;
-          const uint64_t da = umma_smem_desc(q_u + sub * C::Q_SUB_BYTES + within, 16, 8 * C::QROW, C::QK_SW);
-          const uint64_t db = umma_smem_desc(k_u + sub * C::K_SUB_BYTES + within, 16, 8 * C::QROW, C::QK_SW);
-          if (QK8) tc_mma_i8_ss(tmem + C::COL_S + kTN * (t & 1), da, db, idesc_qk, s > 0 ? 1u : 0u);
-          else tc_mma_f16_ss(tmem + C::COL_S + kTN * (t & 1), da, db, idesc_qk, s > 0 ? 1u : 0u);
+          const uint64_t da = umma_desc_advance(dq, sub * C::Q_SUB_BYTES + within);
+          const uint64_t db = umma_desc_advance(dk, buf * C::K_TILE_BYTES + sub * C::K_SUB_BYTES + within);
+          if (QK8) tc_mma_i8_ss(tmem + C::COL_S + kTN * buf, da, db, idesc_qk, s > 0 ? 1u : 0u);
+          else tc_mma_f16_ss(tmem + C::COL_S + kTN * buf, da, db, idesc_qk, s > 0 ? 1u : 0u);
         }
-        tc_commit(&bars[S_FULL + (t & 1)]);
-        return true;
-      };
-      ok = mbar_wait(&bars[Q_FULL], 0, a.status);
-      if (ok) ok = issue_qk(0);
-      if (ok && ntiles > 1) ok = issue_qk(1);
-      for (int j = 0; j < ntiles && ok; ++j) {
-        const int vs = j % C::NVS;
+        tc_commit(&bars[S_FULL + buf]);
+      }
+      __syncwarp();
+      return true;
+    };
+    static_assert(C::NKS == 2 && C::NVS == 2, "the issuer is unrolled over two stages");
+    ok = __all_sync(0xffffffffu, mbar_wait(&bars[Q_FULL], 0, a.status));
+    if (ok) ok = issue_qk(0, 0);
+    if (ok && ntiles > 1) ok = issue_qk(1, 1);
+    for (int j0 = 0; j0 < ntiles && ok; j0 += 2) {
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int j = j0 + u;
+        if (j >= ntiles || !ok) break;
+        const uint32_t par = (j0 >> 1) & 1;
         TR(4096 + 8 * j + 0);
-        ok = mbar_wait(&bars[P_FULL + (j & 1)], (j >> 1) & 1, a.status);
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars[P_FULL + u], par, a.status));
         TR(4096 + 8 * j + 1);
-        if (ok) ok = mbar_wait(&bars[V_FULL + vs], (j / C::NVS) & 1, a.status);
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars[V_FULL + u], par, a.status));
         if (!ok) break;
         tc_fence_after();
-        const uint32_t v_u = smem_u32(smem + C::OFF_V + vs * C::V_TILE_BYTES);
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < kTN / 16; ++kk)
-          tc_mma_f16_ts(tmem + C::COL_O, tmem + C::COL_S + kTN * (j & 1) + 8 * kk,
-                        umma_smem_desc(v_u + kk * 2048, C::V_SUB_BYTES, 1024, kUmmaSw128), idesc_pv,
-                        (j > 0 || kk > 0) ? 1u : 0u);
-        tc_commit(&bars[PV_DONE + (j & 1)]);
+          for (int kk = 0; kk < kTN / 16; ++kk)
+            tc_mma_f16_ts(tmem + C::COL_O, tmem + C::COL_S + kTN * u + 8 * kk,
+                          umma_desc_advance(dv, u * C::V_TILE_BYTES + kk * 2048), idesc_pv,
+                          (j > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(&bars[PV_DONE + u]);
+        }
+        __syncwarp();
         TR(4096 + 8 * j + 2);
-        if (j + 2 < ntiles) ok = issue_qk(j + 2);
+        if (j + 2 < ntiles) ok = issue_qk(j + 2, u);
         TR(4096 + 8 * j + 3);
-        if (j == ntiles - 1) tc_commit(&bars[O_DONE]);
+        if (j == ntiles - 1 && elect_one()) tc_commit(&bars[O_DONE]);
+        __syncwarp();
       }
     }
   } else {
     // ======================= softmax / correction / epilogue =======================
-    // Thread = (query row, column part): part h = warp >> 2 owns S columns [h kCT, (h + 1) kCT) of
-    // every tile and O columns [h D / kHalves, ...).  With two parts the row maxima and the final
-    // row sums cross between the two warps of a lane group through shared memory.
-    const int lg = warp & 3, h = warp >> 2;
+    // Thread = query row: warp w reads and writes tensor-memory lanes [32 w, 32 w + 32).
+    const int lg = warp;
     const int row = 32 * lg + lane;
     const int m = m_block + row;                // this thread's query row
     const float qs = QK8 ? ((m < m_len) ? __ldg(a.q_scale + bh * a.M + m) : 0.f) : a.scale_log2;
     const int qpos = m + causal_diag;
     const uint32_t t_row = tmem + ((uint32_t)(32 * lg) << 16);
-    constexpr int OC = D / kHalves;             // O columns owned by this thread
-    const uint32_t t_o = t_row + C::COL_O + OC * h;
+    const uint32_t t_o = t_row + C::COL_O;
     float m_run = -INFINITY, l_run = 0.f;
 
     for (int j = 0; j < ntiles; ++j) {
@@ -375,36 +418,34 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
       const int ss = j % kScaleStages;
       const uint32_t t_s = t_row + C::COL_S + kTN * (j & 1);
       if (warp == 0 && lane == 0) TR(8 * j + 0);
-      if (QK8) ok = mbar_wait(&bars[KS_FULL + ss], (j / kScaleStages) & 1, a.status);
-      if (ok) ok = mbar_wait(&bars[S_FULL + (j & 1)], (j >> 1) & 1, a.status);
+      ok = mbar_wait(&bars[S_FULL + (j & 1)], (j >> 1) & 1, a.status);
       if (!ok) break;
       tc_fence_after();
       if (warp == 0 && lane == 0) TR(8 * j + 1);
-      uint32_t r[kCT];
+      uint32_t r[kTN];
 #pragma unroll
-      for (int c = 0; c < kCT / 32; ++c) tc_ld32(t_s + kCT * h + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
+      for (int c = 0; c < kTN / 32; ++c) tc_ld32(t_s + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
       tc_wait_ld();
 #pragma unroll
-      for (int c = 0; c < kCT / 32; ++c) tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
+      for (int c = 0; c < kTN / 32; ++c) tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
       if (warp == 0 && lane == 0) TR(8 * j + 2);
-      const float* ksv = ks_smem + ss * kTN + kCT * h;
+      const float* ksv = ks_smem + ss * kTN;
       const bool need_mask = (n_block + kTN > n_len) || (a.causal && n_block + kTN - 1 > m_block + causal_diag) ||
                              (a.window_left >= 0 && n_block <= m_block + kTM - 1 + causal_diag - a.window_left);
-      float tmax = need_mask ? logits_inplace<QK8, true, kCT>(r, ksv, qs, n_block + kCT * h, n_len, a.causal, qpos, a.window_left)
-                             : logits_inplace<QK8, false, kCT>(r, ksv, qs, n_block + kCT * h, n_len, a.causal, qpos, a.window_left);
-      if (kHalves == 2) {
-        // full-row max: both parts have loaded their S columns before this barrier, so the P
-        // stores below (which overwrite S columns of the other part) cannot race with them
-        float* xm = xch + (j & 1) * (kHalves * kTM);
-        xm[h * kTM + row] = tmax;
-        asm volatile("bar.sync %0, 64;" ::"r"(1 + lg) : "memory");
-        tmax = fmaxf(tmax, xm[(h ^ 1) * kTM + row]);
+      // Speculative single sweep: P is formed against the running max while the tile's own max is
+      // still being collected.  Lazy rescale makes that the final answer whenever no row of the
+      // warp outgrew its running max by more than 2^8 (P <= 256 then: harmless in fp16 / bf16 and
+      // in the fp32 sum; out = O / l does not depend on which reference max was used).  Otherwise
+      // (the first tile, and rarely later) the max moves, O is corrected and P is formed again.
+      const float xs = need_mask ? 1.f : qs;      // masked tiles keep finished logits in r, the others t
+      float mx, psum;
+      {
+        const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
+        if (need_mask) softmax_pass<QK8, true, true, VT>(r, ksv, qs, xs, neg_m, n_block, n_len, a.causal, qpos, a.window_left, t_s, mx, psum);
+        else softmax_pass<QK8, false, true, VT>(r, ksv, qs, xs, neg_m, n_block, n_len, a.causal, qpos, a.window_left, t_s, mx, psum);
       }
+      const float tmax = need_mask ? mx : mx * qs;
       if (warp == 0 && lane == 0) TR(8 * j + 3);
-      // Lazy rescale: the running max moves only when some row of the warp outgrew it by
-      // more than 2^8 (P then stays <= 256, harmless in fp16/bf16 and in the fp32 sum);
-      // out = O / l does not depend on which reference max was used.  Both parts of a row see
-      // the same maxima and take the same decision.
       const bool grow = (m_run == -INFINITY) ? (tmax > -INFINITY) : (tmax > m_run + kLazyRescaleLog2);
       float resc = 1.f;
       if (__any_sync(0xffffffffu, grow)) {
@@ -418,7 +459,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
           tc_fence_after();
           const float2 resc2 = make_float2(resc, resc);
 #pragma unroll 1
-          for (int c = 0; c < OC / 32; ++c) {
+          for (int c = 0; c < D / 32; ++c) {
             uint32_t o[32];
             tc_ld32(t_o + 32 * c, o);
             tc_wait_ld();
@@ -432,37 +473,12 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
             tc_st32(t_o + 32 * c, o);
           }
         }
+        tc_wait_st();   // the speculative P stores are done before P is stored again
+        float unused;
+        softmax_pass<QK8, false, false, VT>(r, ksv, qs, xs, (m_run == -INFINITY) ? 0.f : -m_run, n_block, n_len, a.causal,
+                                            qpos, a.window_left, t_s, unused, psum);
       }
-      // ---- P = 2^(s - m), row sum, P -> tensor memory as 16-bit pairs over the buffer's first columns ----
-      const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-      const float2 neg_m2 = make_float2(-m_use, -m_use);
-      float2 sum_a = make_float2(0.f, 0.f), sum_b = sum_a;
-#pragma unroll
-      for (int c = 0; c < kCT / 32; ++c) {
-        uint32_t pk[16];
-#ifndef SL8_STAGE2
-#define SL8_STAGE2 8
-#endif
-        constexpr int G2 = SL8_STAGE2;
-#pragma unroll
-        for (int g0 = 0; g0 < 16; g0 += G2) {
-          float2 x[G2];
-#pragma unroll
-          for (int u = 0; u < G2; ++u) x[u] = add2(bits2(r[32 * c + 2 * (g0 + u)], r[32 * c + 2 * (g0 + u) + 1]), neg_m2);
-#pragma unroll
-          for (int u = 0; u < G2; ++u) x[u] = make_float2(ex2_approx(x[u].x), ex2_approx(x[u].y));
-#pragma unroll
-          for (int u = 0; u < G2; u += 2) {
-            sum_a = add2(sum_a, x[u]);
-            sum_b = add2(sum_b, x[u + 1]);
-          }
-#pragma unroll
-          for (int u = 0; u < G2; ++u) pk[g0 + u] = pack2<VT>(x[u].x, x[u].y);
-        }
-        tc_st16(t_s + (kCT / 2) * h + 16 * c, pk);
-      }
-      const float2 st = add2(sum_a, sum_b);
-      l_run = l_run * resc + (st.x + st.y);
+      l_run = l_run * resc + psum;
       if (warp == 0 && lane == 0) TR(8 * j + 4);
       tc_wait_st();
       tc_fence_before();
@@ -477,23 +493,17 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
     if (ok) ok = mbar_wait(&bars[O_DONE], 0, a.status);
     if (ok) {
       tc_fence_after();
-      float l_tot = l_run;
-      if (kHalves == 2) {
-        float* xl = xch + (ntiles & 1) * (kHalves * kTM);
-        xl[h * kTM + row] = l_run;
-        asm volatile("bar.sync %0, 64;" ::"r"(1 + lg) : "memory");
-        l_tot += xl[(h ^ 1) * kTM + row];
-      }
+      const float l_tot = l_run;
       const bool live = m < m_len;
       const float inv = (live && l_tot > 0.f) ? 1.f / l_tot : 0.f;
 #pragma unroll 1
-      for (int c = 0; c < OC / 32; ++c) {
+      for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
         tc_ld32(t_o + 32 * c, o);
         tc_wait_ld();
         tc_regs_ready(o);
         if (m < a.M) {
-          uint4* dst = reinterpret_cast<uint4*>(out_bh + (int64_t)m * D + OC * h + 32 * c);
+          uint4* dst = reinterpret_cast<uint4*>(out_bh + (int64_t)m * D + 32 * c);
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             uint4 w;
@@ -505,7 +515,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
           }
         }
       }
-      if (a.lse != nullptr && m < a.M && h == 0)
+      if (a.lse != nullptr && m < a.M)
         a.lse[bh * a.M + m] = (live && l_tot > 0.f) ? (m_run * 0.6931471805599453f + logf(l_tot)) : -INFINITY;
     }
     tc_fence_before();

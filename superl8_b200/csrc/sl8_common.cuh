@@ -152,6 +152,14 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
+// One lane of a converged warp (the same lane on every call): the lane that issues MMAs.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred)::"memory");
+  return pred != 0;
+}
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                    smem_u32(bar))
@@ -273,6 +281,14 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+// The same, as a volatile statement: keeps its place among the other volatile statements, for
+// code that orders its special-function work by hand.
+__device__ __forceinline__ float ex2_issue(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // UMMA shared-memory matrix descriptor (64 bit): start address, leading-dimension
 // and stride byte offsets (all >> 4), descriptor version 1, swizzle mode in the
 // top three bits (0 none, 2 = 128 B, 4 = 64 B, 6 = 32 B).
@@ -287,6 +303,11 @@ __host__ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr, 
   return d;
 }
 constexpr uint32_t kUmmaSw128 = 2, kUmmaSw64 = 4, kUmmaSw32 = 6;
+// The same descriptor moved by `bytes` inside shared memory: only the 14-bit start-address
+// field changes (no carry out of it for any valid shared-memory address).
+__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t desc, uint32_t bytes) {
+  return (desc & 0xFFFFFFFF00000000ull) | static_cast<uint32_t>(static_cast<uint32_t>(desc) + (bytes >> 4));
+}
 
 // UMMA instruction descriptor (32 bit).  c_fmt: 1 = fp32, 2 = int32.  a/b_fmt:
 // kind::f16 -> 0 fp16, 1 bf16; kind::i8 -> 0 unsigned, 1 signed.  *_mn_major: the
