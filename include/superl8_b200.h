@@ -168,6 +168,29 @@ size_t sl8_attn_fp16_fwd_workspace(const sl8_fp16_fwd_params* p);
 int sl8_attn_fp16_fwd(const sl8_fp16_fwd_params* p, void* workspace, size_t workspace_bytes,
                       void* stream);
 
+/* ---- backward -------------------------------------------------------------- */
+
+/*
+ * Replaces `attn_bwd` (reference csrc/kernel/attn_bwd.cu:62-109, kernels
+ * csrc/include/attn_bwd.cuh:156-331 and :337-535, binding csrc/fni8_api.cpp:256-259; the
+ * mathematics it implements are superl8/autograd.py:29-45).  q, o, dout, dq: [B, Hq, M, D];
+ * k, v, dk, dv: [B, Hkv, N, D]; lse: fp32 [B, Hq, M], natural log, as the forward returns it.
+ * One dtype for all 16-bit tensors (reference: fp16 only; bf16 also served).  D in {32, 64, 128}
+ * (the reference's set).  dk / dv are summed over the query heads of a KV head.  M == 0 or
+ * N == 0 zero-fills the gradients (attn_bwd.cu:88).  Two passes, no atomics: bitwise
+ * reproducible.  workspace: sl8_attn_bwd_workspace() bytes (status word + fp32 [B, Hq, M]).
+ */
+typedef struct sl8_bwd_params {
+  const void* q; const void* k; const void* v; const void* o; const void* dout;
+  const float* lse;
+  void* dq; void* dk; void* dv;
+  int32_t B, Hq, Hkv, M, N, D;
+  int32_t dtype; int32_t causal;
+  float softmax_scale;
+} sl8_bwd_params;
+size_t sl8_attn_bwd_workspace(const sl8_bwd_params* p);
+int sl8_attn_bwd(const sl8_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- decode: split-KV, one query row per sequence ----------------------- */
 
 typedef struct sl8_decode_params {

@@ -144,6 +144,53 @@ def attention_fp32_ragged(q, k, v, seqlens_q, seqlens_k, causal=False, scale=Non
     return out
 
 
+def attention_lse_fp32(q, k, causal: bool = False, scale: float | None = None) -> torch.Tensor:
+    """Natural-log row sums of the scaled, masked logits: what the forward saves for the
+    backward, recomputed the way reference superl8/ops.py:49-58 does when it is missing."""
+    qf, kf = q.detach().cpu().float(), k.detach().cpu().float()
+    kf, _ = _expand_kv(kf, kf, qf.shape[1])
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    s = torch.einsum("bhmd,bhnd->bhmn", qf, kf) * scale
+    if causal:
+        m_len, n_len = s.shape[-2], s.shape[-1]
+        s = s.masked_fill(~torch.ones(m_len, n_len, dtype=torch.bool).tril(n_len - m_len), float("-inf"))
+    return torch.logsumexp(s, dim=-1).float()
+
+
+def attention_backward_fp32(q, k, v, out, d_out, causal: bool = False, scale: float | None = None, lse=None):
+    """Exact FlashAttention-2 gradient in fp32: reference superl8/autograd.py:29-45, with the
+    grouped-head sum the reference's kernel pair performs (csrc/include/attn_bwd.cuh:399-404).
+    P = exp(S - lse) when ``lse`` is given (what the kernels do, attn_bwd.cuh:260), else softmax.
+    Returns fp32 (dq [B,Hq,M,D], dk, dv [B,Hkv,N,D])."""
+    qf, kf, vf, of, dof = (t.detach().cpu().float() for t in (q, k, v, out, d_out))
+    Hq, Hkv = qf.shape[1], kf.shape[1]
+    rep = Hq // Hkv
+    kf, vf = _expand_kv(kf, vf, Hq)
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    s = torch.einsum("bhmd,bhnd->bhmn", qf, kf) * scale
+    if causal:
+        m_len, n_len = s.shape[-2], s.shape[-1]
+        s = s.masked_fill(~torch.ones(m_len, n_len, dtype=torch.bool).tril(n_len - m_len), float("-inf"))
+    if lse is None:
+        p = torch.softmax(s, dim=-1)
+    else:
+        p = torch.exp(s - lse.detach().cpu().float().unsqueeze(-1))
+    p = torch.nan_to_num(p, nan=0.0)
+    dv = torch.einsum("bhmn,bhmd->bhnd", p, dof)
+    dp = torch.einsum("bhmd,bhnd->bhmn", dof, vf)
+    drow = (dof * of).sum(dim=-1, keepdim=True)
+    ds = p * (dp - drow)
+    dq = torch.einsum("bhmn,bhnd->bhmd", ds, kf) * scale
+    dk = torch.einsum("bhmn,bhmd->bhnd", ds, qf) * scale
+    if rep > 1:
+        B, _, N, D = dk.shape
+        dk = dk.view(B, Hkv, rep, N, D).sum(dim=2)
+        dv = dv.view(B, Hkv, rep, N, D).sum(dim=2)
+    return dq, dk, dv
+
+
 # --------------------------------------------------------------------------- kernel restatements
 
 def int32_logits(q_i8: torch.Tensor, k_i8: torch.Tensor) -> torch.Tensor:

@@ -169,8 +169,9 @@ def tensor_peak(kind_i8: bool, iters: int = 4096, device=None) -> float:
 
 
 def attn_fp16_fwd(q, k, v, causal=False, scale=None, window_left=-1, mask=None, *, seqlens_q=None, seqlens_k=None,
-                  backend=_lib.SL8_BACKEND_AUTO):
-    """Full-precision forward.  Reference binding csrc/fni8_api.cpp:234-244."""
+                  backend=_lib.SL8_BACKEND_AUTO, want_lse=False):
+    """Full-precision forward.  Reference binding csrc/fni8_api.cpp:234-244.  ``want_lse``: also
+    return the natural-log row sums [B, H, M] (what the backward consumes)."""
     what = "superl8_b200 fp16 fwd"
     _check_cuda(q, k, v)
     _check(q.dtype in (torch.float16, torch.bfloat16), f"{what}: q must be float16 or bfloat16")
@@ -195,11 +196,12 @@ def attn_fp16_fwd(q, k, v, causal=False, scale=None, window_left=-1, mask=None, 
     _check(k.shape[3] == D and v.shape[3] == D and v.shape[2] == N, f"{what}: K/V shape mismatch")
     _check(D in (32, 64, 72, 80, 128, 256), f"{what}: head dim must be 32/64/72/80/128/256, got {D}")
     out = torch.empty((B, H, M, D), dtype=v.dtype, device=v.device)
+    lse = torch.empty((B, H, M), dtype=torch.float32, device=v.device) if want_lse else None
     if out.numel() == 0:
-        return out
+        return (out, lse) if want_lse else out
     sc = (1.0 / math.sqrt(D)) if scale is None else float(scale)
     p = _lib.Fp16FwdParams(
-        q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), lse=None,
+        q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), lse=None if lse is None else lse.data_ptr(),
         seqlens_q=None if seqlens_q is None else seqlens_q.data_ptr(),
         seqlens_k=None if seqlens_k is None else seqlens_k.data_ptr(),
         B=B, Hq=H, Hkv=Hkv, M=M, N=N, D=D, dtype=_DTYPE[q.dtype], causal=int(bool(causal)),
@@ -208,7 +210,7 @@ def attn_fp16_fwd(q, k, v, causal=False, scale=None, window_left=-1, mask=None, 
         ws = _status_buffer(q.device)
         rc = _lib.load().sl8_attn_fp16_fwd(C.byref(p), _ptr(ws), ws.numel() * 4, _stream(q.device))
     _lib.check(rc, "attn_fp16_fwd", 1)
-    return out
+    return (out, lse) if want_lse else out
 
 
 def _decode_workspace(device, nbytes: int) -> torch.Tensor:
@@ -252,31 +254,35 @@ def attn_int8_decode(q, q_scale, k, k_scale, v, num_splits=-1, *, context_lens=N
 
 
 def attn_bwd(q, k, v, o, do_, lse, scale, causal=False):
-    """Exact FlashAttention-2 gradient in fp32 torch ops on the tensors' device
-    (the reference's own first definition of the backward, superl8/autograd.py:30-45).
-    The reference later binds a CUDA kernel pair here (csrc/fni8_api.cpp:256-259);
-    a native kernel for this row is not written yet."""
-    qf, kf, vf, of, dof = (t.float() for t in (q, k, v, o, do_))
-    Hq, Hkv = qf.shape[1], kf.shape[1]
-    rep = Hq // Hkv
-    if rep > 1:
-        kf = kf.repeat_interleave(rep, dim=1)
-        vf = vf.repeat_interleave(rep, dim=1)
-    s = torch.einsum("bhmd,bhnd->bhmn", qf, kf) * scale
-    if causal:
-        m, n = s.shape[-2], s.shape[-1]
-        keep = torch.ones(m, n, device=s.device, dtype=torch.bool).tril(n - m)
-        s = s.masked_fill(~keep, float("-inf"))
-    p = torch.exp(s - lse.unsqueeze(-1)) if lse is not None and lse.numel() else torch.softmax(s, dim=-1)
-    p = torch.nan_to_num(p, nan=0.0)
-    dv = torch.einsum("bhmn,bhmd->bhnd", p, dof)
-    dp = torch.einsum("bhmd,bhnd->bhmn", dof, vf)
-    drow = (dof * of).sum(dim=-1, keepdim=True)
-    ds = p * (dp - drow)
-    dq = torch.einsum("bhmn,bhnd->bhmd", ds, kf) * scale
-    dk = torch.einsum("bhmn,bhmd->bhnd", ds, qf) * scale
-    if rep > 1:
-        B, _, N, D = dk.shape
-        dk = dk.view(B, Hkv, rep, N, D).sum(dim=2)
-        dv = dv.view(B, Hkv, rep, N, D).sum(dim=2)
-    return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
+    """Reference binding csrc/fni8_api.cpp:256-259 (op csrc/kernel/attn_bwd.cu:62-109):
+    (dq, dk, dv) of the attention with logits scale * q.k, from the forward's output ``o``, its
+    natural-log row sums ``lse`` [B, Hq, M] and the output gradient ``do_``.  q, o, do_
+    [B, Hq, M, D]; k, v [B, Hkv, N, D]; dk / dv are summed over the query heads of a KV head."""
+    what = "superl8_b200 bwd"
+    for t in (q, k, v, o, do_, lse):
+        _check(t.is_cuda, f"{what}: all inputs must be CUDA")
+        _check(t.device == q.device, f"{what}: all inputs must be on the same device")
+    _check(q.dtype in (torch.float16, torch.bfloat16) and all(t.dtype == q.dtype for t in (k, v, o, do_)),
+           f"{what}: q/k/v/o/do must be float16 (or all bfloat16)")
+    _check(lse.dtype == torch.float32, f"{what}: lse must be float32")
+    _check(all(t.dim() == 4 for t in (q, k, v, o, do_)), f"{what}: expect [B,H,S,D]")
+    q, k, v, o, do_, lse = (t.contiguous() for t in (q, k, v, o, do_, lse))
+    B, H, M, D = q.shape
+    Hkv, N = k.shape[1], k.shape[2]
+    _check(Hkv > 0 and H % Hkv == 0, f"{what}: H_q must be divisible by H_kv (GQA)")
+    _check(D in (32, 64, 128), f"{what}: head dim must be 32/64/128, got {D}")
+    _check(k.shape == v.shape and k.shape[0] == B and k.shape[3] == D, f"{what}: K/V shape mismatch")
+    _check(o.shape == q.shape and do_.shape == q.shape, f"{what}: o/do must have q's shape")
+    _check(lse.numel() == B * H * M, f"{what}: lse must be [B,H,M]")
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    p = _lib.BwdParams(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), o=o.data_ptr(), dout=do_.data_ptr(),
+                       lse=lse.data_ptr(), dq=dq.data_ptr(), dk=dk.data_ptr(), dv=dv.data_ptr(),
+                       B=B, Hq=H, Hkv=Hkv, M=M, N=N, D=D, dtype=_DTYPE[q.dtype], causal=int(bool(causal)),
+                       softmax_scale=float(scale))
+    lib = _lib.load()
+    with torch.cuda.device(q.device):
+        nbytes = lib.sl8_attn_bwd_workspace(C.byref(p))
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)   # D_m = sum_d dO.O per query row
+        rc = lib.sl8_attn_bwd(C.byref(p), _ptr(ws), nbytes, _stream(q.device))
+    _lib.check(rc, "attn_bwd", 3 if (M and N and q.numel() and k.numel()) else 0)
+    return dq, dk, dv

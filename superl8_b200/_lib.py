@@ -68,6 +68,15 @@ class DecodeParams(C.Structure):
     ]
 
 
+class BwdParams(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("dout", C.c_void_p),
+        ("lse", C.c_void_p), ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
+        ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("M", C.c_int32), ("N", C.c_int32), ("D", C.c_int32),
+        ("dtype", C.c_int32), ("causal", C.c_int32), ("softmax_scale", C.c_float),
+    ]
+
+
 # name -> (restype, argtypes); every symbol declared in include/superl8_b200.h
 SIGNATURES = {
     "sl8_abi_version": (C.c_int, []),
@@ -86,6 +95,8 @@ SIGNATURES = {
                                     C.c_void_p, C.c_size_t, C.c_void_p]),
     "sl8_attn_fp16_fwd_workspace": (C.c_size_t, [C.POINTER(Fp16FwdParams)]),
     "sl8_attn_fp16_fwd": (C.c_int, [C.POINTER(Fp16FwdParams), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "sl8_attn_bwd_workspace": (C.c_size_t, [C.POINTER(BwdParams)]),
+    "sl8_attn_bwd": (C.c_int, [C.POINTER(BwdParams), C.c_void_p, C.c_size_t, C.c_void_p]),
     "sl8_choose_n_splits": (C.c_int, [C.c_int64, C.c_int64]),
     "sl8_attn_int8_decode_workspace": (C.c_size_t, [C.POINTER(DecodeParams)]),
     "sl8_attn_int8_decode": (C.c_int, [C.POINTER(DecodeParams), C.c_void_p, C.c_size_t, C.c_void_p]),

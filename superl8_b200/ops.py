@@ -60,6 +60,17 @@ def attn_fp16_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, 
     return _C.attn_fp16_fwd(q.contiguous(), k.contiguous(), v.contiguous(), causal, scale, window_left, mask)
 
 
+def backward_cuda(q, k, v, out, lse, d_out, *, causal: bool = False, scale: float | None = None):
+    """Fused backward -> (dq, dk, dv) in the inputs' 16-bit dtype (reference superl8/ops.py:39-67).
+    ``lse`` [B, H, M] fp32 (natural log) from the forward; when None it is produced by the
+    full-precision forward kernel (the reference recomputes it with dense torch ops)."""
+    sc = (1.0 / math.sqrt(q.shape[-1])) if scale is None else float(scale)
+    if lse is None:
+        _, lse = _C.attn_fp16_fwd(q, k, v, causal, sc, want_lse=True)
+    return _C.attn_bwd(q.contiguous(), k.contiguous(), v.contiguous(), out.contiguous(), d_out.contiguous(),
+                       lse.contiguous(), sc, causal)
+
+
 def attn_int8_decode(q, k, v, *, scale: float | None = None, rotate: bool = False, num_splits: int | None = None):
     """Decode (M = 1) via split-KV from fp16 q, k, v; quantises Q and the whole K first,
     exactly like the reference entry (superl8/ops.py:230-267)."""

@@ -132,6 +132,55 @@ def attention_cases():
     np.savez_compressed(OUT / "attention_fp32.npz", **out)
 
 
+def backward_cases():
+    """Gradients of the reference's own definitions: superl8/autograd.py::_attn_backward for
+    equal head counts, and autograd through tests/reference.py::attention_fp32_oracle (the
+    check its CUDA-backward tests use, tests/test_attn_bwd_cuda.py:43-46) for grouped heads."""
+    from superl8.autograd import _attn_backward
+
+    out = {}
+    g = gen(51)
+
+    def fwd_and_lse(q, k, v, causal, scale):
+        kf, vf = k.float(), v.float()
+        rep = q.shape[1] // k.shape[1]
+        if rep > 1:
+            kf, vf = kf.repeat_interleave(rep, dim=1), vf.repeat_interleave(rep, dim=1)
+        s = torch.einsum("bhmd,bhnd->bhmn", q.float(), kf) * scale
+        if causal:
+            m, n = s.shape[-2:]
+            s = s.masked_fill(~torch.ones(m, n, dtype=torch.bool).tril(n - m), float("-inf"))
+        lse = torch.logsumexp(s, dim=-1).float()     # as superl8/ops.py:49-58 recomputes it
+        o = torch.einsum("bhmn,bhnd->bhmd", torch.softmax(s, dim=-1), vf).half()
+        return o, lse
+
+    cases = {
+        "mha": (1, 2, 2, 48, 48, 32, False, 32 ** -0.5),
+        "mha_causal": (2, 2, 2, 70, 70, 64, True, 64 ** -0.5),
+        "rect_causal": (1, 2, 2, 40, 56, 32, True, 0.25),
+        "gqa_causal": (1, 4, 2, 50, 50, 64, True, 64 ** -0.5),
+        "mqa": (1, 4, 1, 33, 65, 128, False, 128 ** -0.5),
+    }
+    for name, (B, Hq, Hkv, M, N, D, causal, scale) in cases.items():
+        q = torch.randn(B, Hq, M, D, generator=g).half()
+        k = torch.randn(B, Hkv, N, D, generator=g).half()
+        v = torch.randn(B, Hkv, N, D, generator=g).half()
+        do = torch.randn(B, Hq, M, D, generator=g).half()
+        o, lse = fwd_and_lse(q, k, v, causal, scale)
+        if Hq == Hkv:
+            dq, dk, dv = _attn_backward(q, k, v, o, do, causal, scale)
+        else:
+            qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+            ref_oracles.attention_fp32_oracle(qf, kf, vf, causal=causal, scale=scale).backward(do.float())
+            dq, dk, dv = qf.grad, kf.grad, vf.grad
+        for key, val in dict(q=q, k=k, v=v, o=o, do=do).items():
+            out[f"{name}__{key}"] = bits(val)
+        out[f"{name}__lse"] = lse.numpy()
+        out[f"{name}__dq"], out[f"{name}__dk"], out[f"{name}__dv"] = dq.numpy(), dk.numpy(), dv.numpy()
+        out[f"{name}__cfg"] = np.array([int(causal), scale])
+    np.savez_compressed(OUT / "attn_backward.npz", **out)
+
+
 if __name__ == "__main__":
     torch.set_num_threads(1)
     quant_cases()
@@ -139,5 +188,6 @@ if __name__ == "__main__":
     gate_cases()
     qk_cases()
     attention_cases()
+    backward_cases()
     for f in sorted(OUT.glob("*.npz")):
         print(f.name, f.stat().st_size)

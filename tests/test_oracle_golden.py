@@ -115,3 +115,23 @@ def test_choose_n_splits_reference_values():
     assert oracle.choose_n_splits_reference(64000, 24) == 250
     assert oracle.choose_n_splits_reference(100000, 24) == 256
     assert oracle.choose_n_splits_reference(100, 8) == 3
+
+
+def test_backward_restatement_matches_the_reference_gradients():
+    # reference superl8/autograd.py::_attn_backward (equal head counts) and autograd through its
+    # fp32 oracle (grouped heads); P from the saved row sums and P from softmax must agree too.
+    g = np.load(GOLDEN / "attn_backward.npz")
+    for name in ("mha", "mha_causal", "rect_causal", "gqa_causal", "mqa"):
+        q, k, v, o, do = (from_bits(g[f"{name}__{n}"], "float16") for n in ("q", "k", "v", "o", "do"))
+        causal, scale = bool(g[f"{name}__cfg"][0]), float(g[f"{name}__cfg"][1])
+        lse = torch.from_numpy(g[f"{name}__lse"])
+        assert torch.allclose(oracle.attention_lse_fp32(q, k, causal, scale), lse, rtol=0, atol=2e-6), name
+        for use_lse in (None, lse):
+            dq, dk, dv = oracle.attention_backward_fp32(q, k, v, o, do, causal, scale, lse=use_lse)
+            for got, key in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+                ref = torch.from_numpy(g[f"{name}__{key}"])
+                assert got.shape == ref.shape
+                # grouped-head goldens come from autograd through the fp32 oracle, which never
+                # rounds O to fp16; the analytic form reads the stored fp16 O in D = sum(dO * O)
+                tol = 2e-5 if name.startswith(("mha", "rect")) else 2e-3
+                assert float((got - ref).abs().max()) <= tol * max(1.0, float(ref.abs().max())), (name, key)
