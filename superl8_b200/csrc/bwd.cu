@@ -67,6 +67,24 @@ __device__ __forceinline__ void stage_rows(uint8_t* dst, const uint8_t* src, int
   }
 }
 
+// The same copy as asynchronous 16-byte cp.async (zero-fill for rows >= valid); the caller
+// commits the group and waits for it before the tile is read.
+template <int D>
+__device__ __forceinline__ void stage_rows_async(uint8_t* dst, const uint8_t* src, int rows, int valid) {
+  constexpr int VEC = 2 * D / 16;
+  const uint32_t dst_u = smem_u32(dst);
+  for (int idx = threadIdx.x; idx < rows * VEC; idx += kBwdThreads) {
+    const int r = idx / VEC, c = (idx % VEC) * 16;
+    const bool live = r < valid;
+    const uint8_t* g = live ? src + (int64_t)r * 2 * D + c : src;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_u + r * BwdCfg<D>::STRIDE + c), "l"(g),
+                 "r"(live ? 16 : 0)
+                 : "memory");
+  }
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 // D_m = sum_d dO[m, d] * O[m, d] in fp32; one warp per row.
 template <typename VT>
 __global__ void bwd_delta_kernel(const VT* __restrict__ o, const VT* __restrict__ dout, float* __restrict__ delta,
@@ -92,8 +110,8 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_dq_kernel(BwdArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
   uint8_t* sq = smem;
   uint8_t* sdo = sq + BM * C::STRIDE;
-  uint8_t* sk = sdo + BM * C::STRIDE;
-  uint8_t* sv = sk + BN * C::STRIDE;
+  uint8_t* skv = sdo + BM * C::STRIDE;           // two stages of {K tile, V tile}
+  constexpr int KV_STAGE = 2 * BN * C::STRIDE;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -129,13 +147,21 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_dq_kernel(BwdArgs a) {
   for (int i = 0; i < C::NT; ++i) dq[i][0] = dq[i][1] = dq[i][2] = dq[i][3] = 0.f;
 
   const int n_end = a.causal ? max(0, min(a.N, m_block + BM + diag)) : a.N;
-  const uint32_t sq_u = smem_u32(sq), sdo_u = smem_u32(sdo), sk_u = smem_u32(sk), sv_u = smem_u32(sv);
+  const uint32_t sq_u = smem_u32(sq), sdo_u = smem_u32(sdo);
+  auto load_kv = [&](int n_block, int stage) {
+    stage_rows_async<D>(skv + stage * KV_STAGE, k_bh + (int64_t)n_block * D * 2, BN, a.N - n_block);
+    stage_rows_async<D>(skv + stage * KV_STAGE + BN * C::STRIDE, v_bh + (int64_t)n_block * D * 2, BN, a.N - n_block);
+    cp_async_commit();
+  };
+  if (n_end > 0) load_kv(0, 0);
 
-  for (int n_block = 0; n_block < n_end; n_block += BN) {
-    __syncthreads();   // previous tile consumed (and Q / dO staged on the first pass)
-    stage_rows<D>(sk, k_bh + (int64_t)n_block * D * 2, BN, a.N - n_block);
-    stage_rows<D>(sv, v_bh + (int64_t)n_block * D * 2, BN, a.N - n_block);
+  for (int n_block = 0, it = 0; n_block < n_end; n_block += BN, ++it) {
+    // this tile has landed, and every warp is done with the tile before it (whose stage the
+    // next load overwrites); on the first pass this also publishes Q / dO
+    cp_async_wait_all();
     __syncthreads();
+    if (n_block + BN < n_end) load_kv(n_block + BN, (it + 1) & 1);
+    const uint32_t sk_u = smem_u32(skv + (it & 1) * KV_STAGE), sv_u = sk_u + BN * C::STRIDE;
 
     // ---- S = Q K^T and dP = dO V^T ----
     float s[8][4], dp[8][4];
@@ -214,10 +240,9 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_dkv_kernel(BwdArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
   uint8_t* sk = smem;
   uint8_t* sv = sk + BN * C::STRIDE;
-  uint8_t* sq = sv + BN * C::STRIDE;
-  uint8_t* sdo = sq + BMQ * C::STRIDE;
-  float* s_lse2 = reinterpret_cast<float*>(sdo + BMQ * C::STRIDE);
-  float* s_dlt = s_lse2 + BMQ;
+  uint8_t* sqd = sv + BN * C::STRIDE;            // two stages of {Q tile, dO tile}
+  constexpr int QD_STAGE = 2 * BMQ * C::STRIDE;
+  float* s_rows = reinterpret_cast<float*>(sqd + 2 * QD_STAGE);   // two stages of {lse * log2 e, D_m}
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -241,24 +266,39 @@ __global__ void __launch_bounds__(kBwdThreads) bwd_dkv_kernel(BwdArgs a) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) dk[i][e] = dv[i][e] = 0.f;
 
-  const uint32_t sq_u = smem_u32(sq), sdo_u = smem_u32(sdo), sk_u = smem_u32(sk), sv_u = smem_u32(sv);
+  const uint32_t sk_u = smem_u32(sk), sv_u = smem_u32(sv);
   // first query row that sees a key of this block: n <= m + diag
   const int m_start = a.causal ? max(0, n_block - diag) / BMQ * BMQ : 0;
-
-  for (int hg = 0; hg < G; ++hg) {
-    const int64_t bh = (int64_t)b * a.Hq + (int64_t)kvh * G + hg;
+  const int tiles_per_head = (a.M - m_start + BMQ - 1) / BMQ;
+  const int total = G * tiles_per_head;
+  // tile i of the walk = (query head i / tiles_per_head of the group, query rows m_start + ...)
+  auto load_tile = [&](int i, int stage) {
+    const int64_t bh = (int64_t)b * a.Hq + (int64_t)kvh * G + i / tiles_per_head;
+    const int m_block = m_start + (i % tiles_per_head) * BMQ;
     const uint8_t* q_bh = reinterpret_cast<const uint8_t*>(a.q) + bh * (int64_t)a.M * D * 2;
     const uint8_t* do_bh = reinterpret_cast<const uint8_t*>(a.dout) + bh * (int64_t)a.M * D * 2;
-    for (int m_block = m_start; m_block < a.M; m_block += BMQ) {
-      __syncthreads();   // previous tile consumed (and K / V staged on the first pass)
-      stage_rows<D>(sq, q_bh + (int64_t)m_block * D * 2, BMQ, a.M - m_block);
-      stage_rows<D>(sdo, do_bh + (int64_t)m_block * D * 2, BMQ, a.M - m_block);
-      if (threadIdx.x < BMQ) {
-        const int m = m_block + threadIdx.x;
-        s_lse2[threadIdx.x] = (m < a.M) ? __ldg(a.lse + bh * a.M + m) * kLog2e : -INFINITY;
-        s_dlt[threadIdx.x] = (m < a.M) ? a.delta[bh * a.M + m] : 0.f;
-      }
+    stage_rows_async<D>(sqd + stage * QD_STAGE, q_bh + (int64_t)m_block * D * 2, BMQ, a.M - m_block);
+    stage_rows_async<D>(sqd + stage * QD_STAGE + BMQ * C::STRIDE, do_bh + (int64_t)m_block * D * 2, BMQ, a.M - m_block);
+    cp_async_commit();
+    if (threadIdx.x < BMQ) {
+      const int m = m_block + threadIdx.x;
+      s_rows[stage * 2 * BMQ + threadIdx.x] = (m < a.M) ? __ldg(a.lse + bh * a.M + m) * kLog2e : -INFINITY;
+      s_rows[stage * 2 * BMQ + BMQ + threadIdx.x] = (m < a.M) ? a.delta[bh * a.M + m] : 0.f;
+    }
+  };
+  load_tile(0, 0);
+
+  for (int i = 0; i < total; ++i) {
+    {
+      // this tile has landed, and every warp is done with the tile before it (whose stage the
+      // next load overwrites); on the first pass this also publishes K / V
+      cp_async_wait_all();
       __syncthreads();
+      if (i + 1 < total) load_tile(i + 1, (i + 1) & 1);
+      const int m_block = m_start + (i % tiles_per_head) * BMQ;
+      const uint32_t sq_u = smem_u32(sqd + (i & 1) * QD_STAGE), sdo_u = sq_u + BMQ * C::STRIDE;
+      const float* s_lse2 = s_rows + (i & 1) * 2 * BMQ;
+      const float* s_dlt = s_lse2 + BMQ;
 
       // ---- S^T = K Q^T and dP^T = V dO^T (rows = keys, columns = queries) ----
       float st[JT][4], dpt[JT][4];
@@ -344,8 +384,8 @@ template <int D, typename VT>
 int launch_bwd(const BwdArgs& a, int B, cudaStream_t s) {
   using C = BwdCfg<D>;
   constexpr int BMQ = D >= 128 ? 32 : 64;
-  constexpr int smem_dq = 4 * 64 * C::STRIDE;
-  constexpr int smem_dkv = (2 * 64 + 2 * BMQ) * C::STRIDE + 2 * BMQ * 4;
+  constexpr int smem_dq = 6 * 64 * C::STRIDE;                               // Q, dO, two stages of K + V
+  constexpr int smem_dkv = (2 * 64 + 4 * BMQ) * C::STRIDE + 4 * BMQ * 4;    // K, V, two stages of Q + dO + row data
   SL8_CUDA_TRY(cudaFuncSetAttribute(bwd_dq_kernel<D, VT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dq));
   SL8_CUDA_TRY(cudaFuncSetAttribute(bwd_dkv_kernel<D, VT, BMQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dkv));
   const int64_t rows = (int64_t)B * a.Hq * a.M;
