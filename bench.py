@@ -472,6 +472,22 @@ def main():
                                        "traffic": 794.5e6 / 775.8e6 * dbytes},
                           "device_status": _C.device_status()}
         del dq, dk8, dks, dv
+        # ---- backward (dQ pass + dK/dV pass) on a cfg2-shaped training step per rank ----
+        bB, bHq, bHkv, bS, bD = 2, 32, 8, 4096, 128
+        gb = torch.Generator(device="cpu").manual_seed(2002 + rank)
+        bq, bk, bv, bdo = (torch.randn(bB, h, bS, bD, generator=gb).half().to(dev) for h in (bHq, bHkv, bHkv, bHq))
+        bout, blse = _C.attn_fp16_fwd(bq, bk, bv, True, None, want_lse=True)
+        msb = timed(lambda: s8.backward_cuda(bq, bk, bv, bout, blse, bdo, causal=True), args.steps, args.warmup, world)
+        bflops = 10.0 * bB * bHq * bS * bS * bD * 0.5      # five contractions, causal half
+        tb = world * bflops / (msb * 1e-3) / 1e12
+        line["backward"] = {"metric": "attn_bwd_tflops", "value": tb, "unit": "TFLOP/s", "ms_per_step": msb,
+                            "config": {"workload": f"B{bB} Hq{bHq} Hkv{bHkv} S{bS} D{bD} causal fp16, per GPU",
+                                       "flops": "10*B*Hq*S^2*D/2 (dV, dP, S, dQ, dK)"},
+                            "roofline": {"bound": "tensor", "achieved": tb / world, "peak": peaks["bf16_tflops"],
+                                         "unit": "TFLOP/s", "frac": tb / world / peaks["bf16_tflops"],
+                                         "peak_source": peaks["source"] + " bf16 dense (burst)", "traffic": None,
+                                         "kernels": "bwd_dq_kernel + bwd_dkv_kernel (mma.sync m16n8k16)"}}
+        del bq, bk, bv, bdo, bout, blse
 
     if rank == 0 and world == 1:
         try:
