@@ -168,6 +168,44 @@ size_t sl8_attn_fp16_fwd_workspace(const sl8_fp16_fwd_params* p);
 int sl8_attn_fp16_fwd(const sl8_fp16_fwd_params* p, void* workspace, size_t workspace_bytes,
                       void* stream);
 
+/* ---- packed variable-length prefill ------------------------------------------------- */
+
+/*
+ * Replaces `attn_int8_varlen` (reference csrc/kernel/attn_varlen_fwd.cu:45-110, kernel
+ * csrc/include/attn_varlen_fwd.cuh:25-190, binding csrc/fni8_api.cpp; Python wrapper
+ * superl8/ops.py:318-364).  Token-major packed tensors, the flash_attn_varlen convention:
+ * q / out [total_q, Hq, D], k / v [total_k, Hkv, D], q_scale [total_q, Hq] (folded),
+ * k_scale [total_k, Hkv]; cu_seqlens_q / cu_seqlens_k: int32 [B + 1] cumulative token offsets on
+ * the device.  Every sequence attends within itself; the causal diagonal is aligned to the
+ * sequence end.  D in {32, 64, 128} (the reference's set); V fp16 (reference) or bf16.
+ * max_seqlen_q sizes the grid (no host read of cu_seqlens).  workspace: 256 bytes (status word).
+ */
+typedef struct sl8_varlen_params {
+  const int8_t* q; const float* q_scale;
+  const int8_t* k; const float* k_scale;
+  const void* v; void* out;
+  const int32_t* cu_seqlens_q; const int32_t* cu_seqlens_k;
+  int32_t B, Hq, Hkv, D;
+  int64_t total_q, total_k;
+  int32_t max_seqlen_q;
+  int32_t v_dtype; int32_t causal;
+  int32_t backend;        /* SL8_BACKEND_* (tcgen05 for D = 64/128, else mma.sync) */
+} sl8_varlen_params;
+int sl8_attn_int8_varlen(const sl8_varlen_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Per-sequence K mean and smoothing + quantisation for the packed layout (reference
+ * superl8/ops.py:268-315 `_varlen_smooth_k`, then `quantize_int8_rowwise`):
+ * mean[b, h, :] = fp32 mean of k[cu[b]:cu[b+1], h, :]; k_i8 / k_scale = row quantisation of
+ * round_to_dtype(k - mean of the token's own sequence).  k_smoothed (nullable) receives the
+ * smoothed keys.  mean: fp32 [B, heads, D].
+ */
+int sl8_k_mean_packed(const void* k, int dtype, int64_t total_tokens, int32_t heads, int64_t D,
+                      const int32_t* cu_seqlens, int32_t n_seq, float* mean, void* stream);
+int sl8_smooth_quant_k_packed(const void* k, int dtype, int64_t total_tokens, int32_t heads, int64_t D,
+                              const int32_t* cu_seqlens, int32_t n_seq, const float* mean,
+                              int8_t* k_i8, float* k_scale, void* k_smoothed, void* stream);
+
 /* ---- backward -------------------------------------------------------------- */
 
 /*

@@ -144,6 +144,57 @@ def attention_fp32_ragged(q, k, v, seqlens_q, seqlens_k, causal=False, scale=Non
     return out
 
 
+def varlen_smooth_k(k: torch.Tensor, cu_seqlens_k) -> torch.Tensor:
+    """Reference superl8/ops.py:268-315 (`_varlen_smooth_k`): packed keys [total, H, D] minus the
+    per-(head, channel) fp32 mean of each token's own sequence (`mean(dim=1)` over the sequence's
+    tokens, as the reference forms it), rounded back to k's dtype."""
+    kf = k.detach().cpu().float()
+    bounds = [int(x) for x in cu_seqlens_k]
+    parts = []
+    for b in range(len(bounds) - 1):
+        seg = kf[bounds[b]:bounds[b + 1]]
+        if seg.shape[0]:
+            parts.append((seg.unsqueeze(0) - seg.unsqueeze(0).mean(dim=1, keepdim=True)).squeeze(0).to(k.dtype))
+    return torch.cat(parts, 0) if parts else kf.to(k.dtype)
+
+
+def attn_int8_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, causal=False, scale=None, rule: str = "cuda"):
+    """Reference superl8/ops.py:318-364 + csrc/include/attn_varlen_fwd.cuh:25-190 as a loop over
+    sequences: smooth K per sequence, quantise rows, fold the scale, and run the int8 kernel
+    mathematics (attn_int8_fwd above; bottom-right causal diagonal) on every sequence alone.
+    q, k, v packed [total, H, D]; returns [total_q, Hq, D] in v's dtype."""
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    k_s = varlen_smooth_k(k, cu_seqlens_k)
+    q_i8, q_scale = quantize_rowwise(q.detach().cpu(), rule)
+    k_i8, k_scale = quantize_rowwise(k_s, rule)
+    q_scale = fold_scale(q_scale, scale)
+    out = torch.zeros(q.shape, dtype=v.dtype)
+    cq, ck = [int(x) for x in cu_seqlens_q], [int(x) for x in cu_seqlens_k]
+    for b in range(len(cq) - 1):
+        qs_, ks_ = slice(cq[b], cq[b + 1]), slice(ck[b], ck[b + 1])
+        if cq[b + 1] == cq[b]:
+            continue
+        tr = lambda t: t.transpose(0, 1).unsqueeze(0).contiguous()      # [S, H, ...] -> [1, H, S, ...]
+        o = attn_int8_fwd(tr(q_i8[qs_]), tr(q_scale[qs_]).squeeze(-1), tr(k_i8[ks_]), tr(k_scale[ks_]).squeeze(-1),
+                          tr(v.detach().cpu()[ks_]), causal=causal)
+        out[qs_] = o[0].transpose(0, 1)
+    return out
+
+
+def attention_fp32_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, causal=False, scale=None):
+    """fp32 attention of every packed sequence on its own (the pattern of reference
+    tests/reference.py:154-169)."""
+    out = torch.zeros(q.shape, dtype=torch.float32)
+    cq, ck = [int(x) for x in cu_seqlens_q], [int(x) for x in cu_seqlens_k]
+    tr = lambda t: t.transpose(0, 1).unsqueeze(0)
+    for b in range(len(cq) - 1):
+        if cq[b + 1] > cq[b] and ck[b + 1] > ck[b]:
+            o = attention_fp32(tr(q[cq[b]:cq[b + 1]]), tr(k[ck[b]:ck[b + 1]]), tr(v[ck[b]:ck[b + 1]]), causal, scale)
+            out[cq[b]:cq[b + 1]] = o[0].transpose(0, 1)
+    return out
+
+
 def attention_lse_fp32(q, k, causal: bool = False, scale: float | None = None) -> torch.Tensor:
     """Natural-log row sums of the scaled, masked logits: what the forward saves for the
     backward, recomputed the way reference superl8/ops.py:49-58 does when it is missing."""

@@ -12,6 +12,7 @@
 
 #include "attn_decode.cuh"
 #include "attn_int8_fwd.cuh"
+#include "attn_varlen_fwd.cuh"
 #include "quant_rowwise.cuh"
 
 namespace {
@@ -105,6 +106,31 @@ extern "C" int ref_attn_int8_decode(const int8_t* q, const float* qs, const int8
     case 64: return decode_d<64>(q, qs, k, ks, (const __half*)v, (__half*)out, o_part, m_part, l_part, N, n_splits, BHq, Hq, g, s);
     case 128: return decode_d<128>(q, qs, k, ks, (const __half*)v, (__half*)out, o_part, m_part, l_part, N, n_splits, BHq, Hq, g, s);
     case 256: return decode_d<256>(q, qs, k, ks, (const __half*)v, (__half*)out, o_part, m_part, l_part, N, n_splits, BHq, Hq, g, s);
+  }
+  return -1;
+}
+
+// reference csrc/kernel/attn_varlen_fwd.cu:18-41 (grid and launch of the packed variable-length kernel)
+template <int D>
+static int varlen_d(const int8_t* q, const float* qs, const int8_t* k, const float* ks, const __half* v, __half* out,
+                    const int* cu_q, const int* cu_k, int batch, int max_seqlen_q, int h_q, int h_kv, int causal,
+                    cudaStream_t s) {
+  const dim3 grid((max_seqlen_q + fni8::BLOCK_M - 1) / fni8::BLOCK_M, (unsigned)batch, (unsigned)h_q);
+  if (causal)
+    fni8::attn_int8_varlen_fwd_kernel<D, true><<<grid, fni8::THREADS, 0, s>>>(q, qs, k, ks, v, out, cu_q, cu_k, h_q, h_kv, h_q / h_kv);
+  else
+    fni8::attn_int8_varlen_fwd_kernel<D, false><<<grid, fni8::THREADS, 0, s>>>(q, qs, k, ks, v, out, cu_q, cu_k, h_q, h_kv, h_q / h_kv);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ref_attn_int8_varlen(const int8_t* q, const float* qs, const int8_t* k, const float* ks, const void* v,
+                                    void* out, const int* cu_q, const int* cu_k, int batch, int max_seqlen_q, int Hq,
+                                    int Hkv, int D, int causal, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (D) {
+    case 32: return varlen_d<32>(q, qs, k, ks, (const __half*)v, (__half*)out, cu_q, cu_k, batch, max_seqlen_q, Hq, Hkv, causal, s);
+    case 64: return varlen_d<64>(q, qs, k, ks, (const __half*)v, (__half*)out, cu_q, cu_k, batch, max_seqlen_q, Hq, Hkv, causal, s);
+    case 128: return varlen_d<128>(q, qs, k, ks, (const __half*)v, (__half*)out, cu_q, cu_k, batch, max_seqlen_q, Hq, Hkv, causal, s);
   }
   return -1;
 }

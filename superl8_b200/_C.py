@@ -253,6 +253,45 @@ def attn_int8_decode(q, q_scale, k, k_scale, v, num_splits=-1, *, context_lens=N
     return out
 
 
+def attn_int8_varlen(q, q_scale, k, k_scale, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, causal=False, *,
+                     backend=_lib.SL8_BACKEND_AUTO):
+    """Packed variable-length prefill.  Reference binding `attn_int8_varlen`
+    (csrc/kernel/attn_varlen_fwd.cu:45-110): q / k int8 [total, H, D], scales fp32 [total, H],
+    v fp16 [total_k, Hkv, D], cu_seqlens int32 [B + 1]; returns [total_q, Hq, D] in v's dtype."""
+    what = "superl8_b200 varlen"
+    for t in (q, k, v, q_scale, k_scale, cu_seqlens_q, cu_seqlens_k):
+        _check(t.is_cuda, f"{what}: all inputs must be CUDA tensors")
+        _check(t.device == q.device, f"{what}: all inputs must be on the same device")
+    _check(q.dtype == torch.int8 and k.dtype == torch.int8, f"{what}: q/k must be int8")
+    _check(q_scale.dtype == torch.float32 and k_scale.dtype == torch.float32, f"{what}: scales must be float32")
+    _check(v.dtype in (torch.float16, torch.bfloat16), f"{what}: v must be float16 or bfloat16")
+    _check(cu_seqlens_q.dtype == torch.int32 and cu_seqlens_k.dtype == torch.int32, f"{what}: cu_seqlens must be int32")
+    _check(q.dim() == 3 and k.dim() == 3 and v.dim() == 3, f"{what}: expect [total,H,D]")
+    _check(all(t.is_contiguous() for t in (q, k, v, q_scale, k_scale, cu_seqlens_q, cu_seqlens_k)),
+           f"{what}: inputs must be contiguous")
+    total_q, H, D = q.shape
+    total_k, Hkv = k.shape[0], k.shape[1]
+    B = cu_seqlens_q.numel() - 1
+    _check(B >= 1 and cu_seqlens_k.numel() == B + 1, f"{what}: cu_seqlens mismatch")
+    _check(Hkv > 0 and H % Hkv == 0, f"{what}: H_q must be divisible by H_kv (GQA)")
+    _check(k.shape[2] == D and v.shape[2] == D and v.shape[1] == Hkv and v.shape[0] == total_k, f"{what}: K/V shape")
+    _check(q_scale.numel() == total_q * H and k_scale.numel() == total_k * Hkv, f"{what}: scale shape mismatch")
+    _check(D in (32, 64, 128), f"{what}: head dim must be 32/64/128, got {D}")
+    out = torch.empty((total_q, H, D), dtype=v.dtype, device=v.device)
+    if out.numel() == 0:
+        return out
+    p = _lib.VarlenParams(q=q.data_ptr(), q_scale=q_scale.data_ptr(), k=k.data_ptr(), k_scale=k_scale.data_ptr(),
+                          v=v.data_ptr(), out=out.data_ptr(), cu_seqlens_q=cu_seqlens_q.data_ptr(),
+                          cu_seqlens_k=cu_seqlens_k.data_ptr(), B=B, Hq=H, Hkv=Hkv, D=D, total_q=total_q,
+                          total_k=total_k, max_seqlen_q=int(max_seqlen_q), v_dtype=_DTYPE[v.dtype],
+                          causal=int(bool(causal)), backend=int(backend))
+    with torch.cuda.device(q.device):
+        ws = _status_buffer(q.device)
+        rc = _lib.load().sl8_attn_int8_varlen(C.byref(p), _ptr(ws), ws.numel() * 4, _stream(q.device))
+    _lib.check(rc, "attn_int8_varlen", 1)
+    return out
+
+
 def attn_bwd(q, k, v, o, do_, lse, scale, causal=False):
     """Reference binding csrc/fni8_api.cpp:256-259 (op csrc/kernel/attn_bwd.cu:62-109):
     (dq, dk, dv) of the attention with logits scale * q.k, from the forward's output ``o``, its

@@ -68,6 +68,16 @@ class DecodeParams(C.Structure):
     ]
 
 
+class VarlenParams(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("q_scale", C.c_void_p), ("k", C.c_void_p), ("k_scale", C.c_void_p),
+        ("v", C.c_void_p), ("out", C.c_void_p), ("cu_seqlens_q", C.c_void_p), ("cu_seqlens_k", C.c_void_p),
+        ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("D", C.c_int32),
+        ("total_q", C.c_int64), ("total_k", C.c_int64), ("max_seqlen_q", C.c_int32),
+        ("v_dtype", C.c_int32), ("causal", C.c_int32), ("backend", C.c_int32),
+    ]
+
+
 class BwdParams(C.Structure):
     _fields_ = [
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("dout", C.c_void_p),
@@ -95,6 +105,11 @@ SIGNATURES = {
                                     C.c_void_p, C.c_size_t, C.c_void_p]),
     "sl8_attn_fp16_fwd_workspace": (C.c_size_t, [C.POINTER(Fp16FwdParams)]),
     "sl8_attn_fp16_fwd": (C.c_int, [C.POINTER(Fp16FwdParams), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "sl8_attn_int8_varlen": (C.c_int, [C.POINTER(VarlenParams), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "sl8_k_mean_packed": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int32, C.c_int64, C.c_void_p, C.c_int32,
+                                    C.c_void_p, C.c_void_p]),
+    "sl8_smooth_quant_k_packed": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int32, C.c_int64, C.c_void_p,
+                                            C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "sl8_attn_bwd_workspace": (C.c_size_t, [C.POINTER(BwdParams)]),
     "sl8_attn_bwd": (C.c_int, [C.POINTER(BwdParams), C.c_void_p, C.c_size_t, C.c_void_p]),
     "sl8_choose_n_splits": (C.c_int, [C.c_int64, C.c_int64]),

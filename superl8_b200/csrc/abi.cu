@@ -71,3 +71,26 @@ int sl8_make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? SL8_OK : SL8_ERR_CUDA;
 }
+
+// Token-major packed tensor [tokens, heads, inner]: dimensions {inner, heads, tokens}, a box of
+// box_rows tokens of one head (coordinates: inner offset, head, first token).
+int sl8_make_tmap_packed(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t heads,
+                         uint64_t tokens, uint32_t box_inner, uint32_t box_rows, int swizzle_bytes) {
+  std::call_once(g_encode_once, resolve_encode);
+  if (g_encode == nullptr) return SL8_ERR_CUDA;
+  CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                           : (elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16
+                                                              : CU_TENSOR_MAP_DATA_TYPE_UINT32);
+  CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_NONE;
+  if (swizzle_bytes == 32) sw = CU_TENSOR_MAP_SWIZZLE_32B;
+  if (swizzle_bytes == 64) sw = CU_TENSOR_MAP_SWIZZLE_64B;
+  if (swizzle_bytes == 128) sw = CU_TENSOR_MAP_SWIZZLE_128B;
+  cuuint64_t dims[3] = {inner, heads ? heads : 1, tokens ? tokens : 1};
+  cuuint64_t strides[2] = {inner * elem_bytes, inner * elem_bytes * (heads ? heads : 1)};
+  cuuint32_t box[3] = {box_inner, 1, box_rows};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? SL8_OK : SL8_ERR_CUDA;
+}

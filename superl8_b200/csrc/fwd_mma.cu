@@ -34,6 +34,10 @@ struct FwdArgs {
   float scale_log2;     // 16-bit mode
   const void* mask;     // 16-bit mode: additive bias (natural log), element type of q, or null
   int64_t mask_sb, mask_sh, mask_sm, mask_sn;   // strides in elements, 0 on broadcast axes
+  // Packed token-major tensors [tokens, heads, D] (scales [tokens, heads]) when non-null:
+  // sequence b owns tokens [cu_q[b], cu_q[b+1]) of q / out and [cu_k[b], cu_k[b+1]) of k / v.
+  const int32_t* cu_q;
+  const int32_t* cu_k;
 };
 
 template <int D, bool I8>
@@ -49,15 +53,15 @@ struct MmaCfg {
   static constexpr int SMEM = Q_BYTES + K_BYTES + V_BYTES + kBN * 4;
 };
 
-// Copies `rows` x `row_bytes` from global (row pitch = row_bytes) into a padded
+// Copies `rows` x `row_bytes` from global (row pitch `pitch` bytes) into a padded
 // shared tile, 8 bytes at a time; rows >= valid_rows and the pad bytes become 0.
 __device__ __forceinline__ void stage_tile(uint8_t* dst, int dst_stride, int dst_row_bytes, const uint8_t* src,
-                                           int row_bytes, int rows, int valid_rows) {
+                                           int row_bytes, int rows, int valid_rows, int64_t pitch) {
   const int words = dst_row_bytes / 8;
   for (int idx = threadIdx.x; idx < rows * words; idx += kThreads) {
     const int r = idx / words, c = (idx % words) * 8;
     uint2 val = make_uint2(0, 0);
-    if (r < valid_rows && c < row_bytes) val = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)r * row_bytes + c));
+    if (r < valid_rows && c < row_bytes) val = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)r * pitch + c));
     *reinterpret_cast<uint2*>(dst + r * dst_stride + c) = val;
   }
 }
@@ -78,28 +82,39 @@ __global__ void __launch_bounds__(kThreads) fwd_mma_kernel(FwdArgs a) {
   const int b = (int)(bh / a.Hq);
   const int G = a.Hq / a.Hkv;
   const int64_t kv_bh = (int64_t)b * a.Hkv + (bh % a.Hq) / G;
-  const int m_len = a.seqlens_q ? min(max(a.seqlens_q[b], 0), a.M) : a.M;
-  const int n_len = a.seqlens_k ? min(max(a.seqlens_k[b], 0), a.N) : a.N;
+  const bool packed = a.cu_q != nullptr;
+  const int hq = (int)(bh % a.Hq), hkv = hq / G;
+  const int q0 = packed ? a.cu_q[b] : 0, k0 = packed ? a.cu_k[b] : 0;   // first token of the sequence
+  const int m_len = packed ? a.cu_q[b + 1] - q0 : (a.seqlens_q ? min(max(a.seqlens_q[b], 0), a.M) : a.M);
+  const int n_len = packed ? a.cu_k[b + 1] - k0 : (a.seqlens_k ? min(max(a.seqlens_k[b], 0), a.N) : a.N);
+  const int m_store = packed ? m_len : a.M;   // rows this block may write (packed: never a neighbour's)
+  // rows of one head: elements between consecutive rows, and where the head's first row is
+  const int64_t q_rowe = packed ? (int64_t)a.Hq * D : D, kv_rowe = packed ? (int64_t)a.Hkv * D : D;
+  const int64_t q_off = packed ? ((int64_t)q0 * a.Hq + hq) * D : bh * (int64_t)a.M * D;
+  const int64_t kv_off = packed ? ((int64_t)k0 * a.Hkv + hkv) * D : kv_bh * (int64_t)a.N * D;
+  const int64_t qs_row = packed ? a.Hq : 1, ks_row = packed ? a.Hkv : 1;
+  const float* qs_base = I8 ? a.q_scale + (packed ? (int64_t)q0 * a.Hq + hq : bh * (int64_t)a.M) : nullptr;
+  const float* ks_base = I8 ? a.k_scale + (packed ? (int64_t)k0 * a.Hkv + hkv : kv_bh * (int64_t)a.N) : nullptr;
   // heavy (late) query tiles first when causal
   const int m_block = (a.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x) * kBM;
-  VT* out_bh = reinterpret_cast<VT*>(a.out) + bh * (int64_t)a.M * D;
+  VT* out_bh = reinterpret_cast<VT*>(a.out) + q_off;
 
   if (m_block >= m_len) {  // padded rows of a ragged batch: zeros
     for (int idx = threadIdx.x; idx < kBM * D / 2; idx += kThreads) {
       const int r = idx / (D / 2), c = (idx % (D / 2)) * 2;
-      if (m_block + r < a.M) *reinterpret_cast<uint32_t*>(out_bh + (int64_t)(m_block + r) * D + c) = 0u;
+      if (m_block + r < m_store) *reinterpret_cast<uint32_t*>(out_bh + (int64_t)(m_block + r) * q_rowe + c) = 0u;
     }
     if (a.lse) for (int r = threadIdx.x; r < kBM; r += kThreads)
-        if (m_block + r < a.M) a.lse[bh * a.M + m_block + r] = -INFINITY;
+        if (m_block + r < m_store) a.lse[bh * a.M + m_block + r] = -INFINITY;
     return;
   }
 
-  const uint8_t* q_bh = reinterpret_cast<const uint8_t*>(a.q) + bh * (int64_t)a.M * D * C::QK_ELEM;
-  const uint8_t* k_bh = reinterpret_cast<const uint8_t*>(a.k) + kv_bh * (int64_t)a.N * D * C::QK_ELEM;
-  const uint8_t* v_bh = reinterpret_cast<const uint8_t*>(a.v) + kv_bh * (int64_t)a.N * D * 2;
+  const uint8_t* q_bh = reinterpret_cast<const uint8_t*>(a.q) + q_off * C::QK_ELEM;
+  const uint8_t* k_bh = reinterpret_cast<const uint8_t*>(a.k) + kv_off * C::QK_ELEM;
+  const uint8_t* v_bh = reinterpret_cast<const uint8_t*>(a.v) + kv_off * 2;
 
-  stage_tile(sq, C::QK_STRIDE, C::QK_STRIDE, q_bh + (int64_t)m_block * D * C::QK_ELEM, D * C::QK_ELEM, kBM,
-             m_len - m_block);
+  stage_tile(sq, C::QK_STRIDE, C::QK_STRIDE, q_bh + (int64_t)m_block * q_rowe * C::QK_ELEM, D * C::QK_ELEM, kBM,
+             m_len - m_block, q_rowe * C::QK_ELEM);
 
   const int causal_diag = a.causal ? n_len - m_len : 0;
   const int row0 = m_block + 16 * warp + g;       // this thread's rows: row0, row0 + 8
@@ -109,7 +124,7 @@ __global__ void __launch_bounds__(kThreads) fwd_mma_kernel(FwdArgs a) {
   for (int h = 0; h < 2; ++h) {
     const int m = row0 + 8 * h;
     qpos[h] = m + causal_diag;
-    qs[h] = I8 ? ((m < m_len) ? __ldg(a.q_scale + bh * a.M + m) : 0.f) : a.scale_log2;
+    qs[h] = I8 ? ((m < m_len) ? __ldg(qs_base + m * qs_row) : 0.f) : a.scale_log2;
   }
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   float o[C::NT][4];
@@ -124,12 +139,13 @@ __global__ void __launch_bounds__(kThreads) fwd_mma_kernel(FwdArgs a) {
 
   for (int n_block = n_begin; n_block < n_end; n_block += kBN) {
     __syncthreads();  // previous tile fully consumed (and Q staged on the first pass)
-    stage_tile(sk, C::QK_STRIDE, C::QK_STRIDE, k_bh + (int64_t)n_block * D * C::QK_ELEM, D * C::QK_ELEM, kBN,
-               n_len - n_block);
-    stage_tile(sv, C::V_STRIDE, C::V_STRIDE, v_bh + (int64_t)n_block * D * 2, D * 2, kBN, n_len - n_block);
+    stage_tile(sk, C::QK_STRIDE, C::QK_STRIDE, k_bh + (int64_t)n_block * kv_rowe * C::QK_ELEM, D * C::QK_ELEM, kBN,
+               n_len - n_block, kv_rowe * C::QK_ELEM);
+    stage_tile(sv, C::V_STRIDE, C::V_STRIDE, v_bh + (int64_t)n_block * kv_rowe * 2, D * 2, kBN, n_len - n_block,
+               kv_rowe * 2);
     if (I8 && threadIdx.x < kBN) {
       const int gn = n_block + threadIdx.x;
-      sks[threadIdx.x] = (gn < n_len) ? __ldg(a.k_scale + kv_bh * a.N + gn) : 0.f;
+      sks[threadIdx.x] = (gn < n_len) ? __ldg(ks_base + gn * ks_row) : 0.f;
     }
     __syncthreads();
 
@@ -256,10 +272,10 @@ __global__ void __launch_bounds__(kThreads) fwd_mma_kernel(FwdArgs a) {
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
     const int m = row0 + 8 * h;
-    if (m >= a.M) continue;
+    if (m >= m_store) continue;
     const bool live = m < m_len;
     const float inv = (live && l_run[h] > 0.f) ? 1.f / l_run[h] : 0.f;
-    VT* orow = out_bh + (int64_t)m * D;
+    VT* orow = out_bh + (int64_t)m * q_rowe;
 #pragma unroll
     for (int nt = 0; nt < D / 8; ++nt)
       *reinterpret_cast<uint32_t*>(orow + 8 * nt + 2 * t) = pack2<VT>(o[nt][2 * h] * inv, o[nt][2 * h + 1] * inv);
@@ -302,6 +318,17 @@ int sl8_fwd_mma_int8(const sl8_fwd_params* p, cudaStream_t s) {
   a.q = p->q; a.q_scale = p->q_scale; a.k = p->k; a.k_scale = p->k_scale; a.v = p->v; a.out = p->out;
   a.lse = p->lse; a.seqlens_q = p->seqlens_q; a.seqlens_k = p->seqlens_k;
   a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N; a.causal = p->causal; a.window_left = p->window_left;
+  if (p->v_dtype == SL8_F16) return launch_d<__half, true>(a, p->B, p->D, s);
+  if (p->v_dtype == SL8_BF16) return launch_d<__nv_bfloat16, true>(a, p->B, p->D, s);
+  return SL8_ERR_BAD_DTYPE;
+}
+
+// packed variable-length int8-QK forward on the mma.sync path; validated by the caller
+int sl8_fwd_mma_int8_varlen(const sl8_varlen_params* p, cudaStream_t s) {
+  FwdArgs a{};
+  a.q = p->q; a.q_scale = p->q_scale; a.k = p->k; a.k_scale = p->k_scale; a.v = p->v; a.out = p->out;
+  a.cu_q = p->cu_seqlens_q; a.cu_k = p->cu_seqlens_k;
+  a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->max_seqlen_q; a.N = 0; a.causal = p->causal; a.window_left = -1;
   if (p->v_dtype == SL8_F16) return launch_d<__half, true>(a, p->B, p->D, s);
   if (p->v_dtype == SL8_BF16) return launch_d<__nv_bfloat16, true>(a, p->B, p->D, s);
   return SL8_ERR_BAD_DTYPE;

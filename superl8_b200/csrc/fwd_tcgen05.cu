@@ -45,6 +45,7 @@
 #include <type_traits>
 
 int sl8_fwd_mma_int8(const sl8_fwd_params* p, cudaStream_t s);  // fwd_mma.cu
+int sl8_fwd_mma_int8_varlen(const sl8_varlen_params* p, cudaStream_t s);  // fwd_mma.cu
 
 namespace sl8 {
 namespace {
@@ -91,6 +92,11 @@ struct TcArgs {
   float* lse;
   const int32_t* seqlens_q;
   const int32_t* seqlens_k;
+  // Packed token-major tensors [tokens, heads, D] (scales [tokens, heads]) when non-null:
+  // sequence b owns tokens [cu_q[b], cu_q[b+1]) of q / out and [cu_k[b], cu_k[b+1]) of k / v.
+  // The tensor maps are then {D, heads, tokens} instead of {D, rows, batch * heads}.
+  const int32_t* cu_q;
+  const int32_t* cu_k;
   int* status;
   int Hq, Hkv, M, N;
   int causal, window_left;
@@ -205,7 +211,7 @@ __device__ __forceinline__ void softmax_pass(uint32_t (&r)[kTN], const float* __
   mx = fmaxf(mx0, mx1);
 }
 
-template <int D, typename VT, bool QK8>
+template <int D, typename VT, bool QK8, bool PACKED>
 __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                                                                const __grid_constant__ CUtensorMap k_map,
                                                                const __grid_constant__ CUtensorMap v_map, TcArgs a) {
@@ -221,23 +227,35 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
   const int b = (int)(bh / a.Hq);
   const int G = a.Hq / a.Hkv;
   const int kv_bh = b * a.Hkv + (int)(bh % a.Hq) / G;
-  const int m_len = a.seqlens_q ? min(max(a.seqlens_q[b], 0), a.M) : a.M;
-  const int n_len = a.seqlens_k ? min(max(a.seqlens_k[b], 0), a.N) : a.N;
+  constexpr bool packed = PACKED;   // token-major packed tensors (a.cu_q / a.cu_k set)
+  const int hq = (int)(bh % a.Hq), hkv = hq / G;
+  const int q0 = packed ? a.cu_q[b] : 0, k0 = packed ? a.cu_k[b] : 0;   // first token of the sequence
+  const int m_len = packed ? a.cu_q[b + 1] - q0 : (a.seqlens_q ? min(max(a.seqlens_q[b], 0), a.M) : a.M);
+  const int n_len = packed ? a.cu_k[b + 1] - k0 : (a.seqlens_k ? min(max(a.seqlens_k[b], 0), a.N) : a.N);
+  // Where this block writes: base of its head's rows, elements between rows, and the rows it
+  // may write (packed: never a neighbour's).
+  const int o_rows = packed ? m_len : a.M;
+  const int64_t o_row = packed ? (int64_t)a.Hq * D : D;
+  VT* const ob = reinterpret_cast<VT*>(a.out) + (packed ? ((int64_t)q0 * a.Hq + hq) * D : bh * (int64_t)a.M * D);
+  // TMA coordinates 1 and 2 of row r: dense (r, batch * heads + head), packed (head, first token + r)
+#define SL8_QC1(r) (packed ? hq : (r))
+#define SL8_QC2(r) (packed ? q0 + (r) : (int)bh)
+#define SL8_KC1(r) (packed ? hkv : (r))
+#define SL8_KC2(r) (packed ? k0 + (r) : kv_bh)
   const int m_block = (a.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x) * kTM;
   const int causal_diag = a.causal ? n_len - m_len : 0;
   const int n_end = a.causal ? max(0, min(n_len, m_block + kTM + causal_diag)) : n_len;
   int n_begin = 0;
   if (a.window_left >= 0) n_begin = max(0, (m_block + causal_diag - a.window_left + 1)) / kTN * kTN;
   const int ntiles = (m_block < m_len && n_end > n_begin) ? (n_end - n_begin + kTN - 1) / kTN : 0;
-  VT* out_bh = reinterpret_cast<VT*>(a.out) + bh * (int64_t)a.M * D;
 
   if (ntiles == 0) {  // no visible key for any row of the tile (or padded rows): zeros
     for (int idx = threadIdx.x; idx < kTM * (D / 8); idx += kTcThreads) {
       const int r = idx / (D / 8), c = (idx % (D / 8)) * 8;
-      if (m_block + r < a.M) *reinterpret_cast<uint4*>(out_bh + (int64_t)(m_block + r) * D + c) = make_uint4(0, 0, 0, 0);
+      if (m_block + r < o_rows) *reinterpret_cast<uint4*>(ob + (int64_t)(m_block + r) * o_row + c) = make_uint4(0, 0, 0, 0);
     }
     if (a.lse) for (int r = threadIdx.x; r < kTM; r += kTcThreads)
-        if (m_block + r < a.M) a.lse[bh * a.M + m_block + r] = -INFINITY;
+        if (m_block + r < o_rows) a.lse[bh * a.M + m_block + r] = -INFINITY;
     return;
   }
 
@@ -276,7 +294,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
 #pragma unroll
       for (int c = 0; c < C::QSUBS; ++c)
         tma_load_3d(smem + C::OFF_Q + c * C::Q_SUB_BYTES, &q_map, &bars[Q_FULL], c * (C::QROW / (QK8 ? 1 : 2)),
-                    m_block, (int)bh);
+                    SL8_QC1(m_block), SL8_QC2(m_block));
     }
     auto load_k = [&](int t) -> bool {   // lane 0 only
       const int ks = t % C::NKS;
@@ -285,7 +303,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
 #pragma unroll
       for (int c = 0; c < C::QSUBS; ++c)
         tma_load_3d(smem + C::OFF_K + ks * C::K_TILE_BYTES + c * C::K_SUB_BYTES, &k_map, &bars[K_FULL + ks],
-                    c * (C::QROW / (QK8 ? 1 : 2)), n_begin + t * kTN, kv_bh);
+                    c * (C::QROW / (QK8 ? 1 : 2)), SL8_KC1(n_begin + t * kTN), SL8_KC2(n_begin + t * kTN));
       return true;
     };
     // K runs two tiles ahead of V: the issuer asks for K_{j+2} as soon as P.V_j is queued.
@@ -300,7 +318,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
 #pragma unroll
       for (int i = 0; i < kTN / 32; ++i) {
         const int n = n_begin + t * kTN + lane + 32 * i;
-        dst[i] = (QK8 && t < ntiles && n < n_len) ? __ldg(a.k_scale + (int64_t)kv_bh * a.N + n) : 0.f;
+        dst[i] = (QK8 && t < ntiles && n < n_len) ? __ldg(packed ? a.k_scale + ((int64_t)(k0 + n) * a.Hkv + hkv) : a.k_scale + (int64_t)kv_bh * a.N + n) : 0.f;
       }
     };
     float ks0[kTN / 32], ks1[kTN / 32], ks2[kTN / 32];
@@ -333,7 +351,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
 #pragma unroll
           for (int c = 0; c < C::VSUBS; ++c)
             tma_load_3d(smem + C::OFF_V + vs * C::V_TILE_BYTES + c * C::V_SUB_BYTES, &v_map, &bars[V_FULL + vs],
-                        c * 64, n_block, kv_bh);
+                        c * 64, SL8_KC1(n_block), SL8_KC2(n_block));
         }
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -407,7 +425,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
     const int lg = warp;
     const int row = 32 * lg + lane;
     const int m = m_block + row;                // this thread's query row
-    const float qs = QK8 ? ((m < m_len) ? __ldg(a.q_scale + bh * a.M + m) : 0.f) : a.scale_log2;
+    const float qs = QK8 ? ((m < m_len) ? __ldg(packed ? a.q_scale + ((int64_t)(q0 + m) * a.Hq + hq) : a.q_scale + bh * a.M + m) : 0.f) : a.scale_log2;
     const int qpos = m + causal_diag;
     const uint32_t t_row = tmem + ((uint32_t)(32 * lg) << 16);
     const uint32_t t_o = t_row + C::COL_O;
@@ -496,14 +514,14 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
       const float l_tot = l_run;
       const bool live = m < m_len;
       const float inv = (live && l_tot > 0.f) ? 1.f / l_tot : 0.f;
-#pragma unroll 1
+  #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
         tc_ld32(t_o + 32 * c, o);
         tc_wait_ld();
         tc_regs_ready(o);
-        if (m < a.M) {
-          uint4* dst = reinterpret_cast<uint4*>(out_bh + (int64_t)m * D + 32 * c);
+        if (m < o_rows) {
+          uint4* dst = reinterpret_cast<uint4*>(ob + (int64_t)m * o_row + 32 * c);
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             uint4 w;
@@ -515,7 +533,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
           }
         }
       }
-      if (a.lse != nullptr && m < a.M)
+      if (a.lse != nullptr && m < o_rows)
         a.lse[bh * a.M + m] = (live && l_tot > 0.f) ? (m_run * 0.6931471805599453f + logf(l_tot)) : -INFINITY;
     }
     tc_fence_before();
@@ -604,29 +622,45 @@ __global__ void __launch_bounds__(128) qk_logits_kernel(const __grid_constant__ 
   }
 }
 
+// Dense call: M, N = rows per head.  Packed call (a.cu_q set): M = longest query sequence (sizes
+// the grid), total_q / total_k = tokens in the packed tensors.
 template <int D, typename VT, bool QK8>
 int launch_tc_impl(const void* q, const void* k, const void* v, int B, int Hq, int Hkv, int M, int N, const TcArgs& a,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, int64_t total_q = 0, int64_t total_k = 0) {
   using C = TcCfg<D, QK8>;
   constexpr int es = QK8 ? 1 : 2;
   CUtensorMap q_map, k_map, v_map;
-  int rc = sl8_make_tmap_3d(&q_map, q, es, D, M, (uint64_t)B * Hq, C::QROW / es, kTM, C::QROW);
-  if (rc == SL8_OK) rc = sl8_make_tmap_3d(&k_map, k, es, D, N, (uint64_t)B * Hkv, C::QROW / es, kTN, C::QROW);
-  if (rc == SL8_OK) rc = sl8_make_tmap_3d(&v_map, v, 2, D, N, (uint64_t)B * Hkv, 64, kTN, 128);
+  int rc;
+  if (a.cu_q != nullptr) {
+    rc = sl8_make_tmap_packed(&q_map, q, es, D, Hq, total_q, C::QROW / es, kTM, C::QROW);
+    if (rc == SL8_OK) rc = sl8_make_tmap_packed(&k_map, k, es, D, Hkv, total_k, C::QROW / es, kTN, C::QROW);
+    if (rc == SL8_OK) rc = sl8_make_tmap_packed(&v_map, v, 2, D, Hkv, total_k, 64, kTN, 128);
+  } else {
+    rc = sl8_make_tmap_3d(&q_map, q, es, D, M, (uint64_t)B * Hq, C::QROW / es, kTM, C::QROW);
+    if (rc == SL8_OK) rc = sl8_make_tmap_3d(&k_map, k, es, D, N, (uint64_t)B * Hkv, C::QROW / es, kTN, C::QROW);
+    if (rc == SL8_OK) rc = sl8_make_tmap_3d(&v_map, v, 2, D, N, (uint64_t)B * Hkv, 64, kTN, 128);
+  }
   if (rc != SL8_OK) return rc;
-  SL8_CUDA_TRY(cudaFuncSetAttribute(fwd_tc_kernel<D, VT, QK8>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
   dim3 grid((M + kTM - 1) / kTM, (unsigned)((int64_t)B * Hq));
-  fwd_tc_kernel<D, VT, QK8><<<grid, kTcThreads, C::SMEM, stream>>>(q_map, k_map, v_map, a);
+  if (a.cu_q != nullptr) {
+    if (!QK8 || D == 256) return SL8_ERR_UNSUPPORTED;   // the packed op is int8-QK, D <= 128
+    constexpr bool kPk = QK8 && D != 256;               // (keeps the unused instantiations out of the image)
+    SL8_CUDA_TRY(cudaFuncSetAttribute(fwd_tc_kernel<D, VT, QK8, kPk>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+    fwd_tc_kernel<D, VT, QK8, kPk><<<grid, kTcThreads, C::SMEM, stream>>>(q_map, k_map, v_map, a);
+  } else {
+    SL8_CUDA_TRY(cudaFuncSetAttribute(fwd_tc_kernel<D, VT, QK8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+    fwd_tc_kernel<D, VT, QK8, false><<<grid, kTcThreads, C::SMEM, stream>>>(q_map, k_map, v_map, a);
+  }
   return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
 }
 
 template <typename VT, bool QK8>
 int launch_tc_d(int D, const void* q, const void* k, const void* v, int B, int Hq, int Hkv, int M, int N,
-                const TcArgs& a, cudaStream_t s) {
+                const TcArgs& a, cudaStream_t s, int64_t total_q = 0, int64_t total_k = 0) {
   switch (D) {
-    case 64: return launch_tc_impl<64, VT, QK8>(q, k, v, B, Hq, Hkv, M, N, a, s);
-    case 128: return launch_tc_impl<128, VT, QK8>(q, k, v, B, Hq, Hkv, M, N, a, s);
-    case 256: return launch_tc_impl<256, VT, QK8>(q, k, v, B, Hq, Hkv, M, N, a, s);
+    case 64: return launch_tc_impl<64, VT, QK8>(q, k, v, B, Hq, Hkv, M, N, a, s, total_q, total_k);
+    case 128: return launch_tc_impl<128, VT, QK8>(q, k, v, B, Hq, Hkv, M, N, a, s, total_q, total_k);
+    case 256: return launch_tc_impl<256, VT, QK8>(q, k, v, B, Hq, Hkv, M, N, a, s, total_q, total_k);
   }
   return SL8_ERR_UNSUPPORTED;
 }
@@ -680,6 +714,37 @@ extern "C" int sl8_attn_int8_fwd(const sl8_fwd_params* p, void* workspace, size_
   return p->v_dtype == SL8_F16
              ? launch_tc_d<__half, true>(p->D, p->q, p->k, p->v, p->B, p->Hq, p->Hkv, p->M, p->N, a, s)
              : launch_tc_d<__nv_bfloat16, true>(p->D, p->q, p->k, p->v, p->B, p->Hq, p->Hkv, p->M, p->N, a, s);
+}
+
+extern "C" int sl8_attn_int8_varlen(const sl8_varlen_params* p, void* workspace, size_t workspace_bytes,
+                                    void* stream) {
+  if (p == nullptr) return SL8_ERR_NULL;
+  if (p->B < 0 || p->Hq < 0 || p->Hkv < 0 || p->total_q < 0 || p->total_k < 0 || p->max_seqlen_q < 0)
+    return SL8_ERR_BAD_SHAPE;
+  if (p->D != 32 && p->D != 64 && p->D != 128) return SL8_ERR_BAD_HEAD_DIM;
+  if (p->v_dtype != SL8_F16 && p->v_dtype != SL8_BF16) return SL8_ERR_BAD_DTYPE;
+  if (p->Hq > 0 && (p->Hkv <= 0 || p->Hq % p->Hkv != 0)) return SL8_ERR_BAD_SHAPE;
+  if (p->B == 0 || p->Hq == 0 || p->total_q == 0 || p->max_seqlen_q == 0) return SL8_OK;   // nothing to write
+  if (!p->q || !p->q_scale || !p->out || !p->cu_seqlens_q || !p->cu_seqlens_k) return SL8_ERR_NULL;
+  if (p->total_k > 0 && (!p->k || !p->k_scale || !p->v)) return SL8_ERR_NULL;
+  if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->out)) return SL8_ERR_MISALIGNED;
+  if ((int64_t)p->B * p->Hq > 65535 || p->total_q > INT32_MAX || p->total_k > INT32_MAX) return SL8_ERR_TOO_LARGE;
+  if (workspace == nullptr || workspace_bytes < 256) return SL8_ERR_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int backend = p->backend;
+  const bool tc_ok = (p->D == 64 || p->D == 128) && p->total_k > 0;
+  if (backend == SL8_BACKEND_AUTO) backend = tc_ok ? SL8_BACKEND_TCGEN05 : SL8_BACKEND_MMA;
+  if (backend == SL8_BACKEND_MMA) return sl8_fwd_mma_int8_varlen(p, s);
+  if (backend != SL8_BACKEND_TCGEN05 || !tc_ok) return SL8_ERR_UNSUPPORTED;
+  TcArgs a{};
+  a.q_scale = p->q_scale; a.k_scale = p->k_scale; a.out = p->out;
+  a.cu_q = p->cu_seqlens_q; a.cu_k = p->cu_seqlens_k; a.status = reinterpret_cast<int*>(workspace);
+  a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->max_seqlen_q; a.N = 0; a.causal = p->causal; a.window_left = -1;
+  return p->v_dtype == SL8_F16
+             ? launch_tc_d<__half, true>(p->D, p->q, p->k, p->v, p->B, p->Hq, p->Hkv, p->max_seqlen_q, 0, a, s,
+                                         p->total_q, p->total_k)
+             : launch_tc_d<__nv_bfloat16, true>(p->D, p->q, p->k, p->v, p->B, p->Hq, p->Hkv, p->max_seqlen_q, 0, a, s,
+                                                p->total_q, p->total_k);
 }
 
 // 16-bit Q/K forward on the tcgen05 path (D = 64, 128, 256, N > 0); parameters were validated

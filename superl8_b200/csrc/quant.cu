@@ -31,10 +31,27 @@ struct QuantArgs {
   int32_t* flag;        // query mode (nullable): OR-ed with 1 if any row is outlier dominated
   int64_t rows;
   int64_t rows_per_head;
+  // key mode on a token-major packed tensor [tokens, heads, K]: row = token * heads + head and
+  // the mean row is sequence(token) * heads + head, sequence bounds in cu_seqlens[n_seq + 1]
+  const int32_t* cu_seqlens;
+  int n_seq;
+  int heads;
   int K;
   float fold;
   float ratio_threshold;
 };
+
+// Row of the mean table for a row of the key tensor (see QuantArgs).
+__device__ __forceinline__ int64_t mean_row(const QuantArgs& a, int64_t row) {
+  if (a.cu_seqlens == nullptr) return row / a.rows_per_head;
+  const int token = (int)(row / a.heads), head = (int)(row % a.heads);
+  int lo = 0, hi = a.n_seq;   // largest s with cu_seqlens[s] <= token
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(a.cu_seqlens + mid) <= token) lo = mid; else hi = mid;
+  }
+  return (int64_t)lo * a.heads + head;
+}
 
 __device__ __forceinline__ float quant_one(float x, float s) {
   float v = rintf(__fdiv_rn(x, s));
@@ -118,7 +135,7 @@ __global__ void __launch_bounds__(kQuantThreads) quant_rows_vec_kernel(QuantArgs
       Vec8<T>::unpack(raw[v], f[v]);
     }
     if (MODE == kKeySmooth) {
-      const int64_t bh = live ? row / a.rows_per_head : 0;
+      const int64_t bh = live ? mean_row(a, row) : 0;
       const float* mr = a.mean + bh * a.K;
 #pragma unroll
       for (int v = 0; v < NV; ++v) {
@@ -250,7 +267,7 @@ __global__ void __launch_bounds__(kQuantThreads) quant_rows_generic_kernel(Quant
   for (int64_t row = (int64_t)blockIdx.x * (kQuantThreads / 32) + warp; row < a.rows;
        row += (int64_t)gridDim.x * (kQuantThreads / 32)) {
     const T* xr = reinterpret_cast<const T*>(a.x) + row * a.K;
-    const float* mr = (MODE == kKeySmooth) ? a.mean + (row / a.rows_per_head) * a.K : nullptr;
+    const float* mr = (MODE == kKeySmooth) ? a.mean + mean_row(a, row) * a.K : nullptr;
     auto elem = [&](int c) -> float {
       float v = to_f32<T>(xr[c]);
       if (MODE == kKeySmooth) v = to_f32<T>(from_f32<T>(v - mr[c]));
@@ -395,10 +412,83 @@ __global__ void k_mean_finish_kernel(const float* __restrict__ partial, int nchu
   }
 }
 
+// Packed token-major keys [tokens, heads, K]: mean over the tokens of one sequence for one head.
+// grid (heads, sequences).  Same thread map and fixed summation order as the dense kernel:
+// thread (rl, cv) sums tokens rl, rl + RL, ... for the 8 columns of vector cv, the RL lanes are
+// added in index order, and the sum is multiplied by 1 / len.
+template <typename T>
+__global__ void __launch_bounds__(kMeanThreads) k_mean_packed_kernel(
+    const T* __restrict__ k, int heads, int K, const int32_t* __restrict__ cu_seqlens, float* __restrict__ mean) {
+  extern __shared__ float red[];  // [RL][K]
+  const int kvec = K >> 3;
+  int cvp = 1;
+  while (cvp < kvec) cvp <<= 1;
+  const int RL = kMeanThreads / cvp;
+  const int cv = threadIdx.x % cvp;
+  const int rl = threadIdx.x / cvp;
+  const int head = blockIdx.x, seq = blockIdx.y;
+  const int64_t t0 = cu_seqlens[seq], t1 = cu_seqlens[seq + 1];
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (cv < kvec) {
+    for (int64_t t = t0 + rl; t < t1; t += RL) {
+      const uint4 u = __ldg(reinterpret_cast<const uint4*>(k + (t * heads + head) * K) + cv);
+      float f[8];
+      Vec8<T>::unpack(u, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[rl * K + cv * 8 + i] = acc[i];
+  }
+  __syncthreads();
+  const int64_t len = t1 - t0;
+  const float inv = len > 0 ? __fdiv_rn(1.0f, (float)len) : 0.0f;
+  for (int c = threadIdx.x; c < K; c += kMeanThreads) {
+    float s = 0.0f;
+    for (int r = 0; r < RL; ++r) s += red[r * K + c];
+    mean[((int64_t)seq * heads + head) * K + c] = s * inv;
+  }
+}
+
 }  // namespace
 }  // namespace sl8
 
 using namespace sl8;
+
+extern "C" int sl8_k_mean_packed(const void* k, int dtype, int64_t total_tokens, int32_t heads, int64_t D,
+                                 const int32_t* cu_seqlens, int32_t n_seq, float* mean, void* stream) {
+  if (total_tokens < 0 || heads < 0 || D < 0 || n_seq < 0) return SL8_ERR_BAD_SHAPE;
+  if (dtype != SL8_F16 && dtype != SL8_BF16) return SL8_ERR_BAD_DTYPE;
+  if (D % 8 != 0 || D > 2048) return SL8_ERR_BAD_HEAD_DIM;
+  if (n_seq == 0 || heads == 0 || D == 0) return SL8_OK;
+  if (mean == nullptr || cu_seqlens == nullptr || (total_tokens > 0 && k == nullptr)) return SL8_ERR_NULL;
+  if (!aligned16(k)) return SL8_ERR_MISALIGNED;
+  if (n_seq > 65535) return SL8_ERR_TOO_LARGE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int cvp = 1;
+  while (cvp < (int)(D >> 3)) cvp <<= 1;
+  const size_t smem = (size_t)(kMeanThreads / cvp) * D * sizeof(float);
+  dim3 grid((unsigned)heads, (unsigned)n_seq);
+  if (dtype == SL8_F16)
+    k_mean_packed_kernel<__half><<<grid, kMeanThreads, smem, s>>>(reinterpret_cast<const __half*>(k), heads, (int)D, cu_seqlens, mean);
+  else
+    k_mean_packed_kernel<__nv_bfloat16><<<grid, kMeanThreads, smem, s>>>(reinterpret_cast<const __nv_bfloat16*>(k), heads, (int)D, cu_seqlens, mean);
+  return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
+}
+
+extern "C" int sl8_smooth_quant_k_packed(const void* k, int dtype, int64_t total_tokens, int32_t heads, int64_t D,
+                                         const int32_t* cu_seqlens, int32_t n_seq, const float* mean,
+                                         int8_t* k_i8, float* k_scale, void* k_smoothed, void* stream) {
+  if (total_tokens < 0 || heads < 0 || D < 0 || n_seq < 0) return SL8_ERR_BAD_SHAPE;
+  if (D > (1 << 30)) return SL8_ERR_TOO_LARGE;
+  if (dtype == SL8_F32) return SL8_ERR_BAD_DTYPE;
+  if (total_tokens * heads > 0 && (mean == nullptr || cu_seqlens == nullptr || n_seq == 0)) return SL8_ERR_NULL;
+  QuantArgs a{};
+  a.x = k; a.q = k_i8; a.scale = k_scale; a.mean = mean; a.smoothed = k_smoothed;
+  a.rows = total_tokens * heads; a.K = (int)D; a.rows_per_head = 1;
+  a.cu_seqlens = cu_seqlens; a.n_seq = n_seq; a.heads = heads;
+  return dispatch<kKeySmooth>(a, dtype, static_cast<cudaStream_t>(stream));
+}
 
 extern "C" int sl8_quantize_i8_rowwise(const void* x, int x_dtype, int64_t M, int64_t K, int8_t* q,
                                        float* scale, void* stream) {

@@ -325,3 +325,7 @@ __host__ __device__ __forceinline__ uint32_t umma_idesc(uint32_t c_fmt, uint32_t
 // [heads, rows, inner] contiguous tensor.  Implemented in abi.cu.
 int sl8_make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t rows,
                      uint64_t heads, uint32_t box_inner, uint32_t box_rows, int swizzle_bytes);
+// The same for a token-major packed tensor [tokens, heads, inner]: dimensions {inner, heads,
+// tokens}, box = box_rows tokens of one head.
+int sl8_make_tmap_packed(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t heads,
+                         uint64_t tokens, uint32_t box_inner, uint32_t box_rows, int swizzle_bytes);

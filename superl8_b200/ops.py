@@ -7,7 +7,7 @@ import math
 import torch
 
 from . import _C, _lib
-from .quant import _capturing, quantize_q, quantize_qk, smooth_quantize_k, k_mean
+from .quant import _capturing, quantize_q, quantize_qk, smooth_quantize_k, k_mean, varlen_smooth_quantize_k
 
 last_gate_decision: bool | None = None  # whether the most recent attn_int8_fwd call was demoted
 
@@ -58,6 +58,21 @@ def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, 
 def attn_fp16_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, mask=None, window_left: int = -1):
     """Full-precision forward (reference superl8/ops.py:178-227)."""
     return _C.attn_fp16_fwd(q.contiguous(), k.contiguous(), v.contiguous(), causal, scale, window_left, mask)
+
+
+def attn_int8_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int, max_seqlen_k: int, *,
+                     causal: bool = False, scale: float | None = None):
+    """Packed variable-length int8 prefill (reference superl8/ops.py:318-364): q, k, v token-major
+    [total_tokens, H, D] fp16, cu_seqlens int32 [batch + 1]; every sequence attends within itself,
+    the causal diagonal is aligned to the sequence end; K is smoothed with the mean of the token's
+    own sequence.  Returns [total_q, H, D] in v's dtype.  ``max_seqlen_k`` is accepted for
+    signature compatibility (the reference uses it to detect equal-length batches on the host)."""
+    softmax_scale = (1.0 / math.sqrt(q.shape[-1])) if scale is None else float(scale)
+    q_i8, q_scale, _ = quantize_q(q, softmax_scale)
+    k_i8, k_scale, _, _ = varlen_smooth_quantize_k(k, cu_seqlens_k)
+    return _C.attn_int8_varlen(q_i8, q_scale.squeeze(-1).contiguous(), k_i8, k_scale.squeeze(-1).contiguous(),
+                               v.contiguous(), cu_seqlens_q.contiguous(), cu_seqlens_k.contiguous(),
+                               int(max_seqlen_q), causal)
 
 
 def backward_cuda(q, k, v, out, lse, d_out, *, causal: bool = False, scale: float | None = None):

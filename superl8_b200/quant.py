@@ -92,6 +92,44 @@ def smooth_quantize_k(k: torch.Tensor, mean: torch.Tensor, want_smoothed: bool =
     return k_i8, k_scale, k_s
 
 
+def varlen_smooth_quantize_k(k: torch.Tensor, cu_seqlens_k: torch.Tensor, want_smoothed: bool = False,
+                             k_mean_override: torch.Tensor | None = None):
+    """Packed keys [total, H, D]: per-sequence K mean (reference superl8/ops.py:268-315
+    `_varlen_smooth_k`), then k_s = dtype(float(k) - mean of the token's own sequence) and the row
+    quantiser, all on the device with no read of cu_seqlens on the host.  ``k_mean_override``
+    (fp32 [B, H, D]) replaces the computed means (exact reproduction of another implementation's).
+    Returns (k_i8 [total, H, D], k_scale [total, H, 1], k_mean fp32 [B, H, D], k_s or None)."""
+    _require_cuda(k, "varlen_smooth_quantize_k")
+    if k.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("superl8_b200 varlen_smooth_quantize_k: k must be float16 or bfloat16")
+    if k.dim() != 3:
+        raise RuntimeError("superl8_b200 varlen_smooth_quantize_k: expect [total,H,D]")
+    k = k.contiguous()
+    cu = cu_seqlens_k.contiguous()
+    total, H, D = k.shape
+    B = cu.numel() - 1
+    if k_mean_override is not None:
+        mean = k_mean_override.to(device=k.device, dtype=torch.float32).reshape(B, H, D).contiguous()
+    else:
+        mean = torch.zeros((B, H, D), dtype=torch.float32, device=k.device)
+    k_i8 = torch.empty(k.shape, dtype=torch.int8, device=k.device)
+    k_scale = torch.empty((total, H, 1), dtype=torch.float32, device=k.device)
+    k_s = torch.empty_like(k) if want_smoothed else None
+    if k.numel() and B > 0:
+        lib = _lib.load()
+        with torch.cuda.device(k.device):
+            st = _C._stream(k.device)
+            if k_mean_override is None:
+                rc = lib.sl8_k_mean_packed(k.data_ptr(), _C._DTYPE[k.dtype], total, H, D, cu.data_ptr(), B,
+                                           mean.data_ptr(), st)
+                _lib.check(rc, "k_mean_packed", 1)
+            rc = lib.sl8_smooth_quant_k_packed(k.data_ptr(), _C._DTYPE[k.dtype], total, H, D, cu.data_ptr(), B,
+                                               mean.data_ptr(), k_i8.data_ptr(), k_scale.data_ptr(),
+                                               None if k_s is None else k_s.data_ptr(), st)
+            _lib.check(rc, "smooth_quant_k_packed", 1)
+    return k_i8, k_scale, mean, k_s
+
+
 def quantize_q(q: torch.Tensor, softmax_scale: float, want_gate: bool = False,
                ratio_threshold: float = OUTLIER_RATIO_THRESHOLD):
     """Q prologue in one pass: codes, folded scale [..., M, 1] and (optionally) the

@@ -181,6 +181,23 @@ def backward_cases():
     np.savez_compressed(OUT / "attn_backward.npz", **out)
 
 
+def varlen_cases():
+    """Packed-layout K prologue of the reference: superl8/ops.py::_varlen_smooth_k (ragged and
+    equal-length branches) followed by its row quantiser."""
+    from superl8.ops import _varlen_smooth_k
+
+    out = {}
+    g = gen(61)
+    for name, lens, H, D in (("ragged", [37, 5, 0, 120, 64], 2, 64), ("equal", [48, 48, 48], 3, 32)):
+        cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
+        k = (torch.randn(int(cu[-1]), H, D, generator=g) + 0.3).half()
+        k_s = _varlen_smooth_k(k, cu, max(lens))
+        k_i8, k_scale = quantize_int8_rowwise(k_s)
+        out[f"{name}__k"], out[f"{name}__cu"] = bits(k), cu.numpy()
+        out[f"{name}__k_s"], out[f"{name}__k_i8"], out[f"{name}__k_scale"] = bits(k_s), k_i8.numpy(), k_scale.numpy()
+    np.savez_compressed(OUT / "varlen_prologue.npz", **out)
+
+
 if __name__ == "__main__":
     torch.set_num_threads(1)
     quant_cases()
@@ -189,5 +206,6 @@ if __name__ == "__main__":
     qk_cases()
     attention_cases()
     backward_cases()
+    varlen_cases()
     for f in sorted(OUT.glob("*.npz")):
         print(f.name, f.stat().st_size)

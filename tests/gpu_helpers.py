@@ -72,3 +72,13 @@ def quantized_inputs(cfg, B, Hq, Hkv, M, D, N=None, dtype=torch.float16, device=
              k_scale=k_scale.squeeze(-1).contiguous(), k_mean=k_mean)
     d["dev"] = {n: t.to(device) for n, t in d.items()}
     return d
+
+
+def ref_attn_int8_varlen(q_i8, q_scale, k_i8, k_scale, v, cu_q, cu_k, max_seqlen_q, causal):
+    """The reference's packed variable-length kernel on the same int8 inputs."""
+    total_q, Hq, D = q_i8.shape
+    out = torch.empty((total_q, Hq, D), dtype=torch.float16, device=v.device)
+    rc = ref_lib().ref_attn_int8_varlen(_p(q_i8), _p(q_scale), _p(k_i8), _p(k_scale), _p(v), _p(out), _p(cu_q), _p(cu_k),
+                                        cu_q.numel() - 1, int(max_seqlen_q), Hq, k_i8.shape[1], D, int(causal), _stream())
+    assert rc == 0
+    return out

@@ -135,3 +135,26 @@ def test_backward_restatement_matches_the_reference_gradients():
                 # rounds O to fp16; the analytic form reads the stored fp16 O in D = sum(dO * O)
                 tol = 2e-5 if name.startswith(("mha", "rect")) else 2e-3
                 assert float((got - ref).abs().max()) <= tol * max(1.0, float(ref.abs().max())), (name, key)
+
+
+def test_varlen_k_prologue_matches_the_reference():
+    # reference superl8/ops.py::_varlen_smooth_k (ragged and equal-length branches) + its row quantiser
+    g = np.load(GOLDEN / "varlen_prologue.npz")
+    for name in ("ragged", "equal"):
+        k = from_bits(g[f"{name}__k"], "float16")
+        cu = g[f"{name}__cu"]
+        k_s = oracle.varlen_smooth_k(k, cu)
+        assert np.array_equal(k_s.view(torch.int16).numpy(), g[f"{name}__k_s"]), name
+        q, s = oracle.quantize_rowwise(k_s, rule="cpu")
+        assert np.array_equal(q.numpy(), g[f"{name}__k_i8"]) and np.array_equal(s.numpy(), g[f"{name}__k_scale"]), name
+
+
+def test_varlen_restatement_equals_the_dense_one_per_sequence():
+    # one packed sequence == the dense restatement on that sequence
+    q, k, v = oracle.make_batch(7, 1, 4, 2, 90, 64, Sk=130)
+    pk = lambda t: t[0].transpose(0, 1).contiguous()
+    cu_q, cu_k = [0, 90], [0, 130]
+    out = oracle.attn_int8_varlen(pk(q), pk(k), pk(v), cu_q, cu_k, causal=True)
+    q_i8, q_scale, k_i8, k_scale, _ = oracle.quantize_qk(q, k)
+    ref = oracle.attn_int8_fwd(q_i8, q_scale.squeeze(-1), k_i8, k_scale.squeeze(-1), v, causal=True)
+    assert oracle.cos_sim(out, pk(ref)) >= 0.99999
