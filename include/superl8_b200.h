@@ -264,6 +264,25 @@ int sl8_attn_int8_decode(const sl8_decode_params* p, void* workspace, size_t wor
                          void* stream);
 
 /*
+ * Decode against an int8 V cache with one fp32 scale per (batch, KV head, channel): replaces
+ * `attn_int8_decode_kv8` (reference csrc/include/attn_decode.cuh:141-224 `decode_split_i8v_kernel`,
+ * Python wrapper superl8/ops.py:671-727 `attn_decode_cached`).  p->v is int8 [B, Hkv, N, D];
+ * v_scale fp32 [B, Hkv, D]; everything else as sl8_attn_int8_decode (same workspace size).
+ * O accumulates p * float(v) and the channel scale multiplies the split partial.
+ */
+int sl8_attn_int8_decode_kv8(const sl8_decode_params* p, const float* v_scale, void* workspace,
+                             size_t workspace_bytes, void* stream);
+
+/*
+ * Per-channel symmetric int8 of V for that cache (reference superl8/quant/core.py:98-110
+ * `quantize_v_perchannel`): v_scale[bh, d] = max_n |v[bh, n, d]| / 127 (0 -> 1),
+ * v_i8 = clamp(rint(v / v_scale), -127, 127).  v: fp16 / bf16 [BH, N, D].
+ * workspace: sl8_k_mean_workspace(BH, N, D) bytes.
+ */
+int sl8_quantize_v_perchannel(const void* v, int dtype, int64_t BH, int64_t N, int64_t D, int8_t* v_i8,
+                              float* v_scale, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Decode for callers that cannot allocate device memory.  No counterpart in the
  * reference (its op allocates its partials with at::empty on every call,
  * csrc/kernel/attn_decode.cu:214-217).

@@ -302,11 +302,22 @@ def choose_n_splits_reference(n_len: int, bhq: int) -> int:
     return max(1, min(min(max(s_occ, s_lo), s_hi), 256))
 
 
-def attn_int8_decode(q_i8, q_scale, k_i8, k_scale, v, n_splits: int = 1, context_lens=None):
+def quantize_v_perchannel(v: torch.Tensor):
+    """Reference superl8/quant/core.py:98-110: symmetric int8 per CHANNEL of V (scale over the
+    key axis), scale = amax / 127 (0 -> 1).  Returns (v_i8 [..., N, D], scale fp32 [..., 1, D])."""
+    vf = v.detach().cpu().float()
+    scale = vf.abs().amax(dim=-2, keepdim=True) / Q_MAX
+    safe = torch.where(scale == 0, torch.ones_like(scale), scale)
+    return torch.round(vf / safe).clamp_(-Q_MAX, Q_MAX).to(torch.int8), safe
+
+
+def attn_int8_decode(q_i8, q_scale, k_i8, k_scale, v, n_splits: int = 1, context_lens=None, v_scale=None):
     """Reference csrc/include/attn_decode.cuh:68-131 (split) and :442-465 (combine): split s
     owns keys [s*per, min(len, (s+1)*per)), per = ceil(N / n_splits); partial (o, m, l) in
     the exp2 domain; merge o = sum o_s 2^(m_s - gm) / sum l_s 2^(m_s - gm) -> fp16.
-    q_i8 [B,Hq,1,D], q_scale [B,Hq(,1)], k_i8 [B,Hkv,N,D], k_scale [B,Hkv,N], v fp16."""
+    q_i8 [B,Hq,1,D], q_scale [B,Hq(,1)], k_i8 [B,Hkv,N,D], k_scale [B,Hkv,N], v fp16 -- or, with
+    ``v_scale`` [B,Hkv,D], the int8-V cache of attn_decode.cuh:141-224: o accumulates
+    p * float(v_i8) and the per-channel scale multiplies the partial."""
     q_i8, k_i8, v = q_i8.detach().cpu(), k_i8.detach().cpu(), v.detach().cpu()
     qs = q_scale.detach().cpu().float().reshape(q_i8.shape[0], q_i8.shape[1])
     ks = k_scale.detach().cpu().float()
@@ -332,7 +343,8 @@ def attn_int8_decode(q_i8, q_scale, k_i8, k_scale, v, n_splits: int = 1, context
                 p = torch.exp2(s[n0:n1] - m)
                 ms.append(m)
                 ls.append(p.sum())
-                os_.append(p @ v[b, hk, n0:n1].float())
+                o_s = p @ v[b, hk, n0:n1].float()
+                os_.append(o_s if v_scale is None else o_s * v_scale.detach().cpu().float().reshape(B, Hkv, D)[b, hk])
             if not ms:
                 continue
             gm = torch.stack(ms).max()

@@ -134,3 +134,29 @@ extern "C" int ref_attn_int8_varlen(const int8_t* q, const float* qs, const int8
   }
   return -1;
 }
+
+// reference csrc/kernel/attn_decode.cu: int8-V cache variant (decode_split_i8v_kernel + the same combine)
+template <int D>
+static int decode_kv8_d(const int8_t* q, const float* qs, const int8_t* k, const float* ks, const int8_t* v,
+                        const float* vs, __half* out, float* o_part, float* m_part, float* l_part, int N, int n_splits,
+                        int64_t BHq, int Hq, int g, cudaStream_t s) {
+  fni8::decode_split_i8v_kernel<D><<<dim3(n_splits, (unsigned)BHq), fni8::DEC_WARP, 0, s>>>(
+      q, qs, k, ks, v, vs, o_part, m_part, l_part, N, n_splits, Hq, g);
+  fni8::decode_combine_kernel<D><<<(unsigned)BHq, fni8::DEC_WARP, 0, s>>>(o_part, m_part, l_part, out, n_splits);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ref_attn_int8_decode_kv8(const int8_t* q, const float* qs, const int8_t* k, const float* ks,
+                                        const int8_t* v, const float* vs, void* out, float* o_part, float* m_part,
+                                        float* l_part, int B, int Hq, int Hkv, int N, int D, int n_splits, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  const int g = Hq / Hkv;
+  const int64_t BHq = (int64_t)B * Hq;
+  switch (D) {
+    case 32: return decode_kv8_d<32>(q, qs, k, ks, v, vs, (__half*)out, o_part, m_part, l_part, N, n_splits, BHq, Hq, g, s);
+    case 64: return decode_kv8_d<64>(q, qs, k, ks, v, vs, (__half*)out, o_part, m_part, l_part, N, n_splits, BHq, Hq, g, s);
+    case 128: return decode_kv8_d<128>(q, qs, k, ks, v, vs, (__half*)out, o_part, m_part, l_part, N, n_splits, BHq, Hq, g, s);
+    case 256: return decode_kv8_d<256>(q, qs, k, ks, v, vs, (__half*)out, o_part, m_part, l_part, N, n_splits, BHq, Hq, g, s);
+  }
+  return -1;
+}

@@ -253,6 +253,41 @@ def attn_int8_decode(q, q_scale, k, k_scale, v, num_splits=-1, *, context_lens=N
     return out
 
 
+def attn_int8_decode_kv8(q, q_scale, k, k_scale, v_i8, v_scale, num_splits=-1, *, context_lens=None):
+    """Decode against an int8 K / int8 V cache.  Reference binding `attn_int8_decode_kv8`
+    (kernel csrc/include/attn_decode.cuh:141-224): v_i8 int8 [B, Hkv, N, D], v_scale fp32
+    [B, Hkv, D] (one scale per channel); everything else as attn_int8_decode."""
+    what = "superl8_b200 decode kv8"
+    _check(v_i8.is_cuda and v_i8.dtype == torch.int8, f"{what}: v must be an int8 CUDA tensor")
+    _check(v_scale.is_cuda and v_scale.dtype == torch.float32, f"{what}: v_scale must be a float32 CUDA tensor")
+    B, H, Hkv, M, N, D = _fwd_checks(q, q_scale, k, k_scale, v_i8, what)
+    _check(M == 1, f"{what}: query length M must be 1 (decode)")
+    _check(D in (32, 64, 128, 256), f"{what}: head dim must be 32/64/128/256, got {D}")
+    _check(v_scale.numel() == B * Hkv * D, f"{what}: v_scale must be per-channel [B,H_kv,D]")
+    num_splits = int(num_splits)
+    _check(num_splits != 0, f"{what}: num_splits=0 is invalid; use -1 for auto or 1..256")
+    if num_splits < 0:
+        num_splits = -1
+    _check(num_splits <= 256, f"{what}: num_splits must be 1..256, got {num_splits}")
+    if context_lens is not None:
+        _check(context_lens.is_cuda and context_lens.dtype == torch.int32 and context_lens.numel() == B
+               and context_lens.is_contiguous(), f"{what}: context_lens must be a contiguous int32 [B] CUDA tensor")
+    out = torch.empty((B, H, 1, D), dtype=torch.float16, device=q.device)
+    if out.numel() == 0:
+        return out
+    v_i8, v_scale = v_i8.contiguous(), v_scale.contiguous()
+    p = _lib.DecodeParams(
+        q=q.data_ptr(), q_scale=q_scale.data_ptr(), k=k.data_ptr(), k_scale=k_scale.data_ptr(), v=v_i8.data_ptr(),
+        out=out.data_ptr(), context_lens=None if context_lens is None else context_lens.data_ptr(),
+        B=B, Hq=H, Hkv=Hkv, N=N, D=D, num_splits=num_splits)
+    lib = _lib.load()
+    with torch.cuda.device(q.device):
+        ws = _decode_workspace(q.device, int(lib.sl8_attn_int8_decode_workspace(C.byref(p))))
+        rc = lib.sl8_attn_int8_decode_kv8(C.byref(p), v_scale.data_ptr(), _ptr(ws), ws.numel(), _stream(q.device))
+    _lib.check(rc, "attn_int8_decode_kv8", 2 if N > 0 else 0)
+    return out
+
+
 def attn_int8_varlen(q, q_scale, k, k_scale, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, causal=False, *,
                      backend=_lib.SL8_BACKEND_AUTO):
     """Packed variable-length prefill.  Reference binding `attn_int8_varlen`

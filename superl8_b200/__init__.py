@@ -9,6 +9,7 @@ from . import _C, quant  # noqa: F401
 from .autograd import attn  # noqa: F401
 from .ops import (  # noqa: F401
     attn_decode,
+    attn_decode_cached,
     attn_decode_int8_cache,
     attn_fp16_fwd,
     attn_int8_decode,
@@ -16,6 +17,7 @@ from .ops import (  # noqa: F401
     attn_int8_varlen,
     backward_cuda,
     quantize_i8_rowwise,
+    quantize_kv_cache,
 )
 from .quant import (  # noqa: F401
     LOG2E,
@@ -27,7 +29,7 @@ from .quant import (  # noqa: F401
 )
 
 __all__ = [
-    "attn", "attn_decode", "attn_decode_int8_cache", "attn_fp16_fwd", "attn_int8_decode", "attn_int8_fwd",
+    "attn", "attn_decode", "attn_decode_cached", "attn_decode_int8_cache", "quantize_kv_cache", "attn_fp16_fwd", "attn_int8_decode", "attn_int8_fwd",
     "attn_int8_varlen", "backward_cuda", "quantize_i8_rowwise", "quantize_int8_rowwise", "quantize_qk", "smooth_k", "detect_q_outlier_domination",
     "LOG2E", "Q_MAX",
 ]

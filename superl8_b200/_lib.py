@@ -115,6 +115,9 @@ SIGNATURES = {
     "sl8_choose_n_splits": (C.c_int, [C.c_int64, C.c_int64]),
     "sl8_attn_int8_decode_workspace": (C.c_size_t, [C.POINTER(DecodeParams)]),
     "sl8_attn_int8_decode": (C.c_int, [C.POINTER(DecodeParams), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "sl8_attn_int8_decode_kv8": (C.c_int, [C.POINTER(DecodeParams), C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "sl8_quantize_v_perchannel": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
+                                            C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "sl8_attn_int8_decode_static": (C.c_int, [C.POINTER(DecodeParams), C.c_void_p, C.c_void_p]),
     "sl8_tensor_peak_probe": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_double), C.c_void_p, C.c_size_t, C.c_void_p]),
     "sl8_read_device_status": (C.c_int, [C.c_void_p, C.c_void_p]),

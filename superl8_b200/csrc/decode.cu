@@ -30,16 +30,18 @@ constexpr int kDecConsumerWarps = 4;  // 16 keys of a tile each
 constexpr int kDecThreads = 32 * (kDecConsumerWarps + 1);
 constexpr int kDecHeadsPerBlock = 16; // M of the mma tile
 
-template <int D>
+// V8: the V cache is int8 with one fp32 scale per (batch, KV head, channel).
+template <int D, bool V8>
 struct DecodeCfg {
   static constexpr int K_ROW_BYTES = D < 128 ? D : 128;
   static constexpr int K_SUBS = D / K_ROW_BYTES;
   static constexpr int K_SW_BITS = K_ROW_BYTES == 128 ? 3 : (K_ROW_BYTES == 64 ? 2 : 1);
-  static constexpr int V_ROW_BYTES = (2 * D) < 128 ? 2 * D : 128;
-  static constexpr int V_SUBS = 2 * D / V_ROW_BYTES;
-  static constexpr int V_SW_BITS = V_ROW_BYTES == 128 ? 3 : 2;
+  static constexpr int V_ELEM = V8 ? 1 : 2;
+  static constexpr int V_ROW_BYTES = (V_ELEM * D) < 128 ? V_ELEM * D : 128;
+  static constexpr int V_SUBS = V_ELEM * D / V_ROW_BYTES;
+  static constexpr int V_SW_BITS = V_ROW_BYTES == 128 ? 3 : (V_ROW_BYTES == 64 ? 2 : 1);
   static constexpr int K_BYTES = kDecTile * D;
-  static constexpr int V_BYTES = kDecTile * D * 2;
+  static constexpr int V_BYTES = kDecTile * D * V_ELEM;
   static constexpr int STAGE_BYTES = K_BYTES + V_BYTES;
   static constexpr int STAGES = D == 256 ? 3 : 4;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
@@ -49,6 +51,7 @@ struct DecodeArgs {
   const int8_t* q;
   const float* q_scale;
   const float* k_scale;
+  const float* v_scale;   // int8-V cache only: [B, Hkv, D]
   const int32_t* context_lens;
   float* o_part;
   float* m_part;
@@ -57,11 +60,11 @@ struct DecodeArgs {
   int B, Hq, Hkv, N, per, n_splits;
 };
 
-template <int D>
+template <int D, bool V8>
 __global__ void __launch_bounds__(kDecThreads) decode_split_kernel(const __grid_constant__ CUtensorMap k_map,
                                                                    const __grid_constant__ CUtensorMap v_map,
                                                                    DecodeArgs a) {
-  using C = DecodeCfg<D>;
+  using C = DecodeCfg<D, V8>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
@@ -126,8 +129,8 @@ __global__ void __launch_bounds__(kDecThreads) decode_split_kernel(const __grid_
           tma_load_3d(kd + c * (kDecTile * C::K_ROW_BYTES), &k_map, &full_bar[st], c * C::K_ROW_BYTES, row, bkv);
 #pragma unroll
         for (int c = 0; c < C::V_SUBS; ++c)
-          tma_load_3d(vd + c * (kDecTile * C::V_ROW_BYTES), &v_map, &full_bar[st], c * (C::V_ROW_BYTES / 2), row,
-                      bkv);
+          tma_load_3d(vd + c * (kDecTile * C::V_ROW_BYTES), &v_map, &full_bar[st], c * (C::V_ROW_BYTES / C::V_ELEM),
+                      row, bkv);
         issued = i + 1;
       }
       if (!ok) {
@@ -242,6 +245,35 @@ __global__ void __launch_bounds__(kDecThreads) decode_split_kernel(const __grid_
           }
         }
         // ---- O += P . V ----
+        if (V8) {
+          // int8 V: one transposing ldmatrix (16-bit granularity) brings, for this warp's 16 keys,
+          // 32 channels as byte pairs -- register = {v[2t][2g], v[2t][2g+1], v[2t+1][2g],
+          // v[2t+1][2g+1]} -- i.e. the B fragments of an "even channels" and an "odd channels"
+          // 8-wide tile.  byte -> fp16 exactly: (b ^ 0x80) | 0x6400 is 1152 + v.  The accumulator
+          // tile nt = 4 q + 2 c + par therefore holds channel 32 q + 16 c + 2 n + par in column n.
+          const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+          auto cvt = [&](uint32_t x, uint32_t sel) -> uint32_t {
+            const uint32_t u = __byte_perm(x, 0x64646464u, sel);
+            const __half2 h = __hsub2(*reinterpret_cast<const __half2*>(&u), bias);
+            return *reinterpret_cast<const uint32_t*>(&h);
+          };
+#pragma unroll
+          for (int q4 = 0; q4 < D / 32; ++q4) {
+            const int key_in_tile = 16 * warp + 8 * (mi & 1) + mr;
+            const int dc = 2 * q4 + (mi >> 1);  // 16-byte chunk (16 channels) of the V row
+            constexpr int CPR = C::V_ROW_BYTES / 16;
+            const uint32_t off = (dc / CPR) * (kDecTile * C::V_ROW_BYTES) +
+                                 swizzle_offset<C::V_SW_BITS>(key_in_tile * C::V_ROW_BYTES + (dc % CPR) * 16);
+            uint32_t r[4];
+            ldmatrix_x4_trans(r, vbase + off);
+#pragma unroll
+            for (int c2 = 0; c2 < 2; ++c2) {
+              const uint32_t x0 = r[2 * c2] ^ 0x80808080u, x1 = r[2 * c2 + 1] ^ 0x80808080u;
+              mma_f16_16816(o[4 * q4 + 2 * c2], pa, cvt(x0, 0x4240u), cvt(x1, 0x4240u));
+              mma_f16_16816(o[4 * q4 + 2 * c2 + 1], pa, cvt(x0, 0x4341u), cvt(x1, 0x4341u));
+            }
+          }
+        } else
 #pragma unroll
         for (int nt = 0; nt < D / 8; nt += 2) {
           const int key_in_tile = 16 * warp + 8 * (mi & 1) + mr;
@@ -280,9 +312,16 @@ __global__ void __launch_bounds__(kDecThreads) decode_split_kernel(const __grid_
         l_w[warp * kDecHeadsPerBlock + r] = l_run[h];
       }
 #pragma unroll
-      for (int nt = 0; nt < D / 8; ++nt)
-        *reinterpret_cast<float2*>(&o_w[(warp * kDecHeadsPerBlock + r) * D + 8 * nt + 2 * t]) =
-            make_float2(o[nt][2 * h], o[nt][2 * h + 1]);
+      for (int nt = 0; nt < D / 8; ++nt) {
+        if (V8) {   // column n of tile nt = channel 32 (nt / 4) + 16 ((nt / 2) & 1) + 2 n + (nt & 1)
+          const int ch = 32 * (nt >> 2) + 16 * ((nt >> 1) & 1) + 4 * t + (nt & 1);
+          o_w[(warp * kDecHeadsPerBlock + r) * D + ch] = o[nt][2 * h];
+          o_w[(warp * kDecHeadsPerBlock + r) * D + ch + 2] = o[nt][2 * h + 1];
+        } else {
+          *reinterpret_cast<float2*>(&o_w[(warp * kDecHeadsPerBlock + r) * D + 8 * nt + 2 * t]) =
+              make_float2(o[nt][2 * h], o[nt][2 * h + 1]);
+        }
+      }
     }
   }
   __syncthreads();
@@ -299,6 +338,8 @@ __global__ void __launch_bounds__(kDecThreads) decode_split_kernel(const __grid_
       lsum += l_w[w * kDecHeadsPerBlock + r] * wgt;
     }
     const int64_t row = (int64_t)split * BHq + bhq0 + r;
+    // the per-channel V scale factors out of the key sum (reference attn_decode.cuh:212-218)
+    if (V8) acc *= __ldg(a.v_scale + (int64_t)bkv * D + d);
     a.o_part[row * D + d] = acc;
     if (d == 0) {
       a.m_part[row] = gm;
@@ -336,36 +377,36 @@ __global__ void __launch_bounds__(128) decode_combine_kernel(const float* __rest
   }
 }
 
-template <int D>
-int launch_decode(const sl8_decode_params& p, int n_splits, int* status, float* o_part, float* m_part,
-                  float* l_part, cudaStream_t stream) {
-  using C = DecodeCfg<D>;
+template <int D, bool V8>
+int launch_decode(const sl8_decode_params& p, const float* v_scale, int n_splits, int* status, float* o_part,
+                  float* m_part, float* l_part, cudaStream_t stream) {
+  using C = DecodeCfg<D, V8>;
   CUtensorMap k_map, v_map;
   const uint64_t heads = (uint64_t)p.B * p.Hkv;
   int rc = sl8_make_tmap_3d(&k_map, p.k, 1, D, p.N, heads, C::K_ROW_BYTES, kDecTile, C::K_ROW_BYTES);
   if (rc != SL8_OK) return rc;
-  rc = sl8_make_tmap_3d(&v_map, p.v, 2, D, p.N, heads, C::V_ROW_BYTES / 2, kDecTile, C::V_ROW_BYTES);
+  rc = sl8_make_tmap_3d(&v_map, p.v, C::V_ELEM, D, p.N, heads, C::V_ROW_BYTES / C::V_ELEM, kDecTile, C::V_ROW_BYTES);
   if (rc != SL8_OK) return rc;
   static bool attr_done[8] = {false};
   int dev = 0;
   SL8_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 8 && !attr_done[dev]) {
-    SL8_CUDA_TRY(cudaFuncSetAttribute(decode_split_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    SL8_CUDA_TRY(cudaFuncSetAttribute(decode_split_kernel<D, V8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       C::SMEM_BYTES));
     attr_done[dev] = true;
   } else if (dev >= 8) {
-    SL8_CUDA_TRY(cudaFuncSetAttribute(decode_split_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    SL8_CUDA_TRY(cudaFuncSetAttribute(decode_split_kernel<D, V8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       C::SMEM_BYTES));
   }
   DecodeArgs a{};
-  a.q = p.q; a.q_scale = p.q_scale; a.k_scale = p.k_scale; a.context_lens = p.context_lens;
+  a.q = p.q; a.q_scale = p.q_scale; a.k_scale = p.k_scale; a.v_scale = v_scale; a.context_lens = p.context_lens;
   a.o_part = o_part; a.m_part = m_part; a.l_part = l_part; a.status = status;
   a.B = p.B; a.Hq = p.Hq; a.Hkv = p.Hkv; a.N = p.N;
   a.per = (p.N + n_splits - 1) / n_splits;
   a.n_splits = n_splits;
   const int G = p.Hq / p.Hkv;
   dim3 grid(n_splits, (unsigned)heads, (G + kDecHeadsPerBlock - 1) / kDecHeadsPerBlock);
-  decode_split_kernel<D><<<grid, kDecThreads, C::SMEM_BYTES, stream>>>(k_map, v_map, a);
+  decode_split_kernel<D, V8><<<grid, kDecThreads, C::SMEM_BYTES, stream>>>(k_map, v_map, a);
   decode_combine_kernel<D><<<(unsigned)((int64_t)p.B * p.Hq), 128, 0, stream>>>(
       o_part, m_part, l_part, p.context_lens, reinterpret_cast<__half*>(p.out), p.Hq, p.N, a.per, n_splits);
   return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
@@ -413,8 +454,10 @@ extern "C" size_t sl8_attn_int8_decode_workspace(const sl8_decode_params* p) {
   return 256 + rows * (size_t)(p->D + 2) * sizeof(float);
 }
 
-extern "C" int sl8_attn_int8_decode(const sl8_decode_params* p, void* workspace, size_t workspace_bytes,
-                                    void* stream) {
+namespace {
+// Common body of the fp16-V and int8-V entry points (v_scale == nullptr: fp16 V).
+int decode_entry(const sl8_decode_params* p, const float* v_scale, bool v8, void* workspace, size_t workspace_bytes,
+                 void* stream) {
   int rc = validate(p);
   if (rc != SL8_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -425,7 +468,7 @@ extern "C" int sl8_attn_int8_decode(const sl8_decode_params* p, void* workspace,
     SL8_CUDA_TRY(cudaMemsetAsync(p->out, 0, (size_t)BHq * p->D * sizeof(__half), s));
     return SL8_OK;
   }
-  if (!p->q || !p->q_scale || !p->k || !p->k_scale || !p->v) return SL8_ERR_NULL;
+  if (!p->q || !p->q_scale || !p->k || !p->k_scale || !p->v || (v8 && !v_scale)) return SL8_ERR_NULL;
   if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->out)) return SL8_ERR_MISALIGNED;
   if ((int64_t)p->B * p->Hkv > 65535) return SL8_ERR_TOO_LARGE;
   if (workspace == nullptr || workspace_bytes < sl8_attn_int8_decode_workspace(p)) return SL8_ERR_WORKSPACE;
@@ -435,13 +478,33 @@ extern "C" int sl8_attn_int8_decode(const sl8_decode_params* p, void* workspace,
   float* o_part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + 256);
   float* m_part = o_part + (size_t)ns * BHq * p->D;
   float* l_part = m_part + (size_t)ns * BHq;
+  if (v8) {
+    switch (p->D) {
+      case 32: return launch_decode<32, true>(*p, v_scale, ns, status, o_part, m_part, l_part, s);
+      case 64: return launch_decode<64, true>(*p, v_scale, ns, status, o_part, m_part, l_part, s);
+      case 128: return launch_decode<128, true>(*p, v_scale, ns, status, o_part, m_part, l_part, s);
+      case 256: return launch_decode<256, true>(*p, v_scale, ns, status, o_part, m_part, l_part, s);
+    }
+    return SL8_ERR_BAD_HEAD_DIM;
+  }
   switch (p->D) {
-    case 32: return launch_decode<32>(*p, ns, status, o_part, m_part, l_part, s);
-    case 64: return launch_decode<64>(*p, ns, status, o_part, m_part, l_part, s);
-    case 128: return launch_decode<128>(*p, ns, status, o_part, m_part, l_part, s);
-    case 256: return launch_decode<256>(*p, ns, status, o_part, m_part, l_part, s);
+    case 32: return launch_decode<32, false>(*p, nullptr, ns, status, o_part, m_part, l_part, s);
+    case 64: return launch_decode<64, false>(*p, nullptr, ns, status, o_part, m_part, l_part, s);
+    case 128: return launch_decode<128, false>(*p, nullptr, ns, status, o_part, m_part, l_part, s);
+    case 256: return launch_decode<256, false>(*p, nullptr, ns, status, o_part, m_part, l_part, s);
   }
   return SL8_ERR_BAD_HEAD_DIM;
+}
+}  // namespace
+
+extern "C" int sl8_attn_int8_decode(const sl8_decode_params* p, void* workspace, size_t workspace_bytes,
+                                    void* stream) {
+  return decode_entry(p, nullptr, false, workspace, workspace_bytes, stream);
+}
+
+extern "C" int sl8_attn_int8_decode_kv8(const sl8_decode_params* p, const float* v_scale, void* workspace,
+                                        size_t workspace_bytes, void* stream) {
+  return decode_entry(p, v_scale, true, workspace, workspace_bytes, stream);
 }
 
 
@@ -502,10 +565,10 @@ extern "C" int sl8_attn_int8_decode_static(const sl8_decode_params* p, int32_t* 
   float* m_part = o_part + (size_t)ns * BHq * p->D;
   float* l_part = m_part + (size_t)ns * BHq;
   switch (p->D) {
-    case 32: return launch_decode<32>(*p, ns, status, o_part, m_part, l_part, s);
-    case 64: return launch_decode<64>(*p, ns, status, o_part, m_part, l_part, s);
-    case 128: return launch_decode<128>(*p, ns, status, o_part, m_part, l_part, s);
-    case 256: return launch_decode<256>(*p, ns, status, o_part, m_part, l_part, s);
+    case 32: return launch_decode<32, false>(*p, nullptr, ns, status, o_part, m_part, l_part, s);
+    case 64: return launch_decode<64, false>(*p, nullptr, ns, status, o_part, m_part, l_part, s);
+    case 128: return launch_decode<128, false>(*p, nullptr, ns, status, o_part, m_part, l_part, s);
+    case 256: return launch_decode<256, false>(*p, nullptr, ns, status, o_part, m_part, l_part, s);
   }
   return SL8_ERR_BAD_HEAD_DIM;
 }

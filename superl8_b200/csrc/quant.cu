@@ -412,6 +412,78 @@ __global__ void k_mean_finish_kernel(const float* __restrict__ partial, int nchu
   }
 }
 
+// ---- per-channel V quantiser (int8-V cache) -------------------------------------------
+// grid (chunks, BH): per-channel max |v| over the chunk's rows, same thread map as the K mean.
+template <typename T>
+__global__ void __launch_bounds__(kMeanThreads) v_colamax_partial_kernel(const T* __restrict__ v, int64_t N, int K,
+                                                                         float* __restrict__ partial, int nchunks) {
+  extern __shared__ float red[];  // [RL][K]
+  const int kvec = K >> 3;
+  int cvp = 1;
+  while (cvp < kvec) cvp <<= 1;
+  const int RL = kMeanThreads / cvp;
+  const int cv = threadIdx.x % cvp;
+  const int rl = threadIdx.x / cvp;
+  const int64_t bh = blockIdx.y;
+  const int64_t r0 = (int64_t)blockIdx.x * kMeanChunkRows;
+  const int64_t r1 = min(N, r0 + kMeanChunkRows);
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (cv < kvec) {
+    const T* vb = v + bh * N * K;
+    for (int64_t r = r0 + rl; r < r1; r += RL) {
+      const uint4 u = __ldg(reinterpret_cast<const uint4*>(vb + r * K) + cv);
+      float f[8];
+      Vec8<T>::unpack(u, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = fmaxf(acc[i], fabsf(f[i]));
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[rl * K + cv * 8 + i] = acc[i];
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < K; c += kMeanThreads) {
+    float m = 0.0f;
+    for (int r = 0; r < RL; ++r) m = fmaxf(m, red[r * K + c]);
+    partial[(bh * nchunks + blockIdx.x) * K + c] = m;
+  }
+}
+
+// scale[bh, c] = amax / 127 (0 -> 1), the rule of reference superl8/quant/core.py:107-108
+__global__ void v_scale_finish_kernel(const float* __restrict__ partial, int nchunks, int K, float* __restrict__ scale) {
+  const int64_t bh = blockIdx.x;
+  for (int c = threadIdx.x; c < K; c += blockDim.x) {
+    float m = 0.0f;
+    for (int j = 0; j < nchunks; ++j) m = fmaxf(m, partial[(bh * nchunks + j) * K + c]);
+    const float sc = __fdiv_rn(m, kQMax);
+    scale[bh * K + c] = sc == 0.0f ? 1.0f : sc;
+  }
+}
+
+// codes = clamp(rint(v / scale[channel]), -127, 127) (core.py:109); 8 channels per thread
+template <typename T>
+__global__ void __launch_bounds__(256) v_quant_perchannel_kernel(const T* __restrict__ v, const float* __restrict__ scale,
+                                                                 int8_t* __restrict__ q, int64_t N, int K,
+                                                                 int64_t total_vec) {
+  const int kvec = K >> 3;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_vec; i += (int64_t)gridDim.x * blockDim.x) {
+    const int cv = (int)(i % kvec);
+    const int64_t row = i / kvec, bh = row / N;
+    const uint4 u = __ldg(reinterpret_cast<const uint4*>(v) + i);
+    float f[8];
+    Vec8<T>::unpack(u, f);
+    const float4 s0 = __ldg(reinterpret_cast<const float4*>(scale + bh * K + cv * 8));
+    const float4 s1 = __ldg(reinterpret_cast<const float4*>(scale + bh * K + cv * 8 + 4));
+    const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    uint32_t w[2] = {0u, 0u};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int c = (int)quant_one(f[e], sc[e]);
+      w[e >> 2] |= (uint32_t)(c & 0xff) << (8 * (e & 3));
+    }
+    *reinterpret_cast<uint2*>(q + i * 8) = make_uint2(w[0], w[1]);
+  }
+}
+
 // Packed token-major keys [tokens, heads, K]: mean over the tokens of one sequence for one head.
 // grid (heads, sequences).  Same thread map and fixed summation order as the dense kernel:
 // thread (rl, cv) sums tokens rl, rl + RL, ... for the 8 columns of vector cv, the RL lanes are
@@ -454,6 +526,42 @@ __global__ void __launch_bounds__(kMeanThreads) k_mean_packed_kernel(
 }  // namespace sl8
 
 using namespace sl8;
+
+extern "C" int sl8_quantize_v_perchannel(const void* v, int dtype, int64_t BH, int64_t N, int64_t D, int8_t* v_i8,
+                                         float* v_scale, void* workspace, size_t workspace_bytes, void* stream) {
+  if (BH < 0 || N < 0 || D < 0) return SL8_ERR_BAD_SHAPE;
+  if (dtype != SL8_F16 && dtype != SL8_BF16) return SL8_ERR_BAD_DTYPE;
+  if (D % 8 != 0 || D > 2048) return SL8_ERR_BAD_HEAD_DIM;
+  if (BH == 0 || D == 0) return SL8_OK;
+  if (v_scale == nullptr) return SL8_ERR_NULL;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (N == 0) {   // no key: amax 0 -> scale 1 (core.py:108)
+    v_scale_finish_kernel<<<(unsigned)BH, 128, 0, s>>>(nullptr, 0, (int)D, v_scale);
+    return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
+  }
+  if (v == nullptr || v_i8 == nullptr) return SL8_ERR_NULL;
+  if (!aligned16(v) || !aligned16(v_i8) || !aligned16(v_scale)) return SL8_ERR_MISALIGNED;
+  if (BH > 65535) return SL8_ERR_TOO_LARGE;
+  if (workspace == nullptr || workspace_bytes < sl8_k_mean_workspace(BH, N, D)) return SL8_ERR_WORKSPACE;
+  const int nchunks = (int)((N + kMeanChunkRows - 1) / kMeanChunkRows);
+  float* partial = reinterpret_cast<float*>(workspace);
+  int cvp = 1;
+  while (cvp < (int)(D >> 3)) cvp <<= 1;
+  const size_t smem = (size_t)(kMeanThreads / cvp) * D * sizeof(float);
+  dim3 grid((unsigned)nchunks, (unsigned)BH);
+  const int64_t total_vec = BH * N * (D >> 3);
+  const unsigned qblocks = (unsigned)std::min<int64_t>((total_vec + 255) / 256, (int64_t)kNumSms * 16);
+  if (dtype == SL8_F16) {
+    v_colamax_partial_kernel<__half><<<grid, kMeanThreads, smem, s>>>(reinterpret_cast<const __half*>(v), N, (int)D, partial, nchunks);
+    v_scale_finish_kernel<<<(unsigned)BH, 128, 0, s>>>(partial, nchunks, (int)D, v_scale);
+    v_quant_perchannel_kernel<__half><<<qblocks, 256, 0, s>>>(reinterpret_cast<const __half*>(v), v_scale, v_i8, N, (int)D, total_vec);
+  } else {
+    v_colamax_partial_kernel<__nv_bfloat16><<<grid, kMeanThreads, smem, s>>>(reinterpret_cast<const __nv_bfloat16*>(v), N, (int)D, partial, nchunks);
+    v_scale_finish_kernel<<<(unsigned)BH, 128, 0, s>>>(partial, nchunks, (int)D, v_scale);
+    v_quant_perchannel_kernel<__nv_bfloat16><<<qblocks, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(v), v_scale, v_i8, N, (int)D, total_vec);
+  }
+  return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
+}
 
 extern "C" int sl8_k_mean_packed(const void* k, int dtype, int64_t total_tokens, int32_t heads, int64_t D,
                                  const int32_t* cu_seqlens, int32_t n_seq, float* mean, void* stream) {

@@ -115,6 +115,49 @@ def attn_decode_int8_cache(q, k_i8, k_scale, v, *, scale: float | None = None, n
                                context_lens=context_lens)
 
 
+def quantize_kv_cache(k, v, *, v_quant: str = "per_channel", rotate: bool = False):
+    """Quantise a K/V cache once for int8-KV decode (reference superl8/ops.py:541-589):
+    K is smoothed (per-channel mean over its keys) and quantised per row; V is quantised per
+    channel.  Returns (k_i8 [B,H,N,D], k_scale [B,H,N], v_i8 [B,H,N,D], v_scale [B,H,D]).
+    ``v_quant="per_token"`` belongs to the reference's paged decode, which is not part of this
+    library."""
+    if v_quant not in ("per_channel", "per_token"):
+        raise ValueError(f"v_quant must be 'per_channel' or 'per_token', got {v_quant!r}")
+    if v_quant == "per_token":
+        raise NotImplementedError("superl8_b200: per-token V scales are served by the reference's paged decode only")
+    from .quant import quantize_v_perchannel, rotate_last
+
+    mean = k_mean(k)
+    if rotate:
+        _, _, k_s = smooth_quantize_k(k, mean, want_smoothed=True)
+        k_i8, k_scale = _C.quantize_i8_rowwise(rotate_last(k_s).reshape(-1, k.shape[-1]).contiguous())
+        k_i8, k_scale = k_i8.reshape(k.shape), k_scale.reshape(*k.shape[:-1])
+    else:
+        k_i8, k_scale, _ = smooth_quantize_k(k, mean)
+        k_scale = k_scale.squeeze(-1)
+    v_i8, v_scale = quantize_v_perchannel(v)
+    return k_i8.contiguous(), k_scale.contiguous(), v_i8, v_scale.squeeze(-2).contiguous()
+
+
+def attn_decode_cached(q, k_i8, k_scale, v_i8, v_scale, *, scale: float | None = None, rotate: bool = False,
+                       num_splits: int | None = None, context_lens=None):
+    """Decode (M = 1) against a pre-quantised int8 K / int8 V cache from quantize_kv_cache
+    (reference superl8/ops.py:671-727): only the query row is quantised per call.
+    ``context_lens`` int32 [B] gives per-sequence lengths of a padded cache."""
+    assert q.shape[-2] == 1, f"decode expects M=1, got M={q.shape[-2]}"
+    if v_scale.shape[-1] == k_i8.shape[2] and v_scale.shape[-1] != k_i8.shape[3]:
+        raise RuntimeError("attn_decode_cached received a per-token V scale [B,H,N]; this kernel takes "
+                           "per-channel V scales [B,H,D]")
+    s = (1.0 / math.sqrt(q.shape[-1])) if scale is None else scale
+    if rotate:
+        from .quant import rotate_last
+        q = rotate_last(q)
+    q_i8, q_scale, _ = quantize_q(q, s)
+    ns = -1 if num_splits is None else int(num_splits)
+    return _C.attn_int8_decode_kv8(q_i8, q_scale.reshape(q.shape[0], q.shape[1], 1).contiguous(), k_i8.contiguous(),
+                                   k_scale.contiguous(), v_i8, v_scale, ns, context_lens=context_lens)
+
+
 def quantize_i8_rowwise(x: torch.Tensor):
     """[M, K] -> (int8 [M, K], fp32 [M]) (reference superl8/ops.py:975-991; CUDA tensors only)."""
     return _C.quantize_i8_rowwise(x)

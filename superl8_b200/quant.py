@@ -92,6 +92,28 @@ def smooth_quantize_k(k: torch.Tensor, mean: torch.Tensor, want_smoothed: bool =
     return k_i8, k_scale, k_s
 
 
+def quantize_v_perchannel(v: torch.Tensor):
+    """Symmetric int8 per CHANNEL of V, scale over the key axis (reference
+    superl8/quant/core.py:98-110): returns (v_i8 [..., N, D], v_scale fp32 [..., 1, D])."""
+    _require_cuda(v, "quantize_v_perchannel")
+    if v.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("superl8_b200 quantize_v_perchannel: v must be float16 or bfloat16")
+    v = v.contiguous()
+    N, D = v.shape[-2], v.shape[-1]
+    BH = int(math.prod(v.shape[:-2]))
+    v_i8 = torch.empty(v.shape, dtype=torch.int8, device=v.device)
+    v_scale = torch.empty((*v.shape[:-2], 1, D), dtype=torch.float32, device=v.device)
+    if BH * D:
+        lib = _lib.load()
+        with torch.cuda.device(v.device):
+            ws_bytes = int(lib.sl8_k_mean_workspace(BH, N, D))
+            ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=v.device)
+            rc = lib.sl8_quantize_v_perchannel(v.data_ptr(), _C._DTYPE[v.dtype], BH, N, D, v_i8.data_ptr(),
+                                               v_scale.data_ptr(), ws.data_ptr(), ws_bytes, _C._stream(v.device))
+        _lib.check(rc, "quantize_v_perchannel", 3 if N > 0 else 1)
+    return v_i8, v_scale
+
+
 def varlen_smooth_quantize_k(k: torch.Tensor, cu_seqlens_k: torch.Tensor, want_smoothed: bool = False,
                              k_mean_override: torch.Tensor | None = None):
     """Packed keys [total, H, D]: per-sequence K mean (reference superl8/ops.py:268-315

@@ -198,6 +198,24 @@ def varlen_cases():
     np.savez_compressed(OUT / "varlen_prologue.npz", **out)
 
 
+def v_cache_cases():
+    """Per-channel V quantiser of the reference (superl8/quant/core.py::quantize_v_perchannel)."""
+    from superl8.quant.core import quantize_v_perchannel
+
+    out = {}
+    g = gen(71)
+    cases = {"f16": torch.randn(2, 2, 200, 64, generator=g).half() * 1.7,
+             "bf16": (torch.randn(1, 2, 1100, 64, generator=g) * 0.3).bfloat16()}
+    cases["f16"][0, 1, :, 5] = 0          # a zero channel -> scale 1
+    cases["f16"][1, 0, 17, 9] = 300.0     # an outlier sets its channel's scale
+    for name, v in cases.items():
+        v_i8, v_scale = quantize_v_perchannel(v)
+        out[f"{name}__v"] = bits(v)
+        out[f"{name}__dtype"] = np.array(str(v.dtype).replace("torch.", ""))
+        out[f"{name}__v_i8"], out[f"{name}__v_scale"] = v_i8.numpy(), v_scale.numpy()
+    np.savez_compressed(OUT / "v_perchannel.npz", **out)
+
+
 if __name__ == "__main__":
     torch.set_num_threads(1)
     quant_cases()
@@ -207,5 +225,6 @@ if __name__ == "__main__":
     attention_cases()
     backward_cases()
     varlen_cases()
+    v_cache_cases()
     for f in sorted(OUT.glob("*.npz")):
         print(f.name, f.stat().st_size)

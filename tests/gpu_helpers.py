@@ -82,3 +82,18 @@ def ref_attn_int8_varlen(q_i8, q_scale, k_i8, k_scale, v, cu_q, cu_k, max_seqlen
                                         cu_q.numel() - 1, int(max_seqlen_q), Hq, k_i8.shape[1], D, int(causal), _stream())
     assert rc == 0
     return out
+
+
+def ref_attn_int8_decode_kv8(q_i8, q_scale, k_i8, k_scale, v_i8, v_scale, n_splits):
+    """The reference's int8-V split + combine kernels on the same inputs."""
+    B, Hq, _, D = q_i8.shape
+    Hkv, N = k_i8.shape[1], k_i8.shape[2]
+    dev = q_i8.device
+    out = torch.empty((B, Hq, 1, D), dtype=torch.float16, device=dev)
+    o_part = torch.empty((n_splits, B * Hq, D), dtype=torch.float32, device=dev)
+    m_part = torch.empty((n_splits, B * Hq), dtype=torch.float32, device=dev)
+    l_part = torch.empty((n_splits, B * Hq), dtype=torch.float32, device=dev)
+    rc = ref_lib().ref_attn_int8_decode_kv8(_p(q_i8), _p(q_scale), _p(k_i8), _p(k_scale), _p(v_i8), _p(v_scale), _p(out),
+                                            _p(o_part), _p(m_part), _p(l_part), B, Hq, Hkv, N, D, n_splits, _stream())
+    assert rc == 0
+    return out

@@ -158,3 +158,11 @@ def test_varlen_restatement_equals_the_dense_one_per_sequence():
     q_i8, q_scale, k_i8, k_scale, _ = oracle.quantize_qk(q, k)
     ref = oracle.attn_int8_fwd(q_i8, q_scale.squeeze(-1), k_i8, k_scale.squeeze(-1), v, causal=True)
     assert oracle.cos_sim(out, pk(ref)) >= 0.99999
+
+
+def test_v_perchannel_quantiser_matches_the_reference():
+    g = np.load(GOLDEN / "v_perchannel.npz")
+    for name in ("f16", "bf16"):
+        v = from_bits(g[f"{name}__v"], str(g[f"{name}__dtype"]))
+        v_i8, v_scale = oracle.quantize_v_perchannel(v)
+        assert np.array_equal(v_i8.numpy(), g[f"{name}__v_i8"]) and np.array_equal(v_scale.numpy(), g[f"{name}__v_scale"])
