@@ -273,12 +273,24 @@ def run_kernel_case(args):
             qs, ks = q_scale.squeeze(-1).contiguous(), k_scale.squeeze(-1).contiguous()
             for _ in range(n):
                 _C.attn_int8_fwd(q_i8, qs, k_i8, ks, v, True, -1)
+    elif args.kernel_case == "backward":
+        g = torch.Generator(device="cpu").manual_seed(2002)
+        bq, bk, bv, bdo = (torch.randn(2, h, 4096, 128, generator=g).half().to(dev) for h in (32, 8, 8, 32))
+        bout, blse = _C.attn_fp16_fwd(bq, bk, bv, True, None, want_lse=True)
+        for _ in range(n):
+            s8.backward_cuda(bq, bk, bv, bout, blse, bdo, causal=True)
     else:
         dcfg = workloads.DecodeCfg(B=16)
         lens = workloads.decode_lengths(dcfg, 0, 16)
         dq, dk8, dks, dv, dlens = workloads.decode_inputs(dcfg, lens, dev)
-        for _ in range(n):
-            s8.attn_decode_int8_cache(dq, dk8, dks, dv, context_lens=dlens)
+        if args.kernel_case == "decode_kv8":
+            dv8, dvs = quant.quantize_v_perchannel(dv)
+            dvs = dvs.squeeze(-2).contiguous()
+            for _ in range(n):
+                s8.attn_decode_cached(dq, dk8, dks, dv8, dvs, context_lens=dlens)
+        else:
+            for _ in range(n):
+                s8.attn_decode_int8_cache(dq, dk8, dks, dv, context_lens=dlens)
     torch.cuda.synchronize()
     print(f"kernel-case {args.kernel_case}: {n} launches, device status {_C.device_status()}", file=sys.stderr)
 
@@ -324,7 +336,7 @@ def main():
     ap.add_argument("--skip-extras", action="store_true", help="only the headline workload")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: every GPU owns a full batch; strong: the batch's units are split across the GPUs")
-    ap.add_argument("--kernel-case", default="", choices=["", "prefill_int8", "prefill_fp16", "decode", "quant_q", "quant_k"],
+    ap.add_argument("--kernel-case", default="", choices=["", "prefill_int8", "prefill_fp16", "decode", "decode_kv8", "backward", "quant_q", "quant_k"],
                     help="launch ONE kernel family on a small case (for profilers): W warm-up + K launches, no JSON")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -471,7 +483,23 @@ def main():
                                        "peak_source": peaks["source"] + " copy bandwidth",
                                        "traffic": 794.5e6 / 775.8e6 * dbytes},
                           "device_status": _C.device_status()}
-        del dq, dk8, dks, dv
+        # ---- the same decode against an int8 V cache (per-channel scales): D + 4 + D bytes per key ----
+        dv8, dvs = quant.quantize_v_perchannel(dv)
+        dvs = dvs.squeeze(-2).contiguous()
+        del dv
+        d8bytes = sum(int(n) for n in lens) * dcfg.Hkv * (2 * dcfg.D + 4)
+        msd8 = timed(lambda: s8.attn_decode_cached(dq, dk8, dks, dv8, dvs, context_lens=dlens), max(args.steps, 10),
+                     args.warmup, world)
+        gd8 = world * d8bytes / (msd8 * 1e-3) / 1e9
+        line["decode_kv8"] = {"metric": "int8_kv_decode_hbm_gbs", "value": gd8, "unit": "GB/s", "ms_per_step": msd8,
+                              "config": {"workload": "cfg5 with an int8 V cache (one fp32 scale per channel): "
+                                                     "2D + 4 bytes per key and KV head"},
+                              "roofline": {"bound": "hbm", "achieved": gd8 / world, "peak": peaks["hbm_gbs"],
+                                           "unit": "GB/s", "frac": gd8 / world / peaks["hbm_gbs"],
+                                           "frac_of_nominal": gd8 / world / NOMINAL_HBM_GBS,
+                                           "peak_source": peaks["source"] + " copy bandwidth", "traffic": None},
+                              "speedup_vs_fp16_v": msd / msd8}
+        del dq, dk8, dks, dv8, dvs
         # ---- backward (dQ pass + dK/dV pass) on a cfg2-shaped training step per rank ----
         bB, bHq, bHkv, bS, bD = 2, 32, 8, 4096, 128
         gb = torch.Generator(device="cpu").manual_seed(2002 + rank)
