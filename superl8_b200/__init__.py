@@ -14,6 +14,7 @@ from .ops import (  # noqa: F401
     attn_fp16_fwd,
     attn_int8_decode,
     attn_int8_fwd,
+    attn_int8_fwd_host,
     attn_int8_varlen,
     backward_cuda,
     quantize_i8_rowwise,
@@ -30,6 +31,6 @@ from .quant import (  # noqa: F401
 
 __all__ = [
     "attn", "attn_decode", "attn_decode_cached", "attn_decode_int8_cache", "quantize_kv_cache", "attn_fp16_fwd", "attn_int8_decode", "attn_int8_fwd",
-    "attn_int8_varlen", "backward_cuda", "quantize_i8_rowwise", "quantize_int8_rowwise", "quantize_qk", "smooth_k", "detect_q_outlier_domination",
+    "attn_int8_fwd_host", "attn_int8_varlen", "backward_cuda", "quantize_i8_rowwise", "quantize_int8_rowwise", "quantize_qk", "smooth_k", "detect_q_outlier_domination",
     "LOG2E", "Q_MAX",
 ]

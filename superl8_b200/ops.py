@@ -55,6 +55,71 @@ def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, 
                             backend=backend)
 
 
+_aux_streams: dict = {}
+
+
+def attn_int8_fwd_host(q, k, v, out=None, *, chunk_batch: int | None = None, **kw):
+    """attn_int8_fwd for tensors that live in (pinned) host memory: q, k, v fp16/bf16 [B, H, S, D]
+    on the CPU, result written to ``out`` (pinned CPU tensor, allocated when None) and returned.
+
+    Batch elements are independent units, so the batch is cut into chunks of ``chunk_batch``
+    (default: B / 8, at least 1) that travel through three streams -- host->device copies, the
+    prologue + attention kernels on the caller's current stream, device->host copies -- with two
+    device staging slots, so that the two copy directions and the kernels overlap.  The accuracy
+    gate is evaluated per chunk (the same as calling the op on every chunk).  The caller's stream
+    is ordered after the last device->host copy on return; the copies themselves are asynchronous
+    for pinned tensors.  Keyword arguments are those of attn_int8_fwd (no seqlens)."""
+    if q.is_cuda or k.is_cuda or v.is_cuda:
+        raise RuntimeError("superl8_b200 attn_int8_fwd_host: q, k, v must be host tensors (see attn_int8_fwd)")
+    if not torch.cuda.is_available():
+        raise RuntimeError("superl8_b200 attn_int8_fwd_host: needs a CUDA device")
+    dev = torch.device("cuda", torch.cuda.current_device())
+    B = q.shape[0]
+    if out is None:
+        out = torch.empty(q.shape, dtype=v.dtype).pin_memory()
+    if B == 0 or q.numel() == 0:
+        return out
+    nb = max(1, B // 8) if chunk_batch is None else max(1, int(chunk_batch))
+    cur = torch.cuda.current_stream(dev)
+    if dev.index not in _aux_streams:
+        _aux_streams[dev.index] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
+    h2d, d2h = _aux_streams[dev.index]
+    h2d.wait_stream(cur)
+    slots = [tuple(torch.empty((nb, *t.shape[1:]), dtype=t.dtype, device=dev) for t in (q, k, v)) for _ in range(2)]
+    freed = [None, None]     # recorded on the compute stream when a slot's kernels are queued
+    starts = list(range(0, B, nb))
+
+    def upload(i):
+        b0, b1, s = starts[i], min(B, starts[i] + nb), i % 2
+        with torch.cuda.stream(h2d):
+            if freed[s] is not None:
+                h2d.wait_event(freed[s])
+            for dst, src in zip(slots[s], (q, k, v)):
+                dst[:b1 - b0].copy_(src[b0:b1], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(h2d)
+        return ev
+
+    arrived = upload(0)
+    for i in range(len(starts)):
+        b0, b1, s = starts[i], min(B, starts[i] + nb), i % 2
+        nxt = upload(i + 1) if i + 1 < len(starts) else None     # queued before this chunk's gate sync
+        cur.wait_event(arrived)
+        o = attn_int8_fwd(*(t[:b1 - b0] for t in slots[s]), **kw)
+        freed[s] = torch.cuda.Event()
+        freed[s].record(cur)
+        with torch.cuda.stream(d2h):
+            d2h.wait_event(freed[s])
+            out[b0:b1].copy_(o, non_blocking=True)
+        o.record_stream(d2h)
+        arrived = nxt
+    for t3 in slots:
+        for t in t3:
+            t.record_stream(h2d)
+    cur.wait_stream(d2h)
+    return out
+
+
 def attn_fp16_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, mask=None, window_left: int = -1):
     """Full-precision forward (reference superl8/ops.py:178-227)."""
     return _C.attn_fp16_fwd(q.contiguous(), k.contiguous(), v.contiguous(), causal, scale, window_left, mask)

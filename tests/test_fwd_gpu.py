@@ -277,3 +277,16 @@ def test_fp16_fwd_additive_mask(D, dtype, device):
     assert oracle.cos_sim(out, ref) >= 0.9999
     with pytest.raises(RuntimeError, match="mask"):
         _C.attn_fp16_fwd(q.to(device), k.to(device), v.to(device), False, None, -1, base[:, :, :, :5])
+
+
+def test_host_buffer_entry_point_equals_the_device_one(device):
+    # pinned host tensors in, pinned host tensor out, chunks of the batch on three streams
+    q, k, v = oracle.make_batch(77, 5, 4, 2, 200, 64)
+    ref = s8.attn_int8_fwd(q.to(device), k.to(device), v.to(device), causal=True).cpu()
+    hq, hk, hv = (t.pin_memory() for t in (q, k, v))
+    for chunk in (None, 2, 5, 8):
+        out = s8.attn_int8_fwd_host(hq, hk, hv, causal=True, chunk_batch=chunk)
+        torch.cuda.synchronize()
+        assert out.is_pinned() and torch.equal(out, ref), chunk
+    with pytest.raises(RuntimeError, match="host tensors"):
+        s8.attn_int8_fwd_host(q.to(device), hk, hv)
