@@ -323,6 +323,10 @@ int sl8_attn_int8_decode_static(const sl8_decode_params* p, int32_t* device_stat
  */
 int sl8_tensor_peak_probe(int kind_i8, int iters, double* ops_per_launch, void* workspace,
                           size_t workspace_bytes, void* stream);
+/* The same probe with N = n_cols (64, 128 or 256) columns per instruction: what the pipe sustains
+ * for the instruction shapes a kernel actually issues (smaller N = shorter instructions). */
+int sl8_tensor_peak_probe_n(int kind_i8, int n_cols, int iters, double* ops_per_launch, void* workspace,
+                            size_t workspace_bytes, void* stream);
 
 /* Synchronises the stream and returns the device status word of a workspace
  * (SL8_OK or SL8_ERR_DEVICE_TIMEOUT); clears it. */

@@ -148,9 +148,9 @@ def qk_logits_i32(q_i8: torch.Tensor, k_i8: torch.Tensor) -> torch.Tensor:
     return s
 
 
-def tensor_peak(kind_i8: bool, iters: int = 4096, device=None) -> float:
+def tensor_peak(kind_i8: bool, iters: int = 4096, device=None, n_cols: int = 256) -> float:
     """Measured tensor-pipe peak in T(FL)OP/s for kind::i8 (or kind::f16): times the probe launch
-    with CUDA events after one warm-up launch."""
+    with CUDA events after one warm-up launch.  ``n_cols`` (64, 128, 256) = N of the instruction."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     lib = _lib.load()
     ops = C.c_double(0.0)
@@ -160,8 +160,8 @@ def tensor_peak(kind_i8: bool, iters: int = 4096, device=None) -> float:
         for i in range(2):
             if i == 1:
                 e0.record()
-            rc = lib.sl8_tensor_peak_probe(int(bool(kind_i8)), int(iters), C.byref(ops), _ptr(ws), ws.numel() * 4,
-                                           _stream(device))
+            rc = lib.sl8_tensor_peak_probe_n(int(bool(kind_i8)), int(n_cols), int(iters), C.byref(ops), _ptr(ws),
+                                             ws.numel() * 4, _stream(device))
             _lib.check(rc, "tensor_peak_probe", 1)
         e1.record()
         torch.cuda.synchronize(device)

@@ -60,8 +60,9 @@ struct DecodeArgs {
   int B, Hq, Hkv, N, per, n_splits;
 };
 
+// int8 V: a stage is 16 KB at D = 128, so three blocks fit an SM if registers allow
 template <int D, bool V8>
-__global__ void __launch_bounds__(kDecThreads) decode_split_kernel(const __grid_constant__ CUtensorMap k_map,
+__global__ void __launch_bounds__(kDecThreads, (V8 && D <= 128) ? 3 : 1) decode_split_kernel(const __grid_constant__ CUtensorMap k_map,
                                                                    const __grid_constant__ CUtensorMap v_map,
                                                                    DecodeArgs a) {
   using C = DecodeCfg<D, V8>;

@@ -791,7 +791,7 @@ extern "C" int sl8_dbg_read_trace(long long* host_out, int n) {
 namespace sl8 {
 namespace {
 template <bool I8>
-__global__ void __launch_bounds__(128) tensor_peak_kernel(int iters, int* status) {
+__global__ void __launch_bounds__(128) tensor_peak_kernel(int iters, int n_cols, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int A_BYTES = 128 * 128, B_BYTES = 256 * 128;
@@ -813,7 +813,7 @@ __global__ void __launch_bounds__(128) tensor_peak_kernel(int iters, int* status
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   if (threadIdx.x == 0) {
-    const uint32_t idesc = I8 ? umma_idesc(2, 1, 1, 0, 0, 128, 256) : umma_idesc(1, 0, 0, 0, 0, 128, 256);
+    const uint32_t idesc = I8 ? umma_idesc(2, 1, 1, 0, 0, 128, n_cols) : umma_idesc(1, 0, 0, 0, 0, 128, n_cols);
     const uint32_t a_u = smem_u32(smem), b_u = smem_u32(smem + A_BYTES);
     for (int it = 0; it < iters; ++it) {
 #pragma unroll
@@ -839,19 +839,25 @@ __global__ void __launch_bounds__(128) tensor_peak_kernel(int iters, int* status
 
 extern "C" int sl8_tensor_peak_probe(int kind_i8, int iters, double* ops_per_launch, void* workspace,
                                      size_t workspace_bytes, void* stream) {
+  return sl8_tensor_peak_probe_n(kind_i8, 256, iters, ops_per_launch, workspace, workspace_bytes, stream);
+}
+
+extern "C" int sl8_tensor_peak_probe_n(int kind_i8, int n_cols, int iters, double* ops_per_launch, void* workspace,
+                                       size_t workspace_bytes, void* stream) {
   if (iters <= 0 || iters > (1 << 20)) return SL8_ERR_BAD_SHAPE;
+  if (n_cols != 64 && n_cols != 128 && n_cols != 256) return SL8_ERR_BAD_SHAPE;
   if (workspace == nullptr || workspace_bytes < 256) return SL8_ERR_WORKSPACE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int smem = 128 * 128 + 256 * 128 + 1024 + 64;
   const int grid = kNumSms;
   // K per instruction: 32 int8 or 16 halves (both 32 bytes)
-  if (ops_per_launch) *ops_per_launch = 2.0 * 128 * 256 * (kind_i8 ? 32 : 16) * 4.0 * iters * grid;
+  if (ops_per_launch) *ops_per_launch = 2.0 * 128 * n_cols * (kind_i8 ? 32 : 16) * 4.0 * iters * grid;
   if (kind_i8) {
     SL8_CUDA_TRY(cudaFuncSetAttribute(tensor_peak_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    tensor_peak_kernel<true><<<grid, 128, smem, s>>>(iters, reinterpret_cast<int*>(workspace));
+    tensor_peak_kernel<true><<<grid, 128, smem, s>>>(iters, n_cols, reinterpret_cast<int*>(workspace));
   } else {
     SL8_CUDA_TRY(cudaFuncSetAttribute(tensor_peak_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    tensor_peak_kernel<false><<<grid, 128, smem, s>>>(iters, reinterpret_cast<int*>(workspace));
+    tensor_peak_kernel<false><<<grid, 128, smem, s>>>(iters, n_cols, reinterpret_cast<int*>(workspace));
   }
   return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
 }
