@@ -1,0 +1,104 @@
+// The softmax sweep shared by the tensor-memory forward kernels: one pass over 64 accumulator
+// columns of a thread's query row (conversion, scaling, running max, 2^x, row sum, packing of P).
+#pragma once
+#include "sl8_common.cuh"
+
+namespace sl8 {
+
+constexpr int kSweepCols = 64;   // columns per sweep = one tcgen05.ld of 2 x 32 columns per thread
+
+constexpr float kLazyRescaleLog2 = 8.0f;
+
+
+__device__ __forceinline__ float2 bits2(uint32_t a, uint32_t b) {
+  return make_float2(__uint_as_float(a), __uint_as_float(b));
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+
+// One streaming pass over the kSweepCols columns of this thread's row:
+//   FIRST: r holds the accumulators.  int8 mode: t = float(acc) * k_scale[n]; 16-bit mode: t = acc.
+//          MASK = false leaves t in r (the exponent is then fma(t, qs, -m): scale and max
+//          subtraction in one instruction per pair); MASK = true (tiles on the diagonal, the
+//          window edge or the tail) leaves the finished logits t * qs, -inf where masked (xs = 1).
+//          The maximum of what is left in r is tracked (the caller scales it by qs >= 0).
+//          The reference multiplies (float(acc) * q_scale) * k_scale
+//          (csrc/include/attn_int8_fwd.cuh:137); the two orders differ by fp32 rounding only.
+//   both:  P = 2^(r * xs - m) goes to tensor memory as 16-bit pairs over the first kSweepCols / 2 columns
+//          of the S buffer, and its fp32 row sum is returned.
+// The sweep is software-pipelined by hand, in groups of G pairs: the ex2 of group g are issued,
+// then the conversion / scaling / max of group g + 1 (work for the FMA and ALU pipes that does
+// not depend on them), and only then the sums and the packing of group g.  A warp issues in
+// order, so this is what lets the special-function unit run while the other pipes work.
+template <bool QK8, bool MASK, bool FIRST, typename VT>
+__device__ __forceinline__ void softmax_pass(uint32_t (&r)[kSweepCols], const float* __restrict__ ksv, float qs, float xs,
+                                             float neg_m, int n_block, int n_len, int causal, int qpos,
+                                             int window_left, uint32_t t_p, float& mx, float& sum) {
+  const float2 qs2 = make_float2(qs, qs), xs2 = make_float2(xs, xs), neg_m2 = make_float2(neg_m, neg_m);
+  const float2* ks2 = reinterpret_cast<const float2*>(ksv);
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+  float2 sum_a = make_float2(0.f, 0.f), sum_b = sum_a;
+  constexpr int G = 4;                 // pairs per group
+  constexpr int NG = kSweepCols / 2 / G;      // groups per row
+  float2 x[2][G];
+  uint32_t pk[16];
+  // exponent arguments of group g -> x[g & 1]
+  auto prep = [&](int g, float2 (&xo)[G]) {
+    float2 p[G];
+#pragma unroll
+    for (int u = 0; u < G; ++u) {
+      const int i = g * G + u;
+      if (FIRST && QK8) p[u] = mul2(make_float2((float)(int)r[2 * i], (float)(int)r[2 * i + 1]), ks2[i]);
+      else p[u] = bits2(r[2 * i], r[2 * i + 1]);
+    }
+    if (FIRST && MASK) {
+#pragma unroll
+      for (int u = 0; u < G; ++u) {
+        p[u] = mul2(p[u], qs2);
+        const int gn = n_block + 2 * (g * G + u);
+        const bool v0 = (gn < n_len) && (!causal || gn <= qpos) && (window_left < 0 || gn > qpos - window_left);
+        const bool v1 = (gn + 1 < n_len) && (!causal || gn + 1 <= qpos) && (window_left < 0 || gn + 1 > qpos - window_left);
+        p[u].x = v0 ? p[u].x : -INFINITY;
+        p[u].y = v1 ? p[u].y : -INFINITY;
+      }
+    }
+    if (FIRST) {
+#pragma unroll
+      for (int u = 0; u < G; u += 2) {
+        mx0 = max3f(mx0, p[u].x, p[u].y);
+        mx1 = max3f(mx1, p[u + 1].x, p[u + 1].y);
+      }
+      if (QK8 || MASK) {
+#pragma unroll
+        for (int u = 0; u < G; ++u) {
+          r[2 * (g * G + u)] = __float_as_uint(p[u].x);
+          r[2 * (g * G + u) + 1] = __float_as_uint(p[u].y);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < G; ++u) xo[u] = __ffma2_rn(p[u], xs2, neg_m2);
+  };
+  prep(0, x[0]);
+#pragma unroll
+  for (int g = 0; g < NG; ++g) {
+    float2(&xc)[G] = x[g & 1];
+#pragma unroll
+    for (int u = 0; u < G; ++u) xc[u] = make_float2(ex2_issue(xc[u].x), ex2_issue(xc[u].y));
+    if (g + 1 < NG) prep(g + 1, x[(g + 1) & 1]);
+#pragma unroll
+    for (int u = 0; u < G; u += 2) {
+      sum_a = add2(sum_a, xc[u]);
+      sum_b = add2(sum_b, xc[u + 1]);
+    }
+#pragma unroll
+    for (int u = 0; u < G; ++u) pk[(g * G + u) & 15] = pack2<VT>(xc[u].x, xc[u].y);
+    if (((g + 1) * G) % 16 == 0) tc_st16(t_p + 16 * (((g + 1) * G) / 16 - 1), pk);
+  }
+  const float2 st = add2(sum_a, sum_b);
+  sum = st.x + st.y;
+  mx = fmaxf(mx0, mx1);
+}
+
+
+}  // namespace sl8
