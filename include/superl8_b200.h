@@ -168,6 +168,28 @@ size_t sl8_attn_fp16_fwd_workspace(const sl8_fp16_fwd_params* p);
 int sl8_attn_fp16_fwd(const sl8_fp16_fwd_params* p, void* workspace, size_t workspace_bytes,
                       void* stream);
 
+/* ---- full W8A8 prefill (int8 P.V) ------------------------------------------------------ */
+
+/*
+ * Replaces `attn_w8a8_fwd` (reference csrc/kernel/attn_w8a8_fwd.cu:72-160, kernel
+ * csrc/include/attn_w8a8_fwd.cuh:30-235, binding csrc/fni8_api.cpp:249-255; the
+ * `int8_pv=True` branch of superl8/ops.py:152-166).  q, k as for sl8_attn_int8_fwd; v int8
+ * [B, Hkv, N, D] with v_scale fp32 [B, Hkv, D] (sl8_quantize_v_perchannel); out fp16.
+ * P is re-quantised to int8 per query row and 64-key tile (per_warp_quant == 0) or per row and
+ * 32-key half of the tile (per_warp_quant != 0, the reference's default).  causal_diag = N - M
+ * aligns the causal diagonal to the sequence end (the Python layer passes it).  D in
+ * {32, 64, 128, 256}.  No workspace.
+ */
+typedef struct sl8_w8a8_params {
+  const int8_t* q; const float* q_scale;
+  const int8_t* k; const float* k_scale;
+  const int8_t* v; const float* v_scale;
+  void* out;
+  int32_t B, Hq, Hkv, M, N, D;
+  int32_t causal; int32_t causal_diag; int32_t per_warp_quant;
+} sl8_w8a8_params;
+int sl8_attn_w8a8_fwd(const sl8_w8a8_params* p, void* stream);
+
 /* ---- packed variable-length prefill ------------------------------------------------- */
 
 /*

@@ -292,6 +292,65 @@ def attn_int8_fwd(q_i8, q_scale, k_i8, k_scale, v, causal=False, window_left=-1,
     return (out, lse) if want_lse else out
 
 
+def attn_w8a8_fwd(q_i8, q_scale, k_i8, k_scale, v_i8, v_scale, causal=False, causal_diag=0, per_warp=True):
+    """Reference csrc/include/attn_w8a8_fwd.cuh:93-222, tile by tile (64 keys): logits as in
+    attn_int8_fwd; per tile m_new = max(m, tile max), P = exp2(s - m_new); p_scale =
+    max(max(P) / 127, 2e-38) per row and tile, or per row and 32-key half (per_warp);
+    P8 = rint(P / p_scale); O = O * exp2(m - m_new) + (P8 @ V8) * p_scale * v_scale; l from the
+    unquantised P; out = O / l -> fp16.  q_scale [B,Hq,M], k_scale [B,Hkv,N], v_scale [B,Hkv,D]."""
+    f32 = np.float32
+    q_i8, k_i8, v_i8 = q_i8.detach().cpu(), k_i8.detach().cpu(), v_i8.detach().cpu()
+    qs, ks = q_scale.detach().cpu().float().numpy(), k_scale.detach().cpu().float().numpy()
+    B, Hq, M, D = q_i8.shape
+    Hkv, N = k_i8.shape[1], k_i8.shape[2]
+    vs = v_scale.detach().cpu().float().reshape(B, Hkv, D).numpy()
+    g = Hq // Hkv
+    out = torch.zeros((B, Hq, M, D), dtype=torch.float16)
+    if M == 0 or N == 0:
+        return out
+    row = np.arange(M).reshape(-1, 1)
+    col = np.arange(N).reshape(1, -1)
+    valid = np.ones((M, N), dtype=bool)
+    if causal:
+        valid &= col <= row + causal_diag
+    inv127 = f32(1.0) / f32(127.0)
+    with np.errstate(over="ignore", invalid="ignore", divide="ignore"):
+        for b in range(B):
+            for h in range(Hq):
+                hk = h // g
+                acc = int32_logits(q_i8[b, h], k_i8[b, hk]).numpy().astype(f32)
+                s = (acc * qs[b, h].reshape(-1, 1).astype(f32)) * ks[b, hk].reshape(1, -1).astype(f32)
+                s = np.where(valid, s, -np.inf).astype(f32)
+                v8 = v_i8[b, hk].numpy().astype(np.int32)
+                m_i = np.full(M, -np.inf, dtype=f32)
+                l_i = np.zeros(M, dtype=f32)
+                o = np.zeros((M, D), dtype=f32)
+                for n0 in range(0, N, 64):
+                    st = s[:, n0:n0 + 64]
+                    if st.shape[1] < 64:
+                        st = np.concatenate([st, np.full((M, 64 - st.shape[1]), -np.inf, dtype=f32)], axis=1)
+                    vt = np.zeros((64, D), dtype=np.int32)
+                    vt[:min(64, N - n0)] = v8[n0:n0 + 64]
+                    m_new = np.maximum(m_i, st.max(axis=1))
+                    live = np.isfinite(m_new)
+                    p = np.where(np.isfinite(st) & live[:, None], np.exp2(st - np.where(live, m_new, 0)[:, None]), 0).astype(f32)
+                    rescale = np.where(np.isfinite(m_i) & live, np.exp2(m_i - np.where(live, m_new, 0)), 1).astype(f32)
+                    o *= rescale[:, None]
+                    l_i = (l_i * rescale + p.sum(axis=1, dtype=f32)).astype(f32)
+                    m_i = np.maximum(m_i, m_new)
+                    halves = ((0, 32), (32, 64)) if per_warp else ((0, 64),)
+                    contrib = np.zeros((M, D), dtype=f32)
+                    for lo, hi in halves:
+                        pmax = p[:, lo:hi].max(axis=1)
+                        p_scale = np.maximum(pmax * inv127, f32(2e-38)).astype(f32)
+                        p8 = np.rint(p[:, lo:hi] * (f32(1.0) / p_scale)[:, None]).astype(np.int32)
+                        contrib += (p8 @ vt[lo:hi]).astype(f32) * p_scale[:, None]
+                    o += contrib * vs[b, hk].reshape(1, -1)
+                inv = np.where(l_i > 0, f32(1.0) / np.where(l_i > 0, l_i, 1), 0).astype(f32)
+                out[b, h] = torch.from_numpy((o * inv[:, None]).astype(np.float16))
+    return out
+
+
 def choose_n_splits_reference(n_len: int, bhq: int) -> int:
     """Reference csrc/kernel/attn_decode.cu:33-53."""
     if n_len <= 0 or bhq <= 0:

@@ -13,6 +13,7 @@
 #include "attn_decode.cuh"
 #include "attn_int8_fwd.cuh"
 #include "attn_varlen_fwd.cuh"
+#include "attn_w8a8_fwd.cuh"
 #include "quant_rowwise.cuh"
 
 namespace {
@@ -157,6 +158,41 @@ extern "C" int ref_attn_int8_decode_kv8(const int8_t* q, const float* qs, const 
     case 64: return decode_kv8_d<64>(q, qs, k, ks, v, vs, (__half*)out, o_part, m_part, l_part, N, n_splits, BHq, Hq, g, s);
     case 128: return decode_kv8_d<128>(q, qs, k, ks, v, vs, (__half*)out, o_part, m_part, l_part, N, n_splits, BHq, Hq, g, s);
     case 256: return decode_kv8_d<256>(q, qs, k, ks, v, vs, (__half*)out, o_part, m_part, l_part, N, n_splits, BHq, Hq, g, s);
+  }
+  return -1;
+}
+
+// reference csrc/kernel/attn_w8a8_fwd.cu:16-39 (static shared memory variant: D = 32, 64, 128)
+template <int D, bool PW>
+static int w8a8_d(const int8_t* q, const float* qs, const int8_t* k, const float* ks, const int8_t* v, const float* vs,
+                  __half* out, int causal, int M, int N, int64_t BH, int Hq, int g, int diag, cudaStream_t s) {
+  const dim3 grid((M + fni8::BLOCK_M - 1) / fni8::BLOCK_M, (unsigned)BH);
+  if (causal)
+    fni8::attn_w8a8_fwd_kernel<D, true, PW><<<grid, fni8::THREADS, 0, s>>>(q, qs, k, ks, v, vs, out, M, N, Hq, g, diag);
+  else
+    fni8::attn_w8a8_fwd_kernel<D, false, PW><<<grid, fni8::THREADS, 0, s>>>(q, qs, k, ks, v, vs, out, M, N, Hq, g, diag);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ref_attn_w8a8_fwd(const int8_t* q, const float* qs, const int8_t* k, const float* ks, const int8_t* v,
+                                 const float* vs, void* out, int causal, int causal_diag, int per_warp, int B, int Hq,
+                                 int Hkv, int M, int N, int D, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  const int g = Hq / Hkv;
+  const int64_t BH = (int64_t)B * Hq;
+  __half* o = (__half*)out;
+  if (per_warp) {
+    switch (D) {
+      case 32: return w8a8_d<32, true>(q, qs, k, ks, v, vs, o, causal, M, N, BH, Hq, g, causal_diag, s);
+      case 64: return w8a8_d<64, true>(q, qs, k, ks, v, vs, o, causal, M, N, BH, Hq, g, causal_diag, s);
+      case 128: return w8a8_d<128, true>(q, qs, k, ks, v, vs, o, causal, M, N, BH, Hq, g, causal_diag, s);
+    }
+  } else {
+    switch (D) {
+      case 32: return w8a8_d<32, false>(q, qs, k, ks, v, vs, o, causal, M, N, BH, Hq, g, causal_diag, s);
+      case 64: return w8a8_d<64, false>(q, qs, k, ks, v, vs, o, causal, M, N, BH, Hq, g, causal_diag, s);
+      case 128: return w8a8_d<128, false>(q, qs, k, ks, v, vs, o, causal, M, N, BH, Hq, g, causal_diag, s);
+    }
   }
   return -1;
 }

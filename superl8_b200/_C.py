@@ -253,6 +253,28 @@ def attn_int8_decode(q, q_scale, k, k_scale, v, num_splits=-1, *, context_lens=N
     return out
 
 
+def attn_w8a8_fwd(q, q_scale, k, k_scale, v, v_scale, causal=False, causal_diag=0, per_warp_quant=True):
+    """Full-W8A8 forward (int8 Q.K^T and int8 P.V).  Reference binding csrc/fni8_api.cpp:249-255
+    (op csrc/kernel/attn_w8a8_fwd.cu:72-160): v int8 [B, Hkv, N, D], v_scale fp32 [B, Hkv, D];
+    returns fp16 [B, Hq, M, D]."""
+    what = "superl8_b200 w8a8"
+    _check(v.is_cuda and v.dtype == torch.int8, f"{what}: q/k/v must be int8")
+    _check(v_scale.is_cuda and v_scale.dtype == torch.float32, f"{what}: scales must be float32")
+    B, H, Hkv, M, N, D = _fwd_checks(q, q_scale, k, k_scale, v, what)
+    _check(v_scale.is_contiguous() and v_scale.numel() == B * Hkv * D, f"{what}: scale shape mismatch")
+    _check(D in (32, 64, 128, 256), f"{what}: head dim must be 32/64/128/256, got {D}")
+    out = torch.empty((B, H, M, D), dtype=torch.float16, device=q.device)
+    if out.numel() == 0:
+        return out
+    p = _lib.W8A8Params(q=q.data_ptr(), q_scale=q_scale.data_ptr(), k=k.data_ptr(), k_scale=k_scale.data_ptr(),
+                        v=v.data_ptr(), v_scale=v_scale.data_ptr(), out=out.data_ptr(), B=B, Hq=H, Hkv=Hkv, M=M, N=N,
+                        D=D, causal=int(bool(causal)), causal_diag=int(causal_diag), per_warp_quant=int(bool(per_warp_quant)))
+    with torch.cuda.device(q.device):
+        rc = _lib.load().sl8_attn_w8a8_fwd(C.byref(p), _stream(q.device))
+    _lib.check(rc, "attn_w8a8_fwd", 1)
+    return out
+
+
 def attn_int8_decode_kv8(q, q_scale, k, k_scale, v_i8, v_scale, num_splits=-1, *, context_lens=None):
     """Decode against an int8 K / int8 V cache.  Reference binding `attn_int8_decode_kv8`
     (kernel csrc/include/attn_decode.cuh:141-224): v_i8 int8 [B, Hkv, N, D], v_scale fp32

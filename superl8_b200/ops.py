@@ -20,7 +20,9 @@ def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, 
 
     Same contract as the reference entry (superl8/ops.py:70-175): per-row int8 Q and
     smoothed K with exp2-ready folded scales, fp32 softmax, 16-bit P.V, bottom-right
-    aligned causal mask, optional left window.  The accuracy gate (any Q row with
+    aligned causal mask, optional left window.  ``int8_pv=True`` takes the full-W8A8 route
+    instead (V per-channel int8, P re-quantised per tile; ``per_warp_quant`` picks the finer
+    per-32-key P scale; fp16 output; no gate, as in the reference).  The accuracy gate (any Q row with
     max|q|/median|q| > 12) demotes the whole call to the full-precision kernel; it is
     evaluated inside the Q quantisation pass and costs one 4-byte device->host read,
     skipped during CUDA-graph capture like the reference's.
@@ -28,10 +30,21 @@ def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, 
     lengths for padded ragged batches.
     """
     global last_gate_decision
-    if int8_pv:
-        raise NotImplementedError("superl8_b200: int8 P.V (int8_pv=True) is not implemented; P.V runs in v's dtype")
-    del per_warp_quant
     s = (1.0 / math.sqrt(q.shape[-1])) if scale is None else scale
+    if int8_pv:
+        # reference superl8/ops.py:152-166: no gate on this branch, no window, V per channel
+        if window_left >= 0:
+            raise ValueError("window_left is only supported on the fp16-PV path (int8_pv=False)")
+        if seqlens_q is not None or seqlens_k is not None:
+            raise ValueError("seqlens are only supported on the fp16-PV path (int8_pv=False)")
+        from .quant import quantize_v_perchannel
+
+        q_i8, q_scale, k_i8, k_scale, _ = quantize_qk(q, k, softmax_scale=s, rotate=rotate)
+        v_i8, v_scale = quantize_v_perchannel(v)
+        last_gate_decision = None
+        return _C.attn_w8a8_fwd(q_i8, q_scale.squeeze(-1).contiguous(), k_i8, k_scale.squeeze(-1).contiguous(), v_i8,
+                                v_scale.squeeze(-2).contiguous(), causal,
+                                causal_diag=(k.shape[-2] - q.shape[-2]) if causal else 0, per_warp_quant=per_warp_quant)
     use_gate = internal_accuracy_gate and not _capturing()
     if rotate:
         if use_gate:

@@ -97,3 +97,14 @@ def ref_attn_int8_decode_kv8(q_i8, q_scale, k_i8, k_scale, v_i8, v_scale, n_spli
                                             _p(o_part), _p(m_part), _p(l_part), B, Hq, Hkv, N, D, n_splits, _stream())
     assert rc == 0
     return out
+
+
+def ref_attn_w8a8_fwd(q_i8, q_scale, k_i8, k_scale, v_i8, v_scale, causal, causal_diag, per_warp):
+    """The reference's full-W8A8 kernel on the same int8 inputs (D = 32, 64, 128)."""
+    B, Hq, M, D = q_i8.shape
+    Hkv, N = k_i8.shape[1], k_i8.shape[2]
+    out = torch.empty((B, Hq, M, D), dtype=torch.float16, device=q_i8.device)
+    rc = ref_lib().ref_attn_w8a8_fwd(_p(q_i8), _p(q_scale), _p(k_i8), _p(k_scale), _p(v_i8), _p(v_scale), _p(out),
+                                     int(causal), int(causal_diag), int(per_warp), B, Hq, Hkv, M, N, D, _stream())
+    assert rc == 0
+    return out

@@ -166,3 +166,18 @@ def test_v_perchannel_quantiser_matches_the_reference():
         v = from_bits(g[f"{name}__v"], str(g[f"{name}__dtype"]))
         v_i8, v_scale = oracle.quantize_v_perchannel(v)
         assert np.array_equal(v_i8.numpy(), g[f"{name}__v_i8"]) and np.array_equal(v_scale.numpy(), g[f"{name}__v_scale"])
+
+
+def test_w8a8_restatement_quality_and_ladder():
+    # reference tests/test_attn_fwd_w8a8.py:37-75: the int8-P.V route meets its own bars against
+    # the fp32 oracle and is no better than the fp16-P.V route
+    q, k, v = oracle.make_batch(9, 1, 4, 2, 150, 64)
+    q_i8, q_scale, k_i8, k_scale, _ = oracle.quantize_qk(q, k)
+    v_i8, v_scale = oracle.quantize_v_perchannel(v)
+    ref = oracle.attention_fp32(q, k, v, causal=True)
+    for per_warp in (True, False):
+        out = oracle.attn_w8a8_fwd(q_i8, q_scale.squeeze(-1), k_i8, k_scale.squeeze(-1), v_i8, v_scale.squeeze(-2),
+                                   causal=True, causal_diag=0, per_warp=per_warp)
+        oracle.assert_int8_quality(out, ref, min_cos=0.998, max_rel_l1=0.03, min_sqnr_db=18.0, what=f"w8a8 {per_warp}")
+    fp16pv = oracle.attn_int8_fwd(q_i8, q_scale.squeeze(-1), k_i8, k_scale.squeeze(-1), v, causal=True)
+    assert oracle.rel_l1(fp16pv, ref) <= oracle.rel_l1(out, ref) + 1e-4
