@@ -81,6 +81,14 @@ int sl8_quant_q_prologue(const void* q, int dtype, int64_t rows, int64_t D, floa
                          float* plain_scale, int32_t* outlier_flag, void* stream);
 
 /*
+ * The accuracy gate alone (reference superl8/quant/core.py:113-145, which superl8/ops.py:118-130 runs
+ * before it quantises): *outlier_flag |= 1 when some row of q [rows, D] has
+ * max|q| / (median|q| + 1e-10) > ratio_threshold.  Reads q once, writes nothing else.
+ */
+int sl8_q_outlier_gate(const void* q, int dtype, int64_t rows, int64_t D, float ratio_threshold,
+                       int32_t* outlier_flag, void* stream);
+
+/*
  * K prologue, step 1: per-(batch, kv-head) fp32 mean over the keys,
  * k[BH, N, D] -> mean[BH, D]  (reference superl8/quant/core.py:29-44, 81-85).
  * seqlens (nullable, int32[B], with heads_per_batch = Hkv) restricts sequence b

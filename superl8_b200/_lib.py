@@ -103,6 +103,7 @@ SIGNATURES = {
     "sl8_quantize_i8_rowwise": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "sl8_quant_q_prologue": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_float, C.c_float,
                                        C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "sl8_q_outlier_gate": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_float, C.c_void_p, C.c_void_p]),
     "sl8_k_mean_workspace": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64]),
     "sl8_k_mean": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int32,
                              C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),

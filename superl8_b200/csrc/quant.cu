@@ -19,7 +19,9 @@ constexpr int kQuantThreads = 256;
 constexpr float kQMax = 127.0f;
 constexpr float kQMaxInv = 1.0f / 127.0f;
 
-enum QuantMode { kPlain = 0, kQueryFoldGate = 1, kKeySmooth = 2 };
+// kGateOnly: the outlier statistic of the query mode alone -- rows are read, nothing is written
+// but the flag (the reference runs its gate before it quantises, superl8/ops.py:118-130)
+enum QuantMode { kPlain = 0, kQueryFoldGate = 1, kKeySmooth = 2, kGateOnly = 3 };
 
 struct QuantArgs {
   const void* x;
@@ -166,7 +168,7 @@ __global__ void __launch_bounds__(kQuantThreads) quant_rows_vec_kernel(QuantArgs
     float s = amax * kQMaxInv;
     s = (s == 0.0f) ? 1.0f : s;
 
-    if (MODE == kQueryFoldGate && a.flag != nullptr) {
+    if ((MODE == kQueryFoldGate || MODE == kGateOnly) && a.flag != nullptr) {
       // max / (median + 1e-10) > thr  <=>  at least rank_need elements e satisfy
       // max / (|e| + 1e-10) > thr, because the quotient is monotone in |e|.  Elements whose
       // y = |e| + 1e-10 is clearly below / above max / thr are decided by a comparison; only
@@ -207,6 +209,7 @@ __global__ void __launch_bounds__(kQuantThreads) quant_rows_vec_kernel(QuantArgs
       for (int off = LPR / 2; off > 0; off >>= 1) cnt += __shfl_xor_sync(FULL, cnt, off);
       if (live && cnt >= rank_need) any_outlier = 1;
     }
+    if (MODE == kGateOnly) continue;
 
     // Codes.  Fast path: t = x * (1/s) + 1.5 * 2^23 rounds x / s to the nearest integer in one
     // fused operation (its low byte is the code).  1/s carries a 2^-24 relative error, so the
@@ -249,7 +252,7 @@ __global__ void __launch_bounds__(kQuantThreads) quant_rows_vec_kernel(QuantArgs
       }
     }
   }
-  if (MODE == kQueryFoldGate && a.flag != nullptr) {
+  if ((MODE == kQueryFoldGate || MODE == kGateOnly) && a.flag != nullptr) {
     any_outlier = __syncthreads_or(any_outlier);
     if (threadIdx.x == 0 && any_outlier) atomicOr(a.flag, 1);
   }
@@ -279,7 +282,7 @@ __global__ void __launch_bounds__(kQuantThreads) quant_rows_generic_kernel(Quant
     for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(FULL, amax, off));
     float s = amax * kQMaxInv;
     s = (s == 0.0f) ? 1.0f : s;
-    if (MODE == kQueryFoldGate && a.flag != nullptr) {
+    if ((MODE == kQueryFoldGate || MODE == kGateOnly) && a.flag != nullptr) {
       int cnt = 0;
       for (int c = lane; c < a.K; c += 32)
         cnt += (__fdiv_rn(amax, fabsf(elem(c)) + 1e-10f) > a.ratio_threshold) ? 1 : 0;
@@ -287,6 +290,7 @@ __global__ void __launch_bounds__(kQuantThreads) quant_rows_generic_kernel(Quant
       for (int off = 16; off > 0; off >>= 1) cnt += __shfl_xor_sync(FULL, cnt, off);
       if (cnt >= rank_need) any_outlier = 1;
     }
+    if (MODE == kGateOnly) continue;
     int8_t* qr = a.q + row * a.K;
     for (int c = lane; c < a.K; c += 32) {
       const float e = elem(c);
@@ -303,7 +307,7 @@ __global__ void __launch_bounds__(kQuantThreads) quant_rows_generic_kernel(Quant
       }
     }
   }
-  if (MODE == kQueryFoldGate && a.flag != nullptr) {
+  if ((MODE == kQueryFoldGate || MODE == kGateOnly) && a.flag != nullptr) {
     any_outlier = __syncthreads_or(any_outlier);
     if (threadIdx.x == 0 && any_outlier) atomicOr(a.flag, 1);
   }
@@ -325,7 +329,7 @@ void launch_vec(const QuantArgs& a, cudaStream_t s) {
 template <typename T, int MODE>
 int launch_2byte(const QuantArgs& a, cudaStream_t s) {
   const int kvec = a.K / 8;
-  const bool vec_ok = (a.K % 8 == 0) && aligned16(a.x) && (reinterpret_cast<uintptr_t>(a.q) % 8 == 0) &&
+  const bool vec_ok = (a.K % 8 == 0) && aligned16(a.x) && (MODE == kGateOnly || reinterpret_cast<uintptr_t>(a.q) % 8 == 0) &&
                       (MODE != kKeySmooth || (aligned16(a.mean) && (a.smoothed == nullptr || aligned16(a.smoothed))));
   // lanes per row x vectors per lane: four 16-byte vectors per lane amortise the per-row work
   // (reductions, scale, reciprocal, threshold) over 32 elements
@@ -345,7 +349,8 @@ template <int MODE>
 int dispatch(const QuantArgs& a, int dtype, cudaStream_t s) {
   if (a.rows < 0 || a.K < 0) return SL8_ERR_BAD_SHAPE;
   if (a.rows == 0 || a.K == 0) return SL8_OK;
-  if (a.x == nullptr || a.q == nullptr || a.scale == nullptr) return SL8_ERR_NULL;
+  if (a.x == nullptr || (MODE != kGateOnly && (a.q == nullptr || a.scale == nullptr))) return SL8_ERR_NULL;
+  if (MODE == kGateOnly && a.flag == nullptr) return SL8_ERR_NULL;
   switch (dtype) {
     case SL8_F16: return launch_2byte<__half, MODE>(a, s);
     case SL8_BF16: return launch_2byte<__nv_bfloat16, MODE>(a, s);
@@ -526,6 +531,14 @@ __global__ void __launch_bounds__(kMeanThreads) k_mean_packed_kernel(
 }  // namespace sl8
 
 using namespace sl8;
+
+extern "C" int sl8_q_outlier_gate(const void* q, int dtype, int64_t rows, int64_t D, float ratio_threshold,
+                                  int32_t* outlier_flag, void* stream) {
+  if (D > (1 << 30)) return SL8_ERR_TOO_LARGE;
+  QuantArgs a{};
+  a.x = q; a.flag = outlier_flag; a.rows = rows; a.K = (int)D; a.rows_per_head = 1; a.ratio_threshold = ratio_threshold;
+  return dispatch<kGateOnly>(a, dtype, static_cast<cudaStream_t>(stream));
+}
 
 extern "C" int sl8_quantize_v_perchannel(const void* v, int dtype, int64_t BH, int64_t N, int64_t D, int8_t* v_i8,
                                          float* v_scale, void* workspace, size_t workspace_bytes, void* stream) {

@@ -7,7 +7,8 @@ import math
 import torch
 
 from . import _C, _lib
-from .quant import _capturing, quantize_q, quantize_qk, smooth_quantize_k, k_mean, varlen_smooth_quantize_k
+from .quant import (_capturing, k_mean, q_outlier_flag, quantize_q, quantize_qk, smooth_quantize_k,
+                    varlen_smooth_quantize_k)
 
 last_gate_decision: bool | None = None  # whether the most recent attn_int8_fwd call was demoted
 
@@ -24,8 +25,9 @@ def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, 
     instead (V per-channel int8, P re-quantised per tile; ``per_warp_quant`` picks the finer
     per-32-key P scale; fp16 output; no gate, as in the reference).  The accuracy gate (any Q row with
     max|q|/median|q| > 12) demotes the whole call to the full-precision kernel; it is
-    evaluated inside the Q quantisation pass and costs one 4-byte device->host read,
-    skipped during CUDA-graph capture like the reference's.
+    evaluated inside the Q quantisation pass (or, right after a demoted call, by a read-only
+    pass before any quantisation) and costs one 4-byte device->host read, skipped during
+    CUDA-graph capture like the reference's.
     ``seqlens_q`` / ``seqlens_k`` (int32 [B], not in the reference) give per-sequence
     lengths for padded ragged batches.
     """
@@ -54,8 +56,18 @@ def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, 
                 return _C.attn_fp16_fwd(q, k, v, causal, s, window_left, None, seqlens_q=seqlens_q, seqlens_k=seqlens_k)
         q_i8, q_scale, k_i8, k_scale, _ = quantize_qk(q, k, softmax_scale=s, rotate=True, seqlens_k=seqlens_k)
     else:
-        q_i8, q_scale, flag = quantize_q(q, s, want_gate=use_gate)
-        if use_gate and bool(flag.item()):
+        if use_gate and last_gate_decision:
+            # The previous call was demoted: ask the gate first (one read of Q, as the reference
+            # orders it) instead of quantising a Q that is probably not going to be used.
+            flag = q_outlier_flag(q)
+            demote = bool(flag.item())
+            if not demote:
+                q_i8, q_scale, _ = quantize_q(q, s, want_gate=False)
+        else:
+            # gate statistic fused into the quantisation pass
+            q_i8, q_scale, flag = quantize_q(q, s, want_gate=use_gate)
+            demote = use_gate and bool(flag.item())
+        if demote:
             last_gate_decision = True
             if v.dtype == q.dtype and k.dtype == q.dtype:
                 return _C.attn_fp16_fwd(q, k, v, causal, s, window_left, None, seqlens_q=seqlens_q, seqlens_k=seqlens_k)

@@ -174,6 +174,22 @@ def quantize_q(q: torch.Tensor, softmax_scale: float, want_gate: bool = False,
     return q_i8, q_scale, flag
 
 
+def q_outlier_flag(q: torch.Tensor, ratio_threshold: float = OUTLIER_RATIO_THRESHOLD) -> torch.Tensor:
+    """Device flag (int32 [1], non-zero = some row of q is outlier dominated) from one read of q,
+    nothing quantised: the gate the reference evaluates before it quantises."""
+    _require_cuda(q, "q_outlier_flag")
+    q = q.contiguous()
+    D = q.shape[-1]
+    rows = q.numel() // D if D else 0
+    flag = torch.zeros(1, dtype=torch.int32, device=q.device)
+    if q.numel():
+        with torch.cuda.device(q.device):
+            rc = _lib.load().sl8_q_outlier_gate(q.data_ptr(), _C._DTYPE[q.dtype], rows, D, C.c_float(ratio_threshold),
+                                                flag.data_ptr(), _C._stream(q.device))
+        _lib.check(rc, "q_outlier_gate", 1)
+    return flag
+
+
 def _capturing() -> bool:
     try:
         return bool(torch.cuda.is_current_stream_capturing())
@@ -187,8 +203,7 @@ def detect_q_outlier_domination(q: torch.Tensor, *, ratio_threshold: float = OUT
     reference (superl8/quant/core.py:113-145): the answer needs a device->host read."""
     if _capturing():
         return False
-    _q_i8, _q_scale, flag = quantize_q(q, 1.0, want_gate=True, ratio_threshold=ratio_threshold)
-    return bool(flag.item())
+    return bool(q_outlier_flag(q, ratio_threshold).item())
 
 
 def rotate_last(x: torch.Tensor) -> torch.Tensor:

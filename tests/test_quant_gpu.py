@@ -182,3 +182,30 @@ def test_gate_exact_at_the_threshold_boundary(device):
         for lo in range(0, 3000, 500):
             blk = x[lo:lo + 500]
             assert s8.detect_q_outlier_domination(blk.view(1, 1, -1, D).contiguous().to(device)) == bool(e[lo:lo + 500].any())
+
+
+def test_gate_only_kernel_equals_the_fused_gate(device):
+    # the statistic evaluated alone (one read of Q) and inside the quantisation pass must agree
+    g = np.load(GOLDEN / "outlier_gate.npz")
+    for name in ("clean", "spike", "chan20", "d64", "near"):
+        q = from_bits(g[f"{name}__q"], "float16").to(device)
+        alone = bool(quant.q_outlier_flag(q).item())
+        fused = bool(quant.quantize_q(q, 1.0, want_gate=True)[2].item())
+        assert alone == fused == bool(g[f"{name}__flag"]), name
+    x = torch.randn(33, 72, device=device)          # fp32 / odd width: generic kernel
+    x[5, 3] = 500.0
+    assert bool(quant.q_outlier_flag(x).item()) and not bool(quant.q_outlier_flag(torch.randn(33, 72, device=device)).item())
+
+
+def test_attention_asks_the_gate_first_after_a_demotion(device):
+    q, k, v = (t.to(device) for t in oracle.make_batch(91, 1, 4, 2, 128, 64))
+    qo = q.clone()
+    qo[..., 5] *= 40.0
+    a1 = s8.attn_int8_fwd(qo, k, v, causal=True)          # demoted (fused gate)
+    assert s8.ops.last_gate_decision is True
+    a2 = s8.attn_int8_fwd(qo, k, v, causal=True)          # demoted again (gate asked first)
+    assert s8.ops.last_gate_decision is True and torch.equal(a1, a2)
+    b1 = s8.attn_int8_fwd(q, k, v, causal=True)           # gate first, passes, then quantise
+    assert s8.ops.last_gate_decision is False
+    b2 = s8.attn_int8_fwd(q, k, v, causal=True)           # fused gate
+    assert torch.equal(b1, b2)
