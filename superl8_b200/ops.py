@@ -83,12 +83,12 @@ def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, 
 _aux_streams: dict = {}
 
 
-def attn_int8_fwd_host(q, k, v, out=None, *, chunk_batch: int | None = None, **kw):
+def attn_int8_fwd_host(q, k, v, out=None, *, chunk_batch: int | None = None, staging_slots: int = 2, **kw):
     """attn_int8_fwd for tensors that live in (pinned) host memory: q, k, v fp16/bf16 [B, H, S, D]
     on the CPU, result written to ``out`` (pinned CPU tensor, allocated when None) and returned.
 
     Batch elements are independent units, so the batch is cut into chunks of ``chunk_batch``
-    (default: B / 8, at least 1) that travel through three streams -- host->device copies, the
+    (default: B / 16, at least 1) that travel through three streams -- host->device copies, the
     prologue + attention kernels on the caller's current stream, device->host copies -- with two
     device staging slots, so that the two copy directions and the kernels overlap.  The accuracy
     gate is evaluated per chunk (the same as calling the op on every chunk).  The caller's stream
@@ -104,18 +104,19 @@ def attn_int8_fwd_host(q, k, v, out=None, *, chunk_batch: int | None = None, **k
         out = torch.empty(q.shape, dtype=v.dtype).pin_memory()
     if B == 0 or q.numel() == 0:
         return out
-    nb = max(1, B // 8) if chunk_batch is None else max(1, int(chunk_batch))
+    nb = max(1, B // 16) if chunk_batch is None else max(1, int(chunk_batch))
     cur = torch.cuda.current_stream(dev)
     if dev.index not in _aux_streams:
         _aux_streams[dev.index] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
     h2d, d2h = _aux_streams[dev.index]
     h2d.wait_stream(cur)
-    slots = [tuple(torch.empty((nb, *t.shape[1:]), dtype=t.dtype, device=dev) for t in (q, k, v)) for _ in range(2)]
-    freed = [None, None]     # recorded on the compute stream when a slot's kernels are queued
+    ns = max(2, int(staging_slots))
+    slots = [tuple(torch.empty((nb, *t.shape[1:]), dtype=t.dtype, device=dev) for t in (q, k, v)) for _ in range(ns)]
+    freed = [None] * ns      # recorded on the compute stream when a slot's kernels are queued
     starts = list(range(0, B, nb))
 
     def upload(i):
-        b0, b1, s = starts[i], min(B, starts[i] + nb), i % 2
+        b0, b1, s = starts[i], min(B, starts[i] + nb), i % ns
         with torch.cuda.stream(h2d):
             if freed[s] is not None:
                 h2d.wait_event(freed[s])
@@ -127,7 +128,7 @@ def attn_int8_fwd_host(q, k, v, out=None, *, chunk_batch: int | None = None, **k
 
     arrived = upload(0)
     for i in range(len(starts)):
-        b0, b1, s = starts[i], min(B, starts[i] + nb), i % 2
+        b0, b1, s = starts[i], min(B, starts[i] + nb), i % ns
         nxt = upload(i + 1) if i + 1 < len(starts) else None     # queued before this chunk's gate sync
         cur.wait_event(arrived)
         o = attn_int8_fwd(*(t[:b1 - b0] for t in slots[s]), **kw)
