@@ -60,9 +60,10 @@ struct DecodeArgs {
   int B, Hq, Hkv, N, per, n_splits;
 };
 
-// int8 V: a stage is 16 KB at D = 128, so three blocks fit an SM if registers allow
+// Blocks per SM the register budget must allow: two with an fp16 V (96 KB of stages each at
+// D = 128; 168 registers is the most two 5-warp blocks can have), three with an int8 V (64 KB).
 template <int D, bool V8>
-__global__ void __launch_bounds__(kDecThreads, (V8 && D <= 128) ? 3 : 1) decode_split_kernel(const __grid_constant__ CUtensorMap k_map,
+__global__ void __launch_bounds__(kDecThreads, D > 128 ? 1 : (V8 ? 3 : 2)) decode_split_kernel(const __grid_constant__ CUtensorMap k_map,
                                                                    const __grid_constant__ CUtensorMap v_map,
                                                                    DecodeArgs a) {
   using C = DecodeCfg<D, V8>;
