@@ -495,7 +495,9 @@ def main():
                               "roofline": {"bound": "hbm", "achieved": gd8 / world, "peak": peaks["hbm_gbs"],
                                            "unit": "GB/s", "frac": gd8 / world / peaks["hbm_gbs"],
                                            "frac_of_nominal": gd8 / world / NOMINAL_HBM_GBS,
-                                           "peak_source": peaks["source"] + " copy bandwidth", "traffic": None},
+                                           "peak_source": peaks["source"] + " copy bandwidth",
+                                           # ncu, 16 sequences: 534.6 MB moved for 519.9 MB algorithmic
+                                           "traffic": 534.6e6 / 519.9e6 * d8bytes},
                               "speedup_vs_fp16_v": msd / msd8}
         del dq, dk8, dks, dv8, dvs
         # ---- backward (dQ pass + dK/dV pass) on a cfg2-shaped training step per rank ----
@@ -511,7 +513,9 @@ def main():
                                        "flops": "10*B*Hq*S^2*D/2 (dV, dP, S, dQ, dK)"},
                             "roofline": {"bound": "tensor", "achieved": tb / world, "peak": peaks["bf16_tflops"],
                                          "unit": "TFLOP/s", "frac": tb / world / peaks["bf16_tflops"],
-                                         "peak_source": peaks["source"] + " bf16 dense (burst)", "traffic": None,
+                                         "peak_source": peaks["source"] + " bf16 dense (burst)",
+                                         # ncu on this shape: dQ pass 215.0 MB + dK/dV pass 194.4 MB
+                                         "traffic": 409.4e6,
                                          "kernels": "bwd_dq_kernel + bwd_dkv_kernel (mma.sync m16n8k16)"}}
         del bq, bk, bv, bdo, bout, blse
 
