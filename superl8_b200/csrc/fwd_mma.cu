@@ -50,7 +50,8 @@ struct MmaCfg {
   static constexpr int Q_BYTES = kBM * QK_STRIDE;
   static constexpr int K_BYTES = kBN * QK_STRIDE;
   static constexpr int V_BYTES = kBN * V_STRIDE;
-  static constexpr int SMEM = Q_BYTES + K_BYTES + V_BYTES + kBN * 4;
+  static constexpr int STAGE_BYTES = K_BYTES + V_BYTES + kBN * 4;   // K tile, V tile, k_scale tile
+  static constexpr int SMEM = Q_BYTES + 2 * STAGE_BYTES;
 };
 
 // Copies `rows` x `row_bytes` from global (row pitch `pitch` bytes) into a padded
@@ -66,14 +67,28 @@ __device__ __forceinline__ void stage_tile(uint8_t* dst, int dst_stride, int dst
   }
 }
 
+// The same copy as asynchronous 8-byte cp.async (zero fill where the synchronous copy writes
+// zeros); the caller commits the group and waits for it before the tile is read.
+__device__ __forceinline__ void stage_tile_async(uint8_t* dst, int dst_stride, int dst_row_bytes, const uint8_t* src,
+                                                 int row_bytes, int rows, int valid_rows, int64_t pitch) {
+  const int words = dst_row_bytes / 8;
+  const uint32_t dst_u = smem_u32(dst);
+  for (int idx = threadIdx.x; idx < rows * words; idx += kThreads) {
+    const int r = idx / words, c = (idx % words) * 8;
+    const bool live = r < valid_rows && c < row_bytes;
+    const uint8_t* g = live ? src + (int64_t)r * pitch + c : src;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst_u + r * dst_stride + c), "l"(g),
+                 "r"(live ? 8 : 0)
+                 : "memory");
+  }
+}
+
 template <int D, typename VT, bool I8>
 __global__ void __launch_bounds__(kThreads) fwd_mma_kernel(FwdArgs a) {
   using C = MmaCfg<D, I8>;
   extern __shared__ __align__(16) uint8_t smem[];
   uint8_t* sq = smem;
-  uint8_t* sk = sq + C::Q_BYTES;
-  uint8_t* sv = sk + C::K_BYTES;
-  float* sks = reinterpret_cast<float*>(sv + C::V_BYTES);
+  uint8_t* skv = sq + C::Q_BYTES;   // two stages of {K tile, V tile, k_scale tile}
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -135,19 +150,32 @@ __global__ void __launch_bounds__(kThreads) fwd_mma_kernel(FwdArgs a) {
   int n_begin = 0;
   if (a.window_left >= 0) n_begin = max(0, (m_block + causal_diag - a.window_left + 1)) / kBN * kBN;
 
-  const uint32_t sq_u = smem_u32(sq), sk_u = smem_u32(sk), sv_u = smem_u32(sv);
-
-  for (int n_block = n_begin; n_block < n_end; n_block += kBN) {
-    __syncthreads();  // previous tile fully consumed (and Q staged on the first pass)
-    stage_tile(sk, C::QK_STRIDE, C::QK_STRIDE, k_bh + (int64_t)n_block * kv_rowe * C::QK_ELEM, D * C::QK_ELEM, kBN,
-               n_len - n_block, kv_rowe * C::QK_ELEM);
-    stage_tile(sv, C::V_STRIDE, C::V_STRIDE, v_bh + (int64_t)n_block * kv_rowe * 2, D * 2, kBN, n_len - n_block,
-               kv_rowe * 2);
+  const uint32_t sq_u = smem_u32(sq);
+  // tile n_block -> stage st, asynchronously (the k_scale values with plain stores: they are
+  // published by the barrier at the top of the iteration that reads them)
+  auto load_kv = [&](int n_block, int st) {
+    uint8_t* sk_ = skv + st * C::STAGE_BYTES;
+    uint8_t* sv_ = sk_ + C::K_BYTES;
+    stage_tile_async(sk_, C::QK_STRIDE, C::QK_STRIDE, k_bh + (int64_t)n_block * kv_rowe * C::QK_ELEM, D * C::QK_ELEM, kBN,
+                     n_len - n_block, kv_rowe * C::QK_ELEM);
+    stage_tile_async(sv_, C::V_STRIDE, C::V_STRIDE, v_bh + (int64_t)n_block * kv_rowe * 2, D * 2, kBN, n_len - n_block,
+                     kv_rowe * 2);
+    asm volatile("cp.async.commit_group;" ::: "memory");
     if (I8 && threadIdx.x < kBN) {
       const int gn = n_block + threadIdx.x;
-      sks[threadIdx.x] = (gn < n_len) ? __ldg(ks_base + gn * ks_row) : 0.f;
+      reinterpret_cast<float*>(sv_ + C::V_BYTES)[threadIdx.x] = (gn < n_len) ? __ldg(ks_base + gn * ks_row) : 0.f;
     }
+  };
+  if (n_begin < n_end) load_kv(n_begin, 0);
+
+  for (int n_block = n_begin, it = 0; n_block < n_end; n_block += kBN, ++it) {
+    // this tile has landed and every warp is done with the tile before it (whose stage the next
+    // load overwrites); on the first pass this also publishes Q
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
+    if (n_block + kBN < n_end) load_kv(n_block + kBN, (it + 1) & 1);
+    const uint32_t sk_u = smem_u32(skv + (it & 1) * C::STAGE_BYTES), sv_u = sk_u + C::K_BYTES;
+    const float* sks = reinterpret_cast<const float*>(skv + (it & 1) * C::STAGE_BYTES + C::K_BYTES + C::V_BYTES);
 
     // ---- S = Q . K^T ----
     float sv_f[8][4];
