@@ -115,7 +115,13 @@ enum Bar {
 
 #ifdef SL8_TRACE
 __device__ long long g_trace[8192];
-#define TR(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0) g_trace[(slot)] = clock64(); } while (0)
+#ifndef SL8_TRACE_X
+#define SL8_TRACE_X 0
+#endif
+#ifndef SL8_TRACE_Y
+#define SL8_TRACE_Y 0
+#endif
+#define TR(slot) do { if (blockIdx.x == SL8_TRACE_X && blockIdx.y == SL8_TRACE_Y) g_trace[(slot)] = clock64(); } while (0)
 #else
 #define TR(slot) do {} while (0)
 #endif
