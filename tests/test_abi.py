@@ -88,3 +88,43 @@ def test_python_layer_refuses_cpu_tensors():
         s8.quantize_int8_rowwise(x)
     with pytest.raises(RuntimeError, match="CUDA"):
         s8.attn_int8_fwd(x.view(1, 1, 4, 128), x.view(1, 1, 4, 128), x.view(1, 1, 4, 128))
+
+
+STRUCTS = {
+    "sl8_fwd_params": _lib.FwdParams, "sl8_fp16_fwd_params": _lib.Fp16FwdParams,
+    "sl8_decode_params": _lib.DecodeParams, "sl8_w8a8_params": _lib.W8A8Params,
+    "sl8_varlen_params": _lib.VarlenParams, "sl8_bwd_params": _lib.BwdParams,
+}
+
+
+def test_ctypes_structs_have_the_layout_the_c_compiler_gives_the_header(tmp_path):
+    """Every parameter struct of the header, compiled as plain C, has the field order, offsets
+    and size of its ctypes mirror (a silent mismatch would hand kernels shifted pointers)."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    found = set(re.findall(r"typedef struct (sl8_[a-z0-9_]+)", text))
+    assert found == set(STRUCTS), f"header structs {sorted(found)} vs ctypes mirrors {sorted(STRUCTS)}"
+    lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void) {"]
+    for cname, cls in STRUCTS.items():
+        lines.append(f'  printf("{cname} size %zu\\n", sizeof({cname}));')
+        for fname, _ in cls._fields_:
+            lines.append(f'  printf("{cname} {fname} %zu\\n", offsetof({cname}, {fname}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
+    got = {(a, b): int(c) for a, b, c in (ln.split() for ln in out.splitlines())}
+    for cname, cls in STRUCTS.items():
+        assert got[(cname, "size")] == C.sizeof(cls), cname
+        for fname, _ in cls._fields_:
+            assert got[(cname, fname)] == getattr(cls, fname).offset, f"{cname}.{fname}"
+        # and the header has no field the mirror lacks
+        body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), text, flags=re.S).group(1)
+        n_fields = sum(len(decl.split(",")) for decl in body.split(";") if decl.strip())
+        assert n_fields == len(cls._fields_), f"{cname}: {n_fields} fields in the header"
