@@ -225,7 +225,9 @@ def run_reference(args, cfg):
     rank, world, _ = dist_setup(args.gpus)
     if rank != 0:
         return
-    cores = torch.get_num_threads()
+    # every host core this process may use (a launcher such as torchrun pins OMP_NUM_THREADS to 1)
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(cores)
     groups = 1
     for _ in range(args.warmup):
         cpu_reference_sample(cfg, groups)
@@ -521,6 +523,7 @@ def main():
 
     if rank == 0 and world == 1:
         try:
+            torch.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
             sec, ops = cpu_reference_sample(cfg, 16)
             line["cpu_baseline"] = {"value": ops / sec / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                                     "sample": f"16 KV groups (128 query heads = 2 batch elements) of {cfg.name}: CPU quantiser + "

@@ -114,22 +114,37 @@ enum Bar {
 };
 
 #ifdef SL8_TRACE
-__device__ long long g_trace[8192];
-#ifndef SL8_TRACE_X
-#define SL8_TRACE_X 0
+// Clock-stamp trace of up to eight blocks (build-time option, never in the shipped library):
+// the blocks whose linear index is SL8_TRACE_BASE + k * SL8_TRACE_STRIDE, k = 0..7.
+constexpr int kTraceBlocks = 8, kTraceSlots = 8192;
+__device__ long long g_trace[kTraceBlocks * kTraceSlots];
+#ifndef SL8_TRACE_BASE
+#define SL8_TRACE_BASE 0
 #endif
-#ifndef SL8_TRACE_Y
-#define SL8_TRACE_Y 0
+#ifndef SL8_TRACE_STRIDE
+#define SL8_TRACE_STRIDE 1
 #endif
-#define TR(slot) do { if (blockIdx.x == SL8_TRACE_X && blockIdx.y == SL8_TRACE_Y) g_trace[(slot)] = clock64(); } while (0)
+__device__ __forceinline__ uint32_t sl8_smid() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ int trace_block() {
+  const int lin = blockIdx.y * gridDim.x + blockIdx.x - SL8_TRACE_BASE;
+  return (lin >= 0 && lin % SL8_TRACE_STRIDE == 0 && lin / SL8_TRACE_STRIDE < kTraceBlocks) ? lin / SL8_TRACE_STRIDE : -1;
+}
+#define TR(slot) do { const int tb_ = trace_block(); if (tb_ >= 0) g_trace[tb_ * kTraceSlots + (slot)] = clock64(); } while (0)
+#define TRV(slot, val) do { const int tb_ = trace_block(); if (tb_ >= 0) g_trace[tb_ * kTraceSlots + (slot)] = (val); } while (0)
 #else
 #define TR(slot) do {} while (0)
+#define TRV(slot, val) do {} while (0)
 #endif
 
 template <int D, typename VT, bool QK8, bool PACKED>
 __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                                                                const __grid_constant__ CUtensorMap k_map,
-                                                               const __grid_constant__ CUtensorMap v_map, TcArgs a) {
+                                                               const __grid_constant__ CUtensorMap v_map,
+                                                               const __grid_constant__ CUtensorMap o_map, TcArgs a) {
   using C = TcCfg<D, QK8>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -175,6 +190,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
   }
 
   if (threadIdx.x == 0) {
+    TR(8188);
+    TRV(8191, (long long)sl8_smid());
     mbar_init(&bars[Q_FULL], 1);
     mbar_init(&bars[O_DONE], 1);
     for (int i = 0; i < 2; ++i) {
@@ -198,6 +215,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   bool ok = true;
+  if (threadIdx.x == 0) TR(8189);
 
   if (warp == kProducerWarp) {
     // ======================= producer =======================
@@ -423,12 +441,49 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
       if (warp == 0 && lane == 0) TR(8 * j + 5);
     }
     // ---- epilogue ----
+    if (warp == 0 && lane == 0) TR(8185);
     if (ok) ok = mbar_wait(&bars[O_DONE], 0, a.status);
+    if (warp == 0 && lane == 0) TR(8186);
     if (ok) {
       tc_fence_after();
       const float l_tot = l_run;
       const bool live = m < m_len;
       const float inv = (live && l_tot > 0.f) ? 1.f / l_tot : 0.f;
+      if (!packed) {
+        // Dense layout: the warp's 32 rows are staged in shared memory (the V stages are free, every
+        // P.V has completed) in the 128-byte-swizzled layout of the output tensor map -- 16-byte
+        // chunk j of row r sits at chunk j ^ (r & 7), so the 32 row writes of one instruction
+        // spread over all banks -- and leave as one tile store per 64 channels; rows past M are
+        // dropped by the copy engine, padded rows (seqlens_q) carry zeros as before.
+        uint8_t* const stage = smem + C::OFF_V + lg * (32 * 128) + lane * 128;
+        if (lane == 0) tma_prefetch_desc(&o_map);
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tc_ld32(t_o + 32 * c, o);
+          tc_wait_ld();
+          tc_regs_ready(o);
+          uint8_t* const sub = stage + (c >> 1) * (kTM * 128);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 w;
+            w.x = pack2<VT>(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
+            w.y = pack2<VT>(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
+            w.z = pack2<VT>(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
+            w.w = pack2<VT>(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
+            *reinterpret_cast<uint4*>(sub + ((((c & 1) * 4 + v) ^ (lane & 7)) << 4)) = w;
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && m_block + 32 * lg < a.M) {
+#pragma unroll
+          for (int sb = 0; sb < D / 64; ++sb)
+            tma_store_3d(&o_map, smem + C::OFF_V + sb * (kTM * 128) + lg * (32 * 128), 64 * sb, m_block + 32 * lg, (int)bh);
+          tma_store_commit();
+          tma_store_wait_read();
+        }
+      } else {
   #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
@@ -448,9 +503,11 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
           }
         }
       }
+      }
       if (a.lse != nullptr && m < o_rows)
         a.lse[bh * a.M + m] = (live && l_tot > 0.f) ? (m_run * 0.6931471805599453f + logf(l_tot)) : -INFINITY;
     }
+    if (warp == 0 && lane == 0) TR(8187);
     tc_fence_before();
   }
 
@@ -544,7 +601,7 @@ int launch_tc_impl(const void* q, const void* k, const void* v, int B, int Hq, i
                    cudaStream_t stream, int64_t total_q = 0, int64_t total_k = 0) {
   using C = TcCfg<D, QK8>;
   constexpr int es = QK8 ? 1 : 2;
-  CUtensorMap q_map, k_map, v_map;
+  CUtensorMap q_map, k_map, v_map, o_map;
   int rc;
   if (a.cu_q != nullptr) {
     rc = sl8_make_tmap_packed(&q_map, q, es, D, Hq, total_q, C::QROW / es, kTM, C::QROW);
@@ -554,17 +611,20 @@ int launch_tc_impl(const void* q, const void* k, const void* v, int B, int Hq, i
     rc = sl8_make_tmap_3d(&q_map, q, es, D, M, (uint64_t)B * Hq, C::QROW / es, kTM, C::QROW);
     if (rc == SL8_OK) rc = sl8_make_tmap_3d(&k_map, k, es, D, N, (uint64_t)B * Hkv, C::QROW / es, kTN, C::QROW);
     if (rc == SL8_OK) rc = sl8_make_tmap_3d(&v_map, v, 2, D, N, (uint64_t)B * Hkv, 64, kTN, 128);
+    // output tiles leave through the copy engine: 32 rows (one softmax warp) x 64 channels per store
+    if (rc == SL8_OK) rc = sl8_make_tmap_3d(&o_map, a.out, 2, D, M, (uint64_t)B * Hq, 64, 32, 128);
   }
   if (rc != SL8_OK) return rc;
+  if (a.cu_q != nullptr) o_map = q_map;   // packed rows are written with plain stores
   dim3 grid((M + kTM - 1) / kTM, (unsigned)((int64_t)B * Hq));
   if (a.cu_q != nullptr) {
     if (!QK8 || D == 256) return SL8_ERR_UNSUPPORTED;   // the packed op is int8-QK, D <= 128
     constexpr bool kPk = QK8 && D != 256;               // (keeps the unused instantiations out of the image)
     SL8_CUDA_TRY(cudaFuncSetAttribute(fwd_tc_kernel<D, VT, QK8, kPk>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-    fwd_tc_kernel<D, VT, QK8, kPk><<<grid, kTcThreads, C::SMEM, stream>>>(q_map, k_map, v_map, a);
+    fwd_tc_kernel<D, VT, QK8, kPk><<<grid, kTcThreads, C::SMEM, stream>>>(q_map, k_map, v_map, o_map, a);
   } else {
     SL8_CUDA_TRY(cudaFuncSetAttribute(fwd_tc_kernel<D, VT, QK8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-    fwd_tc_kernel<D, VT, QK8, false><<<grid, kTcThreads, C::SMEM, stream>>>(q_map, k_map, v_map, a);
+    fwd_tc_kernel<D, VT, QK8, false><<<grid, kTcThreads, C::SMEM, stream>>>(q_map, k_map, v_map, o_map, a);
   }
   return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
 }
