@@ -246,7 +246,9 @@ int sl8_smooth_quant_k_packed(const void* k, int dtype, int64_t total_tokens, in
  * One dtype for all 16-bit tensors (reference: fp16 only; bf16 also served).  D in {32, 64, 128}
  * (the reference's set).  dk / dv are summed over the query heads of a KV head.  M == 0 or
  * N == 0 zero-fills the gradients (attn_bwd.cu:88).  Two passes, no atomics: bitwise
- * reproducible.  workspace: sl8_attn_bwd_workspace() bytes (status word + fp32 [B, Hq, M]).
+ * reproducible.  workspace: sl8_attn_bwd_workspace() bytes (status word + fp32 [B, Hq, M]);
+ * the tcgen05 passes zero the status word themselves and raise it to
+ * SL8_ERR_DEVICE_TIMEOUT if a bounded device-side wait expires (sl8_read_device_status).
  */
 typedef struct sl8_bwd_params {
   const void* q; const void* k; const void* v; const void* o; const void* dout;
@@ -255,6 +257,7 @@ typedef struct sl8_bwd_params {
   int32_t B, Hq, Hkv, M, N, D;
   int32_t dtype; int32_t causal;
   float softmax_scale;
+  int32_t backend;        /* SL8_BACKEND_* (AUTO: tcgen05 for D = 64/128, else mma.sync) */
 } sl8_bwd_params;
 size_t sl8_attn_bwd_workspace(const sl8_bwd_params* p);
 int sl8_attn_bwd(const sl8_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream);

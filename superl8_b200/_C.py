@@ -19,6 +19,7 @@ from . import _lib
 _DTYPE = {torch.float16: _lib.SL8_F16, torch.bfloat16: _lib.SL8_BF16, torch.float32: _lib.SL8_F32}
 _status_ws: dict = {}
 _decode_ws: dict = {}
+_bwd_ws: dict = {}      # the last backward workspace per (device, stream): its status word is read by device_status
 
 
 def _stream(device) -> int:
@@ -57,6 +58,9 @@ def device_status(device=None) -> int:
     ws = _decode_ws.get((device.index, torch.cuda.current_stream(device).cuda_stream))
     if rc == 0 and ws is not None:
         rc = lib.sl8_read_device_status(_ptr(ws), _stream(device))
+    bws = _bwd_ws.get((device.index, torch.cuda.current_stream(device).cuda_stream))
+    if rc == 0 and bws is not None:
+        rc = lib.sl8_read_device_status(_ptr(bws), _stream(device))
     return rc
 
 
@@ -349,7 +353,7 @@ def attn_int8_varlen(q, q_scale, k, k_scale, v, cu_seqlens_q, cu_seqlens_k, max_
     return out
 
 
-def attn_bwd(q, k, v, o, do_, lse, scale, causal=False):
+def attn_bwd(q, k, v, o, do_, lse, scale, causal=False, *, backend=_lib.SL8_BACKEND_AUTO):
     """Reference binding csrc/fni8_api.cpp:256-259 (op csrc/kernel/attn_bwd.cu:62-109):
     (dq, dk, dv) of the attention with logits scale * q.k, from the forward's output ``o``, its
     natural-log row sums ``lse`` [B, Hq, M] and the output gradient ``do_``.  q, o, do_
@@ -374,11 +378,13 @@ def attn_bwd(q, k, v, o, do_, lse, scale, causal=False):
     p = _lib.BwdParams(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), o=o.data_ptr(), dout=do_.data_ptr(),
                        lse=lse.data_ptr(), dq=dq.data_ptr(), dk=dk.data_ptr(), dv=dv.data_ptr(),
                        B=B, Hq=H, Hkv=Hkv, M=M, N=N, D=D, dtype=_DTYPE[q.dtype], causal=int(bool(causal)),
-                       softmax_scale=float(scale))
+                       softmax_scale=float(scale), backend=int(backend))
     lib = _lib.load()
     with torch.cuda.device(q.device):
         nbytes = lib.sl8_attn_bwd_workspace(C.byref(p))
-        ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)   # D_m = sum_d dO.O per query row
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)   # status word; D_m = sum_d dO.O per query row
+        ws[:256].zero_()
         rc = lib.sl8_attn_bwd(C.byref(p), _ptr(ws), nbytes, _stream(q.device))
+        _bwd_ws[(q.device.index, torch.cuda.current_stream(q.device).cuda_stream)] = ws
     _lib.check(rc, "attn_bwd", 3 if (M and N and q.numel() and k.numel()) else 0)
     return dq, dk, dv

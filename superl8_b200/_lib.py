@@ -92,7 +92,7 @@ class BwdParams(C.Structure):
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("dout", C.c_void_p),
         ("lse", C.c_void_p), ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
         ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("M", C.c_int32), ("N", C.c_int32), ("D", C.c_int32),
-        ("dtype", C.c_int32), ("causal", C.c_int32), ("softmax_scale", C.c_float),
+        ("dtype", C.c_int32), ("causal", C.c_int32), ("softmax_scale", C.c_float), ("backend", C.c_int32),
     ]
 
 

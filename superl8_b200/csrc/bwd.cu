@@ -27,6 +27,8 @@
 #include "sl8_common.cuh"
 #include "sl8_mma.cuh"
 
+int sl8_bwd_tc(const sl8_bwd_params* p, float* delta, int* status, cudaStream_t s);   // bwd_tcgen05.cu
+
 namespace sl8 {
 namespace {
 
@@ -396,6 +398,15 @@ int launch_bwd(const BwdArgs& a, int B, cudaStream_t s) {
   return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
 }
 
+// D_m alone (the tensor-memory passes read it from the workspace)
+template <typename VT>
+int launch_delta(const BwdArgs& a, int B, int D, cudaStream_t s) {
+  const int64_t rows = (int64_t)B * a.Hq * a.M;
+  bwd_delta_kernel<VT><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(reinterpret_cast<const VT*>(a.o),
+                                                                 reinterpret_cast<const VT*>(a.dout), a.delta, rows, D);
+  return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
+}
+
 template <typename VT>
 int launch_bwd_d(const BwdArgs& a, int B, int D, cudaStream_t s) {
   switch (D) {
@@ -445,6 +456,18 @@ extern "C" int sl8_attn_bwd(const sl8_bwd_params* p, void* workspace, size_t wor
   a.delta = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256);
   a.dq = p->dq; a.dk = p->dk; a.dv = p->dv;
   a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N; a.causal = p->causal; a.scale = p->softmax_scale;
+  int backend = p->backend;
+  const bool tc_ok = p->D == 64 || p->D == 128;
+  if (backend == SL8_BACKEND_AUTO) backend = tc_ok ? SL8_BACKEND_TCGEN05 : SL8_BACKEND_MMA;
+  if (backend == SL8_BACKEND_TCGEN05) {
+    if (!tc_ok) return SL8_ERR_UNSUPPORTED;
+    SL8_CUDA_TRY(cudaMemsetAsync(workspace, 0, 256, s));   // status word of the bounded waits
+    const int rc = p->dtype == SL8_F16 ? launch_delta<__half>(a, p->B, p->D, s)
+                                       : launch_delta<__nv_bfloat16>(a, p->B, p->D, s);
+    if (rc != SL8_OK) return rc;
+    return sl8_bwd_tc(p, a.delta, reinterpret_cast<int*>(workspace), s);
+  }
+  if (backend != SL8_BACKEND_MMA) return SL8_ERR_UNSUPPORTED;
   if (p->dtype == SL8_F16) return launch_bwd_d<__half>(a, p->B, p->D, s);
   return launch_bwd_d<__nv_bfloat16>(a, p->B, p->D, s);
 }

@@ -1,0 +1,387 @@
+// Backward on the Blackwell tensor-core path (D = 64, 128): the same two atomic-free passes as
+// bwd.cu -- the mathematics of superl8/autograd.py:29-45, pass structure of
+// csrc/include/attn_bwd.cuh:156-331 (dQ) and :337-535 (dK / dV) -- with every contraction a
+// tcgen05.mma kind::f16 on TMA-staged tiles and the accumulators in tensor memory.
+//
+// One kernel template serves both passes.  A block owns 128 "rows" and streams 128-"column"
+// tiles past them:
+//   dK/dV pass  rows = 128 keys of one (batch, KV head); columns = 128 queries of one query head
+//               of the group (all heads of the group, all query tiles that see a key of the block)
+//                 S^T  = K Q^T          (both operands from shared memory)
+//                 dP^T = V dO^T
+//                 P^T  = 2^(S^T scale log2e - lse log2e),  dS^T = P^T (dP^T - D_m)
+//                 dV  += P^T dO         (P^T from tensor memory, dO tile read MN-major)
+//                 dK  += dS^T Q         (dS^T from tensor memory, Q tile read MN-major)
+//   dQ pass     rows = 128 queries of one (batch, query head); columns = 128 keys
+//                 S = Q K^T, dP = dO V^T, dS = P (dP - D_m),  dQ += dS K
+// Tensor memory (512 columns): S at [0,128), dP at [128,256), first accumulator at [256,256+D),
+// second at [384,384+D).  P (16-bit pairs) overwrites the first 64 columns of S, dS those of dP.
+// Six warps: 0-3 compute (thread = row = tensor-memory lane), 4 = TMA producer (the fixed row
+// tiles once, then column tiles through two stages, plus the per-query lse / D_m of a column
+// tile in the dK/dV pass), 5 = tensor-memory allocation and MMA issue.  Per column tile the
+// issuer queues S and dP, the compute warps turn them into P and dS 32 columns at a time, the
+// issuer queues the accumulating MMAs behind them and frees the stage.
+// Rows and columns past the end of a tensor arrive as zeros (TMA fill) and carry lse = +inf,
+// so P = dS = 0 there; the causal mask is the forward's bottom-right one (key n visible to
+// query m iff n <= m + N - M), evaluated per element only on tiles that straddle the diagonal.
+// Every mbarrier wait is bounded; on expiry the status word is raised and the block exits.
+#include "sl8_common.cuh"
+
+#include <type_traits>
+
+namespace sl8 {
+namespace {
+
+constexpr int kBT = 128;                       // rows per block, columns per tile
+constexpr int kBtThreads = 192;
+constexpr float kLog2eB = 1.4426950408889634f;
+
+template <int D>
+struct BtCfg {
+  static constexpr int SUBS = 2 * D / 128;               // 64-channel (128-byte) sub-tiles of a row
+  static constexpr int SUB_BYTES = kBT * 128;
+  static constexpr int TILE_BYTES = kBT * 2 * D;
+  static constexpr int KSTEPS = 2 * D / 32;              // MMA K steps over the head dimension
+  static constexpr int OFF_A1 = 0;
+  static constexpr int OFF_A2 = OFF_A1 + TILE_BYTES;
+  static constexpr int OFF_ST = OFF_A2 + TILE_BYTES;     // two stages of {B1 tile, B2 tile}
+  static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  static constexpr int OFF_ROWDATA = OFF_ST + 2 * STAGE_BYTES;   // two stages of kBT x {lse log2e, D_m}
+  static constexpr int OFF_BAR = OFF_ROWDATA + 2 * kBT * 8;
+  static constexpr int SMEM = OFF_BAR + 256 + 1024;
+  static constexpr uint32_t COL_S = 0, COL_DP = 128, COL_ACC1 = 256, COL_ACC2 = 384;
+};
+
+struct BtArgs {
+  const float* lse;
+  const float* delta;
+  void* out1;          // dK/dV pass: dV; dQ pass: dQ
+  void* out2;          // dK/dV pass: dK
+  int* status;
+  int Hq, Hkv, M, N;
+  int causal;
+  float scale;
+};
+
+enum BtBar { FIX_FULL = 0, ACC_DONE, SDP_FULL, PDS_FULL, ST_FULL, ST_EMPTY = ST_FULL + 2, BT_NUM_BARS = ST_EMPTY + 2 };
+
+template <int D, typename VT, bool DKV>
+__global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_constant__ CUtensorMap a1_map,
+                                                              const __grid_constant__ CUtensorMap a2_map,
+                                                              const __grid_constant__ CUtensorMap b1_map,
+                                                              const __grid_constant__ CUtensorMap b2_map, BtArgs a) {
+  using C = BtCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float2* rowdata = reinterpret_cast<float2*>(smem + C::OFF_ROWDATA);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BT_NUM_BARS);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = a.Hq / a.Hkv;
+  const int diag = a.causal ? a.N - a.M : 0;
+  // rows of this block, and the walk over column tiles
+  const int fixed_bh = blockIdx.y;                       // dK/dV: batch * Hkv + kv head; dQ: batch * Hq + query head
+  const int b = DKV ? fixed_bh / a.Hkv : fixed_bh / a.Hq;
+  const int kvh = DKV ? fixed_bh % a.Hkv : (fixed_bh % a.Hq) / G;
+  const int row_block = DKV ? blockIdx.x * kBT : (a.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x) * kBT;
+  int col_begin, tiles_per_head, heads;
+  if (DKV) {
+    // first query that sees a key of this block: n <= m + diag
+    col_begin = a.causal ? max(0, row_block - diag) / kBT * kBT : 0;
+    tiles_per_head = col_begin < a.M ? (a.M - col_begin + kBT - 1) / kBT : 0;
+    heads = G;
+  } else {
+    col_begin = 0;
+    const int n_end = a.causal ? max(0, min(a.N, row_block + kBT + diag)) : a.N;
+    tiles_per_head = (n_end + kBT - 1) / kBT;
+    heads = 1;
+  }
+  const int total = heads * tiles_per_head;
+  // head (TMA coordinate 2) and first column of tile i
+  auto tile_head = [&](int i) { return DKV ? b * a.Hq + kvh * G + i / tiles_per_head : b * a.Hkv + kvh; };
+  auto tile_col = [&](int i) { return col_begin + (i % tiles_per_head) * kBT; };
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars[FIX_FULL], 1);
+    mbar_init(&bars[ACC_DONE], 1);
+    mbar_init(&bars[SDP_FULL], 1);
+    mbar_init(&bars[PDS_FULL], 4);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars[ST_FULL + i], DKV ? 2 : 1);   // the tile bytes, and (dK/dV) the lse / D_m rows of the tile
+      mbar_init(&bars[ST_EMPTY + i], 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tc_alloc(tmem_slot, 512);
+    tc_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  bool ok = true;
+
+  if (warp == 4) {
+    // ======================= producer =======================
+    if (lane == 0) {
+      tma_prefetch_desc(&a1_map);
+      tma_prefetch_desc(&a2_map);
+      tma_prefetch_desc(&b1_map);
+      tma_prefetch_desc(&b2_map);
+      mbar_expect_tx(&bars[FIX_FULL], 2 * C::TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < C::SUBS; ++c) {
+        tma_load_3d(smem + C::OFF_A1 + c * C::SUB_BYTES, &a1_map, &bars[FIX_FULL], 64 * c, row_block, fixed_bh);
+        tma_load_3d(smem + C::OFF_A2 + c * C::SUB_BYTES, &a2_map, &bars[FIX_FULL], 64 * c, row_block, fixed_bh);
+      }
+    }
+    for (int i = 0; i < total && ok; ++i) {
+      const int st = i & 1;
+      if (i >= 2) ok = mbar_wait(&bars[ST_EMPTY + st], ((i >> 1) - 1) & 1, a.status);
+      if (!ok) break;
+      const int head = tile_head(i), col = tile_col(i);
+      if (lane == 0) {
+        mbar_expect_tx(&bars[ST_FULL + st], C::STAGE_BYTES);
+        uint8_t* dst = smem + C::OFF_ST + st * C::STAGE_BYTES;
+#pragma unroll
+        for (int c = 0; c < C::SUBS; ++c) {
+          tma_load_3d(dst + c * C::SUB_BYTES, &b1_map, &bars[ST_FULL + st], 64 * c, col, head);
+          tma_load_3d(dst + C::TILE_BYTES + c * C::SUB_BYTES, &b2_map, &bars[ST_FULL + st], 64 * c, col, head);
+        }
+      }
+      if (DKV) {
+        // per-query statistics of the tile's columns: {lse * log2 e (or +inf: P = 0), D_m}
+#pragma unroll
+        for (int r = lane; r < kBT; r += 32) {
+          const int m = col + r;
+          float l = INFINITY, d = 0.f;
+          if (m < a.M) {
+            const float v = __ldg(a.lse + (int64_t)head * a.M + m);
+            l = (v > -INFINITY) ? v * kLog2eB : INFINITY;
+            d = __ldg(a.delta + (int64_t)head * a.M + m);
+          }
+          rowdata[st * kBT + r] = make_float2(l, d);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[ST_FULL + st]);
+      }
+    }
+  } else if (warp == 5) {
+    // ======================= MMA issuer =======================
+    constexpr uint32_t vfmt = std::is_same<VT, __nv_bfloat16>::value ? 1u : 0u;
+    const uint32_t idesc_s = umma_idesc(1, vfmt, vfmt, 0, 0, kBT, kBT);
+    const uint32_t idesc_acc = umma_idesc(1, vfmt, vfmt, 0, 1, kBT, D);
+    const uint64_t da1 = umma_smem_desc(smem_u32(smem + C::OFF_A1), 16, 1024, kUmmaSw128);
+    const uint64_t da2 = umma_smem_desc(smem_u32(smem + C::OFF_A2), 16, 1024, kUmmaSw128);
+    const uint64_t db_k = umma_smem_desc(smem_u32(smem + C::OFF_ST), 16, 1024, kUmmaSw128);             // K-major view
+    const uint64_t db_mn = umma_smem_desc(smem_u32(smem + C::OFF_ST), C::SUB_BYTES, 1024, kUmmaSw128);  // MN-major view
+    ok = __all_sync(0xffffffffu, mbar_wait(&bars[FIX_FULL], 0, a.status));
+    for (int i = 0; i < total && ok; ++i) {
+      const int st = i & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&bars[ST_FULL + st], (i >> 1) & 1, a.status));
+      if (!ok) break;
+      tc_fence_after();
+      if (elect_one()) {
+        // S = A1 B1^T, dP = A2 B2^T
+#pragma unroll
+        for (int s = 0; s < C::KSTEPS; ++s) {
+          const uint32_t off = (32 * s / 128) * C::SUB_BYTES + (32 * s % 128);
+          tc_mma_f16_ss(tmem + C::COL_S, umma_desc_advance(da1, off),
+                        umma_desc_advance(db_k, st * C::STAGE_BYTES + off), idesc_s, s > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int s = 0; s < C::KSTEPS; ++s) {
+          const uint32_t off = (32 * s / 128) * C::SUB_BYTES + (32 * s % 128);
+          tc_mma_f16_ss(tmem + C::COL_DP, umma_desc_advance(da2, off),
+                        umma_desc_advance(db_k, st * C::STAGE_BYTES + C::TILE_BYTES + off), idesc_s, s > 0 ? 1u : 0u);
+        }
+        tc_commit(&bars[SDP_FULL]);
+      }
+      __syncwarp();
+      ok = __all_sync(0xffffffffu, mbar_wait(&bars[PDS_FULL], i & 1, a.status));
+      if (!ok) break;
+      tc_fence_after();
+      if (elect_one()) {
+        if (DKV) {
+          // dV += P^T dO (P over the first 64 columns of S; dO = B2, contraction over the tile's queries)
+#pragma unroll
+          for (int kk = 0; kk < kBT / 16; ++kk)
+            tc_mma_f16_ts(tmem + C::COL_ACC1, tmem + C::COL_S + 8 * kk,
+                          umma_desc_advance(db_mn, st * C::STAGE_BYTES + C::TILE_BYTES + kk * 2048), idesc_acc,
+                          (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        // dK += dS^T Q  /  dQ += dS K  (dS over the first 64 columns of dP; B1 read MN-major)
+#pragma unroll
+        for (int kk = 0; kk < kBT / 16; ++kk)
+          tc_mma_f16_ts(tmem + (DKV ? C::COL_ACC2 : C::COL_ACC1), tmem + C::COL_DP + 8 * kk,
+                        umma_desc_advance(db_mn, st * C::STAGE_BYTES + kk * 2048), idesc_acc,
+                        (i > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(&bars[ST_EMPTY + st]);
+        if (i == total - 1) tc_commit(&bars[ACC_DONE]);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ======================= compute / epilogue =======================
+    const int row = 32 * warp + lane;
+    const int grow = row_block + row;                         // key (dK/dV) or query (dQ) of this thread
+    const uint32_t t_row = tmem + ((uint32_t)(32 * warp) << 16);
+    const float scale_log2 = a.scale * kLog2eB;
+    float my_lse2 = INFINITY, my_delta = 0.f;                 // dQ pass: per-row statistics
+    if (!DKV && grow < a.M) {
+      const float v = __ldg(a.lse + (int64_t)fixed_bh * a.M + grow);
+      my_lse2 = (v > -INFINITY) ? v * kLog2eB : INFINITY;
+      my_delta = __ldg(a.delta + (int64_t)fixed_bh * a.M + grow);
+    }
+    for (int i = 0; i < total; ++i) {
+      const int st = i & 1;
+      const int col = tile_col(i);
+      if (DKV) {
+        ok = mbar_wait(&bars[ST_FULL + st], (i >> 1) & 1, a.status);   // publishes the tile's lse / D_m rows
+        if (!ok) break;
+      }
+      ok = mbar_wait(&bars[SDP_FULL], i & 1, a.status);
+      if (!ok) break;
+      tc_fence_after();
+      // does the tile straddle the diagonal?  dK/dV: key = grow, query = col + c; dQ: query = grow, key = col + c
+      // (dQ pass: also the tile that runs past the last key -- its zero-filled keys still give P > 0)
+      const bool need_mask = DKV ? (a.causal && col + diag < row_block + kBT - 1)
+                                 : ((a.causal && col + kBT - 1 > row_block + diag) || col + kBT > a.N);
+      const int key_limit = a.causal ? min(a.N, grow + diag + 1) : a.N;   // dQ pass: keys [0, key_limit) are visible
+      const float2* rd = rowdata + st * kBT;
+#pragma unroll 1
+      for (int c = 0; c < kBT / 32; ++c) {
+        uint32_t s[32], dp[32];
+        tc_ld32(t_row + C::COL_S + 32 * c, s);
+        tc_ld32(t_row + C::COL_DP + 32 * c, dp);
+        tc_wait_ld();
+        tc_regs_ready(s);
+        tc_regs_ready(dp);
+        uint32_t pp[16], ds[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float p0, p1, d0, d1;
+          if (DKV) {
+            const float2 r0 = rd[32 * c + e], r1 = rd[32 * c + e + 1];
+            p0 = ex2_approx(fmaf(__uint_as_float(s[e]), scale_log2, -r0.x));
+            p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), scale_log2, -r1.x));
+            if (need_mask) {
+              p0 = (grow <= col + 32 * c + e + diag) ? p0 : 0.f;
+              p1 = (grow <= col + 32 * c + e + 1 + diag) ? p1 : 0.f;
+            }
+            d0 = p0 * (__uint_as_float(dp[e]) - r0.y);
+            d1 = p1 * (__uint_as_float(dp[e + 1]) - r1.y);
+          } else {
+            p0 = ex2_approx(fmaf(__uint_as_float(s[e]), scale_log2, -my_lse2));
+            p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), scale_log2, -my_lse2));
+            if (need_mask) {
+              p0 = (col + 32 * c + e < key_limit) ? p0 : 0.f;
+              p1 = (col + 32 * c + e + 1 < key_limit) ? p1 : 0.f;
+            }
+            d0 = p0 * (__uint_as_float(dp[e]) - my_delta);
+            d1 = p1 * (__uint_as_float(dp[e + 1]) - my_delta);
+          }
+          pp[e >> 1] = pack2<VT>(p0, p1);
+          ds[e >> 1] = pack2<VT>(d0, d1);
+        }
+        // chunk c of P / dS lands on columns [16 c, 16 c + 16) of S / dP: columns already read
+        if (DKV) tc_st16(t_row + C::COL_S + 16 * c, pp);
+        tc_st16(t_row + C::COL_DP + 16 * c, ds);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[PDS_FULL]);
+    }
+    // ---- epilogue: accumulators -> 16-bit rows ----
+    if (ok && total > 0) ok = mbar_wait(&bars[ACC_DONE], 0, a.status);
+    if (ok) {
+      tc_fence_after();
+      const int rows_total = DKV ? a.N : a.M;
+      VT* o1 = reinterpret_cast<VT*>(a.out1) + ((int64_t)fixed_bh * rows_total + grow) * D;
+      VT* o2 = DKV ? reinterpret_cast<VT*>(a.out2) + ((int64_t)fixed_bh * rows_total + grow) * D : nullptr;
+#pragma unroll 1
+      for (int which = 0; which < (DKV ? 2 : 1); ++which) {
+        const float f = (DKV && which == 0) ? 1.f : a.scale;     // dV unscaled; dK, dQ times the softmax scale
+        VT* dst_row = which == 0 ? o1 : o2;
+        const uint32_t t_acc = t_row + (which == 0 ? C::COL_ACC1 : C::COL_ACC2);
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          if (total > 0) {
+            tc_ld32(t_acc + 32 * c, o);
+            tc_wait_ld();
+            tc_regs_ready(o);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = 0u;
+          }
+          if (grow < rows_total) {
+            uint4* dst = reinterpret_cast<uint4*>(dst_row + 32 * c);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 w;
+              w.x = pack2<VT>(__uint_as_float(o[8 * v + 0]) * f, __uint_as_float(o[8 * v + 1]) * f);
+              w.y = pack2<VT>(__uint_as_float(o[8 * v + 2]) * f, __uint_as_float(o[8 * v + 3]) * f);
+              w.z = pack2<VT>(__uint_as_float(o[8 * v + 4]) * f, __uint_as_float(o[8 * v + 5]) * f);
+              w.w = pack2<VT>(__uint_as_float(o[8 * v + 6]) * f, __uint_as_float(o[8 * v + 7]) * f);
+              dst[v] = w;
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
+  // ---- teardown: every role arrives here, on success and on a timed-out wait ----
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tc_dealloc(tmem, 512);
+  }
+}
+
+template <int D, typename VT>
+int launch_bwd_tc(const sl8_bwd_params* p, float* delta, int* status, cudaStream_t stream) {
+  using C = BtCfg<D>;
+  CUtensorMap q_map, k_map, v_map, do_map;
+  const uint64_t hq = (uint64_t)p->B * p->Hq, hkv = (uint64_t)p->B * p->Hkv;
+  int rc = sl8_make_tmap_3d(&q_map, p->q, 2, D, p->M, hq, 64, kBT, 128);
+  if (rc == SL8_OK) rc = sl8_make_tmap_3d(&do_map, p->dout, 2, D, p->M, hq, 64, kBT, 128);
+  if (rc == SL8_OK) rc = sl8_make_tmap_3d(&k_map, p->k, 2, D, p->N, hkv, 64, kBT, 128);
+  if (rc == SL8_OK) rc = sl8_make_tmap_3d(&v_map, p->v, 2, D, p->N, hkv, 64, kBT, 128);
+  if (rc != SL8_OK) return rc;
+  BtArgs a{};
+  a.lse = p->lse; a.delta = delta; a.status = status;
+  a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N; a.causal = p->causal; a.scale = p->softmax_scale;
+  SL8_CUDA_TRY(cudaFuncSetAttribute(bwd_tc_kernel<D, VT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+  SL8_CUDA_TRY(cudaFuncSetAttribute(bwd_tc_kernel<D, VT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+  // dQ pass: rows = queries (A1 = Q, A2 = dO), columns = keys (B1 = K, B2 = V)
+  a.out1 = p->dq; a.out2 = nullptr;
+  bwd_tc_kernel<D, VT, false><<<dim3((p->M + kBT - 1) / kBT, (unsigned)hq), kBtThreads, C::SMEM, stream>>>(
+      q_map, do_map, k_map, v_map, a);
+  // dK/dV pass: rows = keys (A1 = K, A2 = V), columns = queries (B1 = Q, B2 = dO)
+  a.out1 = p->dv; a.out2 = p->dk;
+  bwd_tc_kernel<D, VT, true><<<dim3((p->N + kBT - 1) / kBT, (unsigned)hkv), kBtThreads, C::SMEM, stream>>>(
+      k_map, v_map, q_map, do_map, a);
+  return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
+}
+
+}  // namespace
+}  // namespace sl8
+
+// The two tensor-memory passes of the backward (D = 64 or 128); parameters were validated and
+// D_m written to `delta` by sl8_attn_bwd (bwd.cu).
+int sl8_bwd_tc(const sl8_bwd_params* p, float* delta, int* status, cudaStream_t s) {
+  using namespace sl8;
+  if (p->D == 128)
+    return p->dtype == SL8_F16 ? launch_bwd_tc<128, __half>(p, delta, status, s)
+                               : launch_bwd_tc<128, __nv_bfloat16>(p, delta, status, s);
+  if (p->D == 64)
+    return p->dtype == SL8_F16 ? launch_bwd_tc<64, __half>(p, delta, status, s)
+                               : launch_bwd_tc<64, __nv_bfloat16>(p, delta, status, s);
+  return SL8_ERR_UNSUPPORTED;
+}

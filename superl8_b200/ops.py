@@ -166,7 +166,8 @@ def attn_int8_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int, max
                                int(max_seqlen_q), causal)
 
 
-def backward_cuda(q, k, v, out, lse, d_out, *, causal: bool = False, scale: float | None = None):
+def backward_cuda(q, k, v, out, lse, d_out, *, causal: bool = False, scale: float | None = None,
+                  backend: int = _lib.SL8_BACKEND_AUTO):
     """Fused backward -> (dq, dk, dv) in the inputs' 16-bit dtype (reference superl8/ops.py:39-67).
     ``lse`` [B, H, M] fp32 (natural log) from the forward; when None it is produced by the
     full-precision forward kernel (the reference recomputes it with dense torch ops)."""
@@ -174,7 +175,7 @@ def backward_cuda(q, k, v, out, lse, d_out, *, causal: bool = False, scale: floa
     if lse is None:
         _, lse = _C.attn_fp16_fwd(q, k, v, causal, sc, want_lse=True)
     return _C.attn_bwd(q.contiguous(), k.contiguous(), v.contiguous(), out.contiguous(), d_out.contiguous(),
-                       lse.contiguous(), sc, causal)
+                       lse.contiguous(), sc, causal, backend=backend)
 
 
 def attn_int8_decode(q, k, v, *, scale: float | None = None, rotate: bool = False, num_splits: int | None = None):

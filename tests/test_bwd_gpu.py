@@ -1,5 +1,5 @@
-"""Backward kernels (dQ pass, dK/dV pass) against the CPU restatement of the reference's exact
-gradient, through the C ABI.  Bars: the reference's own for its CUDA backward are cos >= 0.99,
+"""Backward kernels (dQ pass, dK/dV pass; tcgen05 for D = 64 / 128 and the mma.sync pair for
+every D) against the CPU restatement of the reference's exact gradient, through the C ABI.  Bars: the reference's own for its CUDA backward are cos >= 0.99,
 rel-L1 <= 0.06, SQNR >= 14 dB (tests/test_attn_bwd_cuda.py:24); this path contracts in 16-bit
 with fp32 accumulation and is held to cos >= 0.9999, rel-L1 <= 0.01, SQNR >= 40 dB."""
 
@@ -10,9 +10,15 @@ import torch
 import superl8_b200 as s8
 from conftest import GOLDEN, from_bits
 from oracle import oracle
-from superl8_b200 import _C
+from superl8_b200 import _C, _lib
 
 pytestmark = pytest.mark.gpu
+
+TC, MMA = _lib.SL8_BACKEND_TCGEN05, _lib.SL8_BACKEND_MMA
+
+
+def _backends(D):
+    return (TC, MMA) if D in (64, 128) else (MMA,)
 
 BARS = dict(min_cos=0.9999, max_rel_l1=0.01, min_sqnr_db=40.0)
 
@@ -29,15 +35,19 @@ def test_golden_gradients(device):
         q, k, v, o, do = (from_bits(g[f"{name}__{n}"], "float16").to(device) for n in ("q", "k", "v", "o", "do"))
         causal, scale = bool(g[f"{name}__cfg"][0]), float(g[f"{name}__cfg"][1])
         lse = torch.from_numpy(g[f"{name}__lse"]).to(device)
-        dq, dk, dv = _C.attn_bwd(q, k, v, o, do, lse, scale, causal)
-        assert dq.dtype == torch.float16 and dk.shape == k.shape and dv.shape == v.shape
-        for got, key in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
-            _check(got, torch.from_numpy(g[f"{name}__{key}"]), (name, key))
+        for backend in _backends(q.shape[-1]):
+            dq, dk, dv = _C.attn_bwd(q, k, v, o, do, lse, scale, causal, backend=backend)
+            assert dq.dtype == torch.float16 and dk.shape == k.shape and dv.shape == v.shape
+            for got, key in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+                _check(got, torch.from_numpy(g[f"{name}__{key}"]), (name, key, backend))
+        assert _C.device_status() == 0
 
 
-# the reference's shapes (tests/test_attn_bwd_cuda.py:23) plus grouped heads, ragged sizes, D = 32
+# the reference's shapes (tests/test_attn_bwd_cuda.py:23) plus grouped heads, ragged sizes, D = 32,
+# and sequences of several 128-wide tiles (the stage ring of the tensor-memory passes wraps)
 SHAPES = [(1, 2, 2, 128, 128, 64), (2, 4, 4, 256, 256, 64), (1, 2, 2, 257, 257, 64), (1, 2, 2, 192, 192, 128),
-          (1, 8, 2, 200, 200, 128), (2, 4, 1, 100, 333, 32), (1, 2, 1, 300, 70, 64)]
+          (1, 8, 2, 200, 200, 128), (2, 4, 1, 100, 333, 32), (1, 2, 1, 300, 70, 64), (1, 4, 2, 650, 650, 128),
+          (1, 2, 1, 520, 900, 64), (1, 2, 2, 900, 520, 128)]
 
 
 @pytest.mark.parametrize("shape", SHAPES)
@@ -50,10 +60,14 @@ def test_backward_matches_oracle(device, shape, causal):
     v = torch.randn(B, Hkv, N, D, generator=gen).half()
     do = torch.randn(B, Hq, M, D, generator=gen).half()
     out, lse = _C.attn_fp16_fwd(q.to(device), k.to(device), v.to(device), causal, None, want_lse=True)
-    dq, dk, dv = s8.backward_cuda(q.to(device), k.to(device), v.to(device), out, lse, do.to(device), causal=causal)
     rq, rk, rv = oracle.attention_backward_fp32(q, k, v, out, do, causal)
-    for got, ref, key in ((dq, rq, "dq"), (dk, rk, "dk"), (dv, rv, "dv")):
-        _check(got, ref, (shape, causal, key))
+    for backend in _backends(D):
+        dq, dk, dv = s8.backward_cuda(q.to(device), k.to(device), v.to(device), out, lse, do.to(device), causal=causal,
+                                      backend=backend)
+        assert _C.device_status() == 0
+        for got, ref, key in ((dq, rq, "dq"), (dk, rk, "dk"), (dv, rv, "dv")):
+            assert torch.isfinite(got.float()).all(), (shape, causal, key, backend)
+            _check(got, ref, (shape, causal, key, backend))
     # lse omitted: produced by the forward kernel; same result
     dq2, dk2, dv2 = s8.backward_cuda(q.to(device), k.to(device), v.to(device), out, None, do.to(device), causal=causal)
     assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)
@@ -64,16 +78,18 @@ def test_backward_is_deterministic_and_bf16(device):
     gen = torch.Generator().manual_seed(77)
     q, k, v, do = (torch.randn(2, 4, 256, 64, generator=gen).half().to(device) for _ in range(4))
     out, lse = _C.attn_fp16_fwd(q, k, v, False, None, want_lse=True)
-    r0 = s8.backward_cuda(q, k, v, out, lse, do)
-    for _ in range(3):
-        for a, b in zip(s8.backward_cuda(q, k, v, out, lse, do), r0):
-            assert torch.equal(a, b)
     qb, kb, vb, dob = (t.bfloat16() for t in (q, k, v, do))
     outb, lseb = _C.attn_fp16_fwd(qb, kb, vb, True, None, want_lse=True)
-    got = s8.backward_cuda(qb, kb, vb, outb, lseb, dob, causal=True)
     ref = oracle.attention_backward_fp32(qb, kb, vb, outb, dob, True)
-    for a, b in zip(got, ref):
-        assert a.dtype == torch.bfloat16 and oracle.cos_sim(a, b) >= 0.999 and oracle.rel_l1(a, b) <= 0.03
+    for backend in (TC, MMA):
+        r0 = s8.backward_cuda(q, k, v, out, lse, do, backend=backend)
+        for _ in range(3):
+            for a, b in zip(s8.backward_cuda(q, k, v, out, lse, do, backend=backend), r0):
+                assert torch.equal(a, b)
+        got = s8.backward_cuda(qb, kb, vb, outb, lseb, dob, causal=True, backend=backend)
+        for a, b in zip(got, ref):
+            assert a.dtype == torch.bfloat16 and oracle.cos_sim(a, b) >= 0.999 and oracle.rel_l1(a, b) <= 0.03
+    assert _C.device_status() == 0
 
 
 def test_backward_edge_cases_and_errors(device):
