@@ -16,11 +16,13 @@
 //                 S = Q K^T, dP = dO V^T, dS = P (dP - D_m),  dQ += dS K
 // Tensor memory (512 columns): S at [0,128), dP at [128,256), first accumulator at [256,256+D),
 // second at [384,384+D).  P (16-bit pairs) overwrites the first 64 columns of S, dS those of dP.
-// Six warps: 0-3 compute (thread = row = tensor-memory lane), 4 = TMA producer (the fixed row
-// tiles once, then column tiles through two stages, plus the per-query lse / D_m of a column
-// tile in the dK/dV pass), 5 = tensor-memory allocation and MMA issue.  Per column tile the
-// issuer queues S and dP, the compute warps turn them into P and dS 32 columns at a time, the
-// issuer queues the accumulating MMAs behind them and frees the stage.
+// (The dQ pass has one accumulator and keeps a second S buffer at [384,512).)
+// Ten warps: 0-7 compute (thread = row = tensor-memory lane; warps w and w + 4 share a row group
+// and each takes half of a tile's columns), 8 = TMA producer (the fixed row tiles once, then
+// column tiles through two stages, plus the per-query lse / D_m of a column tile in the dK/dV
+// pass), 9 = tensor-memory allocation and MMA issue.  Per column tile the issuer queues S and
+// dP, the compute warps turn S into P and then dP into dS, the issuer queues the accumulating
+// MMAs behind them (and the next tile's S and dP between them) and frees the stage.
 // Rows and columns past the end of a tensor arrive as zeros (TMA fill) and carry lse = +inf,
 // so P = dS = 0 there; the causal mask is the forward's bottom-right one (key n visible to
 // query m iff n <= m + N - M), evaluated per element only on tiles that straddle the diagonal.
@@ -33,7 +35,9 @@ namespace sl8 {
 namespace {
 
 constexpr int kBT = 128;                       // rows per block, columns per tile
-constexpr int kBtThreads = 192;
+constexpr int kComputeWarps = 8;               // warps w and w + 4 share the rows 32 (w & 3) .. + 32 and split the columns
+constexpr int kBtProducerWarp = kComputeWarps, kBtMmaWarp = kComputeWarps + 1;
+constexpr int kBtThreads = 32 * (kComputeWarps + 2);
 constexpr float kLog2eB = 1.4426950408889634f;
 
 template <int D>
@@ -49,7 +53,8 @@ struct BtCfg {
   static constexpr int OFF_ROWDATA = OFF_ST + 2 * STAGE_BYTES;   // two stages of kBT x {lse log2e, D_m}
   static constexpr int OFF_BAR = OFF_ROWDATA + 2 * kBT * 8;
   static constexpr int SMEM = OFF_BAR + 256 + 1024;
-  static constexpr uint32_t COL_S = 0, COL_DP = 128, COL_ACC1 = 256, COL_ACC2 = 384;
+  static constexpr uint32_t COL_S = 0, COL_DP = 128, COL_ACC1 = 256, COL_ACC2 = 384;   // dK/dV pass
+  static constexpr uint32_t COL_S1 = 384;                                               // dQ pass: second S buffer
 };
 
 struct BtArgs {
@@ -63,7 +68,9 @@ struct BtArgs {
   float scale;
 };
 
-enum BtBar { FIX_FULL = 0, ACC_DONE, SDP_FULL, PDS_FULL, ST_FULL, ST_EMPTY = ST_FULL + 2, BT_NUM_BARS = ST_EMPTY + 2 };
+// S_FULL: the dK/dV pass uses [0] (one S buffer, a phase per tile), the dQ pass [i & 1] (two S buffers).
+enum BtBar { FIX_FULL = 0, ACC_DONE, DP_FULL, P_FULL, DS_FULL, S_FULL, ST_FULL = S_FULL + 2, ST_EMPTY = ST_FULL + 2,
+             BT_NUM_BARS = ST_EMPTY + 2 };
 
 template <int D, typename VT, bool DKV>
 __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_constant__ CUtensorMap a1_map,
@@ -81,10 +88,13 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
   const int G = a.Hq / a.Hkv;
   const int diag = a.causal ? a.N - a.M : 0;
   // rows of this block, and the walk over column tiles
-  const int fixed_bh = blockIdx.y;                       // dK/dV: batch * Hkv + kv head; dQ: batch * Hq + query head
+  // Launch order = heaviest blocks first when causal.  dK/dV pass: grid (batch * Hkv, key blocks) --
+  // the early key blocks of every head, which see the most queries, start first; dQ pass: grid
+  // (query blocks, batch * Hq) with the late query blocks first.
+  const int fixed_bh = DKV ? blockIdx.x : blockIdx.y;    // dK/dV: batch * Hkv + kv head; dQ: batch * Hq + query head
   const int b = DKV ? fixed_bh / a.Hkv : fixed_bh / a.Hq;
   const int kvh = DKV ? fixed_bh % a.Hkv : (fixed_bh % a.Hq) / G;
-  const int row_block = DKV ? blockIdx.x * kBT : (a.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x) * kBT;
+  const int row_block = DKV ? blockIdx.y * kBT : (a.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x) * kBT;
   int col_begin, tiles_per_head, heads;
   if (DKV) {
     // first query that sees a key of this block: n <= m + diag
@@ -105,15 +115,17 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
   if (threadIdx.x == 0) {
     mbar_init(&bars[FIX_FULL], 1);
     mbar_init(&bars[ACC_DONE], 1);
-    mbar_init(&bars[SDP_FULL], 1);
-    mbar_init(&bars[PDS_FULL], 4);
+    mbar_init(&bars[DP_FULL], 1);
+    mbar_init(&bars[P_FULL], kComputeWarps);
+    mbar_init(&bars[DS_FULL], kComputeWarps);
     for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars[S_FULL + i], 1);
       mbar_init(&bars[ST_FULL + i], DKV ? 2 : 1);   // the tile bytes, and (dK/dV) the lse / D_m rows of the tile
       mbar_init(&bars[ST_EMPTY + i], 1);
     }
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == kBtMmaWarp) {
     tc_alloc(tmem_slot, 512);
     tc_relinquish();
     tc_fence_before();
@@ -123,7 +135,7 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   bool ok = true;
 
-  if (warp == 4) {
+  if (warp == kBtProducerWarp) {
     // ======================= producer =======================
     if (lane == 0) {
       tma_prefetch_desc(&a1_map);
@@ -152,14 +164,14 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
         }
       }
       if (DKV) {
-        // per-query statistics of the tile's columns: {lse * log2 e (or +inf: P = 0), D_m}
+        // per-query statistics of the tile's columns: {-lse * log2 e (or -inf: P = 0), D_m}
 #pragma unroll
         for (int r = lane; r < kBT; r += 32) {
           const int m = col + r;
-          float l = INFINITY, d = 0.f;
+          float l = -INFINITY, d = 0.f;
           if (m < a.M) {
             const float v = __ldg(a.lse + (int64_t)head * a.M + m);
-            l = (v > -INFINITY) ? v * kLog2eB : INFINITY;
+            l = (v > -INFINITY) ? -v * kLog2eB : -INFINITY;
             d = __ldg(a.delta + (int64_t)head * a.M + m);
           }
           rowdata[st * kBT + r] = make_float2(l, d);
@@ -168,8 +180,13 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
         if (lane == 0) mbar_arrive(&bars[ST_FULL + st]);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kBtMmaWarp) {
     // ======================= MMA issuer =======================
+    // The whole warp walks the loop and polls the barriers; one elected lane issues and commits.
+    // Order of issue (the tensor pipe executes in this order, which is what lets a later MMA
+    // overwrite the tensor-memory operand of an earlier one):
+    //   dK/dV pass  S_0 dP_0 | dV_i S_{i+1} dK_i dP_{i+1} | ...   (S_{i+1} reuses the columns P_i sat in)
+    //   dQ pass     S_0 dP_0 S_1 | dQ_i dP_{i+1} S_{i+2} | ...     (two S buffers)
     constexpr uint32_t vfmt = std::is_same<VT, __nv_bfloat16>::value ? 1u : 0u;
     const uint32_t idesc_s = umma_idesc(1, vfmt, vfmt, 0, 0, kBT, kBT);
     const uint32_t idesc_acc = umma_idesc(1, vfmt, vfmt, 0, 1, kBT, D);
@@ -177,64 +194,121 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
     const uint64_t da2 = umma_smem_desc(smem_u32(smem + C::OFF_A2), 16, 1024, kUmmaSw128);
     const uint64_t db_k = umma_smem_desc(smem_u32(smem + C::OFF_ST), 16, 1024, kUmmaSw128);             // K-major view
     const uint64_t db_mn = umma_smem_desc(smem_u32(smem + C::OFF_ST), C::SUB_BYTES, 1024, kUmmaSw128);  // MN-major view
-    ok = __all_sync(0xffffffffu, mbar_wait(&bars[FIX_FULL], 0, a.status));
-    for (int i = 0; i < total && ok; ++i) {
-      const int st = i & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(&bars[ST_FULL + st], (i >> 1) & 1, a.status));
-      if (!ok) break;
+    auto wait_all = [&](uint64_t* bar, uint32_t parity) -> bool {
+      const bool r = __all_sync(0xffffffffu, mbar_wait(bar, parity, a.status));
       tc_fence_after();
+      return r;
+    };
+    auto issue_s = [&](int i) {     // S_i = A1 B1_i^T
       if (elect_one()) {
-        // S = A1 B1^T, dP = A2 B2^T
+        const int st = i & 1;
+        const uint32_t col = DKV ? C::COL_S : ((i & 1) ? C::COL_S1 : C::COL_S);
 #pragma unroll
-        for (int s = 0; s < C::KSTEPS; ++s) {
-          const uint32_t off = (32 * s / 128) * C::SUB_BYTES + (32 * s % 128);
-          tc_mma_f16_ss(tmem + C::COL_S, umma_desc_advance(da1, off),
-                        umma_desc_advance(db_k, st * C::STAGE_BYTES + off), idesc_s, s > 0 ? 1u : 0u);
+        for (int k = 0; k < C::KSTEPS; ++k) {
+          const uint32_t off = (32 * k / 128) * C::SUB_BYTES + (32 * k % 128);
+          tc_mma_f16_ss(tmem + col, umma_desc_advance(da1, off), umma_desc_advance(db_k, st * C::STAGE_BYTES + off),
+                        idesc_s, k > 0 ? 1u : 0u);
         }
-#pragma unroll
-        for (int s = 0; s < C::KSTEPS; ++s) {
-          const uint32_t off = (32 * s / 128) * C::SUB_BYTES + (32 * s % 128);
-          tc_mma_f16_ss(tmem + C::COL_DP, umma_desc_advance(da2, off),
-                        umma_desc_advance(db_k, st * C::STAGE_BYTES + C::TILE_BYTES + off), idesc_s, s > 0 ? 1u : 0u);
-        }
-        tc_commit(&bars[SDP_FULL]);
+        tc_commit(&bars[S_FULL + (DKV ? 0 : (i & 1))]);
       }
       __syncwarp();
-      ok = __all_sync(0xffffffffu, mbar_wait(&bars[PDS_FULL], i & 1, a.status));
-      if (!ok) break;
-      tc_fence_after();
+    };
+    auto issue_dp = [&](int i) {    // dP_i = A2 B2_i^T
       if (elect_one()) {
-        if (DKV) {
-          // dV += P^T dO (P over the first 64 columns of S; dO = B2, contraction over the tile's queries)
+        const int st = i & 1;
 #pragma unroll
-          for (int kk = 0; kk < kBT / 16; ++kk)
-            tc_mma_f16_ts(tmem + C::COL_ACC1, tmem + C::COL_S + 8 * kk,
-                          umma_desc_advance(db_mn, st * C::STAGE_BYTES + C::TILE_BYTES + kk * 2048), idesc_acc,
-                          (i > 0 || kk > 0) ? 1u : 0u);
+        for (int k = 0; k < C::KSTEPS; ++k) {
+          const uint32_t off = (32 * k / 128) * C::SUB_BYTES + (32 * k % 128);
+          tc_mma_f16_ss(tmem + C::COL_DP, umma_desc_advance(da2, off),
+                        umma_desc_advance(db_k, st * C::STAGE_BYTES + C::TILE_BYTES + off), idesc_s, k > 0 ? 1u : 0u);
         }
-        // dK += dS^T Q  /  dQ += dS K  (dS over the first 64 columns of dP; B1 read MN-major)
+        tc_commit(&bars[DP_FULL]);
+      }
+      __syncwarp();
+    };
+    auto issue_dv = [&](int i) {    // dV += P_i^T dO_i (P over the first 64 columns of S; B2 read MN-major)
+      if (elect_one()) {
+        const int st = i & 1;
+#pragma unroll
+        for (int kk = 0; kk < kBT / 16; ++kk)
+          tc_mma_f16_ts(tmem + C::COL_ACC1, tmem + C::COL_S + 8 * kk,
+                        umma_desc_advance(db_mn, st * C::STAGE_BYTES + C::TILE_BYTES + kk * 2048), idesc_acc,
+                        (i > 0 || kk > 0) ? 1u : 0u);
+      }
+      __syncwarp();
+    };
+    auto issue_last = [&](int i) {  // dK += dS_i^T Q_i  /  dQ += dS_i K_i (dS over the first 64 columns of dP); frees the stage
+      if (elect_one()) {
+        const int st = i & 1;
 #pragma unroll
         for (int kk = 0; kk < kBT / 16; ++kk)
           tc_mma_f16_ts(tmem + (DKV ? C::COL_ACC2 : C::COL_ACC1), tmem + C::COL_DP + 8 * kk,
-                        umma_desc_advance(db_mn, st * C::STAGE_BYTES + kk * 2048), idesc_acc,
-                        (i > 0 || kk > 0) ? 1u : 0u);
+                        umma_desc_advance(db_mn, st * C::STAGE_BYTES + kk * 2048), idesc_acc, (i > 0 || kk > 0) ? 1u : 0u);
         tc_commit(&bars[ST_EMPTY + st]);
         if (i == total - 1) tc_commit(&bars[ACC_DONE]);
       }
       __syncwarp();
+    };
+    ok = wait_all(&bars[FIX_FULL], 0);
+    if (ok && total > 0) {
+      ok = wait_all(&bars[ST_FULL + 0], 0);
+      if (ok) {
+        issue_s(0);
+        issue_dp(0);
+      }
+      if (!DKV && ok && total > 1) {
+        ok = wait_all(&bars[ST_FULL + 1], 0);
+        if (ok) issue_s(1);
+      }
+    }
+    for (int i = 0; i < total && ok; ++i) {
+      const int st = i & 1;
+      if (DKV) {
+        ok = wait_all(&bars[P_FULL], i & 1);
+        if (!ok) break;
+        issue_dv(i);
+        if (i + 1 < total) {
+          ok = wait_all(&bars[ST_FULL + (st ^ 1)], ((i + 1) >> 1) & 1);
+          if (!ok) break;
+          issue_s(i + 1);
+        }
+        ok = wait_all(&bars[DS_FULL], i & 1);
+        if (!ok) break;
+        issue_last(i);
+        if (i + 1 < total) issue_dp(i + 1);
+      } else {
+        ok = wait_all(&bars[DS_FULL], i & 1);
+        if (!ok) break;
+        issue_last(i);
+        if (i + 1 < total) issue_dp(i + 1);      // its stage was waited for when S_{i+1} was issued
+        if (i + 2 < total) {
+          ok = wait_all(&bars[ST_FULL + st], ((i + 2) >> 1) & 1);
+          if (!ok) break;
+          issue_s(i + 2);                        // into the S buffer the compute warps have finished with
+        }
+      }
     }
   } else {
     // ======================= compute / epilogue =======================
-    const int row = 32 * warp + lane;
+    // Two phases per column tile: P from S (the exponentials), then dS = P (dP - D_m) from dP with
+    // the P kept in registers as 16-bit pairs -- the accumulating MMA that needs P (dK/dV pass) and
+    // the next tile's S run on the tensor pipe while the second phase works.  There is no row
+    // reduction in the backward (lse is an input), so two warps share a row group and each takes
+    // 64 of the tile's 128 columns: two compute warps per scheduler hide each other's latencies.
+    // P and dS land on columns [0, 64) of S and dP, which the lower-half warp reads: the
+    // upper-half warp stores only after a named barrier says that those reads are complete.
+    const int cw = warp & 3, half = warp >> 2;
+    const int row = 32 * cw + lane;
     const int grow = row_block + row;                         // key (dK/dV) or query (dQ) of this thread
-    const uint32_t t_row = tmem + ((uint32_t)(32 * warp) << 16);
+    const uint32_t t_row = tmem + ((uint32_t)(32 * cw) << 16);
     const float scale_log2 = a.scale * kLog2eB;
-    float my_lse2 = INFINITY, my_delta = 0.f;                 // dQ pass: per-row statistics
+    float my_nlse2 = -INFINITY, my_delta = 0.f;               // dQ pass: per-row statistics (-lse log2e; -inf: P = 0)
     if (!DKV && grow < a.M) {
       const float v = __ldg(a.lse + (int64_t)fixed_bh * a.M + grow);
-      my_lse2 = (v > -INFINITY) ? v * kLog2eB : INFINITY;
+      my_nlse2 = (v > -INFINITY) ? -v * kLog2eB : -INFINITY;
       my_delta = __ldg(a.delta + (int64_t)fixed_bh * a.M + grow);
     }
+    const int c0 = 2 * half;                                  // this warp's 32-column chunks: c0, c0 + 1
     for (int i = 0; i < total; ++i) {
       const int st = i & 1;
       const int col = tile_col(i);
@@ -242,7 +316,7 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
         ok = mbar_wait(&bars[ST_FULL + st], (i >> 1) & 1, a.status);   // publishes the tile's lse / D_m rows
         if (!ok) break;
       }
-      ok = mbar_wait(&bars[SDP_FULL], i & 1, a.status);
+      ok = DKV ? mbar_wait(&bars[S_FULL], i & 1, a.status) : mbar_wait(&bars[S_FULL + (i & 1)], (i >> 1) & 1, a.status);
       if (!ok) break;
       tc_fence_after();
       // does the tile straddle the diagonal?  dK/dV: key = grow, query = col + c; dQ: query = grow, key = col + c
@@ -250,50 +324,88 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
       const bool need_mask = DKV ? (a.causal && col + diag < row_block + kBT - 1)
                                  : ((a.causal && col + kBT - 1 > row_block + diag) || col + kBT > a.N);
       const int key_limit = a.causal ? min(a.N, grow + diag + 1) : a.N;   // dQ pass: keys [0, key_limit) are visible
-      const float2* rd = rowdata + st * kBT;
-#pragma unroll 1
-      for (int c = 0; c < kBT / 32; ++c) {
-        uint32_t s[32], dp[32];
-        tc_ld32(t_row + C::COL_S + 32 * c, s);
-        tc_ld32(t_row + C::COL_DP + 32 * c, dp);
+      const float2* rd = rowdata + st * kBT + 32 * c0;                    // dK/dV pass: {-lse log2e, D_m} per column
+      const uint32_t t_s = t_row + (DKV ? C::COL_S : ((i & 1) ? C::COL_S1 : C::COL_S));
+      const int colw = col + 32 * c0;                                     // first column of this warp's half
+      uint32_t pp[32];
+      // ---- phase 1: P ----
+      {
+        uint32_t s[64];
+        tc_ld32(t_s + 32 * c0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+        tc_ld32(t_s + 32 * c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
         tc_wait_ld();
-        tc_regs_ready(s);
-        tc_regs_ready(dp);
-        uint32_t pp[16], ds[16];
+        tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+        tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+        if (DKV && half == 0) {
+          tc_fence_before();
+          named_arrive(1 + cw, 64);
+        }
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float p0, p1, d0, d1;
+        for (int e = 0; e < 64; e += 2) {
+          float p0, p1;
           if (DKV) {
-            const float2 r0 = rd[32 * c + e], r1 = rd[32 * c + e + 1];
-            p0 = ex2_approx(fmaf(__uint_as_float(s[e]), scale_log2, -r0.x));
-            p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), scale_log2, -r1.x));
+            p0 = ex2_approx(fmaf(__uint_as_float(s[e]), scale_log2, rd[e].x));
+            p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), scale_log2, rd[e + 1].x));
             if (need_mask) {
-              p0 = (grow <= col + 32 * c + e + diag) ? p0 : 0.f;
-              p1 = (grow <= col + 32 * c + e + 1 + diag) ? p1 : 0.f;
+              p0 = (grow <= colw + e + diag) ? p0 : 0.f;
+              p1 = (grow <= colw + e + 1 + diag) ? p1 : 0.f;
             }
-            d0 = p0 * (__uint_as_float(dp[e]) - r0.y);
-            d1 = p1 * (__uint_as_float(dp[e + 1]) - r1.y);
           } else {
-            p0 = ex2_approx(fmaf(__uint_as_float(s[e]), scale_log2, -my_lse2));
-            p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), scale_log2, -my_lse2));
+            p0 = ex2_approx(fmaf(__uint_as_float(s[e]), scale_log2, my_nlse2));
+            p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), scale_log2, my_nlse2));
             if (need_mask) {
-              p0 = (col + 32 * c + e < key_limit) ? p0 : 0.f;
-              p1 = (col + 32 * c + e + 1 < key_limit) ? p1 : 0.f;
+              p0 = (colw + e < key_limit) ? p0 : 0.f;
+              p1 = (colw + e + 1 < key_limit) ? p1 : 0.f;
             }
-            d0 = p0 * (__uint_as_float(dp[e]) - my_delta);
-            d1 = p1 * (__uint_as_float(dp[e + 1]) - my_delta);
           }
           pp[e >> 1] = pack2<VT>(p0, p1);
-          ds[e >> 1] = pack2<VT>(d0, d1);
         }
-        // chunk c of P / dS lands on columns [16 c, 16 c + 16) of S / dP: columns already read
-        if (DKV) tc_st16(t_row + C::COL_S + 16 * c, pp);
-        tc_st16(t_row + C::COL_DP + 16 * c, ds);
+      }
+      if (DKV) {
+        if (half == 1) {
+          named_sync(1 + cw, 64);
+          tc_fence_after();
+        }
+        // chunk c of P lands on columns [16 c, 16 c + 16) of S
+        tc_st16(t_s + 16 * c0, *reinterpret_cast<uint32_t(*)[16]>(&pp[0]));
+        tc_st16(t_s + 16 * c0 + 16, *reinterpret_cast<uint32_t(*)[16]>(&pp[16]));
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[P_FULL]);
+      }
+      // ---- phase 2: dS = P (dP - D_m) ----
+      ok = mbar_wait(&bars[DP_FULL], i & 1, a.status);
+      if (!ok) break;
+      tc_fence_after();
+      {
+        uint32_t dp[64], ds[32];
+        tc_ld32(t_row + C::COL_DP + 32 * c0, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
+        tc_ld32(t_row + C::COL_DP + 32 * c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
+        tc_wait_ld();
+        tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
+        tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
+        if (half == 0) {
+          tc_fence_before();
+          named_arrive(5 + cw, 64);
+        }
+#pragma unroll
+        for (int e = 0; e < 64; e += 2) {
+          const float2 p = unpack2<VT>(pp[e >> 1]);
+          const float dl0 = DKV ? rd[e].y : my_delta, dl1 = DKV ? rd[e + 1].y : my_delta;
+          ds[e >> 1] = pack2<VT>(p.x * (__uint_as_float(dp[e]) - dl0), p.y * (__uint_as_float(dp[e + 1]) - dl1));
+        }
+        if (half == 1) {
+          named_sync(5 + cw, 64);
+          tc_fence_after();
+        }
+        tc_st16(t_row + C::COL_DP + 16 * c0, *reinterpret_cast<uint32_t(*)[16]>(&ds[0]));
+        tc_st16(t_row + C::COL_DP + 16 * c0 + 16, *reinterpret_cast<uint32_t(*)[16]>(&ds[16]));
       }
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[PDS_FULL]);
+      if (lane == 0) mbar_arrive(&bars[DS_FULL]);
     }
     // ---- epilogue: accumulators -> 16-bit rows ----
     if (ok && total > 0) ok = mbar_wait(&bars[ACC_DONE], 0, a.status);
@@ -308,7 +420,7 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
         VT* dst_row = which == 0 ? o1 : o2;
         const uint32_t t_acc = t_row + (which == 0 ? C::COL_ACC1 : C::COL_ACC2);
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {   // this warp's half of the channels
           uint32_t o[32];
           if (total > 0) {
             tc_ld32(t_acc + 32 * c, o);
@@ -338,7 +450,7 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
 
   // ---- teardown: every role arrives here, on success and on a timed-out wait ----
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kBtMmaWarp) {
     tc_fence_after();
     tc_dealloc(tmem, 512);
   }
@@ -365,7 +477,7 @@ int launch_bwd_tc(const sl8_bwd_params* p, float* delta, int* status, cudaStream
       q_map, do_map, k_map, v_map, a);
   // dK/dV pass: rows = keys (A1 = K, A2 = V), columns = queries (B1 = Q, B2 = dO)
   a.out1 = p->dv; a.out2 = p->dk;
-  bwd_tc_kernel<D, VT, true><<<dim3((p->N + kBT - 1) / kBT, (unsigned)hkv), kBtThreads, C::SMEM, stream>>>(
+  bwd_tc_kernel<D, VT, true><<<dim3((unsigned)hkv, (p->N + kBT - 1) / kBT), kBtThreads, C::SMEM, stream>>>(
       k_map, v_map, q_map, do_map, a);
   return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
 }

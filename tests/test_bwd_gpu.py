@@ -68,9 +68,10 @@ def test_backward_matches_oracle(device, shape, causal):
         for got, ref, key in ((dq, rq, "dq"), (dk, rk, "dk"), (dv, rv, "dv")):
             assert torch.isfinite(got.float()).all(), (shape, causal, key, backend)
             _check(got, ref, (shape, causal, key, backend))
-    # lse omitted: produced by the forward kernel; same result
+    # lse omitted: produced by the forward kernel; same result (same backend: the default one)
+    dq1, dk1, dv1 = s8.backward_cuda(q.to(device), k.to(device), v.to(device), out, lse, do.to(device), causal=causal)
     dq2, dk2, dv2 = s8.backward_cuda(q.to(device), k.to(device), v.to(device), out, None, do.to(device), causal=causal)
-    assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)
+    assert torch.equal(dq1, dq2) and torch.equal(dk1, dk2) and torch.equal(dv1, dv2)
 
 
 def test_backward_is_deterministic_and_bf16(device):
