@@ -80,7 +80,10 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
   using C = BtCfg<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float2* rowdata = reinterpret_cast<float2*>(smem + C::OFF_ROWDATA);
+  // per stage: 128 floats of -lse log2e, then 128 floats of D_m (read four columns per load: a
+  // broadcast load costs a full shared-memory wavefront whatever its width, and that bandwidth
+  // is what the MMA operand reads need)
+  float* rowdata = reinterpret_cast<float*>(smem + C::OFF_ROWDATA);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BT_NUM_BARS);
 
@@ -174,7 +177,8 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
             l = (v > -INFINITY) ? -v * kLog2eB : -INFINITY;
             d = __ldg(a.delta + (int64_t)head * a.M + m);
           }
-          rowdata[st * kBT + r] = make_float2(l, d);
+          rowdata[st * 2 * kBT + r] = l;
+          rowdata[st * 2 * kBT + kBT + r] = d;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[ST_FULL + st]);
@@ -324,7 +328,8 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
       const bool need_mask = DKV ? (a.causal && col + diag < row_block + kBT - 1)
                                  : ((a.causal && col + kBT - 1 > row_block + diag) || col + kBT > a.N);
       const int key_limit = a.causal ? min(a.N, grow + diag + 1) : a.N;   // dQ pass: keys [0, key_limit) are visible
-      const float2* rd = rowdata + st * kBT + 32 * c0;                    // dK/dV pass: {-lse log2e, D_m} per column
+      const float4* rd_l = reinterpret_cast<const float4*>(rowdata + st * 2 * kBT + 32 * c0);        // dK/dV pass: -lse log2e
+      const float4* rd_d = reinterpret_cast<const float4*>(rowdata + st * 2 * kBT + kBT + 32 * c0);  // and D_m per column
       const uint32_t t_s = t_row + (DKV ? C::COL_S : ((i & 1) ? C::COL_S1 : C::COL_S));
       const int colw = col + 32 * c0;                                     // first column of this warp's half
       uint32_t pp[32];
@@ -344,8 +349,9 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
         for (int e = 0; e < 64; e += 2) {
           float p0, p1;
           if (DKV) {
-            p0 = ex2_approx(fmaf(__uint_as_float(s[e]), scale_log2, rd[e].x));
-            p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), scale_log2, rd[e + 1].x));
+            const float4 l4 = rd_l[e >> 2];
+            p0 = ex2_approx(fmaf(__uint_as_float(s[e]), scale_log2, (e & 2) ? l4.z : l4.x));
+            p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), scale_log2, (e & 2) ? l4.w : l4.y));
             if (need_mask) {
               p0 = (grow <= colw + e + diag) ? p0 : 0.f;
               p1 = (grow <= colw + e + 1 + diag) ? p1 : 0.f;
@@ -392,7 +398,12 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
 #pragma unroll
         for (int e = 0; e < 64; e += 2) {
           const float2 p = unpack2<VT>(pp[e >> 1]);
-          const float dl0 = DKV ? rd[e].y : my_delta, dl1 = DKV ? rd[e + 1].y : my_delta;
+          float dl0 = my_delta, dl1 = my_delta;
+          if (DKV) {
+            const float4 d4 = rd_d[e >> 2];
+            dl0 = (e & 2) ? d4.z : d4.x;
+            dl1 = (e & 2) ? d4.w : d4.y;
+          }
           ds[e >> 1] = pack2<VT>(p.x * (__uint_as_float(dp[e]) - dl0), p.y * (__uint_as_float(dp[e + 1]) - dl1));
         }
         if (half == 1) {
