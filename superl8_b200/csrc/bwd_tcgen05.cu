@@ -17,8 +17,8 @@
 // Tensor memory (512 columns): S at [0,128), dP at [128,256), first accumulator at [256,256+D),
 // second at [384,384+D).  P (16-bit pairs) overwrites the first 64 columns of S, dS those of dP.
 // (The dQ pass has one accumulator and keeps a second S buffer at [384,512).)
-// Ten warps: 0-7 compute (thread = row = tensor-memory lane; warps w and w + 4 share a row group
-// and each takes half of a tile's columns), 8 = TMA producer (the fixed row tiles once, then
+// Ten warps: 0-7 compute (thread = row = tensor-memory lane; warps w and w + 4 share a row group:
+// w forms P from S, w + 4 forms dS from P and dP), 8 = TMA producer (the fixed row tiles once, then
 // column tiles through two stages, plus the per-query lse / D_m of a column tile in the dK/dV
 // pass), 9 = tensor-memory allocation and MMA issue.  Per column tile the issuer queues S and
 // dP, the compute warps turn S into P and then dP into dS, the issuer queues the accumulating
@@ -34,25 +34,45 @@
 namespace sl8 {
 namespace {
 
+SL8_TRACE_DEFINE()
+#ifndef SL8_TRACE_PASS
+#define SL8_TRACE_PASS 1      // which pass a trace build stamps: 0 = dQ, 1 = dK/dV
+#endif
+#define BTR(slot) do { if (DKV == (SL8_TRACE_PASS != 0)) TR(slot); } while (0)
+
 constexpr int kBT = 128;                       // rows per block, columns per tile
-constexpr int kComputeWarps = 8;               // warps w and w + 4 share the rows 32 (w & 3) .. + 32 and split the columns
+constexpr int kComputeWarps = 8;               // warps w and w + 4 share the rows 32 (w & 3) .. + 32: w makes P, w + 4 makes dS
 constexpr int kBtProducerWarp = kComputeWarps, kBtMmaWarp = kComputeWarps + 1;
 constexpr int kBtThreads = 32 * (kComputeWarps + 2);
 constexpr float kLog2eB = 1.4426950408889634f;
 
-template <int D>
+template <int D, bool DKV>
 struct BtCfg {
   static constexpr int SUBS = 2 * D / 128;               // 64-channel (128-byte) sub-tiles of a row
   static constexpr int SUB_BYTES = kBT * 128;
   static constexpr int TILE_BYTES = kBT * 2 * D;
   static constexpr int KSTEPS = 2 * D / 32;              // MMA K steps over the head dimension
+  // Column tiles travel in two rings.  B1 (Q in the dK/dV pass, K in the dQ pass) is read by the
+  // tile's first MMA and by its last, so its stage comes back late: the dQ pass, which has the
+  // room, gives it three stages (a reload is then two tiles ahead of its use).  B2 (dO / V) is
+  // released after the dV MMA (dK/dV pass) or right after dP (dQ pass).
+  static constexpr int NB1 = DKV ? 2 : (D <= 128 ? 3 : 2);
+  static constexpr int NB2 = 2;
   static constexpr int OFF_A1 = 0;
   static constexpr int OFF_A2 = OFF_A1 + TILE_BYTES;
-  static constexpr int OFF_ST = OFF_A2 + TILE_BYTES;     // two stages of {B1 tile, B2 tile}
-  static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-  static constexpr int OFF_ROWDATA = OFF_ST + 2 * STAGE_BYTES;   // two stages of kBT x {lse log2e, D_m}
-  static constexpr int OFF_BAR = OFF_ROWDATA + 2 * kBT * 8;
+  static constexpr int OFF_B1 = OFF_A2 + TILE_BYTES;
+  static constexpr int OFF_B2 = OFF_B1 + NB1 * TILE_BYTES;
+  // dK/dV pass: the per-query statistics ride on one extra K step of the S and dP MMAs.  Operand
+  // tiles of 128 rows x 16 elements (no swizzle: 8-row x 16-byte core matrices, the two K chunks
+  // 2048 bytes apart, 8-row groups 128 bytes apart): a constant one whose rows are {1, 1, 0, ...},
+  // and per B1 stage one holding {hi, lo, 0, ...} of -lse / scale and one of -D_m per query.
+  static constexpr int EXT_BYTES = 2 * (kBT / 8) * 128;
+  static constexpr int OFF_EXT_ONES = OFF_B2 + NB2 * TILE_BYTES;
+  static constexpr int OFF_EXT_S = OFF_EXT_ONES + EXT_BYTES;          // NB1 stages
+  static constexpr int OFF_EXT_DP = OFF_EXT_S + NB1 * EXT_BYTES;      // NB1 stages
+  static constexpr int OFF_BAR = DKV ? OFF_EXT_DP + NB1 * EXT_BYTES : OFF_EXT_ONES;
   static constexpr int SMEM = OFF_BAR + 256 + 1024;
+  static_assert(SMEM <= 232448, "shared memory per block");
   static constexpr uint32_t COL_S = 0, COL_DP = 128, COL_ACC1 = 256, COL_ACC2 = 384;   // dK/dV pass
   static constexpr uint32_t COL_S1 = 384;                                               // dQ pass: second S buffer
 };
@@ -69,21 +89,17 @@ struct BtArgs {
 };
 
 // S_FULL: the dK/dV pass uses [0] (one S buffer, a phase per tile), the dQ pass [i & 1] (two S buffers).
-enum BtBar { FIX_FULL = 0, ACC_DONE, DP_FULL, P_FULL, DS_FULL, S_FULL, ST_FULL = S_FULL + 2, ST_EMPTY = ST_FULL + 2,
-             BT_NUM_BARS = ST_EMPTY + 2 };
+enum BtBar { FIX_FULL = 0, ACC_DONE, DP_FULL, P_FULL, P_READ, DS_FULL, S_FULL, B1_FULL = S_FULL + 2, B1_EMPTY = B1_FULL + 3,
+             B2_FULL = B1_EMPTY + 3, B2_EMPTY = B2_FULL + 2, BT_NUM_BARS = B2_EMPTY + 2 };
 
 template <int D, typename VT, bool DKV>
 __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_constant__ CUtensorMap a1_map,
                                                               const __grid_constant__ CUtensorMap a2_map,
                                                               const __grid_constant__ CUtensorMap b1_map,
                                                               const __grid_constant__ CUtensorMap b2_map, BtArgs a) {
-  using C = BtCfg<D>;
+  using C = BtCfg<D, DKV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  // per stage: 128 floats of -lse log2e, then 128 floats of D_m (read four columns per load: a
-  // broadcast load costs a full shared-memory wavefront whatever its width, and that bandwidth
-  // is what the MMA operand reads need)
-  float* rowdata = reinterpret_cast<float*>(smem + C::OFF_ROWDATA);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BT_NUM_BARS);
 
@@ -119,12 +135,17 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
     mbar_init(&bars[FIX_FULL], 1);
     mbar_init(&bars[ACC_DONE], 1);
     mbar_init(&bars[DP_FULL], 1);
-    mbar_init(&bars[P_FULL], kComputeWarps);
-    mbar_init(&bars[DS_FULL], kComputeWarps);
+    mbar_init(&bars[P_FULL], 4);     // the P warps
+    mbar_init(&bars[P_READ], 4);     // the dS warps, once P is in their registers (dK/dV pass)
+    mbar_init(&bars[DS_FULL], 4);    // the dS warps
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[S_FULL + i], 1);
-      mbar_init(&bars[ST_FULL + i], DKV ? 2 : 1);   // the tile bytes, and (dK/dV) the lse / D_m rows of the tile
-      mbar_init(&bars[ST_EMPTY + i], 1);
+      mbar_init(&bars[B2_FULL + i], 1);
+      mbar_init(&bars[B2_EMPTY + i], 1);
+    }
+    for (int i = 0; i < C::NB1; ++i) {
+      mbar_init(&bars[B1_FULL + i], DKV ? 2 : 1);   // the tile bytes, and (dK/dV) the lse / D_m rows of the tile
+      mbar_init(&bars[B1_EMPTY + i], 1);
     }
     mbar_fence_init();
   }
@@ -140,6 +161,7 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
 
   if (warp == kBtProducerWarp) {
     // ======================= producer =======================
+    const float inv_scale = 1.f / a.scale;
     if (lane == 0) {
       tma_prefetch_desc(&a1_map);
       tma_prefetch_desc(&a2_map);
@@ -152,36 +174,58 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
         tma_load_3d(smem + C::OFF_A2 + c * C::SUB_BYTES, &a2_map, &bars[FIX_FULL], 64 * c, row_block, fixed_bh);
       }
     }
+    if (DKV) {
+      // the statistic tiles: zero everything once (only elements 0 and 1 of a row ever change)
+      uint32_t* ext = reinterpret_cast<uint32_t*>(smem + C::OFF_EXT_ONES);
+      for (int w = lane; w < (1 + 2 * C::NB1) * C::EXT_BYTES / 4; w += 32) ext[w] = 0u;
+      __syncwarp();
+      for (int r = lane; r < kBT; r += 32)
+        *reinterpret_cast<uint32_t*>(smem + C::OFF_EXT_ONES + (r >> 3) * 128 + (r & 7) * 16) = pack2<VT>(1.f, 1.f);
+      fence_proxy_async_smem();
+      __syncwarp();
+    }
     for (int i = 0; i < total && ok; ++i) {
-      const int st = i & 1;
-      if (i >= 2) ok = mbar_wait(&bars[ST_EMPTY + st], ((i >> 1) - 1) & 1, a.status);
-      if (!ok) break;
+      const int s1 = i % C::NB1, s2 = i % C::NB2;
       const int head = tile_head(i), col = tile_col(i);
+      // B2 first: its stage comes back earlier
+      if (i >= C::NB2) ok = mbar_wait(&bars[B2_EMPTY + s2], ((i / C::NB2) - 1) & 1, a.status);
+      if (!ok) break;
       if (lane == 0) {
-        mbar_expect_tx(&bars[ST_FULL + st], C::STAGE_BYTES);
-        uint8_t* dst = smem + C::OFF_ST + st * C::STAGE_BYTES;
+        mbar_expect_tx(&bars[B2_FULL + s2], C::TILE_BYTES);
 #pragma unroll
-        for (int c = 0; c < C::SUBS; ++c) {
-          tma_load_3d(dst + c * C::SUB_BYTES, &b1_map, &bars[ST_FULL + st], 64 * c, col, head);
-          tma_load_3d(dst + C::TILE_BYTES + c * C::SUB_BYTES, &b2_map, &bars[ST_FULL + st], 64 * c, col, head);
-        }
+        for (int c = 0; c < C::SUBS; ++c)
+          tma_load_3d(smem + C::OFF_B2 + s2 * C::TILE_BYTES + c * C::SUB_BYTES, &b2_map, &bars[B2_FULL + s2], 64 * c, col, head);
+      }
+      if (i >= C::NB1) ok = mbar_wait(&bars[B1_EMPTY + s1], ((i / C::NB1) - 1) & 1, a.status);
+      if (!ok) break;
+      if (lane == 0) {
+        mbar_expect_tx(&bars[B1_FULL + s1], C::TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < C::SUBS; ++c)
+          tma_load_3d(smem + C::OFF_B1 + s1 * C::TILE_BYTES + c * C::SUB_BYTES, &b1_map, &bars[B1_FULL + s1], 64 * c, col, head);
       }
       if (DKV) {
-        // per-query statistics of the tile's columns: {-lse * log2 e (or -inf: P = 0), D_m}
+        // per-query statistics of the tile's columns as {hi, lo} 16-bit pairs: x = -lse / scale (so
+        // that (S + x) scale log2e is the exponent; a large negative number where P must be 0:
+        // queries past M, rows without a visible key) and -D_m
+        const float big = std::is_same<VT, __half>::value ? -60000.f : -1e30f;
 #pragma unroll
         for (int r = lane; r < kBT; r += 32) {
           const int m = col + r;
-          float l = -INFINITY, d = 0.f;
+          float x = big, d = 0.f;
           if (m < a.M) {
             const float v = __ldg(a.lse + (int64_t)head * a.M + m);
-            l = (v > -INFINITY) ? -v * kLog2eB : -INFINITY;
-            d = __ldg(a.delta + (int64_t)head * a.M + m);
+            x = (v > -INFINITY) ? fmaxf(-v * inv_scale, big) : big;
+            d = -__ldg(a.delta + (int64_t)head * a.M + m);
           }
-          rowdata[st * 2 * kBT + r] = l;
-          rowdata[st * 2 * kBT + kBT + r] = d;
+          const float xh = to_f32<VT>(from_f32<VT>(x)), dh = to_f32<VT>(from_f32<VT>(d));
+          const uint32_t off = s1 * C::EXT_BYTES + (r >> 3) * 128 + (r & 7) * 16;
+          *reinterpret_cast<uint32_t*>(smem + C::OFF_EXT_S + off) = pack2<VT>(xh, x - xh);
+          *reinterpret_cast<uint32_t*>(smem + C::OFF_EXT_DP + off) = pack2<VT>(dh, d - dh);
         }
+        fence_proxy_async_smem();     // the MMAs read these tiles through the async proxy
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[ST_FULL + st]);
+        if (lane == 0) mbar_arrive(&bars[B1_FULL + s1]);
       }
     }
   } else if (warp == kBtMmaWarp) {
@@ -196,8 +240,15 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
     const uint32_t idesc_acc = umma_idesc(1, vfmt, vfmt, 0, 1, kBT, D);
     const uint64_t da1 = umma_smem_desc(smem_u32(smem + C::OFF_A1), 16, 1024, kUmmaSw128);
     const uint64_t da2 = umma_smem_desc(smem_u32(smem + C::OFF_A2), 16, 1024, kUmmaSw128);
-    const uint64_t db_k = umma_smem_desc(smem_u32(smem + C::OFF_ST), 16, 1024, kUmmaSw128);             // K-major view
-    const uint64_t db_mn = umma_smem_desc(smem_u32(smem + C::OFF_ST), C::SUB_BYTES, 1024, kUmmaSw128);  // MN-major view
+    // column tiles, viewed K-major (for S and dP) and MN-major (for the accumulating MMAs)
+    const uint64_t db1_k = umma_smem_desc(smem_u32(smem + C::OFF_B1), 16, 1024, kUmmaSw128);
+    const uint64_t db2_k = umma_smem_desc(smem_u32(smem + C::OFF_B2), 16, 1024, kUmmaSw128);
+    const uint64_t db1_mn = umma_smem_desc(smem_u32(smem + C::OFF_B1), C::SUB_BYTES, 1024, kUmmaSw128);
+    const uint64_t db2_mn = umma_smem_desc(smem_u32(smem + C::OFF_B2), C::SUB_BYTES, 1024, kUmmaSw128);
+    // statistic tiles (dK/dV pass): K-major, no swizzle, K chunks 2048 bytes apart, 8-row groups 128
+    const uint64_t de_ones = umma_smem_desc(smem_u32(smem + C::OFF_EXT_ONES), 2048, 128, 0);
+    const uint64_t de_s = umma_smem_desc(smem_u32(smem + C::OFF_EXT_S), 2048, 128, 0);
+    const uint64_t de_dp = umma_smem_desc(smem_u32(smem + C::OFF_EXT_DP), 2048, 128, 0);
     auto wait_all = [&](uint64_t* bar, uint32_t parity) -> bool {
       const bool r = __all_sync(0xffffffffu, mbar_wait(bar, parity, a.status));
       tc_fence_after();
@@ -205,103 +256,128 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
     };
     auto issue_s = [&](int i) {     // S_i = A1 B1_i^T
       if (elect_one()) {
-        const int st = i & 1;
+        const int s1 = i % C::NB1;
         const uint32_t col = DKV ? C::COL_S : ((i & 1) ? C::COL_S1 : C::COL_S);
 #pragma unroll
         for (int k = 0; k < C::KSTEPS; ++k) {
           const uint32_t off = (32 * k / 128) * C::SUB_BYTES + (32 * k % 128);
-          tc_mma_f16_ss(tmem + col, umma_desc_advance(da1, off), umma_desc_advance(db_k, st * C::STAGE_BYTES + off),
+          tc_mma_f16_ss(tmem + col, umma_desc_advance(da1, off), umma_desc_advance(db1_k, s1 * C::TILE_BYTES + off),
                         idesc_s, k > 0 ? 1u : 0u);
         }
+        if (DKV) tc_mma_f16_ss(tmem + col, de_ones, umma_desc_advance(de_s, s1 * C::EXT_BYTES), idesc_s, 1u);   // S -= lse / scale
         tc_commit(&bars[S_FULL + (DKV ? 0 : (i & 1))]);
       }
       __syncwarp();
     };
-    auto issue_dp = [&](int i) {    // dP_i = A2 B2_i^T
+    auto issue_dp = [&](int i) {    // dP_i = A2 B2_i^T (dQ pass: nothing else reads the B2 stage)
       if (elect_one()) {
-        const int st = i & 1;
+        const int s2 = i % C::NB2;
 #pragma unroll
         for (int k = 0; k < C::KSTEPS; ++k) {
           const uint32_t off = (32 * k / 128) * C::SUB_BYTES + (32 * k % 128);
-          tc_mma_f16_ss(tmem + C::COL_DP, umma_desc_advance(da2, off),
-                        umma_desc_advance(db_k, st * C::STAGE_BYTES + C::TILE_BYTES + off), idesc_s, k > 0 ? 1u : 0u);
+          tc_mma_f16_ss(tmem + C::COL_DP, umma_desc_advance(da2, off), umma_desc_advance(db2_k, s2 * C::TILE_BYTES + off),
+                        idesc_s, k > 0 ? 1u : 0u);
         }
+        if (DKV) tc_mma_f16_ss(tmem + C::COL_DP, de_ones, umma_desc_advance(de_dp, (i % C::NB1) * C::EXT_BYTES), idesc_s, 1u);   // dP -= D_m
         tc_commit(&bars[DP_FULL]);
+        if (!DKV) tc_commit(&bars[B2_EMPTY + s2]);
       }
       __syncwarp();
     };
-    auto issue_dv = [&](int i) {    // dV += P_i^T dO_i (P over the first 64 columns of S; B2 read MN-major)
+    auto issue_dv = [&](int i) {    // dV += P_i^T dO_i (P over the first 64 columns of S; B2 read MN-major); frees the B2 stage
       if (elect_one()) {
-        const int st = i & 1;
+        const int s2 = i % C::NB2;
 #pragma unroll
         for (int kk = 0; kk < kBT / 16; ++kk)
-          tc_mma_f16_ts(tmem + C::COL_ACC1, tmem + C::COL_S + 8 * kk,
-                        umma_desc_advance(db_mn, st * C::STAGE_BYTES + C::TILE_BYTES + kk * 2048), idesc_acc,
-                        (i > 0 || kk > 0) ? 1u : 0u);
+          tc_mma_f16_ts(tmem + C::COL_ACC1, tmem + C::COL_S + 8 * kk, umma_desc_advance(db2_mn, s2 * C::TILE_BYTES + kk * 2048),
+                        idesc_acc, (i > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(&bars[B2_EMPTY + s2]);
       }
       __syncwarp();
     };
-    auto issue_last = [&](int i) {  // dK += dS_i^T Q_i  /  dQ += dS_i K_i (dS over the first 64 columns of dP); frees the stage
+    auto issue_last = [&](int i) {  // dK += dS_i^T Q_i  /  dQ += dS_i K_i (dS over the first 64 columns of dP); frees the B1 stage
       if (elect_one()) {
-        const int st = i & 1;
+        const int s1 = i % C::NB1;
 #pragma unroll
         for (int kk = 0; kk < kBT / 16; ++kk)
           tc_mma_f16_ts(tmem + (DKV ? C::COL_ACC2 : C::COL_ACC1), tmem + C::COL_DP + 8 * kk,
-                        umma_desc_advance(db_mn, st * C::STAGE_BYTES + kk * 2048), idesc_acc, (i > 0 || kk > 0) ? 1u : 0u);
-        tc_commit(&bars[ST_EMPTY + st]);
+                        umma_desc_advance(db1_mn, s1 * C::TILE_BYTES + kk * 2048), idesc_acc, (i > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(&bars[B1_EMPTY + s1]);
         if (i == total - 1) tc_commit(&bars[ACC_DONE]);
       }
       __syncwarp();
     };
+    auto wait_b1 = [&](int i) { return wait_all(&bars[B1_FULL + i % C::NB1], (i / C::NB1) & 1); };
+    auto wait_b2 = [&](int i) { return wait_all(&bars[B2_FULL + i % C::NB2], (i / C::NB2) & 1); };
     ok = wait_all(&bars[FIX_FULL], 0);
     if (ok && total > 0) {
-      ok = wait_all(&bars[ST_FULL + 0], 0);
-      if (ok) {
-        issue_s(0);
-        issue_dp(0);
-      }
+      ok = wait_b1(0);
+      if (ok) issue_s(0);
+      if (ok) ok = wait_b2(0);
+      if (ok) issue_dp(0);
       if (!DKV && ok && total > 1) {
-        ok = wait_all(&bars[ST_FULL + 1], 0);
+        ok = wait_b1(1);
         if (ok) issue_s(1);
       }
     }
     for (int i = 0; i < total && ok; ++i) {
-      const int st = i & 1;
+      if (lane == 0 && i < 250) BTR(4096 + 8 * i + 0);
       if (DKV) {
         ok = wait_all(&bars[P_FULL], i & 1);
         if (!ok) break;
+        if (lane == 0 && i < 250) BTR(4096 + 8 * i + 1);
         issue_dv(i);
+        if (lane == 0 && i < 250) BTR(4096 + 8 * i + 2);
         if (i + 1 < total) {
-          ok = wait_all(&bars[ST_FULL + (st ^ 1)], ((i + 1) >> 1) & 1);
+          ok = wait_b1(i + 1);
+          if (ok) ok = wait_all(&bars[P_READ], i & 1);     // the dS warps hold P_i: its columns may be overwritten
           if (!ok) break;
+          if (lane == 0 && i < 250) BTR(4096 + 8 * i + 3);
           issue_s(i + 1);
         }
+        if (lane == 0 && i < 250) BTR(4096 + 8 * i + 4);
         ok = wait_all(&bars[DS_FULL], i & 1);
         if (!ok) break;
+        if (lane == 0 && i < 250) BTR(4096 + 8 * i + 5);
         issue_last(i);
-        if (i + 1 < total) issue_dp(i + 1);
+        if (i + 1 < total) {
+          ok = wait_b2(i + 1);
+          if (!ok) break;
+          issue_dp(i + 1);
+        }
+        if (lane == 0 && i < 250) BTR(4096 + 8 * i + 6);
       } else {
         ok = wait_all(&bars[DS_FULL], i & 1);
         if (!ok) break;
+        if (lane == 0 && i < 250) BTR(4096 + 8 * i + 1);
         issue_last(i);
-        if (i + 1 < total) issue_dp(i + 1);      // its stage was waited for when S_{i+1} was issued
-        if (i + 2 < total) {
-          ok = wait_all(&bars[ST_FULL + st], ((i + 2) >> 1) & 1);
+        if (i + 1 < total) {
+          ok = wait_b2(i + 1);
           if (!ok) break;
+          issue_dp(i + 1);
+        }
+        if (lane == 0 && i < 250) BTR(4096 + 8 * i + 2);
+        if (i + 2 < total) {
+          ok = wait_b1(i + 2);
+          if (!ok) break;
+          if (lane == 0 && i < 250) BTR(4096 + 8 * i + 3);
           issue_s(i + 2);                        // into the S buffer the compute warps have finished with
         }
+        if (lane == 0 && i < 250) BTR(4096 + 8 * i + 4);
       }
     }
   } else {
     // ======================= compute / epilogue =======================
-    // Two phases per column tile: P from S (the exponentials), then dS = P (dP - D_m) from dP with
-    // the P kept in registers as 16-bit pairs -- the accumulating MMA that needs P (dK/dV pass) and
-    // the next tile's S run on the tensor pipe while the second phase works.  There is no row
-    // reduction in the backward (lse is an input), so two warps share a row group and each takes
-    // 64 of the tile's 128 columns: two compute warps per scheduler hide each other's latencies.
-    // P and dS land on columns [0, 64) of S and dP, which the lower-half warp reads: the
-    // upper-half warp stores only after a named barrier says that those reads are complete.
-    const int cw = warp & 3, half = warp >> 2;
+    // Warps 0-3 ("P warps") turn S into P = 2^(S scale log2e - lse log2e): one exponential per
+    // element, work for the special-function unit.  Warps 4-7 ("dS warps") read that P back from
+    // tensor memory and turn dP into dS = P (dP - D_m): multiply-add work.  A scheduler hosts one
+    // warp of each kind, so the two kinds of work overlap instead of queueing in one warp, and
+    // the P warps move on to the next tile's S while the dS warps finish this one.  There is no
+    // row reduction in the backward (lse is an input), so the two kinds never exchange more than
+    // P itself.  P (16-bit pairs) overwrites columns [0, 64) of its S buffer, dS those of dP --
+    // chunk c of 32 columns lands on columns [16 c, 16 c + 16), which the same thread has
+    // already read.
+    const int cw = warp & 3, half = warp >> 2;                // row group; 0 = P warp, 1 = dS warp
     const int row = 32 * cw + lane;
     const int grow = row_block + row;                         // key (dK/dV) or query (dQ) of this thread
     const uint32_t t_row = tmem + ((uint32_t)(32 * cw) << 16);
@@ -312,111 +388,106 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
       my_nlse2 = (v > -INFINITY) ? -v * kLog2eB : -INFINITY;
       my_delta = __ldg(a.delta + (int64_t)fixed_bh * a.M + grow);
     }
-    const int c0 = 2 * half;                                  // this warp's 32-column chunks: c0, c0 + 1
     for (int i = 0; i < total; ++i) {
-      const int st = i & 1;
       const int col = tile_col(i);
-      if (DKV) {
-        ok = mbar_wait(&bars[ST_FULL + st], (i >> 1) & 1, a.status);   // publishes the tile's lse / D_m rows
-        if (!ok) break;
-      }
-      ok = DKV ? mbar_wait(&bars[S_FULL], i & 1, a.status) : mbar_wait(&bars[S_FULL + (i & 1)], (i >> 1) & 1, a.status);
-      if (!ok) break;
-      tc_fence_after();
-      // does the tile straddle the diagonal?  dK/dV: key = grow, query = col + c; dQ: query = grow, key = col + c
-      // (dQ pass: also the tile that runs past the last key -- its zero-filled keys still give P > 0)
-      const bool need_mask = DKV ? (a.causal && col + diag < row_block + kBT - 1)
-                                 : ((a.causal && col + kBT - 1 > row_block + diag) || col + kBT > a.N);
-      const int key_limit = a.causal ? min(a.N, grow + diag + 1) : a.N;   // dQ pass: keys [0, key_limit) are visible
-      const float4* rd_l = reinterpret_cast<const float4*>(rowdata + st * 2 * kBT + 32 * c0);        // dK/dV pass: -lse log2e
-      const float4* rd_d = reinterpret_cast<const float4*>(rowdata + st * 2 * kBT + kBT + 32 * c0);  // and D_m per column
       const uint32_t t_s = t_row + (DKV ? C::COL_S : ((i & 1) ? C::COL_S1 : C::COL_S));
-      const int colw = col + 32 * c0;                                     // first column of this warp's half
-      uint32_t pp[32];
-      // ---- phase 1: P ----
-      {
-        uint32_t s[64];
-        tc_ld32(t_s + 32 * c0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-        tc_ld32(t_s + 32 * c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-        tc_wait_ld();
-        tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-        tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-        if (DKV && half == 0) {
-          tc_fence_before();
-          named_arrive(1 + cw, 64);
-        }
+      if (warp == 0 && lane == 0 && i < 250) BTR(8 * i + 0);
+      if (warp == 4 && lane == 0 && i < 250) BTR(2048 + 8 * i + 0);
+      if (half == 0) {
+        // ======== P warp ========
+        ok = DKV ? mbar_wait(&bars[S_FULL], i & 1, a.status) : mbar_wait(&bars[S_FULL + (i & 1)], (i >> 1) & 1, a.status);
+        if (!ok) break;
+        tc_fence_after();
+        if (warp == 0 && lane == 0 && i < 250) BTR(8 * i + 1);
+        // does the tile straddle the diagonal?  dK/dV: key = grow, query = col + c; dQ: query = grow, key = col + c
+        // (dQ pass: also the tile that runs past the last key -- its zero-filled keys still give P > 0)
+        const bool need_mask = DKV ? (a.causal && col + diag < row_block + kBT - 1)
+                                   : ((a.causal && col + kBT - 1 > row_block + diag) || col + kBT > a.N);
+        const int key_limit = a.causal ? min(a.N, grow + diag + 1) : a.N;   // dQ pass: keys [0, key_limit) are visible
 #pragma unroll
-        for (int e = 0; e < 64; e += 2) {
-          float p0, p1;
-          if (DKV) {
-            const float4 l4 = rd_l[e >> 2];
-            p0 = ex2_approx(fmaf(__uint_as_float(s[e]), scale_log2, (e & 2) ? l4.z : l4.x));
-            p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), scale_log2, (e & 2) ? l4.w : l4.y));
-            if (need_mask) {
-              p0 = (grow <= colw + e + diag) ? p0 : 0.f;
-              p1 = (grow <= colw + e + 1 + diag) ? p1 : 0.f;
+        for (int h = 0; h < 2; ++h) {            // two chunks of 32 columns at a time
+          uint32_t s[64], pp[32];
+          tc_ld32(t_s + 64 * h, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+          tc_ld32(t_s + 64 * h + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+          tc_wait_ld();
+          tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+          tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+          const int colw = col + 64 * h;
+#pragma unroll
+          for (int e = 0; e < 64; e += 2) {
+            float p0, p1;
+            if (DKV) {
+              // (S already carries -lse / scale of its query: the extra K step of the S MMA)
+              p0 = ex2_approx(__uint_as_float(s[e]) * scale_log2);
+              p1 = ex2_approx(__uint_as_float(s[e + 1]) * scale_log2);
+              if (need_mask) {
+                p0 = (grow <= colw + e + diag) ? p0 : 0.f;
+                p1 = (grow <= colw + e + 1 + diag) ? p1 : 0.f;
+              }
+            } else {
+              p0 = ex2_approx(fmaf(__uint_as_float(s[e]), scale_log2, my_nlse2));
+              p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), scale_log2, my_nlse2));
+              if (need_mask) {
+                p0 = (colw + e < key_limit) ? p0 : 0.f;
+                p1 = (colw + e + 1 < key_limit) ? p1 : 0.f;
+              }
             }
-          } else {
-            p0 = ex2_approx(fmaf(__uint_as_float(s[e]), scale_log2, my_nlse2));
-            p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), scale_log2, my_nlse2));
-            if (need_mask) {
-              p0 = (colw + e < key_limit) ? p0 : 0.f;
-              p1 = (colw + e + 1 < key_limit) ? p1 : 0.f;
-            }
+            pp[e >> 1] = pack2<VT>(p0, p1);
           }
-          pp[e >> 1] = pack2<VT>(p0, p1);
+          tc_st16(t_s + 32 * h, *reinterpret_cast<uint32_t(*)[16]>(&pp[0]));
+          tc_st16(t_s + 32 * h + 16, *reinterpret_cast<uint32_t(*)[16]>(&pp[16]));
         }
-      }
-      if (DKV) {
-        if (half == 1) {
-          named_sync(1 + cw, 64);
-          tc_fence_after();
-        }
-        // chunk c of P lands on columns [16 c, 16 c + 16) of S
-        tc_st16(t_s + 16 * c0, *reinterpret_cast<uint32_t(*)[16]>(&pp[0]));
-        tc_st16(t_s + 16 * c0 + 16, *reinterpret_cast<uint32_t(*)[16]>(&pp[16]));
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[P_FULL]);
-      }
-      // ---- phase 2: dS = P (dP - D_m) ----
-      ok = mbar_wait(&bars[DP_FULL], i & 1, a.status);
-      if (!ok) break;
-      tc_fence_after();
-      {
-        uint32_t dp[64], ds[32];
-        tc_ld32(t_row + C::COL_DP + 32 * c0, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
-        tc_ld32(t_row + C::COL_DP + 32 * c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
+        if (warp == 0 && lane == 0 && i < 250) BTR(8 * i + 2);
+      } else {
+        // ======== dS warp ========
+        ok = mbar_wait(&bars[P_FULL], i & 1, a.status);
+        if (!ok) break;
+        tc_fence_after();
+        if (warp == 4 && lane == 0 && i < 250) BTR(2048 + 8 * i + 1);
+        uint32_t pp[64];
+        tc_ld32(t_s, *reinterpret_cast<uint32_t(*)[32]>(&pp[0]));
+        tc_ld32(t_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&pp[32]));
         tc_wait_ld();
-        tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
-        tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
-        if (half == 0) {
+        tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&pp[0]));
+        tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&pp[32]));
+        if (DKV) {
+          // P is in registers: the issuer may let the next tile's S overwrite it
           tc_fence_before();
-          named_arrive(5 + cw, 64);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars[P_READ]);
         }
+        ok = mbar_wait(&bars[DP_FULL], i & 1, a.status);
+        if (!ok) break;
+        tc_fence_after();
+        if (warp == 4 && lane == 0 && i < 250) BTR(2048 + 8 * i + 2);
 #pragma unroll
-        for (int e = 0; e < 64; e += 2) {
-          const float2 p = unpack2<VT>(pp[e >> 1]);
-          float dl0 = my_delta, dl1 = my_delta;
-          if (DKV) {
-            const float4 d4 = rd_d[e >> 2];
-            dl0 = (e & 2) ? d4.z : d4.x;
-            dl1 = (e & 2) ? d4.w : d4.y;
+        for (int h = 0; h < 2; ++h) {
+          uint32_t dp[64], ds[32];
+          tc_ld32(t_row + C::COL_DP + 64 * h, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
+          tc_ld32(t_row + C::COL_DP + 64 * h + 32, *reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
+          tc_wait_ld();
+          tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
+          tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
+#pragma unroll
+          for (int e = 0; e < 64; e += 2) {
+            const float2 p = unpack2<VT>(pp[32 * h + (e >> 1)]);
+            // (dK/dV pass: dP already carries -D_m of its query)
+            const float dl = DKV ? 0.f : my_delta;
+            ds[e >> 1] = pack2<VT>(p.x * (__uint_as_float(dp[e]) - dl), p.y * (__uint_as_float(dp[e + 1]) - dl));
           }
-          ds[e >> 1] = pack2<VT>(p.x * (__uint_as_float(dp[e]) - dl0), p.y * (__uint_as_float(dp[e + 1]) - dl1));
+          tc_st16(t_row + C::COL_DP + 32 * h, *reinterpret_cast<uint32_t(*)[16]>(&ds[0]));
+          tc_st16(t_row + C::COL_DP + 32 * h + 16, *reinterpret_cast<uint32_t(*)[16]>(&ds[16]));
         }
-        if (half == 1) {
-          named_sync(5 + cw, 64);
-          tc_fence_after();
-        }
-        tc_st16(t_row + C::COL_DP + 16 * c0, *reinterpret_cast<uint32_t(*)[16]>(&ds[0]));
-        tc_st16(t_row + C::COL_DP + 16 * c0 + 16, *reinterpret_cast<uint32_t(*)[16]>(&ds[16]));
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[DS_FULL]);
+        if (warp == 4 && lane == 0 && i < 250) BTR(2048 + 8 * i + 3);
       }
-      tc_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[DS_FULL]);
     }
     // ---- epilogue: accumulators -> 16-bit rows ----
     if (ok && total > 0) ok = mbar_wait(&bars[ACC_DONE], 0, a.status);
@@ -469,7 +540,6 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
 
 template <int D, typename VT>
 int launch_bwd_tc(const sl8_bwd_params* p, float* delta, int* status, cudaStream_t stream) {
-  using C = BtCfg<D>;
   CUtensorMap q_map, k_map, v_map, do_map;
   const uint64_t hq = (uint64_t)p->B * p->Hq, hkv = (uint64_t)p->B * p->Hkv;
   int rc = sl8_make_tmap_3d(&q_map, p->q, 2, D, p->M, hq, 64, kBT, 128);
@@ -480,21 +550,28 @@ int launch_bwd_tc(const sl8_bwd_params* p, float* delta, int* status, cudaStream
   BtArgs a{};
   a.lse = p->lse; a.delta = delta; a.status = status;
   a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N; a.causal = p->causal; a.scale = p->softmax_scale;
-  SL8_CUDA_TRY(cudaFuncSetAttribute(bwd_tc_kernel<D, VT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-  SL8_CUDA_TRY(cudaFuncSetAttribute(bwd_tc_kernel<D, VT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+  constexpr int smem_dkv = BtCfg<D, true>::SMEM, smem_dq = BtCfg<D, false>::SMEM;
+  SL8_CUDA_TRY(cudaFuncSetAttribute(bwd_tc_kernel<D, VT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dkv));
+  SL8_CUDA_TRY(cudaFuncSetAttribute(bwd_tc_kernel<D, VT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dq));
   // dQ pass: rows = queries (A1 = Q, A2 = dO), columns = keys (B1 = K, B2 = V)
   a.out1 = p->dq; a.out2 = nullptr;
-  bwd_tc_kernel<D, VT, false><<<dim3((p->M + kBT - 1) / kBT, (unsigned)hq), kBtThreads, C::SMEM, stream>>>(
+  bwd_tc_kernel<D, VT, false><<<dim3((p->M + kBT - 1) / kBT, (unsigned)hq), kBtThreads, smem_dq, stream>>>(
       q_map, do_map, k_map, v_map, a);
   // dK/dV pass: rows = keys (A1 = K, A2 = V), columns = queries (B1 = Q, B2 = dO)
   a.out1 = p->dv; a.out2 = p->dk;
-  bwd_tc_kernel<D, VT, true><<<dim3((unsigned)hkv, (p->N + kBT - 1) / kBT), kBtThreads, C::SMEM, stream>>>(
+  bwd_tc_kernel<D, VT, true><<<dim3((unsigned)hkv, (p->N + kBT - 1) / kBT), kBtThreads, smem_dkv, stream>>>(
       k_map, v_map, q_map, do_map, a);
   return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
 }
 
 }  // namespace
 }  // namespace sl8
+
+#ifdef SL8_TRACE
+extern "C" int sl8_dbg_read_trace_bwd(long long* host_out, int n) {
+  return (int)cudaMemcpyFromSymbol(host_out, sl8::g_trace, sizeof(long long) * n);
+}
+#endif
 
 // The two tensor-memory passes of the backward (D = 64 or 128); parameters were validated and
 // D_m written to `delta` by sl8_attn_bwd (bwd.cu).

@@ -113,32 +113,7 @@ enum Bar {
   V_FULL = K_FULL + 2, KS_EMPTY = V_FULL + 2, NUM_BARS = KS_EMPTY + kScaleStages
 };
 
-#ifdef SL8_TRACE
-// Clock-stamp trace of up to eight blocks (build-time option, never in the shipped library):
-// the blocks whose linear index is SL8_TRACE_BASE + k * SL8_TRACE_STRIDE, k = 0..7.
-constexpr int kTraceBlocks = 8, kTraceSlots = 8192;
-__device__ long long g_trace[kTraceBlocks * kTraceSlots];
-#ifndef SL8_TRACE_BASE
-#define SL8_TRACE_BASE 0
-#endif
-#ifndef SL8_TRACE_STRIDE
-#define SL8_TRACE_STRIDE 1
-#endif
-__device__ __forceinline__ uint32_t sl8_smid() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%smid;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ int trace_block() {
-  const int lin = blockIdx.y * gridDim.x + blockIdx.x - SL8_TRACE_BASE;
-  return (lin >= 0 && lin % SL8_TRACE_STRIDE == 0 && lin / SL8_TRACE_STRIDE < kTraceBlocks) ? lin / SL8_TRACE_STRIDE : -1;
-}
-#define TR(slot) do { const int tb_ = trace_block(); if (tb_ >= 0) g_trace[tb_ * kTraceSlots + (slot)] = clock64(); } while (0)
-#define TRV(slot, val) do { const int tb_ = trace_block(); if (tb_ >= 0) g_trace[tb_ * kTraceSlots + (slot)] = (val); } while (0)
-#else
-#define TR(slot) do {} while (0)
-#define TRV(slot, val) do {} while (0)
-#endif
+SL8_TRACE_DEFINE()
 
 template <int D, typename VT, bool QK8, bool PACKED>
 __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map,

@@ -348,6 +348,36 @@ __host__ __device__ __forceinline__ uint32_t umma_idesc(uint32_t c_fmt, uint32_t
          ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 
+// ---- clock-stamp trace (build-time option -DSL8_TRACE, never in the shipped library) --------
+// A translation unit that wants stamps puts SL8_TRACE_DEFINE() inside its anonymous namespace;
+// the blocks whose linear index is SL8_TRACE_BASE + k * SL8_TRACE_STRIDE, k = 0..7, then record
+// clock64() (TR) or a value (TRV) into their 8192 slots.
+#ifdef SL8_TRACE
+constexpr int kTraceBlocks = 8, kTraceSlots = 8192;
+#ifndef SL8_TRACE_BASE
+#define SL8_TRACE_BASE 0
+#endif
+#ifndef SL8_TRACE_STRIDE
+#define SL8_TRACE_STRIDE 1
+#endif
+__device__ __forceinline__ uint32_t sl8_smid() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ int trace_block() {
+  const int lin = blockIdx.y * gridDim.x + blockIdx.x - SL8_TRACE_BASE;
+  return (lin >= 0 && lin % SL8_TRACE_STRIDE == 0 && lin / SL8_TRACE_STRIDE < kTraceBlocks) ? lin / SL8_TRACE_STRIDE : -1;
+}
+#define SL8_TRACE_DEFINE() __device__ long long g_trace[kTraceBlocks * kTraceSlots];
+#define TR(slot) do { const int tb_ = trace_block(); if (tb_ >= 0) g_trace[tb_ * kTraceSlots + (slot)] = clock64(); } while (0)
+#define TRV(slot, val) do { const int tb_ = trace_block(); if (tb_ >= 0) g_trace[tb_ * kTraceSlots + (slot)] = (val); } while (0)
+#else
+#define SL8_TRACE_DEFINE()
+#define TR(slot) do {} while (0)
+#define TRV(slot, val) do {} while (0)
+#endif
+
 }  // namespace sl8
 
 // Host side: builds a 3-D tiled tensor map {inner, rows, heads} over a
