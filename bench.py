@@ -516,9 +516,10 @@ def main():
                             "roofline": {"bound": "tensor", "achieved": tb / world, "peak": peaks["bf16_tflops"],
                                          "unit": "TFLOP/s", "frac": tb / world / peaks["bf16_tflops"],
                                          "peak_source": peaks["source"] + " bf16 dense (burst)",
-                                         # ncu on this shape: dQ pass 215.0 MB + dK/dV pass 194.4 MB
-                                         "traffic": 409.4e6,
-                                         "kernels": "bwd_dq_kernel + bwd_dkv_kernel (mma.sync m16n8k16)"}}
+                                         # ncu on this shape: dQ pass 213.6 MB + dK/dV pass 328.2 MB
+                                         "traffic": 541.8e6,
+                                         "kernels": "bwd_tc_kernel dQ pass + dK/dV pass (tcgen05.mma kind::f16, TMA tiles, "
+                                                    "accumulators in tensor memory)"}}
         del bq, bk, bv, bdo, bout, blse
 
     if rank == 0 and world == 1:

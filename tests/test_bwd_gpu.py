@@ -74,6 +74,35 @@ def test_backward_matches_oracle(device, shape, causal):
     assert torch.equal(dq1, dq2) and torch.equal(dk1, dk2) and torch.equal(dv1, dv2)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_backward_with_large_logits(device, dtype):
+    """Peaked attention rows (logits of a few tens, lse far from 0) and a row-sum gradient
+    with a large mean: the tensor-memory passes carry -lse / scale and -D_m of a query as a
+    {hi, lo} 16-bit pair on an extra step of the S and dP contractions, which has to stay exact
+    enough for both dtypes."""
+    gen = torch.Generator().manual_seed(4242)
+    B, Hq, Hkv, M, N, D = 1, 4, 2, 384, 384, 128
+    q = (3.0 * torch.randn(B, Hq, M, D, generator=gen)).to(dtype)
+    k = (3.0 * torch.randn(B, Hkv, N, D, generator=gen)).to(dtype)
+    v = (torch.randn(B, Hkv, N, D, generator=gen) + 2.0).to(dtype)
+    do = (torch.randn(B, Hq, M, D, generator=gen) + 1.0).to(dtype)
+    for causal in (False, True):
+        out, lse = _C.attn_fp16_fwd(q.to(device), k.to(device), v.to(device), causal, None, want_lse=True)
+        assert float(lse.abs().max()) > 20.0
+        ref = oracle.attention_backward_fp32(q, k, v, out, do, causal)
+        got_tc = s8.backward_cuda(q.to(device), k.to(device), v.to(device), out, lse, do.to(device), causal=causal, backend=TC)
+        got_mma = s8.backward_cuda(q.to(device), k.to(device), v.to(device), out, lse, do.to(device), causal=causal, backend=MMA)
+        assert _C.device_status() == 0
+        for a, b, r, key in zip(got_tc, got_mma, ref, ("dq", "dk", "dv")):
+            assert torch.isfinite(a.float()).all()
+            if dtype == torch.float16:
+                _check(a, r, ("large logits", causal, key))
+            else:
+                assert oracle.cos_sim(a, r) >= 0.999 and oracle.rel_l1(a, r) <= 0.03, (causal, key)
+            # and no further from the oracle than the warp-level kernels are
+            assert oracle.rel_l1(a, r) <= 1.5 * oracle.rel_l1(b, r) + 1e-4, (causal, key, oracle.rel_l1(a, r), oracle.rel_l1(b, r))
+
+
 def test_backward_is_deterministic_and_bf16(device):
     # reference tests/test_attn_bwd_cuda.py:88-96: atomic-free -> bitwise reproducible
     gen = torch.Generator().manual_seed(77)
