@@ -96,7 +96,9 @@ template <int D, typename VT, bool DKV>
 __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_constant__ CUtensorMap a1_map,
                                                               const __grid_constant__ CUtensorMap a2_map,
                                                               const __grid_constant__ CUtensorMap b1_map,
-                                                              const __grid_constant__ CUtensorMap b2_map, BtArgs a) {
+                                                              const __grid_constant__ CUtensorMap b2_map,
+                                                              const __grid_constant__ CUtensorMap o1_map,
+                                                              const __grid_constant__ CUtensorMap o2_map, BtArgs a) {
   using C = BtCfg<D, DKV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -501,19 +503,23 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
         const float f = (DKV && which == 0) ? 1.f : a.scale;     // dV unscaled; dK, dQ times the softmax scale
         VT* dst_row = which == 0 ? o1 : o2;
         const uint32_t t_acc = t_row + (which == 0 ? C::COL_ACC1 : C::COL_ACC2);
+        if (D == 128) {
+          // This warp's 32 rows x 64 channels are staged in shared memory (the B2 ring is free:
+          // every MMA has completed) in the 128-byte-swizzled layout of the output tensor map --
+          // 16-byte chunk j of row r at chunk j ^ (r & 7) -- and leave as one tile store; rows past
+          // the end of the tensor are dropped by the copy engine.
+          uint8_t* const box = smem + C::OFF_B2 + which * C::TILE_BYTES + half * C::SUB_BYTES + cw * (32 * 128);
 #pragma unroll 1
-        for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {   // this warp's half of the channels
-          uint32_t o[32];
-          if (total > 0) {
-            tc_ld32(t_acc + 32 * c, o);
-            tc_wait_ld();
-            tc_regs_ready(o);
-          } else {
+          for (int c = 2 * half; c < 2 * half + 2; ++c) {
+            uint32_t o[32];
+            if (total > 0) {
+              tc_ld32(t_acc + 32 * c, o);
+              tc_wait_ld();
+              tc_regs_ready(o);
+            } else {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) o[e] = 0u;
-          }
-          if (grow < rows_total) {
-            uint4* dst = reinterpret_cast<uint4*>(dst_row + 32 * c);
+              for (int e = 0; e < 32; ++e) o[e] = 0u;
+            }
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               uint4 w;
@@ -521,11 +527,43 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
               w.y = pack2<VT>(__uint_as_float(o[8 * v + 2]) * f, __uint_as_float(o[8 * v + 3]) * f);
               w.z = pack2<VT>(__uint_as_float(o[8 * v + 4]) * f, __uint_as_float(o[8 * v + 5]) * f);
               w.w = pack2<VT>(__uint_as_float(o[8 * v + 6]) * f, __uint_as_float(o[8 * v + 7]) * f);
-              dst[v] = w;
+              *reinterpret_cast<uint4*>(box + lane * 128 + ((((c & 1) * 4 + v) ^ (lane & 7)) << 4)) = w;
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && row_block + 32 * cw < rows_total) {
+            tma_store_3d(which == 0 ? &o1_map : &o2_map, box, 64 * half, row_block + 32 * cw, fixed_bh);
+            tma_store_commit();
+          }
+        } else {
+#pragma unroll 1
+          for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {   // this warp's half of the channels
+            uint32_t o[32];
+            if (total > 0) {
+              tc_ld32(t_acc + 32 * c, o);
+              tc_wait_ld();
+              tc_regs_ready(o);
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) o[e] = 0u;
+            }
+            if (grow < rows_total) {
+              uint4* dst = reinterpret_cast<uint4*>(dst_row + 32 * c);
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint4 w;
+                w.x = pack2<VT>(__uint_as_float(o[8 * v + 0]) * f, __uint_as_float(o[8 * v + 1]) * f);
+                w.y = pack2<VT>(__uint_as_float(o[8 * v + 2]) * f, __uint_as_float(o[8 * v + 3]) * f);
+                w.z = pack2<VT>(__uint_as_float(o[8 * v + 4]) * f, __uint_as_float(o[8 * v + 5]) * f);
+                w.w = pack2<VT>(__uint_as_float(o[8 * v + 6]) * f, __uint_as_float(o[8 * v + 7]) * f);
+                dst[v] = w;
+              }
             }
           }
         }
       }
+      if (D == 128 && lane == 0) tma_store_wait_read();   // the engine has read this warp's staged tiles
     }
     tc_fence_before();
   }
@@ -546,6 +584,11 @@ int launch_bwd_tc(const sl8_bwd_params* p, float* delta, int* status, cudaStream
   if (rc == SL8_OK) rc = sl8_make_tmap_3d(&do_map, p->dout, 2, D, p->M, hq, 64, kBT, 128);
   if (rc == SL8_OK) rc = sl8_make_tmap_3d(&k_map, p->k, 2, D, p->N, hkv, 64, kBT, 128);
   if (rc == SL8_OK) rc = sl8_make_tmap_3d(&v_map, p->v, 2, D, p->N, hkv, 64, kBT, 128);
+  // gradient tiles leave through the copy engine: 32 rows (one compute warp) x 64 channels per store
+  CUtensorMap dq_map, dk_map, dv_map;
+  if (rc == SL8_OK) rc = sl8_make_tmap_3d(&dq_map, p->dq, 2, D, p->M, hq, 64, 32, 128);
+  if (rc == SL8_OK) rc = sl8_make_tmap_3d(&dk_map, p->dk, 2, D, p->N, hkv, 64, 32, 128);
+  if (rc == SL8_OK) rc = sl8_make_tmap_3d(&dv_map, p->dv, 2, D, p->N, hkv, 64, 32, 128);
   if (rc != SL8_OK) return rc;
   BtArgs a{};
   a.lse = p->lse; a.delta = delta; a.status = status;
@@ -556,11 +599,11 @@ int launch_bwd_tc(const sl8_bwd_params* p, float* delta, int* status, cudaStream
   // dQ pass: rows = queries (A1 = Q, A2 = dO), columns = keys (B1 = K, B2 = V)
   a.out1 = p->dq; a.out2 = nullptr;
   bwd_tc_kernel<D, VT, false><<<dim3((p->M + kBT - 1) / kBT, (unsigned)hq), kBtThreads, smem_dq, stream>>>(
-      q_map, do_map, k_map, v_map, a);
+      q_map, do_map, k_map, v_map, dq_map, dq_map, a);
   // dK/dV pass: rows = keys (A1 = K, A2 = V), columns = queries (B1 = Q, B2 = dO)
   a.out1 = p->dv; a.out2 = p->dk;
   bwd_tc_kernel<D, VT, true><<<dim3((unsigned)hkv, (p->N + kBT - 1) / kBT), kBtThreads, smem_dkv, stream>>>(
-      k_map, v_map, q_map, do_map, a);
+      k_map, v_map, q_map, do_map, dv_map, dk_map, a);
   return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
 }
 
