@@ -19,12 +19,13 @@
 // (The dQ pass has one accumulator and keeps a second S buffer at [384,512).)
 // Ten warps: 0-7 compute (thread = row = tensor-memory lane; warps w and w + 4 share a row group:
 // w forms P from S, w + 4 forms dS from P and dP), 8 = TMA producer (the fixed row tiles once, then
-// column tiles through two stages, plus the per-query lse / D_m of a column tile in the dK/dV
-// pass), 9 = tensor-memory allocation and MMA issue.  Per column tile the issuer queues S and
+// the column tiles through two rings of stages, plus -- dK/dV pass -- the per-query lse / D_m of
+// a column tile, which ride on one extra K step of the S and dP MMAs as {hi, lo} 16-bit pairs),
+// 9 = tensor-memory allocation and MMA issue.  Per column tile the issuer queues S and
 // dP, the compute warps turn S into P and then dP into dS, the issuer queues the accumulating
 // MMAs behind them (and the next tile's S and dP between them) and frees the stage.
-// Rows and columns past the end of a tensor arrive as zeros (TMA fill) and carry lse = +inf,
-// so P = dS = 0 there; the causal mask is the forward's bottom-right one (key n visible to
+// Rows and columns past the end of a tensor arrive as zeros (TMA fill) and carry a statistic
+// that makes P = dS = 0 there; the causal mask is the forward's bottom-right one (key n visible to
 // query m iff n <= m + N - M), evaluated per element only on tiles that straddle the diagonal.
 // Every mbarrier wait is bounded; on expiry the status word is raised and the block exits.
 #include "sl8_common.cuh"
