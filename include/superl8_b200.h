@@ -127,6 +127,14 @@ typedef struct sl8_fwd_params {
   int32_t causal;         /* bottom-right aligned: query i sees keys <= i + N - M */
   int32_t window_left;    /* < 0: none; else keys in (pos - window_left, pos] */
   int32_t backend;        /* SL8_BACKEND_* */
+  /* Device-side dispatch (nullable; tcgen05 backend only; no counterpart in the reference, which reads
+   * its gate back to the host, superl8/quant/core.py:145): when gate_flag is non-NULL the kernel
+   * runs only if (*gate_flag != 0) == (gate_want != 0) and otherwise exits at once, leaving `out`
+   * untouched.  Launching this op with gate_want = 0 and sl8_attn_fp16_fwd with gate_want = 1 on
+   * the same `out`, behind the pass that raises the flag (sl8_quant_q_prologue), applies the
+   * accuracy gate without a host read-back, so the whole call can be captured in a CUDA graph. */
+  const int32_t* gate_flag;
+  int32_t gate_want;
 } sl8_fwd_params;
 
 /*
@@ -171,6 +179,8 @@ typedef struct sl8_fp16_fwd_params {
    * (reference csrc/kernel/attn_fp16_fwd.cu:146-168) */
   const void* mask;
   int64_t mask_stride_b, mask_stride_h, mask_stride_m, mask_stride_n;
+  const int32_t* gate_flag;   /* device-side dispatch, as in sl8_fwd_params (nullable; tcgen05 backend, no mask) */
+  int32_t gate_want;
 } sl8_fp16_fwd_params;
 size_t sl8_attn_fp16_fwd_workspace(const sl8_fp16_fwd_params* p);
 int sl8_attn_fp16_fwd(const sl8_fp16_fwd_params* p, void* workspace, size_t workspace_bytes,

@@ -95,13 +95,25 @@ def _fwd_checks(q, q_scale, k, k_scale, v, what):
     return B, H, Hkv, M, N, D
 
 
+def _gate_args(gate_flag, gate_want, device, what):
+    if gate_flag is None:
+        return dict(gate_flag=None, gate_want=0)
+    _check(gate_flag.is_cuda and gate_flag.device == device and gate_flag.dtype == torch.int32 and gate_flag.numel() >= 1,
+           f"{what}: gate_flag must be an int32 CUDA tensor on the inputs' device")
+    return dict(gate_flag=gate_flag.data_ptr(), gate_want=int(bool(gate_want)))
+
+
 def _run_fwd(q, q_scale, k, k_scale, v, causal, want_lse, window_left, seqlens_q=None, seqlens_k=None,
-             backend=_lib.SL8_BACKEND_AUTO):
+             backend=_lib.SL8_BACKEND_AUTO, out=None, gate_flag=None, gate_want=False):
     what = "superl8_b200"
     B, H, Hkv, M, N, D = _fwd_checks(q, q_scale, k, k_scale, v, what)
     _check(v.dtype in (torch.float16, torch.bfloat16), f"{what}: v must be float16 or bfloat16")
     _check(D in (32, 64, 72, 80, 128, 256), f"{what}: head dim must be 32/64/72/80/128/256, got {D}")
-    out = torch.empty((B, H, M, D), dtype=v.dtype, device=v.device)
+    if out is None:
+        out = torch.empty((B, H, M, D), dtype=v.dtype, device=v.device)
+    else:
+        _check(out.shape == (B, H, M, D) and out.dtype == v.dtype and out.device == v.device and out.is_contiguous(),
+               f"{what}: out must be a contiguous [B,H,M,D] tensor of v's dtype on v's device")
     lse = torch.empty((B, H, M) if want_lse else (0,), dtype=torch.float32, device=q.device)
     if M == 0 or B == 0 or H == 0:
         return out, lse
@@ -115,7 +127,7 @@ def _run_fwd(q, q_scale, k, k_scale, v, causal, want_lse, window_left, seqlens_q
         seqlens_q=None if seqlens_q is None else seqlens_q.data_ptr(),
         seqlens_k=None if seqlens_k is None else seqlens_k.data_ptr(),
         B=B, Hq=H, Hkv=Hkv, M=M, N=N, D=D, v_dtype=_DTYPE[v.dtype], causal=int(bool(causal)),
-        window_left=int(window_left), backend=int(backend))
+        window_left=int(window_left), backend=int(backend), **_gate_args(gate_flag, gate_want, q.device, what))
     with torch.cuda.device(q.device):
         ws = _status_buffer(q.device)
         rc = _lib.load().sl8_attn_int8_fwd(C.byref(p), _ptr(ws), ws.numel() * 4, _stream(q.device))
@@ -124,9 +136,12 @@ def _run_fwd(q, q_scale, k, k_scale, v, causal, want_lse, window_left, seqlens_q
 
 
 def attn_int8_fwd(q, q_scale, k, k_scale, v, causal=False, window_left=-1, *, seqlens_q=None, seqlens_k=None,
-                  backend=_lib.SL8_BACKEND_AUTO):
-    """Reference binding csrc/fni8_api.cpp:225-229 (op csrc/kernel/attn_int8_fwd.cu:185-190)."""
-    return _run_fwd(q, q_scale, k, k_scale, v, causal, False, window_left, seqlens_q, seqlens_k, backend)[0]
+                  backend=_lib.SL8_BACKEND_AUTO, out=None, gate_flag=None, gate_want=False):
+    """Reference binding csrc/fni8_api.cpp:225-229 (op csrc/kernel/attn_int8_fwd.cu:185-190).
+    ``out`` (optional) receives the result; ``gate_flag`` (int32 CUDA tensor, optional) makes the
+    launch conditional on the device: the kernel works only if (flag != 0) == gate_want."""
+    return _run_fwd(q, q_scale, k, k_scale, v, causal, False, window_left, seqlens_q, seqlens_k, backend,
+                    out, gate_flag, gate_want)[0]
 
 
 def attn_int8_fwd_train(q, q_scale, k, k_scale, v, causal=False, *, backend=_lib.SL8_BACKEND_AUTO):
@@ -173,9 +188,10 @@ def tensor_peak(kind_i8: bool, iters: int = 4096, device=None, n_cols: int = 256
 
 
 def attn_fp16_fwd(q, k, v, causal=False, scale=None, window_left=-1, mask=None, *, seqlens_q=None, seqlens_k=None,
-                  backend=_lib.SL8_BACKEND_AUTO, want_lse=False):
+                  backend=_lib.SL8_BACKEND_AUTO, want_lse=False, out=None, gate_flag=None, gate_want=False):
     """Full-precision forward.  Reference binding csrc/fni8_api.cpp:234-244.  ``want_lse``: also
-    return the natural-log row sums [B, H, M] (what the backward consumes)."""
+    return the natural-log row sums [B, H, M] (what the backward consumes).  ``out`` / ``gate_flag`` /
+    ``gate_want``: as in attn_int8_fwd (conditional launch decided on the device)."""
     what = "superl8_b200 fp16 fwd"
     _check_cuda(q, k, v)
     _check(q.dtype in (torch.float16, torch.bfloat16), f"{what}: q must be float16 or bfloat16")
@@ -199,7 +215,11 @@ def attn_fp16_fwd(q, k, v, causal=False, scale=None, window_left=-1, mask=None, 
     _check(Hkv > 0 and H % Hkv == 0, f"{what}: H_q must be divisible by H_kv (GQA)")
     _check(k.shape[3] == D and v.shape[3] == D and v.shape[2] == N, f"{what}: K/V shape mismatch")
     _check(D in (32, 64, 72, 80, 128, 256), f"{what}: head dim must be 32/64/72/80/128/256, got {D}")
-    out = torch.empty((B, H, M, D), dtype=v.dtype, device=v.device)
+    if out is None:
+        out = torch.empty((B, H, M, D), dtype=v.dtype, device=v.device)
+    else:
+        _check(out.shape == (B, H, M, D) and out.dtype == v.dtype and out.device == v.device and out.is_contiguous(),
+               f"{what}: out must be a contiguous [B,H,M,D] tensor of v's dtype on v's device")
     lse = torch.empty((B, H, M), dtype=torch.float32, device=v.device) if want_lse else None
     if out.numel() == 0:
         return (out, lse) if want_lse else out
@@ -209,7 +229,8 @@ def attn_fp16_fwd(q, k, v, causal=False, scale=None, window_left=-1, mask=None, 
         seqlens_q=None if seqlens_q is None else seqlens_q.data_ptr(),
         seqlens_k=None if seqlens_k is None else seqlens_k.data_ptr(),
         B=B, Hq=H, Hkv=Hkv, M=M, N=N, D=D, dtype=_DTYPE[q.dtype], causal=int(bool(causal)),
-        window_left=int(window_left), softmax_scale=sc, backend=int(backend), **mk)
+        window_left=int(window_left), softmax_scale=sc, backend=int(backend), **mk,
+        **_gate_args(gate_flag, gate_want, q.device, what))
     with torch.cuda.device(q.device):
         ws = _status_buffer(q.device)
         rc = _lib.load().sl8_attn_fp16_fwd(C.byref(p), _ptr(ws), ws.numel() * 4, _stream(q.device))

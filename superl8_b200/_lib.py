@@ -43,7 +43,7 @@ class FwdParams(C.Structure):
         ("seqlens_q", C.c_void_p), ("seqlens_k", C.c_void_p),
         ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("M", C.c_int32), ("N", C.c_int32),
         ("D", C.c_int32), ("v_dtype", C.c_int32), ("causal", C.c_int32), ("window_left", C.c_int32),
-        ("backend", C.c_int32),
+        ("backend", C.c_int32), ("gate_flag", C.c_void_p), ("gate_want", C.c_int32),
     ]
 
 
@@ -56,6 +56,7 @@ class Fp16FwdParams(C.Structure):
         ("softmax_scale", C.c_float), ("backend", C.c_int32),
         ("mask", C.c_void_p), ("mask_stride_b", C.c_int64), ("mask_stride_h", C.c_int64),
         ("mask_stride_m", C.c_int64), ("mask_stride_n", C.c_int64),
+        ("gate_flag", C.c_void_p), ("gate_want", C.c_int32),
     ]
 
 

@@ -388,6 +388,7 @@ extern "C" int sl8_attn_fp16_fwd(const sl8_fp16_fwd_params* p, void* workspace, 
     return sl8_fwd_tc_fp16(p, reinterpret_cast<int*>(workspace), static_cast<cudaStream_t>(stream));
   }
   if (backend != SL8_BACKEND_MMA) return SL8_ERR_UNSUPPORTED;
+  if (p->gate_flag != nullptr) return SL8_ERR_UNSUPPORTED;   // device-side dispatch: tensor-memory kernel only
   FwdArgs a{};
   a.q = p->q; a.k = p->k; a.v = p->v; a.out = p->out; a.lse = p->lse;
   a.seqlens_q = p->seqlens_q; a.seqlens_k = p->seqlens_k;

@@ -100,6 +100,9 @@ struct TcArgs {
   const int32_t* cu_q;
   const int32_t* cu_k;
   int* status;
+  // Device-side dispatch: when non-null the kernel runs only if (*gate_flag != 0) == (gate_want != 0).
+  const int32_t* gate_flag;
+  int gate_want;
   int Hq, Hkv, M, N;
   int causal, window_left;
   float scale_log2;  // 16-bit Q/K mode: softmax_scale * log2(e)
@@ -121,6 +124,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
                                                                const __grid_constant__ CUtensorMap v_map,
                                                                const __grid_constant__ CUtensorMap o_map, TcArgs a) {
   using C = TcCfg<D, QK8>;
+  // the accuracy gate decided on the device: the kernel of the other precision does the work
+  if (a.gate_flag != nullptr && ((__ldg(a.gate_flag) != 0) != (a.gate_want != 0))) return;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* ks_smem = reinterpret_cast<float*>(smem + C::OFF_KS);
@@ -654,12 +659,14 @@ extern "C" int sl8_attn_int8_fwd(const sl8_fwd_params* p, void* workspace, size_
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int backend = p->backend;
   if (backend == SL8_BACKEND_AUTO) backend = (tc_head_dim(p->D) && p->N > 0) ? SL8_BACKEND_TCGEN05 : SL8_BACKEND_MMA;
+  if (p->gate_flag != nullptr && backend != SL8_BACKEND_TCGEN05) return SL8_ERR_UNSUPPORTED;
   if (backend == SL8_BACKEND_MMA) return sl8_fwd_mma_int8(p, s);
   if (backend != SL8_BACKEND_TCGEN05) return SL8_ERR_UNSUPPORTED;
   if (!tc_head_dim(p->D) || p->N == 0) return SL8_ERR_UNSUPPORTED;
   TcArgs a{};
   a.q_scale = p->q_scale; a.k_scale = p->k_scale; a.out = p->out; a.lse = p->lse;
   a.seqlens_q = p->seqlens_q; a.seqlens_k = p->seqlens_k; a.status = reinterpret_cast<int*>(workspace);
+  a.gate_flag = p->gate_flag; a.gate_want = p->gate_want;
   a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N; a.causal = p->causal; a.window_left = p->window_left;
   return p->v_dtype == SL8_F16
              ? launch_tc_d<__half, true>(p->D, p->q, p->k, p->v, p->B, p->Hq, p->Hkv, p->M, p->N, a, s)
@@ -703,6 +710,7 @@ int sl8_fwd_tc_fp16(const sl8_fp16_fwd_params* p, int* status, cudaStream_t s) {
   if (!tc_head_dim(p->D) || p->N == 0) return SL8_ERR_UNSUPPORTED;
   TcArgs a{};
   a.out = p->out; a.lse = p->lse; a.seqlens_q = p->seqlens_q; a.seqlens_k = p->seqlens_k; a.status = status;
+  a.gate_flag = p->gate_flag; a.gate_want = p->gate_want;
   a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N; a.causal = p->causal; a.window_left = p->window_left;
   a.scale_log2 = p->softmax_scale * 1.4426950408889634f;
   return p->dtype == SL8_F16

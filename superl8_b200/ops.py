@@ -11,6 +11,7 @@ from .quant import (_capturing, k_mean, q_outlier_flag, quantize_q, quantize_qk,
                     varlen_smooth_quantize_k)
 
 last_gate_decision: bool | None = None  # whether the most recent attn_int8_fwd call was demoted
+last_gate_flag: torch.Tensor | None = None  # device flag of the most recent device-side gate (int32 [1])
 
 
 def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, int8_pv: bool = False,
@@ -28,10 +29,17 @@ def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, 
     evaluated inside the Q quantisation pass (or, right after a demoted call, by a read-only
     pass before any quantisation) and costs one 4-byte device->host read, skipped during
     CUDA-graph capture like the reference's.
+    ``internal_accuracy_gate="device"`` (not in the reference) keeps the decision on the GPU: the
+    int8 kernel and the full-precision kernel are both launched on the same output and each
+    reads the flag the Q pass raised, the one whose turn it is not exits at once.  No host
+    read-back, so nothing stalls the stream and the gated call can be captured in a CUDA graph
+    (the reference skips its gate under capture); ``last_gate_flag`` then holds the device flag
+    and ``last_gate_decision`` is None.  Head dims 64/128/256 with one dtype for q, k, v; other
+    cases take the host-side gate.
     ``seqlens_q`` / ``seqlens_k`` (int32 [B], not in the reference) give per-sequence
     lengths for padded ragged batches.
     """
-    global last_gate_decision
+    global last_gate_decision, last_gate_flag
     s = (1.0 / math.sqrt(q.shape[-1])) if scale is None else scale
     if int8_pv:
         # reference superl8/ops.py:152-166: no gate on this branch, no window, V per channel
@@ -47,6 +55,19 @@ def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, 
         return _C.attn_w8a8_fwd(q_i8, q_scale.squeeze(-1).contiguous(), k_i8, k_scale.squeeze(-1).contiguous(), v_i8,
                                 v_scale.squeeze(-2).contiguous(), causal,
                                 causal_diag=(k.shape[-2] - q.shape[-2]) if causal else 0, per_warp_quant=per_warp_quant)
+    if (internal_accuracy_gate == "device" and not rotate and q.shape[-1] in (64, 128, 256) and k.shape[-2] > 0
+            and q.dtype == k.dtype == v.dtype and backend in (_lib.SL8_BACKEND_AUTO, _lib.SL8_BACKEND_TCGEN05)
+            and s >= 0):
+        q_i8, q_scale, flag = quantize_q(q, s, want_gate=True)
+        k_i8, k_scale, _ = smooth_quantize_k(k, k_mean(k, seqlens_k))
+        out = _C.attn_int8_fwd(q_i8, q_scale.squeeze(-1).contiguous(), k_i8, k_scale.squeeze(-1).contiguous(),
+                               v.contiguous(), causal, window_left, seqlens_q=seqlens_q, seqlens_k=seqlens_k,
+                               backend=_lib.SL8_BACKEND_TCGEN05, gate_flag=flag, gate_want=False)
+        _C.attn_fp16_fwd(q, k, v, causal, s, window_left, None, seqlens_q=seqlens_q, seqlens_k=seqlens_k,
+                         backend=_lib.SL8_BACKEND_TCGEN05, out=out, gate_flag=flag, gate_want=True)
+        last_gate_decision, last_gate_flag = None, flag
+        return out
+    internal_accuracy_gate = bool(internal_accuracy_gate)
     use_gate = internal_accuracy_gate and not _capturing()
     if rotate:
         if use_gate:

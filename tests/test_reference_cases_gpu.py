@@ -9,7 +9,7 @@ import torch
 
 import superl8_b200 as s8
 from oracle import oracle
-from superl8_b200 import quant
+from superl8_b200 import _C, quant
 
 
 def _qkv(shape_q, seed, hkv=None, device="cuda"):
@@ -108,3 +108,49 @@ def test_int8_path_can_be_captured_in_a_cuda_graph(device):
     graph.replay()
     torch.cuda.synchronize()
     assert torch.equal(out, eager)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D", [64, 128])
+def test_device_side_gate_matches_the_host_side_gate(device, D):
+    """internal_accuracy_gate="device": both kernels are launched and the flag decides on the GPU
+    which one works.  Same bits as the host-side gate, on inputs that pass the gate and on inputs
+    that trip it."""
+    q, k, v = (t.to(device) for t in _qkv((2, 4, 300, D), 11, hkv=2))
+    for trip in (False, True):
+        if trip:
+            q = q.clone()
+            q[:, :, :, 3] *= 40.0           # one dominant channel in every row: max / median > 12
+        host = s8.attn_int8_fwd(q, k, v, causal=True)
+        assert s8.ops.last_gate_decision is trip
+        dev = s8.attn_int8_fwd(q, k, v, causal=True, internal_accuracy_gate="device")
+        assert s8.ops.last_gate_decision is None and bool(s8.ops.last_gate_flag.item()) is trip
+        assert torch.equal(dev, host)
+    assert _C.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_gated_call_can_be_captured_with_the_device_side_gate(device):
+    """The reference skips its gate under CUDA-graph capture (a host read-back cannot be captured);
+    with the decision on the device the gate stays active inside the graph: one captured graph
+    serves inputs that pass and inputs that trip the gate."""
+    q, k, v = (t.to(device) for t in _qkv((1, 4, 256, 128), 5, hkv=2))
+    q_ok, q_bad = q.clone(), q.clone()
+    q_bad[:, :, :, 7] *= 40.0
+    want_ok = s8.attn_int8_fwd(q_ok, k, v, causal=True)
+    assert s8.ops.last_gate_decision is False
+    want_bad = s8.attn_int8_fwd(q_bad, k, v, causal=True)
+    assert s8.ops.last_gate_decision is True
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        s8.attn_int8_fwd(q, k, v, causal=True, internal_accuracy_gate="device")     # warm-up on the side stream
+    torch.cuda.current_stream().wait_stream(s)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = s8.attn_int8_fwd(q, k, v, causal=True, internal_accuracy_gate="device")
+    for src, want in ((q_ok, want_ok), (q_bad, want_bad), (q_ok, want_ok)):
+        q.copy_(src)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, want)
