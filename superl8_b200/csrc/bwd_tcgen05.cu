@@ -90,7 +90,8 @@ struct BtArgs {
 };
 
 // S_FULL: the dK/dV pass uses [0] (one S buffer, a phase per tile), the dQ pass [i & 1] (two S buffers).
-enum BtBar { FIX_FULL = 0, ACC_DONE, DP_FULL, P_FULL, P_READ, DS_FULL, S_FULL, B1_FULL = S_FULL + 2, B1_EMPTY = B1_FULL + 3,
+// P_FULL in the dK/dV pass: [h] = P of the tile's queries [64 h, 64 h + 64), a phase per tile.
+enum BtBar { FIX_FULL = 0, ACC_DONE, DP_FULL, P_READ, DS_FULL, P_FULL, S_FULL = P_FULL + 2, B1_FULL = S_FULL + 2, B1_EMPTY = B1_FULL + 3,
              B2_FULL = B1_EMPTY + 3, B2_EMPTY = B2_FULL + 2, BT_NUM_BARS = B2_EMPTY + 2 };
 
 template <int D, typename VT, bool DKV>
@@ -139,6 +140,7 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
     mbar_init(&bars[ACC_DONE], 1);
     mbar_init(&bars[DP_FULL], 1);
     mbar_init(&bars[P_FULL], 4);     // the P warps
+    mbar_init(&bars[P_FULL + 1], 4);
     mbar_init(&bars[P_READ], 4);     // the dS warps, once P is in their registers (dK/dV pass)
     mbar_init(&bars[DS_FULL], 4);    // the dS warps
     for (int i = 0; i < 2; ++i) {
@@ -287,14 +289,17 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
       }
       __syncwarp();
     };
-    auto issue_dv = [&](int i) {    // dV += P_i^T dO_i (P over the first 64 columns of S; B2 read MN-major); frees the B2 stage
+    // dV += P_i^T dO_i over the tile's queries [64 h, 64 h + 64) (P over columns [32 h, 32 h + 32) of S;
+    // B2 read MN-major): the first half is queued while the P warps still work on the second.  The
+    // second half frees the B2 stage.
+    auto issue_dv_half = [&](int i, int h) {
       if (elect_one()) {
         const int s2 = i % C::NB2;
 #pragma unroll
-        for (int kk = 0; kk < kBT / 16; ++kk)
+        for (int kk = 4 * h; kk < 4 * h + 4; ++kk)
           tc_mma_f16_ts(tmem + C::COL_ACC1, tmem + C::COL_S + 8 * kk, umma_desc_advance(db2_mn, s2 * C::TILE_BYTES + kk * 2048),
                         idesc_acc, (i > 0 || kk > 0) ? 1u : 0u);
-        tc_commit(&bars[B2_EMPTY + s2]);
+        if (h == 1) tc_commit(&bars[B2_EMPTY + s2]);
       }
       __syncwarp();
     };
@@ -326,10 +331,13 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
     for (int i = 0; i < total && ok; ++i) {
       if (lane == 0 && i < 250) BTR(4096 + 8 * i + 0);
       if (DKV) {
-        ok = wait_all(&bars[P_FULL], i & 1);
+        ok = wait_all(&bars[P_FULL + 0], i & 1);
         if (!ok) break;
         if (lane == 0 && i < 250) BTR(4096 + 8 * i + 1);
-        issue_dv(i);
+        issue_dv_half(i, 0);
+        ok = wait_all(&bars[P_FULL + 1], i & 1);
+        if (!ok) break;
+        issue_dv_half(i, 1);
         if (lane == 0 && i < 250) BTR(4096 + 8 * i + 2);
         if (i + 1 < total) {
           ok = wait_b1(i + 1);
@@ -439,15 +447,18 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
           }
           tc_st16(t_s + 32 * h, *reinterpret_cast<uint32_t(*)[16]>(&pp[0]));
           tc_st16(t_s + 32 * h + 16, *reinterpret_cast<uint32_t(*)[16]>(&pp[16]));
+          if (DKV || h == 1) {     // dK/dV pass: each half of P is handed over on its own
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars[P_FULL + (DKV ? h : 0)]);
+          }
         }
-        tc_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[P_FULL]);
         if (warp == 0 && lane == 0 && i < 250) BTR(8 * i + 2);
       } else {
         // ======== dS warp ========
         ok = mbar_wait(&bars[P_FULL], i & 1, a.status);
+        if (ok && DKV) ok = mbar_wait(&bars[P_FULL + 1], i & 1, a.status);
         if (!ok) break;
         tc_fence_after();
         if (warp == 4 && lane == 0 && i < 250) BTR(2048 + 8 * i + 1);
