@@ -57,7 +57,11 @@ struct BtCfg {
   // tile's first MMA and by its last, so its stage comes back late: the dQ pass, which has the
   // room, gives it three stages (a reload is then two tiles ahead of its use).  B2 (dO / V) is
   // released after the dV MMA (dK/dV pass) or right after dP (dQ pass).
-  static constexpr int NB1 = DKV ? 2 : (D <= 128 ? 3 : 2);
+  // Two S buffers wherever tensor memory has the room: the dQ pass (one accumulator) and the
+  // dK/dV pass at D = 64 (two 64-column accumulators).  With them the next tile's S is ready while
+  // this tile is processed, and the B1 ring gets its third stage (shared memory has the room too).
+  static constexpr bool DBL_S = !DKV || D == 64;
+  static constexpr int NB1 = DBL_S ? 3 : 2;
   static constexpr int NB2 = 2;
   static constexpr int OFF_A1 = 0;
   static constexpr int OFF_A2 = OFF_A1 + TILE_BYTES;
@@ -74,8 +78,9 @@ struct BtCfg {
   static constexpr int OFF_BAR = DKV ? OFF_EXT_DP + NB1 * EXT_BYTES : OFF_EXT_ONES;
   static constexpr int SMEM = OFF_BAR + 256 + 1024;
   static_assert(SMEM <= 232448, "shared memory per block");
-  static constexpr uint32_t COL_S = 0, COL_DP = 128, COL_ACC1 = 256, COL_ACC2 = 384;   // dK/dV pass
-  static constexpr uint32_t COL_S1 = 384;                                               // dQ pass: second S buffer
+  static constexpr uint32_t COL_S = 0, COL_DP = 128, COL_ACC1 = 256;
+  static constexpr uint32_t COL_ACC2 = D == 64 ? 320 : 384;                             // dK/dV pass: dK
+  static constexpr uint32_t COL_S1 = 384;                                               // second S buffer (DBL_S)
 };
 
 struct BtArgs {
@@ -89,7 +94,7 @@ struct BtArgs {
   float scale;
 };
 
-// S_FULL: the dK/dV pass uses [0] (one S buffer, a phase per tile), the dQ pass [i & 1] (two S buffers).
+// S_FULL: with one S buffer [0] completes a phase per tile; with two (DBL_S) tile i uses [i & 1].
 // P_FULL in the dK/dV pass: [h] = P of the tile's queries [64 h, 64 h + 64), a phase per tile.
 enum BtBar { FIX_FULL = 0, ACC_DONE, DP_FULL, P_READ, DS_FULL, P_FULL, S_FULL = P_FULL + 2, B1_FULL = S_FULL + 2, B1_EMPTY = B1_FULL + 3,
              B2_FULL = B1_EMPTY + 3, B2_EMPTY = B2_FULL + 2, BT_NUM_BARS = B2_EMPTY + 2 };
@@ -238,8 +243,9 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
     // The whole warp walks the loop and polls the barriers; one elected lane issues and commits.
     // Order of issue (the tensor pipe executes in this order, which is what lets a later MMA
     // overwrite the tensor-memory operand of an earlier one):
-    //   dK/dV pass  S_0 dP_0 | dV_i S_{i+1} dK_i dP_{i+1} | ...   (S_{i+1} reuses the columns P_i sat in)
-    //   dQ pass     S_0 dP_0 S_1 | dQ_i dP_{i+1} S_{i+2} | ...     (two S buffers)
+    //   one S buffer (dK/dV pass, D = 128)   S_0 dP_0 | dV_i S_{i+1} dK_i dP_{i+1} | ...   (S_{i+1} reuses the columns P_i sat in)
+    //   two S buffers (dQ pass)              S_0 dP_0 S_1 | dQ_i dP_{i+1} S_{i+2} | ...
+    //   two S buffers (dK/dV pass, D = 64)   S_0 dP_0 S_1 | dV_i dK_i dP_{i+1} S_{i+2} | ...
     constexpr uint32_t vfmt = std::is_same<VT, __nv_bfloat16>::value ? 1u : 0u;
     const uint32_t idesc_s = umma_idesc(1, vfmt, vfmt, 0, 0, kBT, kBT);
     const uint32_t idesc_acc = umma_idesc(1, vfmt, vfmt, 0, 1, kBT, D);
@@ -262,7 +268,7 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
     auto issue_s = [&](int i) {     // S_i = A1 B1_i^T
       if (elect_one()) {
         const int s1 = i % C::NB1;
-        const uint32_t col = DKV ? C::COL_S : ((i & 1) ? C::COL_S1 : C::COL_S);
+        const uint32_t col = (C::DBL_S && (i & 1)) ? C::COL_S1 : C::COL_S;
 #pragma unroll
         for (int k = 0; k < C::KSTEPS; ++k) {
           const uint32_t off = (32 * k / 128) * C::SUB_BYTES + (32 * k % 128);
@@ -270,7 +276,7 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
                         idesc_s, k > 0 ? 1u : 0u);
         }
         if (DKV) tc_mma_f16_ss(tmem + col, de_ones, umma_desc_advance(de_s, s1 * C::EXT_BYTES), idesc_s, 1u);   // S -= lse / scale
-        tc_commit(&bars[S_FULL + (DKV ? 0 : (i & 1))]);
+        tc_commit(&bars[S_FULL + (C::DBL_S ? (i & 1) : 0)]);
       }
       __syncwarp();
     };
@@ -297,8 +303,8 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
         const int s2 = i % C::NB2;
 #pragma unroll
         for (int kk = 4 * h; kk < 4 * h + 4; ++kk)
-          tc_mma_f16_ts(tmem + C::COL_ACC1, tmem + C::COL_S + 8 * kk, umma_desc_advance(db2_mn, s2 * C::TILE_BYTES + kk * 2048),
-                        idesc_acc, (i > 0 || kk > 0) ? 1u : 0u);
+          tc_mma_f16_ts(tmem + C::COL_ACC1, tmem + ((C::DBL_S && (i & 1)) ? C::COL_S1 : C::COL_S) + 8 * kk,
+                        umma_desc_advance(db2_mn, s2 * C::TILE_BYTES + kk * 2048), idesc_acc, (i > 0 || kk > 0) ? 1u : 0u);
         if (h == 1) tc_commit(&bars[B2_EMPTY + s2]);
       }
       __syncwarp();
@@ -323,7 +329,7 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
       if (ok) issue_s(0);
       if (ok) ok = wait_b2(0);
       if (ok) issue_dp(0);
-      if (!DKV && ok && total > 1) {
+      if (C::DBL_S && ok && total > 1) {
         ok = wait_b1(1);
         if (ok) issue_s(1);
       }
@@ -339,7 +345,7 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
         if (!ok) break;
         issue_dv_half(i, 1);
         if (lane == 0 && i < 250) BTR(4096 + 8 * i + 2);
-        if (i + 1 < total) {
+        if (!C::DBL_S && i + 1 < total) {
           ok = wait_b1(i + 1);
           if (ok) ok = wait_all(&bars[P_READ], i & 1);     // the dS warps hold P_i: its columns may be overwritten
           if (!ok) break;
@@ -347,35 +353,23 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
           issue_s(i + 1);
         }
         if (lane == 0 && i < 250) BTR(4096 + 8 * i + 4);
-        ok = wait_all(&bars[DS_FULL], i & 1);
-        if (!ok) break;
-        if (lane == 0 && i < 250) BTR(4096 + 8 * i + 5);
-        issue_last(i);
-        if (i + 1 < total) {
-          ok = wait_b2(i + 1);
-          if (!ok) break;
-          issue_dp(i + 1);
-        }
-        if (lane == 0 && i < 250) BTR(4096 + 8 * i + 6);
-      } else {
-        ok = wait_all(&bars[DS_FULL], i & 1);
-        if (!ok) break;
-        if (lane == 0 && i < 250) BTR(4096 + 8 * i + 1);
-        issue_last(i);
-        if (i + 1 < total) {
-          ok = wait_b2(i + 1);
-          if (!ok) break;
-          issue_dp(i + 1);
-        }
-        if (lane == 0 && i < 250) BTR(4096 + 8 * i + 2);
-        if (i + 2 < total) {
-          ok = wait_b1(i + 2);
-          if (!ok) break;
-          if (lane == 0 && i < 250) BTR(4096 + 8 * i + 3);
-          issue_s(i + 2);                        // into the S buffer the compute warps have finished with
-        }
-        if (lane == 0 && i < 250) BTR(4096 + 8 * i + 4);
       }
+      ok = wait_all(&bars[DS_FULL], i & 1);
+      if (!ok) break;
+      if (lane == 0 && i < 250) BTR(4096 + 8 * i + 5);
+      issue_last(i);
+      if (i + 1 < total) {
+        ok = wait_b2(i + 1);
+        if (!ok) break;
+        issue_dp(i + 1);
+      }
+      if (lane == 0 && i < 250) BTR(4096 + 8 * i + 6);
+      if (C::DBL_S && i + 2 < total) {
+        ok = wait_b1(i + 2);
+        if (!ok) break;
+        issue_s(i + 2);      // into the S buffer the compute warps have finished with (DS_FULL of tile i)
+      }
+      if (lane == 0 && i < 250) BTR(4096 + 8 * i + 7);
     }
   } else {
     // ======================= compute / epilogue =======================
@@ -401,12 +395,12 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
     }
     for (int i = 0; i < total; ++i) {
       const int col = tile_col(i);
-      const uint32_t t_s = t_row + (DKV ? C::COL_S : ((i & 1) ? C::COL_S1 : C::COL_S));
+      const uint32_t t_s = t_row + ((C::DBL_S && (i & 1)) ? C::COL_S1 : C::COL_S);
       if (warp == 0 && lane == 0 && i < 250) BTR(8 * i + 0);
       if (warp == 4 && lane == 0 && i < 250) BTR(2048 + 8 * i + 0);
       if (half == 0) {
         // ======== P warp ========
-        ok = DKV ? mbar_wait(&bars[S_FULL], i & 1, a.status) : mbar_wait(&bars[S_FULL + (i & 1)], (i >> 1) & 1, a.status);
+        ok = C::DBL_S ? mbar_wait(&bars[S_FULL + (i & 1)], (i >> 1) & 1, a.status) : mbar_wait(&bars[S_FULL], i & 1, a.status);
         if (!ok) break;
         tc_fence_after();
         if (warp == 0 && lane == 0 && i < 250) BTR(8 * i + 1);
