@@ -186,6 +186,28 @@ size_t sl8_attn_fp16_fwd_workspace(const sl8_fp16_fwd_params* p);
 int sl8_attn_fp16_fwd(const sl8_fp16_fwd_params* p, void* workspace, size_t workspace_bytes,
                       void* stream);
 
+/*
+ * The whole `attn_int8_fwd` step from 16-bit q, k, v in one host call: accuracy gate, Q / K
+ * quantisation prologue and attention (the sequence of superl8/ops.py:70-175) queued back to back,
+ * with the gate decided on the device (gate_flag / gate_want above), so nothing is read back to
+ * the host and the call can be captured in a CUDA graph.  One dtype for q, k, v, out; D in
+ * {64, 128, 256}, N > 0 (SL8_ERR_UNSUPPORTED otherwise: use the separate entry points).
+ * ratio_threshold: the gate's max|q| / median|q| bound (reference: 12); <= 0 switches the gate
+ * off (always the int8 kernel).  After the call the int32 at workspace + 256 is the gate's flag
+ * (non-zero: the full-precision kernel produced `out`) and the status word is at workspace + 0.
+ * No counterpart in the reference's C layer (its Python entry makes these calls one by one).
+ */
+typedef struct sl8_fused_fwd_params {
+  const void* q; const void* k; const void* v; void* out;
+  const int32_t* seqlens_q; const int32_t* seqlens_k;   /* nullable, int32[B] */
+  int32_t B, Hq, Hkv, M, N, D;
+  int32_t dtype; int32_t causal; int32_t window_left;
+  float ratio_threshold;
+  double softmax_scale;
+} sl8_fused_fwd_params;
+size_t sl8_attn_int8_fwd_fused_workspace(const sl8_fused_fwd_params* p);
+int sl8_attn_int8_fwd_fused(const sl8_fused_fwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- full W8A8 prefill (int8 P.V) ------------------------------------------------------ */
 
 /*

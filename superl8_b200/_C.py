@@ -19,6 +19,7 @@ from . import _lib
 _DTYPE = {torch.float16: _lib.SL8_F16, torch.bfloat16: _lib.SL8_BF16, torch.float32: _lib.SL8_F32}
 _status_ws: dict = {}
 _decode_ws: dict = {}
+_fused_ws: dict = {}    # the last fused-forward workspace per (device, stream), likewise
 _bwd_ws: dict = {}      # the last backward workspace per (device, stream): its status word is read by device_status
 
 
@@ -58,9 +59,10 @@ def device_status(device=None) -> int:
     ws = _decode_ws.get((device.index, torch.cuda.current_stream(device).cuda_stream))
     if rc == 0 and ws is not None:
         rc = lib.sl8_read_device_status(_ptr(ws), _stream(device))
-    bws = _bwd_ws.get((device.index, torch.cuda.current_stream(device).cuda_stream))
-    if rc == 0 and bws is not None:
-        rc = lib.sl8_read_device_status(_ptr(bws), _stream(device))
+    for extra in (_bwd_ws, _fused_ws):
+        bws = extra.get((device.index, torch.cuda.current_stream(device).cuda_stream))
+        if rc == 0 and bws is not None:
+            rc = lib.sl8_read_device_status(_ptr(bws), _stream(device))
     return rc
 
 
@@ -147,6 +149,46 @@ def attn_int8_fwd(q, q_scale, k, k_scale, v, causal=False, window_left=-1, *, se
 def attn_int8_fwd_train(q, q_scale, k, k_scale, v, causal=False, *, backend=_lib.SL8_BACKEND_AUTO):
     """Also returns the natural-log LSE.  Reference binding csrc/fni8_api.cpp:230-233."""
     return _run_fwd(q, q_scale, k, k_scale, v, causal, True, -1, None, None, backend)
+
+
+def attn_int8_fwd_fused(q, k, v, causal=False, scale=None, window_left=-1, *, seqlens_q=None, seqlens_k=None,
+                        gate=True, ratio_threshold=12.0):
+    """attn_int8_fwd from 16-bit q, k, v [B, H, S, D] in ONE library call (sl8_attn_int8_fwd_fused):
+    gate, Q / K prologue and both candidate kernels queued back to back, the gate decided on the
+    device.  Returns (out, flag): flag is an int32 [1] view of the workspace, non-zero when the
+    full-precision kernel produced ``out``.  D in {64, 128, 256}, one dtype, N > 0."""
+    what = "superl8_b200 fused fwd"
+    _check_cuda(q, k, v)
+    _check(q.dtype in (torch.float16, torch.bfloat16), f"{what}: q must be float16 or bfloat16")
+    _check(k.dtype == q.dtype and v.dtype == q.dtype, f"{what}: q, k, v must share one dtype")
+    _check(q.dim() == 4 and k.dim() == 4 and v.dim() == 4, f"{what}: expect [B,H,S,D]")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    B, H, M, D = q.shape
+    Hkv, N = k.shape[1], k.shape[2]
+    _check(k.shape[0] == B and v.shape[0] == B and v.shape[1] == Hkv, f"{what}: batch/head mismatch")
+    _check(Hkv > 0 and H % Hkv == 0, f"{what}: H_q must be divisible by H_kv (GQA)")
+    _check(k.shape[3] == D and v.shape[3] == D and v.shape[2] == N, f"{what}: K/V shape mismatch")
+    _check(D in (64, 128, 256), f"{what}: head dim must be 64/128/256, got {D}")
+    for s_ in (seqlens_q, seqlens_k):
+        if s_ is not None:
+            _check(s_.is_cuda and s_.dtype == torch.int32 and s_.numel() == B and s_.is_contiguous(),
+                   f"{what}: seqlens must be contiguous int32 [B] CUDA tensors")
+    out = torch.empty((B, H, M, D), dtype=v.dtype, device=v.device)
+    sc = (1.0 / math.sqrt(D)) if scale is None else float(scale)
+    p = _lib.FusedFwdParams(
+        q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(),
+        seqlens_q=None if seqlens_q is None else seqlens_q.data_ptr(),
+        seqlens_k=None if seqlens_k is None else seqlens_k.data_ptr(),
+        B=B, Hq=H, Hkv=Hkv, M=M, N=N, D=D, dtype=_DTYPE[q.dtype], causal=int(bool(causal)),
+        window_left=int(window_left), ratio_threshold=float(ratio_threshold) if gate else 0.0, softmax_scale=sc)
+    lib = _lib.load()
+    with torch.cuda.device(q.device):
+        nbytes = int(lib.sl8_attn_int8_fwd_fused_workspace(C.byref(p)))
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+        rc = lib.sl8_attn_int8_fwd_fused(C.byref(p), _ptr(ws), nbytes, _stream(q.device))
+        _fused_ws[(q.device.index, torch.cuda.current_stream(q.device).cuda_stream)] = ws
+    _lib.check(rc, "attn_int8_fwd_fused", (5 + (1 if gate else 0)) if out.numel() else 0)
+    return out, ws[256:260].view(torch.int32)
 
 
 def qk_logits_i32(q_i8: torch.Tensor, k_i8: torch.Tensor) -> torch.Tensor:

@@ -58,13 +58,8 @@ def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, 
     if (internal_accuracy_gate == "device" and not rotate and q.shape[-1] in (64, 128, 256) and k.shape[-2] > 0
             and q.dtype == k.dtype == v.dtype and backend in (_lib.SL8_BACKEND_AUTO, _lib.SL8_BACKEND_TCGEN05)
             and s >= 0):
-        q_i8, q_scale, flag = quantize_q(q, s, want_gate=True)
-        k_i8, k_scale, _ = smooth_quantize_k(k, k_mean(k, seqlens_k))
-        out = _C.attn_int8_fwd(q_i8, q_scale.squeeze(-1).contiguous(), k_i8, k_scale.squeeze(-1).contiguous(),
-                               v.contiguous(), causal, window_left, seqlens_q=seqlens_q, seqlens_k=seqlens_k,
-                               backend=_lib.SL8_BACKEND_TCGEN05, gate_flag=flag, gate_want=False)
-        _C.attn_fp16_fwd(q, k, v, causal, s, window_left, None, seqlens_q=seqlens_q, seqlens_k=seqlens_k,
-                         backend=_lib.SL8_BACKEND_TCGEN05, out=out, gate_flag=flag, gate_want=True)
+        # one library call queues the gate, the prologue and both candidate kernels
+        out, flag = _C.attn_int8_fwd_fused(q, k, v, causal, s, window_left, seqlens_q=seqlens_q, seqlens_k=seqlens_k)
         last_gate_decision, last_gate_flag = None, flag
         return out
     internal_accuracy_gate = bool(internal_accuracy_gate)
