@@ -193,13 +193,18 @@ int sl8_attn_fp16_fwd(const sl8_fp16_fwd_params* p, void* workspace, size_t work
  * the host and the call can be captured in a CUDA graph.  One dtype for q, k, v, out; D in
  * {64, 128, 256}, N > 0 (SL8_ERR_UNSUPPORTED otherwise: use the separate entry points).
  * ratio_threshold: the gate's max|q| / median|q| bound (reference: 12); <= 0 switches the gate
- * off (always the int8 kernel).  After the call the int32 at workspace + 256 is the gate's flag
- * (non-zero: the full-precision kernel produced `out`) and the status word is at workspace + 0.
+ * off (always the int8 kernel).  After the call the int32 at workspace + 256 (or *gate_flag) is the
+ * gate's flag (non-zero: the full-precision kernel produced `out`) and the status word is at
+ * workspace + 0 (or device_status).
  * No counterpart in the reference's C layer (its Python entry makes these calls one by one).
  */
 typedef struct sl8_fused_fwd_params {
   const void* q; const void* k; const void* v; void* out;
   const int32_t* seqlens_q; const int32_t* seqlens_k;   /* nullable, int32[B] */
+  int32_t* gate_flag;     /* nullable: a caller-owned device int32 that receives the gate's flag (zeroed by this
+                             call) instead of workspace + 256 */
+  void* device_status;    /* nullable: a caller-owned status word (256 bytes, zeroed by the caller, as the other
+                             ops' workspace) used instead of workspace + 0, which this call zeroes itself */
   int32_t B, Hq, Hkv, M, N, D;
   int32_t dtype; int32_t causal; int32_t window_left;
   float ratio_threshold;

@@ -19,7 +19,6 @@ from . import _lib
 _DTYPE = {torch.float16: _lib.SL8_F16, torch.bfloat16: _lib.SL8_BF16, torch.float32: _lib.SL8_F32}
 _status_ws: dict = {}
 _decode_ws: dict = {}
-_fused_ws: dict = {}    # the last fused-forward workspace per (device, stream), likewise
 _bwd_ws: dict = {}      # the last backward workspace per (device, stream): its status word is read by device_status
 
 
@@ -59,10 +58,9 @@ def device_status(device=None) -> int:
     ws = _decode_ws.get((device.index, torch.cuda.current_stream(device).cuda_stream))
     if rc == 0 and ws is not None:
         rc = lib.sl8_read_device_status(_ptr(ws), _stream(device))
-    for extra in (_bwd_ws, _fused_ws):
-        bws = extra.get((device.index, torch.cuda.current_stream(device).cuda_stream))
-        if rc == 0 and bws is not None:
-            rc = lib.sl8_read_device_status(_ptr(bws), _stream(device))
+    bws = _bwd_ws.get((device.index, torch.cuda.current_stream(device).cuda_stream))
+    if rc == 0 and bws is not None:
+        rc = lib.sl8_read_device_status(_ptr(bws), _stream(device))
     return rc
 
 
@@ -155,7 +153,7 @@ def attn_int8_fwd_fused(q, k, v, causal=False, scale=None, window_left=-1, *, se
                         gate=True, ratio_threshold=12.0):
     """attn_int8_fwd from 16-bit q, k, v [B, H, S, D] in ONE library call (sl8_attn_int8_fwd_fused):
     gate, Q / K prologue and both candidate kernels queued back to back, the gate decided on the
-    device.  Returns (out, flag): flag is an int32 [1] view of the workspace, non-zero when the
+    device.  Returns (out, flag): flag is an int32 [1] device tensor, non-zero when the
     full-precision kernel produced ``out``.  D in {64, 128, 256}, one dtype, N > 0."""
     what = "superl8_b200 fused fwd"
     _check_cuda(q, k, v)
@@ -175,8 +173,11 @@ def attn_int8_fwd_fused(q, k, v, causal=False, scale=None, window_left=-1, *, se
                    f"{what}: seqlens must be contiguous int32 [B] CUDA tensors")
     out = torch.empty((B, H, M, D), dtype=v.dtype, device=v.device)
     sc = (1.0 / math.sqrt(D)) if scale is None else float(scale)
+    status = _status_buffer(q.device)      # the stream's shared status word: device_status() reads it
+    flag = torch.empty(1, dtype=torch.int32, device=q.device)   # zeroed by the call; outlives the workspace
     p = _lib.FusedFwdParams(
-        q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(),
+        q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), device_status=status.data_ptr(),
+        gate_flag=flag.data_ptr(),
         seqlens_q=None if seqlens_q is None else seqlens_q.data_ptr(),
         seqlens_k=None if seqlens_k is None else seqlens_k.data_ptr(),
         B=B, Hq=H, Hkv=Hkv, M=M, N=N, D=D, dtype=_DTYPE[q.dtype], causal=int(bool(causal)),
@@ -186,9 +187,8 @@ def attn_int8_fwd_fused(q, k, v, causal=False, scale=None, window_left=-1, *, se
         nbytes = int(lib.sl8_attn_int8_fwd_fused_workspace(C.byref(p)))
         ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
         rc = lib.sl8_attn_int8_fwd_fused(C.byref(p), _ptr(ws), nbytes, _stream(q.device))
-        _fused_ws[(q.device.index, torch.cuda.current_stream(q.device).cuda_stream)] = ws
     _lib.check(rc, "attn_int8_fwd_fused", (5 + (1 if gate else 0)) if out.numel() else 0)
-    return out, ws[256:260].view(torch.int32)
+    return out, flag
 
 
 def qk_logits_i32(q_i8: torch.Tensor, k_i8: torch.Tensor) -> torch.Tensor:

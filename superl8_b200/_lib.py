@@ -63,7 +63,8 @@ class Fp16FwdParams(C.Structure):
 class FusedFwdParams(C.Structure):
     _fields_ = [
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p),
-        ("seqlens_q", C.c_void_p), ("seqlens_k", C.c_void_p),
+        ("seqlens_q", C.c_void_p), ("seqlens_k", C.c_void_p), ("gate_flag", C.c_void_p),
+        ("device_status", C.c_void_p),
         ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("M", C.c_int32), ("N", C.c_int32), ("D", C.c_int32),
         ("dtype", C.c_int32), ("causal", C.c_int32), ("window_left", C.c_int32),
         ("ratio_threshold", C.c_float), ("softmax_scale", C.c_double),

@@ -54,8 +54,9 @@ extern "C" int sl8_attn_int8_fwd_fused(const sl8_fused_fwd_params* p, void* work
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool gate = p->ratio_threshold > 0.f;
-  int32_t* flag = reinterpret_cast<int32_t*>(ws + l.flag);
+  int32_t* flag = p->gate_flag != nullptr ? p->gate_flag : reinterpret_cast<int32_t*>(ws + l.flag);
   SL8_CUDA_TRY(cudaMemsetAsync(ws, 0, 512, s));        // status word and gate flag
+  if (p->gate_flag != nullptr) SL8_CUDA_TRY(cudaMemsetAsync(p->gate_flag, 0, sizeof(int32_t), s));
   int8_t* q_i8 = reinterpret_cast<int8_t*>(ws + l.q_i8);
   int8_t* k_i8 = reinterpret_cast<int8_t*>(ws + l.k_i8);
   float* q_scale = reinterpret_cast<float*>(ws + l.q_scale);
@@ -78,12 +79,13 @@ extern "C" int sl8_attn_int8_fwd_fused(const sl8_fused_fwd_params* p, void* work
   f.B = p->B; f.Hq = p->Hq; f.Hkv = p->Hkv; f.M = p->M; f.N = p->N; f.D = p->D; f.v_dtype = p->dtype;
   f.causal = p->causal; f.window_left = p->window_left; f.backend = SL8_BACKEND_TCGEN05;
   f.gate_flag = gate ? flag : nullptr; f.gate_want = 0;
-  rc = sl8_attn_int8_fwd(&f, ws, 256, stream);
+  void* status = p->device_status != nullptr ? p->device_status : static_cast<void*>(ws);
+  rc = sl8_attn_int8_fwd(&f, status, 256, stream);
   if (rc != SL8_OK || !gate) return rc;
   sl8_fp16_fwd_params h{};
   h.q = p->q; h.k = p->k; h.v = p->v; h.out = p->out; h.seqlens_q = p->seqlens_q; h.seqlens_k = p->seqlens_k;
   h.B = p->B; h.Hq = p->Hq; h.Hkv = p->Hkv; h.M = p->M; h.N = p->N; h.D = p->D; h.dtype = p->dtype;
   h.causal = p->causal; h.window_left = p->window_left; h.softmax_scale = (float)p->softmax_scale;
   h.backend = SL8_BACKEND_TCGEN05; h.gate_flag = flag; h.gate_want = 1;
-  return sl8_attn_fp16_fwd(&h, ws, 256, stream);
+  return sl8_attn_fp16_fwd(&h, status, 256, stream);
 }
