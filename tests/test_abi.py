@@ -55,6 +55,28 @@ def test_host_side_validation_needs_no_device():
     assert lib.sl8_quantize_i8_rowwise(None, 0, 0, 128, None, None, None) == 0
     assert lib.sl8_quantize_i8_rowwise(None, 0, 4, 128, None, None, None) == _lib.ERR_NULL
     assert lib.sl8_quantize_i8_rowwise(None, 7, 4, 128, C.c_void_p(16), C.c_void_p(16), None) == _lib.ERR_NULL
+    # the one-call forward: head dims of the tensor-memory kernels only, one 16-bit dtype, pointers checked
+    u = _lib.FusedFwdParams(B=1, Hq=4, Hkv=2, M=64, N=64, D=80, dtype=0, softmax_scale=0.1)
+    assert lib.sl8_attn_int8_fwd_fused(C.byref(u), None, 0, None) == _lib.ERR_UNSUPPORTED
+    u = _lib.FusedFwdParams(B=1, Hq=4, Hkv=2, M=64, N=64, D=128, dtype=2, softmax_scale=0.1)
+    assert lib.sl8_attn_int8_fwd_fused(C.byref(u), None, 0, None) == _lib.ERR_BAD_DTYPE
+    u = _lib.FusedFwdParams(B=1, Hq=4, Hkv=3, M=64, N=64, D=128, dtype=0, softmax_scale=0.1)
+    assert lib.sl8_attn_int8_fwd_fused(C.byref(u), None, 0, None) == _lib.ERR_BAD_SHAPE
+    u = _lib.FusedFwdParams(B=1, Hq=4, Hkv=2, M=0, N=64, D=128, dtype=0, softmax_scale=0.1)
+    assert lib.sl8_attn_int8_fwd_fused(C.byref(u), None, 0, None) == 0        # empty output is a no-op
+    u = _lib.FusedFwdParams(B=1, Hq=4, Hkv=2, M=64, N=64, D=128, dtype=0, softmax_scale=0.1)
+    assert lib.sl8_attn_int8_fwd_fused(C.byref(u), None, 0, None) == _lib.ERR_NULL
+    u = _lib.FusedFwdParams(q=16, k=16, v=16, out=16, B=1, Hq=4, Hkv=2, M=64, N=64, D=128, dtype=0, softmax_scale=0.1)
+    assert lib.sl8_attn_int8_fwd_fused(C.byref(u), None, 0, None) == _lib.ERR_WORKSPACE
+    need = lib.sl8_attn_int8_fwd_fused_workspace(C.byref(u))
+    assert need >= 512 + 4 * 64 * 128 + 2 * 64 * 128 + 4 * (4 * 64 + 2 * 64) and need % 256 == 0
+    # the backward: the tensor-memory passes serve D = 64 / 128 only; the device-side gate needs the tcgen05 backend
+    b = _lib.BwdParams(B=1, Hq=2, Hkv=2, M=64, N=64, D=32, dtype=0, backend=_lib.SL8_BACKEND_TCGEN05,
+                       q=16, k=16, v=16, o=16, dout=16, lse=16, dq=16, dk=16, dv=16)
+    assert lib.sl8_attn_bwd(C.byref(b), C.c_void_p(16), 1 << 20, None) == _lib.ERR_UNSUPPORTED
+    f = _lib.FwdParams(q=16, q_scale=16, k=16, k_scale=16, v=16, out=16, B=1, Hq=4, Hkv=2, M=64, N=64, D=128, v_dtype=0,
+                       backend=_lib.SL8_BACKEND_MMA, gate_flag=16)
+    assert lib.sl8_attn_int8_fwd(C.byref(f), C.c_void_p(16), 256, None) == _lib.ERR_UNSUPPORTED
 
 
 def test_split_heuristic_properties():
