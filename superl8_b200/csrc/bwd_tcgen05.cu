@@ -141,6 +141,7 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
   auto tile_col = [&](int i) { return col_begin + (i % tiles_per_head) * kBT; };
 
   if (threadIdx.x == 0) {
+    BTR(8188);
     mbar_init(&bars[FIX_FULL], 1);
     mbar_init(&bars[ACC_DONE], 1);
     mbar_init(&bars[DP_FULL], 1);
@@ -168,6 +169,7 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   bool ok = true;
+  if (threadIdx.x == 0) BTR(8189);
 
   if (warp == kBtProducerWarp) {
     // ======================= producer =======================
@@ -498,7 +500,9 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
       }
     }
     // ---- epilogue: accumulators -> 16-bit rows ----
+    if (warp == 0 && lane == 0) BTR(8185);
     if (ok && total > 0) ok = mbar_wait(&bars[ACC_DONE], 0, a.status);
+    if (warp == 0 && lane == 0) BTR(8186);
     if (ok) {
       tc_fence_after();
       const int rows_total = DKV ? a.N : a.M;
@@ -570,6 +574,7 @@ __global__ void __launch_bounds__(kBtThreads, 1) bwd_tc_kernel(const __grid_cons
         }
       }
       if (D == 128 && lane == 0) tma_store_wait_read();   // the engine has read this warp's staged tiles
+      if (warp == 0 && lane == 0) BTR(8187);
     }
     tc_fence_before();
   }
