@@ -373,16 +373,23 @@ int sl8_quantize_v_perchannel(const void* v, int dtype, int64_t BH, int64_t N, i
  *    SL8_ERR_TOO_LARGE and launches nothing.
  *  - This function calls no cudaMalloc / cudaFree and no allocating library routine.
  *  - The first call on each device looks up the array's device address (once per
- *    device, with that device current); make that first call before any stream capture.
+ *    device, with that device current, under a host lock); make that first call before
+ *    any stream capture.
  *  - All calls on a device share the one array, and it keeps the previous call's
  *    contents (every value a call reads it has written itself first, so nothing needs
  *    clearing between calls).  Two calls that overlap on the GPU -- different streams,
  *    or the same stream from two threads without ordering -- race on it: serialise them.
- *  - device_status (nullable) is a caller-owned device int32, zeroed by the caller; it
- *    is set to SL8_ERR_DEVICE_TIMEOUT if a bounded device-side wait expires.
+ *  - device_status (nullable): a caller-owned, 4-byte aligned device int32, zeroed by the
+ *    caller; it is set to SL8_ERR_DEVICE_TIMEOUT if a bounded device-side wait expires
+ *    (only that one word is touched; read it with sl8_read_device_status).  With NULL the
+ *    word lives at the start of the built-in array: every call zeroes it on the stream
+ *    before its kernels, and sl8_decode_static_status(stream) synchronises the stream
+ *    and returns (and clears) it -- SL8_OK or SL8_ERR_DEVICE_TIMEOUT for the calls made
+ *    on the current device since the last read.
  */
 #define SL8_DECODE_STATIC_SCRATCH_BYTES (32u << 20)
 int sl8_attn_int8_decode_static(const sl8_decode_params* p, int32_t* device_status, void* stream);
+int sl8_decode_static_status(void* stream);
 
 /*
  * Tensor-pipe peak probe: one block per SM issues `iters` x 4 back-to-back tcgen05.mma
@@ -397,6 +404,18 @@ int sl8_tensor_peak_probe(int kind_i8, int iters, double* ops_per_launch, void* 
  * for the instruction shapes a kernel actually issues (smaller N = shorter instructions). */
 int sl8_tensor_peak_probe_n(int kind_i8, int n_cols, int iters, double* ops_per_launch, void* workspace,
                             size_t workspace_bytes, void* stream);
+
+/*
+ * Self-test of the bounded device-side wait every kernel of this library uses: one block waits
+ * on a barrier nothing ever arrives at, with a limit of limit_ns (1 .. 100 000 000) nanoseconds;
+ * when the limit runs out the kernel raises the status word (the first int32 of `workspace`, at
+ * least 256 bytes, zeroed by the caller) to SL8_ERR_DEVICE_TIMEOUT and returns normally, so the
+ * context stays usable.  The second int32 of the workspace receives 2 (the wait gave up) or 1
+ * (it was satisfied, which cannot happen).  Shows a host how an expired wait looks
+ * (sl8_read_device_status) without making any real kernel fail.  No counterpart in the
+ * reference, whose kernels have no inter-thread waits.
+ */
+int sl8_wait_timeout_selftest(void* workspace, size_t workspace_bytes, uint64_t limit_ns, void* stream);
 
 /* Synchronises the stream and returns the device status word of a workspace
  * (SL8_OK or SL8_ERR_DEVICE_TIMEOUT); clears it. */

@@ -3,9 +3,13 @@ device code, compiled from the reference checkout where it lies) behind the exte
 launchers of oracle/ref_kernels.cu, for sm_100a.  Checker only -- the product never loads
 it.  Needs the reference checkout; on a GPU box the prebuilt file is used.
 
-    python oracle/build_ref.py [/path/to/reference]
+    python oracle/build_ref.py /path/to/reference
+
+Without an argument the checkout is looked for in $SUPERL8_REFERENCE_ROOT and then in a
+directory named ``reference`` beside this repository.
 """
 
+import os
 import subprocess
 import sys
 from pathlib import Path
@@ -15,10 +19,20 @@ OUT_DIR = HERE / "_ref"
 LIB = OUT_DIR / "libref_kernels.so"
 
 
-def build_ref(reference_root="/root/reference", force=False):
-    inc = Path(reference_root) / "csrc" / "include"
-    if not inc.is_dir():
+def find_reference(reference_root=None):
+    """The reference checkout: the argument, $SUPERL8_REFERENCE_ROOT, or ../reference; None if absent."""
+    cands = [reference_root, os.environ.get("SUPERL8_REFERENCE_ROOT"), HERE.parent.parent / "reference"]
+    for c in cands:
+        if c and (Path(c) / "csrc" / "include").is_dir():
+            return Path(c)
+    return None
+
+
+def build_ref(reference_root=None, force=False):
+    root = find_reference(reference_root)
+    if root is None:
         return None
+    inc = root / "csrc" / "include"
     src = HERE / "ref_kernels.cu"
     if LIB.exists() and not force and LIB.stat().st_mtime > src.stat().st_mtime:
         return LIB
@@ -32,4 +46,7 @@ def build_ref(reference_root="/root/reference", force=False):
 
 
 if __name__ == "__main__":
-    print(build_ref(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", force=True))
+    lib = build_ref(sys.argv[1] if len(sys.argv) > 1 else None, force=True)
+    if lib is None:
+        sys.exit("no reference checkout: pass its path or set SUPERL8_REFERENCE_ROOT")
+    print(lib)

@@ -246,7 +246,12 @@ def attention_backward_fp32(q, k, v, out, d_out, causal: bool = False, scale: fl
 
 def int32_logits(q_i8: torch.Tensor, k_i8: torch.Tensor) -> torch.Tensor:
     """int32 Q.K^T (reference csrc/include/attn_int8_fwd.cuh:129-133: __dp4a chain).
-    q [..., M, D], k [..., N, D] int8 -> int32 [..., M, N].  Exact: |acc| <= 127^2 * 256 < 2^31."""
+    q [..., M, D], k [..., N, D] int8 -> int32 [..., M, N].  Exact: |acc| <= 127^2 * 256 < 2^31.
+    For D <= 1024 every partial sum is an integer below 2^24, so an fp32 matrix product is exact
+    in any summation order and is used for speed; larger D takes the integer product."""
+    if q_i8.shape[-1] * 127 * 127 < (1 << 24):
+        a, b = q_i8.detach().cpu().float(), k_i8.detach().cpu().float()
+        return torch.matmul(a, b.transpose(-1, -2)).to(torch.int32)
     a = q_i8.detach().cpu().numpy().astype(np.int32)
     b = k_i8.detach().cpu().numpy().astype(np.int32)
     return torch.from_numpy(np.matmul(a, np.swapaxes(b, -1, -2)).astype(np.int32))

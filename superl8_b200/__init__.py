@@ -2,11 +2,11 @@
 
 Public names follow the reference package (reference superl8/__init__.py):
 ``attn_int8_fwd``, ``attn_int8_decode`` (alias ``attn_decode``), ``attn_fp16_fwd``,
-``quantize_i8_rowwise``, ``attn``, and the ``quant`` helpers.
+``quantize_i8_rowwise``, ``attn``, ``attn_ref``, and the ``quant`` helpers.
 """
 
 from . import _C, quant  # noqa: F401
-from .autograd import attn  # noqa: F401
+from .autograd import attn, attn_ref  # noqa: F401
 from .ops import (  # noqa: F401
     attn_decode,
     attn_decode_cached,
@@ -30,7 +30,7 @@ from .quant import (  # noqa: F401
 )
 
 __all__ = [
-    "attn", "attn_decode", "attn_decode_cached", "attn_decode_int8_cache", "quantize_kv_cache", "attn_fp16_fwd", "attn_int8_decode", "attn_int8_fwd",
+    "attn", "attn_ref", "attn_decode", "attn_decode_cached", "attn_decode_int8_cache", "quantize_kv_cache", "attn_fp16_fwd", "attn_int8_decode", "attn_int8_fwd",
     "attn_int8_fwd_host", "attn_int8_varlen", "backward_cuda", "quantize_i8_rowwise", "quantize_int8_rowwise", "quantize_qk", "smooth_k", "detect_q_outlier_domination",
     "LOG2E", "Q_MAX",
 ]

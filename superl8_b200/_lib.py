@@ -146,6 +146,8 @@ SIGNATURES = {
     "sl8_attn_int8_decode_static": (C.c_int, [C.POINTER(DecodeParams), C.c_void_p, C.c_void_p]),
     "sl8_tensor_peak_probe": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_double), C.c_void_p, C.c_size_t, C.c_void_p]),
     "sl8_tensor_peak_probe_n": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "sl8_decode_static_status": (C.c_int, [C.c_void_p]),
+    "sl8_wait_timeout_selftest": (C.c_int, [C.c_void_p, C.c_size_t, C.c_uint64, C.c_void_p]),
     "sl8_read_device_status": (C.c_int, [C.c_void_p, C.c_void_p]),
 }
 

@@ -34,6 +34,35 @@ extern "C" int sl8_read_device_status(void* workspace, void* stream) {
   return host == 0 ? SL8_OK : SL8_ERR_DEVICE_TIMEOUT;
 }
 
+// ---- self-test of the bounded wait ----------------------------------------------------------
+// One block waits, with the kernels' own mbar_wait_limit, on a barrier that nothing ever arrives
+// at; the wait runs out after limit_ns, raises the status word and the kernel returns normally.
+namespace sl8 {
+namespace {
+__global__ void __launch_bounds__(32) wait_selftest_kernel(int* status, unsigned long long limit_ns, int* returned) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  bool ok = true;
+  if (threadIdx.x == 0) ok = mbar_wait_limit(&bar, 0, status, limit_ns);
+  ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+  if (threadIdx.x == 0 && returned != nullptr) *returned = ok ? 1 : 2;   // 2: the wait gave up, as it must
+}
+}  // namespace
+}  // namespace sl8
+
+extern "C" int sl8_wait_timeout_selftest(void* workspace, size_t workspace_bytes, uint64_t limit_ns, void* stream) {
+  if (workspace == nullptr || workspace_bytes < 256) return SL8_ERR_WORKSPACE;
+  if (limit_ns == 0 || limit_ns > 100000000ull) return SL8_ERR_BAD_SHAPE;   // at most 0.1 s
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int* status = reinterpret_cast<int*>(workspace);
+  sl8::wait_selftest_kernel<<<1, 32, 0, s>>>(status, limit_ns, status + 1);
+  return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
+}
+
 namespace {
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,

@@ -22,6 +22,8 @@
 #include "sl8_common.cuh"
 #include "sl8_mma.cuh"
 
+#include <mutex>
+
 namespace sl8 {
 namespace {
 
@@ -138,7 +140,7 @@ __global__ void __launch_bounds__(kDecThreads, D > 128 ? 1 : (V8 ? 3 : 2)) decod
       if (!ok) {
         // let copies already in flight land before the block's shared memory goes away
         for (int i = max(0, issued - C::STAGES); i < issued; ++i)
-          mbar_wait(&full_bar[i % C::STAGES], (i / C::STAGES) & 1, a.status + 1);
+          mbar_wait_quiet(&full_bar[i % C::STAGES], (i / C::STAGES) & 1, kWaitLimitNs);
       }
     }
   } else {
@@ -525,13 +527,16 @@ static __device__ __align__(256) unsigned char g_decode_static_scratch[SL8_DECOD
 namespace {
 constexpr int kMaxStaticDevices = 64;
 void* g_static_scratch_ptr[kMaxStaticDevices] = {nullptr};
+std::mutex g_static_scratch_mutex;
 
 // Device address of the static array on the CURRENT device.  In host code the array's name
-// is only a handle, never a device address, so the address is asked for once per device.
+// is only a handle, never a device address, so the address is asked for once per device
+// (under a lock: two host threads may make their first call on a device together).
 int static_scratch_address(void** out) {
   int dev = 0;
   SL8_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxStaticDevices) return SL8_ERR_TOO_LARGE;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
   if (g_static_scratch_ptr[dev] == nullptr) {
     void* ptr = nullptr;
     SL8_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_decode_static_scratch));
@@ -570,6 +575,9 @@ extern "C" int sl8_attn_int8_decode_static(const sl8_decode_params* p, int32_t* 
   rc = static_scratch_address(&base);
   if (rc != SL8_OK) return rc;
   int* status = device_status ? reinterpret_cast<int*>(device_status) : reinterpret_cast<int*>(base);
+  // The built-in status word starts every call at zero (a memset allocates nothing), so an
+  // expired wait of an earlier call cannot make this one bail out of its waits.
+  if (device_status == nullptr) SL8_CUDA_TRY(cudaMemsetAsync(base, 0, sizeof(int), s));
   float* o_part = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(base) + 256);
   float* m_part = o_part + (size_t)ns * BHq * p->D;
   float* l_part = m_part + (size_t)ns * BHq;
@@ -580,4 +588,11 @@ extern "C" int sl8_attn_int8_decode_static(const sl8_decode_params* p, int32_t* 
     case 256: return launch_decode<256, false>(*p, nullptr, ns, status, o_part, m_part, l_part, s);
   }
   return SL8_ERR_BAD_HEAD_DIM;
+}
+
+extern "C" int sl8_decode_static_status(void* stream) {
+  void* base = nullptr;
+  int rc = static_scratch_address(&base);
+  if (rc != SL8_OK) return rc;
+  return sl8_read_device_status(base, stream);
 }

@@ -109,18 +109,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  Returns false (after raising *status) when the limit expires
 // or when another thread of the grid has already raised the status word, so
 // that every role of a block leaves its loops together.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, int* status,
+                                                unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   unsigned spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 1023u) == 0) {
       if (*reinterpret_cast<volatile int*>(status) != 0) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > limit_ns) {
         atomicExch(status, SL8_ERR_DEVICE_TIMEOUT);
         return false;
       }
     }
+  }
+  return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status) {
+  return mbar_wait_limit(bar, parity, status, kWaitLimitNs);
+}
+// Bounded wait that neither reads nor writes a status word: for the drain of a block that is
+// already leaving on an error and only has to let its own copies in flight land.
+__device__ __forceinline__ bool mbar_wait_quiet(uint64_t* bar, uint32_t parity, unsigned long long limit_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  unsigned spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 1023u) == 0 && globaltimer_ns() - t0 > limit_ns) return false;
   }
   return true;
 }

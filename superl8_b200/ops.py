@@ -3,6 +3,7 @@
 from __future__ import annotations
 
 import math
+import threading
 
 import torch
 
@@ -10,48 +11,94 @@ from . import _C, _lib
 from .quant import (_capturing, k_mean, q_outlier_flag, quantize_q, quantize_qk, smooth_quantize_k,
                     varlen_smooth_quantize_k)
 
-last_gate_decision: bool | None = None  # whether the most recent attn_int8_fwd call was demoted
-last_gate_flag: torch.Tensor | None = None  # device flag of the most recent device-side gate (int32 [1])
+# The outcome of the accuracy gate of the most recent attn_int8_fwd call, kept per (device, stream):
+# calls on different streams or threads do not see each other's decision.  Read it with
+# last_gate(device) -- or through the module attributes ``last_gate_decision`` / ``last_gate_flag``,
+# which answer for the current stream of the current device.
+_gate_lock = threading.Lock()
+_gate_state: dict = {}
+
+
+def _gate_key(device=None):
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    return (idx, torch.cuda.current_stream(device).cuda_stream)
+
+
+def _set_gate(device, decision, flag=None):
+    with _gate_lock:
+        _gate_state[_gate_key(device)] = (decision, flag)
+
+
+def last_gate(device=None):
+    """(decision, flag) of the most recent attn_int8_fwd call on the current stream of ``device``:
+    decision is True (demoted to the full-precision kernel), False (int8 kernel), or None (gate off,
+    skipped under capture, or decided on the device -- then ``flag`` is the int32 [1] device flag)."""
+    if not torch.cuda.is_available():
+        return (None, None)
+    with _gate_lock:
+        return _gate_state.get(_gate_key(device), (None, None))
+
+
+def __getattr__(name):
+    if name == "last_gate_decision":
+        return last_gate()[0]
+    if name == "last_gate_flag":
+        return last_gate()[1]
+    raise AttributeError(name)
+
+
+def _demote(q, k, v, causal, s, window_left, seqlens_q, seqlens_k):
+    """The gate's demotion target: the full-precision kernel (reference superl8/ops.py:120-130)."""
+    if not (v.dtype == q.dtype and k.dtype == q.dtype):
+        q, k = q.to(v.dtype), k.to(v.dtype)
+    return _C.attn_fp16_fwd(q, k, v, causal, s, window_left, None, seqlens_q=seqlens_q, seqlens_k=seqlens_k)
 
 
 def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, int8_pv: bool = False,
                   rotate: bool = False, window_left: int = -1, per_warp_quant: bool = True,
                   internal_accuracy_gate: bool = True, seqlens_q=None, seqlens_k=None,
-                  backend: int = _lib.SL8_BACKEND_AUTO):
+                  backend: int = _lib.SL8_BACKEND_AUTO, expect_demotion: bool | None = None):
     """INT8-QK FlashAttention-2 forward; q, k, v fp16/bf16 [B, H, S, D]; output in v's dtype.
 
     Same contract as the reference entry (superl8/ops.py:70-175): per-row int8 Q and
     smoothed K with exp2-ready folded scales, fp32 softmax, 16-bit P.V, bottom-right
-    aligned causal mask, optional left window.  ``int8_pv=True`` takes the full-W8A8 route
-    instead (V per-channel int8, P re-quantised per tile; ``per_warp_quant`` picks the finer
-    per-32-key P scale; fp16 output; no gate, as in the reference).  The accuracy gate (any Q row with
-    max|q|/median|q| > 12) demotes the whole call to the full-precision kernel; it is
-    evaluated inside the Q quantisation pass (or, right after a demoted call, by a read-only
-    pass before any quantisation) and costs one 4-byte device->host read, skipped during
-    CUDA-graph capture like the reference's.
+    aligned causal mask, optional left window.  The accuracy gate (any Q row with
+    max|q|/median|q| > 12) is asked FIRST, on the original q, and demotes the whole call to the
+    full-precision kernel -- also when ``int8_pv=True``, exactly as the reference orders it
+    (superl8/ops.py:121 before :152).  ``int8_pv=True`` otherwise takes the full-W8A8 route (V
+    per-channel int8, P re-quantised per tile; ``per_warp_quant`` picks the finer per-32-key P
+    scale; fp16 output; no window).  The gate costs one 4-byte device->host read and is skipped
+    during CUDA-graph capture like the reference's.  By default its statistic is gathered inside
+    the Q quantisation pass; when the previous call on this stream was demoted (or
+    ``expect_demotion=True``) a read-only pass asks the gate before anything is quantised, so a
+    stream of demoted calls does not quantise a Q nobody uses.  Both orders give the same result.
     ``internal_accuracy_gate="device"`` (not in the reference) keeps the decision on the GPU: the
     int8 kernel and the full-precision kernel are both launched on the same output and each
     reads the flag the Q pass raised, the one whose turn it is not exits at once.  No host
     read-back, so nothing stalls the stream and the gated call can be captured in a CUDA graph
-    (the reference skips its gate under capture); ``last_gate_flag`` then holds the device flag
-    and ``last_gate_decision`` is None.  Head dims 64/128/256 with one dtype for q, k, v; other
-    cases take the host-side gate.
+    (the reference skips its gate under capture); ``last_gate()`` then returns (None, flag).
+    Head dims 64/128/256 with one dtype for q, k, v; other cases take the host-side gate.
     ``seqlens_q`` / ``seqlens_k`` (int32 [B], not in the reference) give per-sequence
-    lengths for padded ragged batches.
+    lengths for padded ragged batches.  A negative ``scale`` is served by the warp-level
+    backend (the tensor-memory kernel takes row maxima before scaling and wants scale >= 0).
     """
-    global last_gate_decision, last_gate_flag
     s = (1.0 / math.sqrt(q.shape[-1])) if scale is None else scale
+    dev = q.device
     if int8_pv:
-        # reference superl8/ops.py:152-166: no gate on this branch, no window, V per channel
-        if window_left >= 0:
-            raise ValueError("window_left is only supported on the fp16-PV path (int8_pv=False)")
         if seqlens_q is not None or seqlens_k is not None:
             raise ValueError("seqlens are only supported on the fp16-PV path (int8_pv=False)")
+        use_gate = bool(internal_accuracy_gate) and not _capturing()
+        if use_gate and bool(q_outlier_flag(q).item()):
+            _set_gate(dev, True)
+            return _demote(q, k, v, causal, s, window_left, None, None)
+        if window_left >= 0:
+            raise ValueError("window_left is only supported on the fp16-PV path (int8_pv=False)")
         from .quant import quantize_v_perchannel
 
         q_i8, q_scale, k_i8, k_scale, _ = quantize_qk(q, k, softmax_scale=s, rotate=rotate)
         v_i8, v_scale = quantize_v_perchannel(v)
-        last_gate_decision = None
+        _set_gate(dev, False if use_gate else None)
         return _C.attn_w8a8_fwd(q_i8, q_scale.squeeze(-1).contiguous(), k_i8, k_scale.squeeze(-1).contiguous(), v_i8,
                                 v_scale.squeeze(-2).contiguous(), causal,
                                 causal_diag=(k.shape[-2] - q.shape[-2]) if causal else 0, per_warp_quant=per_warp_quant)
@@ -60,23 +107,23 @@ def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, 
             and s >= 0):
         # one library call queues the gate, the prologue and both candidate kernels
         out, flag = _C.attn_int8_fwd_fused(q, k, v, causal, s, window_left, seqlens_q=seqlens_q, seqlens_k=seqlens_k)
-        last_gate_decision, last_gate_flag = None, flag
+        _set_gate(dev, None, flag)
         return out
     internal_accuracy_gate = bool(internal_accuracy_gate)
     use_gate = internal_accuracy_gate and not _capturing()
+    if s < 0 and backend == _lib.SL8_BACKEND_AUTO:
+        backend = _lib.SL8_BACKEND_MMA
     if rotate:
-        if use_gate:
-            _qi, _qs, flag = quantize_q(q, s, want_gate=True)
-            if bool(flag.item()):
-                last_gate_decision = True
-                return _C.attn_fp16_fwd(q, k, v, causal, s, window_left, None, seqlens_q=seqlens_q, seqlens_k=seqlens_k)
+        if use_gate and bool(q_outlier_flag(q).item()):
+            _set_gate(dev, True)
+            return _demote(q, k, v, causal, s, window_left, seqlens_q, seqlens_k)
         q_i8, q_scale, k_i8, k_scale, _ = quantize_qk(q, k, softmax_scale=s, rotate=True, seqlens_k=seqlens_k)
     else:
-        if use_gate and last_gate_decision:
-            # The previous call was demoted: ask the gate first (one read of Q, as the reference
-            # orders it) instead of quantising a Q that is probably not going to be used.
-            flag = q_outlier_flag(q)
-            demote = bool(flag.item())
+        ask_first = last_gate(dev)[0] if expect_demotion is None else expect_demotion
+        if use_gate and ask_first:
+            # ask the gate first (one read of Q, as the reference orders it) instead of quantising a
+            # Q that is probably not going to be used
+            demote = bool(q_outlier_flag(q).item())
             if not demote:
                 q_i8, q_scale, _ = quantize_q(q, s, want_gate=False)
         else:
@@ -84,13 +131,10 @@ def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, 
             q_i8, q_scale, flag = quantize_q(q, s, want_gate=use_gate)
             demote = use_gate and bool(flag.item())
         if demote:
-            last_gate_decision = True
-            if v.dtype == q.dtype and k.dtype == q.dtype:
-                return _C.attn_fp16_fwd(q, k, v, causal, s, window_left, None, seqlens_q=seqlens_q, seqlens_k=seqlens_k)
-            return _C.attn_fp16_fwd(q.to(v.dtype), k.to(v.dtype), v, causal, s, window_left, None,
-                                    seqlens_q=seqlens_q, seqlens_k=seqlens_k)
+            _set_gate(dev, True)
+            return _demote(q, k, v, causal, s, window_left, seqlens_q, seqlens_k)
         k_i8, k_scale, _ = smooth_quantize_k(k, k_mean(k, seqlens_k))
-    last_gate_decision = False if use_gate else None
+    _set_gate(dev, False if use_gate else None)
     return _C.attn_int8_fwd(q_i8, q_scale.squeeze(-1).contiguous(), k_i8, k_scale.squeeze(-1).contiguous(),
                             v.contiguous(), causal, window_left, seqlens_q=seqlens_q, seqlens_k=seqlens_k,
                             backend=backend)

@@ -56,20 +56,55 @@ def outlier_channels(H: int, D: int, seed: int, frac: float = 0.01) -> torch.Ten
     return mask.view(H, D)
 
 
-def prefill_inputs(cfg: PrefillCfg, device, first_unit_batch: int = 0, outliers: bool | None = None):
-    """fp16 Q [B,Hq,S,D], K, V [B,Hkv,S,D] on ``device`` from the device generator, seeded by
-    (configuration, first batch index) so every rank draws its own shard."""
+def _cfg_index(cfg: PrefillCfg) -> int:
+    return int("".join(ch for ch in cfg.name if ch.isdigit())[:1])
+
+
+def _apply_outliers(cfg: PrefillCfg, q, k):
+    """x20 on the seeded 1 % of (head, channel) pairs of q [..., Hq, S, D] and k [..., Hkv, S, D] (in place)."""
+    qm = outlier_channels(cfg.Hq, cfg.D, 7).to(q.device)
+    km = outlier_channels(cfg.Hkv, cfg.D, 8).to(k.device)
+    q.mul_(torch.where(qm, 20.0, 1.0).to(q.dtype).view(cfg.Hq, 1, cfg.D))
+    k.mul_(torch.where(km, 20.0, 1.0).to(k.dtype).view(cfg.Hkv, 1, cfg.D))
+
+
+def prefill_element_cpu(cfg: PrefillCfg, b: int, outliers: bool | None = None, dtype=torch.float16):
+    """Batch element ``b`` of a configuration on the CPU, reproducible anywhere: Q [Hq,S,D], then K, then V
+    [Hkv,S,D] drawn in that order from ``torch.Generator().manual_seed(1000 * cfg + b)``, ~N(0,1), cast to
+    ``dtype``; the outlier channels of cfg3 are applied after the cast.  A (batch, kv-head) unit is the slice
+    q[g*h:g*(h+1)], k[h:h+1], v[h:h+1] with g = Hq / Hkv."""
+    g = torch.Generator().manual_seed(1000 * _cfg_index(cfg) + b)
+    q = torch.randn(cfg.Hq, cfg.S, cfg.D, generator=g).to(dtype)
+    k = torch.randn(cfg.Hkv, cfg.S, cfg.D, generator=g).to(dtype)
+    v = torch.randn(cfg.Hkv, cfg.S, cfg.D, generator=g).to(dtype)
+    if cfg.outliers if outliers is None else outliers:
+        _apply_outliers(cfg, q, k)
+    return q, k, v
+
+
+def prefill_inputs(cfg: PrefillCfg, device, first_unit_batch: int = 0, outliers: bool | None = None,
+                   source: str = "device"):
+    """fp16 Q [B,Hq,S,D], K, V [B,Hkv,S,D] on ``device``.  ``source="device"`` draws from the device
+    generator seeded by (configuration, first batch index) -- fast, what the benchmark times;
+    ``source="cpu"`` stacks prefill_element_cpu(cfg, first_unit_batch + i), the per-element CPU seeds a
+    checker can re-create without the device."""
+    if source == "cpu":
+        els = [prefill_element_cpu(cfg, first_unit_batch + i, outliers) for i in range(cfg.B)]
+        return tuple(torch.stack([e[j] for e in els]).to(device) for j in range(3))
     g = torch.Generator(device=device)
-    g.manual_seed(1000 * int("".join(ch for ch in cfg.name if ch.isdigit())[:1]) + first_unit_batch)
+    g.manual_seed(1000 * _cfg_index(cfg) + first_unit_batch)
     q = torch.randn(cfg.B, cfg.Hq, cfg.S, cfg.D, device=device, dtype=torch.float16, generator=g)
     k = torch.randn(cfg.B, cfg.Hkv, cfg.S, cfg.D, device=device, dtype=torch.float16, generator=g)
     v = torch.randn(cfg.B, cfg.Hkv, cfg.S, cfg.D, device=device, dtype=torch.float16, generator=g)
     if cfg.outliers if outliers is None else outliers:
-        qm = outlier_channels(cfg.Hq, cfg.D, 7).to(device)
-        km = outlier_channels(cfg.Hkv, cfg.D, 8).to(device)
-        q.mul_(torch.where(qm, 20.0, 1.0).to(torch.float16).view(1, cfg.Hq, 1, cfg.D))
-        k.mul_(torch.where(km, 20.0, 1.0).to(torch.float16).view(1, cfg.Hkv, 1, cfg.D))
+        _apply_outliers(cfg, q, k)
     return q, k, v
+
+
+def ragged_lengths(cfg: PrefillCfg, lo: int = 100) -> torch.Tensor:
+    """Per-sequence lengths of the ragged arm of cfg4: uniform in [lo, S] from seed 4004 (int32 [B])."""
+    g = torch.Generator().manual_seed(4004)
+    return torch.randint(lo, cfg.S + 1, (cfg.B,), generator=g, dtype=torch.int32)
 
 
 @dataclass(frozen=True)

@@ -6,13 +6,17 @@ Inputs are seeded; inputs and the reference's outputs are both stored so the tes
 never need the reference.  16-bit floats are stored as raw bit patterns.
 """
 
+import os
 import sys
 from pathlib import Path
 
 import numpy as np
 import torch
 
-ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("SUPERL8_REFERENCE_ROOT")
+if not _root or not (Path(_root) / "superl8").is_dir():
+    sys.exit("usage: python tests/golden/make_golden.py /path/to/reference   (or set SUPERL8_REFERENCE_ROOT)")
+ref_root = Path(_root)
 sys.path.insert(0, str(ref_root))
 sys.path.insert(0, str(ref_root / "tests"))
 

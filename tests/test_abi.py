@@ -151,3 +151,28 @@ def test_ctypes_structs_have_the_layout_the_c_compiler_gives_the_header(tmp_path
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), text, flags=re.S).group(1)
         n_fields = sum(len(decl.split(",")) for decl in body.split(";") if decl.strip())
         assert n_fields == len(cls._fields_), f"{cname}: {n_fields} fields in the header"
+
+
+@pytest.mark.gpu
+def test_bounded_wait_expires_with_a_status_and_leaves_the_context_usable(device):
+    # The one allowed way to see SL8_ERR_DEVICE_TIMEOUT: a one-block self-test waits 1 ms on a barrier
+    # nothing arrives at, with the same wait routine every kernel uses, and returns normally.
+    import torch
+
+    lib = _lib.load()
+    torch.cuda.set_device(device)
+    ws = torch.zeros(64, dtype=torch.int32, device=device)
+    assert lib.sl8_wait_timeout_selftest(C.c_void_p(ws.data_ptr()), 256, 1_000_000, None) == 0
+    torch.cuda.synchronize()
+    assert int(ws[1].item()) == 2                                    # the wait gave up
+    assert lib.sl8_read_device_status(C.c_void_p(ws.data_ptr()), None) == _lib.ERR_DEVICE_TIMEOUT
+    assert lib.sl8_read_device_status(C.c_void_p(ws.data_ptr()), None) == 0   # reading cleared it
+    # limits outside (0, 0.1 s] are refused on the host
+    assert lib.sl8_wait_timeout_selftest(C.c_void_p(ws.data_ptr()), 256, 0, None) == _lib.ERR_BAD_SHAPE
+    assert lib.sl8_wait_timeout_selftest(C.c_void_p(ws.data_ptr()), 256, 10**10, None) == _lib.ERR_BAD_SHAPE
+    # the context is fine: a real kernel runs and is right
+    x = torch.randn(64, 128, device=device, dtype=torch.float16)
+    from superl8_b200 import _C
+    q, s = _C.quantize_i8_rowwise(x)
+    assert torch.equal(s, x.float().abs().amax(-1) * torch.tensor(1.0 / 127.0, dtype=torch.float32, device=device))
+    assert _C.device_status() == 0

@@ -151,3 +151,28 @@ def test_autograd_uses_the_kernels(device):
     rq, rk, rv = oracle.attention_backward_fp32(q, k, v, out.detach(), torch.ones_like(out), True)
     for a, b in ((q.grad, rq), (k.grad, rk), (v.grad, rv)):
         assert oracle.cos_sim(a, b) >= 0.99     # the forward is the int8 one: the reference's bar
+
+
+def test_autograd_with_a_per_channel_key_offset(device):
+    # K smoothing exists for keys with a per-channel mean.  The int8 forward sees k - mean, so its
+    # row statistic lacks scale * q.mean; the wrapper adds it back before the backward (which
+    # recomputes the logits from the unsmoothed k).  Without that every row of P is off by
+    # exp(scale * q.mean) and all three gradients are wrong.
+    q, k, v = oracle.make_batch(47, 1, 4, 2, 192, 64)
+    g = torch.Generator().manual_seed(470)
+    k = (k.float() + 3.0 * torch.randn(1, 2, 1, 64, generator=g)).half()
+    qd, kd, vd = (t.to(device).requires_grad_(True) for t in (q, k, v))
+    out = s8.attn(qd, kd, vd, causal=True)
+    d_out = torch.randn(out.shape, generator=g).half()
+    out.backward(d_out.to(device))
+    oracle.assert_int8_quality(out.detach(), oracle.attention_fp32(q, k, v, causal=True), what="offset-K forward")
+    rq, rk, rv = oracle.attention_backward_fp32(q, k, v, out.detach(), d_out, True)
+    for name, a, b in (("dq", qd.grad, rq), ("dk", kd.grad, rk), ("dv", vd.grad, rv)):
+        assert oracle.cos_sim(a, b) >= 0.99 and oracle.rel_l1(a, b) <= 0.06, (name, oracle.cos_sim(a, b), oracle.rel_l1(a, b))
+
+
+def test_attn_ref_shares_the_analytic_backward(device):
+    # reference superl8/autograd.py:77-108: plain forward + the same gradient formulas, gradcheck-able
+    q, k, v = (torch.randn(1, 2, 6, 8, dtype=torch.float64, device=device, requires_grad=True) for _ in range(3))
+    assert torch.autograd.gradcheck(lambda a, b, c: s8.attn_ref(a, b, c, causal=True), (q, k, v))
+    assert torch.autograd.gradcheck(lambda a, b, c: s8.attn_ref(a, b, c, scale=0.3), (q, k, v))

@@ -290,3 +290,11 @@ def test_host_buffer_entry_point_equals_the_device_one(device):
         assert out.is_pinned() and torch.equal(out, ref), chunk
     with pytest.raises(RuntimeError, match="host tensors"):
         s8.attn_int8_fwd_host(q.to(device), hk, hv)
+
+
+def test_negative_softmax_scale_takes_the_warp_level_kernel(device):
+    # the tensor-memory kernel takes row maxima before scaling (wants scale >= 0); the public entry
+    # routes a negative scale to the mma.sync backend instead of returning a wrong answer
+    q, k, v = oracle.make_batch(78, 1, 4, 2, 200, 128)
+    out = s8.attn_int8_fwd(q.to(device), k.to(device), v.to(device), causal=True, scale=-0.08)
+    oracle.assert_int8_quality(out, oracle.attention_fp32(q, k, v, causal=True, scale=-0.08), what="negative scale")

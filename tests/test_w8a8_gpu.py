@@ -55,3 +55,24 @@ def test_public_int8_pv_route(device):
         z = torch.zeros(1, 1, 8, 96, dtype=torch.int8, device=device)
         _C.attn_w8a8_fwd(z, torch.zeros(1, 1, 8, device=device), z, torch.zeros(1, 1, 8, device=device), z,
                          torch.zeros(1, 1, 96, device=device))
+
+
+def test_int8_pv_is_still_behind_the_accuracy_gate(device):
+    # The reference asks its gate before it looks at int8_pv (superl8/ops.py:121 precedes :152): an
+    # outlier-dominated Q demotes the call to the full-precision kernel on the int8_pv route too.
+    q, k, v = oracle.make_batch(311, 1, 4, 2, 200, 128)
+    q[0, 1, 17, 5] = 70.0
+    assert oracle.detect_q_outlier_domination(q)
+    ref = oracle.attention_fp32(q, k, v, causal=True)
+    out = s8.attn_int8_fwd(q.to(device), k.to(device), v.to(device), causal=True, int8_pv=True)
+    assert s8.ops.last_gate()[0] is True
+    assert oracle.cos_sim(out, ref) >= 0.9999 and oracle.rel_l1(out, ref) <= 5e-3      # the full-precision bar
+    # demoted calls keep the window (the reference returns before its int8_pv window check)
+    outw = s8.attn_int8_fwd(q.to(device), k.to(device), v.to(device), causal=True, int8_pv=True, window_left=64)
+    refw = oracle.attention_fp32(q, k, v, causal=True, window_left=64)
+    assert oracle.cos_sim(outw, refw) >= 0.9999
+    # gate off: the W8A8 kernel runs whatever Q looks like
+    out2 = s8.attn_int8_fwd(q.to(device), k.to(device), v.to(device), causal=True, int8_pv=True,
+                            internal_accuracy_gate=False)
+    assert s8.ops.last_gate()[0] is None and torch.isfinite(out2.float()).all()
+    assert not torch.equal(out2, out)

@@ -57,6 +57,13 @@ def test_static_scratch_decode_matches_workspace_decode(device):
             assert rc == 0, _lib.status_string(rc)
             torch.cuda.synchronize()
             assert int(status.item()) == 0
+            if rep == 1:
+                # without a caller status word the built-in one is used: zeroed by the call, read here
+                out_st2 = torch.full_like(out_st, float("nan"))
+                p2 = _params(dev, B, Hq, Hkv, N, D, out_st2, ns, ldev)
+                assert lib.sl8_attn_int8_decode_static(C.byref(p2), None, None) == 0
+                assert lib.sl8_decode_static_status(None) == 0
+                assert torch.equal(out_st2, out_st)
             # same kernels, same split count -> the tolerance of the decode tests holds with room to spare
             assert torch.isfinite(out_st.float()).all()
             assert oracle.cos_sim(out_st, out_ws) >= 0.99999 and oracle.rel_l1(out_st, out_ws) <= 3e-3
