@@ -213,6 +213,36 @@ typedef struct sl8_fused_fwd_params {
 size_t sl8_attn_int8_fwd_fused_workspace(const sl8_fused_fwd_params* p);
 int sl8_attn_int8_fwd_fused(const sl8_fused_fwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * The same step for tensors in HOST memory (q, k, v, out are host pointers; pinned memory makes
+ * the copies asynchronous and lets the two directions overlap): the call cuts the batch into
+ * chunks of whole (batch, kv-head) units -- consecutive KV heads of one batch element with their
+ * query heads, contiguous in every tensor -- and pipelines host->device copies, the fused step
+ * above (gate decided per chunk on the device, as if the op were called on every chunk) and
+ * device->host copies over a copy-in stream, the caller's stream and a copy-out stream, `slots`
+ * staging slots deep.  The host thread never blocks; on return the caller's stream is ordered
+ * after the last copy-out.  The reference has no such entry: its callers copy tensors to the
+ * device themselves before superl8/ops.py:70-175 runs.
+ * workspace: DEVICE memory, sl8_attn_int8_fwd_host_workspace() bytes (status word at + 0, then
+ * the staging slots); the call allocates nothing on the device.  The first call on a device
+ * creates the two copy streams and the events it keeps (make it before any stream capture).
+ * kv_heads_per_chunk: 0 = choose (about 64 chunks per call, every chunk still filling the GPU);
+ * slots: 0 = 3.  gate_flags (nullable): host int32 [sl8_attn_int8_fwd_host_chunks()], receives every
+ * chunk's gate flag.  Same shape limits as sl8_attn_int8_fwd_fused; no seqlens.
+ */
+typedef struct sl8_host_fwd_params {
+  const void* q; const void* k; const void* v; void* out;   /* HOST pointers, [B, H, S, D] contiguous */
+  int32_t* gate_flags;                                       /* nullable HOST int32 [chunks] */
+  int32_t B, Hq, Hkv, M, N, D;
+  int32_t dtype; int32_t causal; int32_t window_left;
+  float ratio_threshold;
+  double softmax_scale;
+  int32_t kv_heads_per_chunk; int32_t slots;
+} sl8_host_fwd_params;
+size_t sl8_attn_int8_fwd_host_workspace(const sl8_host_fwd_params* p);
+int sl8_attn_int8_fwd_host_chunks(const sl8_host_fwd_params* p);
+int sl8_attn_int8_fwd_host(const sl8_host_fwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- full W8A8 prefill (int8 P.V) ------------------------------------------------------ */
 
 /*

@@ -99,6 +99,15 @@ class VarlenParams(C.Structure):
     ]
 
 
+class HostFwdParams(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p), ("gate_flags", C.c_void_p),
+        ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("M", C.c_int32), ("N", C.c_int32), ("D", C.c_int32),
+        ("dtype", C.c_int32), ("causal", C.c_int32), ("window_left", C.c_int32), ("ratio_threshold", C.c_float),
+        ("softmax_scale", C.c_double), ("kv_heads_per_chunk", C.c_int32), ("slots", C.c_int32),
+    ]
+
+
 class BwdParams(C.Structure):
     _fields_ = [
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("dout", C.c_void_p),
@@ -129,6 +138,9 @@ SIGNATURES = {
     "sl8_attn_fp16_fwd": (C.c_int, [C.POINTER(Fp16FwdParams), C.c_void_p, C.c_size_t, C.c_void_p]),
     "sl8_attn_int8_fwd_fused_workspace": (C.c_size_t, [C.POINTER(FusedFwdParams)]),
     "sl8_attn_int8_fwd_fused": (C.c_int, [C.POINTER(FusedFwdParams), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "sl8_attn_int8_fwd_host_workspace": (C.c_size_t, [C.POINTER(HostFwdParams)]),
+    "sl8_attn_int8_fwd_host_chunks": (C.c_int, [C.POINTER(HostFwdParams)]),
+    "sl8_attn_int8_fwd_host": (C.c_int, [C.POINTER(HostFwdParams), C.c_void_p, C.c_size_t, C.c_void_p]),
     "sl8_attn_w8a8_fwd": (C.c_int, [C.POINTER(W8A8Params), C.c_void_p]),
     "sl8_attn_int8_varlen": (C.c_int, [C.POINTER(VarlenParams), C.c_void_p, C.c_size_t, C.c_void_p]),
     "sl8_k_mean_packed": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int32, C.c_int64, C.c_void_p, C.c_int32,

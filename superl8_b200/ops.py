@@ -141,19 +141,35 @@ def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, 
 
 
 _aux_streams: dict = {}
+_host_ws: dict = {}      # per device: the staging workspace of attn_int8_fwd_host, kept between calls
 
 
-def attn_int8_fwd_host(q, k, v, out=None, *, chunk_batch: int | None = None, staging_slots: int = 2, **kw):
+def _host_workspace(dev, nbytes: int) -> torch.Tensor:
+    buf = _host_ws.get(dev.index)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        _host_ws[dev.index] = buf
+    return buf
+
+
+def attn_int8_fwd_host(q, k, v, out=None, *, chunk_batch: int | None = None, staging_slots: int = 3,
+                       kv_heads_per_chunk: int = 0, gate_flags=None, **kw):
     """attn_int8_fwd for tensors that live in (pinned) host memory: q, k, v fp16/bf16 [B, H, S, D]
     on the CPU, result written to ``out`` (pinned CPU tensor, allocated when None) and returned.
 
-    Batch elements are independent units, so the batch is cut into chunks of ``chunk_batch``
-    (default: B / 16, at least 1) that travel through three streams -- host->device copies, the
-    prologue + attention kernels on the caller's current stream, device->host copies -- with two
-    device staging slots, so that the two copy directions and the kernels overlap.  The accuracy
-    gate is evaluated per chunk (the same as calling the op on every chunk).  The caller's stream
-    is ordered after the last device->host copy on return; the copies themselves are asynchronous
-    for pinned tensors.  Keyword arguments are those of attn_int8_fwd (no seqlens)."""
+    (batch, kv-head) units are independent, so the call is cut into chunks of whole units that
+    travel through three streams -- host->device copies, prologue + attention kernels on the
+    caller's current stream, device->host copies -- ``staging_slots`` deep, so that both copy
+    directions and the kernels overlap.  The accuracy gate is evaluated per chunk (the same as
+    calling the op on every chunk).  The caller's stream is ordered after the last device->host
+    copy on return; the copies are asynchronous for pinned tensors and the host thread never waits.
+
+    The pipeline runs inside the library (sl8_attn_int8_fwd_host: one call, gate decided on the
+    device, staging slots kept per device between calls) for head dims 64/128/256, one 16-bit dtype,
+    scale >= 0 and the keyword arguments causal / scale / window_left / internal_accuracy_gate
+    (True, False or "device"; the host-side gate does not exist here).  ``gate_flags`` (pinned int32
+    [chunks], optional) receives every chunk's gate flag.  Anything else (rotate, int8_pv, an
+    explicit ``chunk_batch``) takes a Python loop over batch chunks with the same three streams."""
     if q.is_cuda or k.is_cuda or v.is_cuda:
         raise RuntimeError("superl8_b200 attn_int8_fwd_host: q, k, v must be host tensors (see attn_int8_fwd)")
     if not torch.cuda.is_available():
@@ -163,6 +179,31 @@ def attn_int8_fwd_host(q, k, v, out=None, *, chunk_batch: int | None = None, sta
     if out is None:
         out = torch.empty(q.shape, dtype=v.dtype).pin_memory()
     if B == 0 or q.numel() == 0:
+        return out
+    known = {"causal", "scale", "window_left", "internal_accuracy_gate"}
+    s = kw.get("scale")
+    s = (1.0 / math.sqrt(q.shape[-1])) if s is None else float(s)
+    if (chunk_batch is None and set(kw) <= known and q.dim() == 4 and q.shape[-1] in (64, 128, 256)
+            and q.dtype == k.dtype == v.dtype == out.dtype and q.dtype in (torch.float16, torch.bfloat16)
+            and k.shape[-2] > 0 and s >= 0 and all(t.is_contiguous() for t in (q, k, v, out))):
+        gate = kw.get("internal_accuracy_gate", True)
+        p = _lib.HostFwdParams(
+            q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(),
+            gate_flags=None if gate_flags is None else gate_flags.data_ptr(),
+            B=B, Hq=q.shape[1], Hkv=k.shape[1], M=q.shape[2], N=k.shape[2], D=q.shape[3], dtype=_C._DTYPE[q.dtype],
+            causal=int(bool(kw.get("causal", False))), window_left=int(kw.get("window_left", -1)),
+            ratio_threshold=12.0 if gate else 0.0, softmax_scale=s, kv_heads_per_chunk=int(kv_heads_per_chunk),
+            slots=int(staging_slots))
+        lib = _lib.load()
+        n_chunks = int(lib.sl8_attn_int8_fwd_host_chunks(p))
+        if gate_flags is not None and (gate_flags.dtype != torch.int32 or gate_flags.numel() < n_chunks or gate_flags.is_cuda):
+            raise RuntimeError(f"superl8_b200 attn_int8_fwd_host: gate_flags must be a host int32 tensor of >= {n_chunks}")
+        with torch.cuda.device(dev):
+            nbytes = int(lib.sl8_attn_int8_fwd_host_workspace(p))
+            ws = _host_workspace(dev, nbytes)
+            rc = lib.sl8_attn_int8_fwd_host(p, ws.data_ptr(), ws.numel(), _C._stream(dev))
+        _lib.check(rc, "attn_int8_fwd_host", n_chunks * (5 + (1 if gate else 0)))
+        _set_gate(dev, None, None)
         return out
     nb = max(1, B // 16) if chunk_batch is None else max(1, int(chunk_batch))
     cur = torch.cuda.current_stream(dev)

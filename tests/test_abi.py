@@ -116,7 +116,7 @@ STRUCTS = {
     "sl8_fwd_params": _lib.FwdParams, "sl8_fp16_fwd_params": _lib.Fp16FwdParams,
     "sl8_decode_params": _lib.DecodeParams, "sl8_w8a8_params": _lib.W8A8Params,
     "sl8_varlen_params": _lib.VarlenParams, "sl8_bwd_params": _lib.BwdParams,
-    "sl8_fused_fwd_params": _lib.FusedFwdParams,
+    "sl8_fused_fwd_params": _lib.FusedFwdParams, "sl8_host_fwd_params": _lib.HostFwdParams,
 }
 
 

@@ -290,6 +290,23 @@ def test_host_buffer_entry_point_equals_the_device_one(device):
         assert out.is_pinned() and torch.equal(out, ref), chunk
     with pytest.raises(RuntimeError, match="host tensors"):
         s8.attn_int8_fwd_host(q.to(device), hk, hv)
+    # the in-library pipeline (sl8_attn_int8_fwd_host): chunks of one KV head, two to four staging slots,
+    # per-chunk gate flags; a chunk with an outlier row is demoted on the device, the others are not
+    q2 = q.clone()
+    q2[3, 2, 17, 5] = 70.0                                  # batch 3, query head 2 -> KV head 1
+    hq2 = q2.pin_memory()
+    for kvc, slots in ((1, 2), (1, 4), (2, 3)):
+        flags = torch.full((16,), -1, dtype=torch.int32).pin_memory()
+        out = s8.attn_int8_fwd_host(hq2, hk, hv, causal=True, kv_heads_per_chunk=kvc, staging_slots=slots, gate_flags=flags)
+        torch.cuda.synchronize()
+        n_chunks = 5 * (2 // kvc)
+        hit = 3 * (2 // kvc) + (1 if kvc == 1 else 0)
+        assert [int(f != 0) for f in flags[:n_chunks]] == [int(i == hit) for i in range(n_chunks)], (kvc, flags)
+        assert torch.equal(out[:3], ref[:3]) and torch.equal(out[4:], ref[4:])
+        full = oracle.attention_fp32(q2[3:4], k[3:4], v[3:4], causal=True)
+        sel = slice(0, 4) if kvc == 2 else slice(2, 4)       # the demoted chunk: full-precision bar
+        assert oracle.cos_sim(out[3:4, sel], full[:, sel]) >= 0.9999
+    assert _C.device_status() == 0
 
 
 def test_negative_softmax_scale_takes_the_warp_level_kernel(device):
