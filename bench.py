@@ -243,7 +243,7 @@ def run_reference(args, cfg):
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(cfg, args, 1),
+        "config": workload_config(cfg, args, max(1, args.gpus)),
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -295,6 +295,70 @@ def run_kernel_case(args):
                 s8.attn_decode_int8_cache(dq, dk8, dks, dv, context_lens=dlens)
     torch.cuda.synchronize()
     print(f"kernel-case {args.kernel_case}: {n} launches, device status {_C.device_status()}", file=sys.stderr)
+
+
+def shard_check(world, rank, dev):
+    """One small batch computed sharded over the ranks, all-gathered over NCCL and compared BITWISE with
+    the same batch computed whole on this GPU (outside every timed region): prefill through the public
+    entry and ragged decode against a quantised cache.  Units are independent, so the two must be equal."""
+    import torch.distributed as dist
+    import superl8_b200 as s8
+    from superl8_b200 import quant, shard, workloads
+    c = workloads.PrefillCfg("cfg1_check", 8, 16, 4, 512, 128, True)
+    q, k, v = workloads.prefill_inputs(c, dev, source="cpu")
+    whole = s8.attn_int8_fwd(q, k, v, causal=True)
+    b_rng, _ = shard.batch_range(c.B, c.Hkv, min(world, c.B), rank % min(world, c.B))
+    sl = slice(b_rng.start, b_rng.stop)
+    local = s8.attn_int8_fwd(q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous(), causal=True)
+    ok_p = torch.equal(shard.gather_batch(local), whole) if world <= c.B else True
+    g = torch.Generator().manual_seed(5151)
+    lens = torch.randint(300, 3000, (8,), generator=g, dtype=torch.int32)
+    n_max = int(lens.max())
+    dq = torch.randn(8, 16, 1, 128, generator=g).half().to(dev)
+    kk = torch.randn(8, 4, n_max, 128, generator=g).half().to(dev)
+    dv = torch.randn(8, 4, n_max, 128, generator=g).half().to(dev)
+    ldev = lens.to(dev)
+    k_i8, k_s, _ = quant.smooth_quantize_k(kk, quant.k_mean(kk, ldev))
+    k_s = k_s.squeeze(-1).contiguous()
+    whole_d = s8.attn_decode_int8_cache(dq, k_i8, k_s, dv, context_lens=ldev)
+    local_d = s8.attn_decode_int8_cache(dq[sl].contiguous(), k_i8[sl].contiguous(), k_s[sl].contiguous(),
+                                        dv[sl].contiguous(), context_lens=ldev[sl].contiguous())
+    ok_d = torch.equal(shard.gather_batch(local_d), whole_d) if world <= 8 else True
+    flag = torch.tensor([int(ok_p), int(ok_d)], device=dev)
+    if world > 1:
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    ok_p, ok_d = bool(flag[0].item()), bool(flag[1].item())
+    return {"prefill": "bitwise equal" if ok_p else "MISMATCH", "decode": "bitwise equal" if ok_d else "MISMATCH",
+            "how": f"B8 Hq16 Hkv4 S512 D128 causal prefill and 8 ragged decode sequences: {min(world, 8)} shards, "
+                   f"all_gather ({'nccl' if world > 1 else 'single rank'}), torch.equal with the unsharded result"}
+
+
+def copy_bandwidth(hin, din, dout, hout, world, reps=3):
+    """Pinned host <-> device copy rates of this step's buffers, per direction and both at once
+    (GB/s per GPU, from the slowest rank's time): the floor under the end-to-end step."""
+    import torch.distributed as dist
+    from superl8_b200 import shard
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    res = {}
+    for name, do_in, do_out in (("h2d_only", True, False), ("d2h_only", False, True), ("both", True, True)):
+        best = None
+        for _ in range(reps):
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            t0 = time.perf_counter()
+            if do_in:
+                with torch.cuda.stream(s_in):
+                    din.copy_(hin, non_blocking=True)
+            if do_out:
+                with torch.cuda.stream(s_out):
+                    hout.copy_(dout, non_blocking=True)
+            torch.cuda.synchronize()
+            dt = shard.max_over_ranks(time.perf_counter() - t0, device="cuda")
+            best = dt if best is None else min(best, dt)
+        nbytes = (hin.numel() * hin.element_size() if do_in else 0) + (hout.numel() * hout.element_size() if do_out else 0)
+        res[name] = {"gbs_per_gpu": nbytes / best / 1e9, "ms": best * 1e3}
+    return res
 
 
 def workload_config(cfg, args, world):
@@ -410,7 +474,11 @@ def main():
 
     ms_e2e = timed(step_e2e, args.steps, args.warmup, world)
     e2e = {"value": total_ops / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
-           "h2d_bytes_per_step": sum(t.numel() * 2 for t in (hq, hk, hv)), "d2h_bytes_per_step": hout.numel() * 2 + 4}
+           "h2d_bytes_per_step": sum(t.numel() * 2 for t in (hq, hk, hv)), "d2h_bytes_per_step": hout.numel() * 2,
+           "entry": "sl8_attn_int8_fwd_host (chunks of (batch, kv-head) units on three streams, gate on the device)"}
+    if not args.skip_extras:
+        # what the PCIe link gives this step's buffers: Q alone in (2.1 GB), the output alone out, both at once
+        e2e["copy_bandwidth"] = copy_bandwidth(hq, q, out, hout, world)
 
     # DRAM traffic per launch from the ncu captures summarised under profiles/ (a B = 2 slice of
     # cfg3 for prefill, 1 M rows for the quantiser, 16 sequences for decode), scaled to this launch
@@ -452,6 +520,18 @@ def main():
         line["int8_path"] = {"value": total_ops / (ms8 * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms8,
                              "gate": "off", "roofline": r8}
         del out
+        # ---- the experiment the configurations describe: ONE global batch, sharded over the GPUs ----
+        b_rng, _h = shard.batch_range(cfg.B, cfg.Hkv, min(world, cfg.B), rank % min(world, cfg.B))
+        qs_, ks_, vs_ = (t[b_rng.start:b_rng.stop] for t in (q, k, v))
+        ms_s = timed(lambda: s8.attn_int8_fwd(qs_, ks_, vs_, causal=cfg.causal, internal_accuracy_gate=gate),
+                     args.steps, args.warmup, world)
+        v_s = cfg.ops / (ms_s * 1e-3) / 1e12
+        line["strong"] = {"prefill": {"value": v_s, "unit": UNIT, "ms_per_step": ms_s, "global_batch": cfg.B,
+                                      "per_gpu_batch": len(b_rng), "split": "shard.batch_range: whole batch elements per rank",
+                                      "efficiency_vs_one_gpu": v_s / value if world > 1 else 1.0,
+                                      "efficiency_note": "strong value / weak value of this run (weak value = N x one GPU's "
+                                                         "throughput on the full batch)"}}
+        del qs_, ks_, vs_
         # ---- quantiser (Q prologue with the gate statistic, on cfg3's Q) ----
         qbytes = q.numel() * 3 + (q.numel() // cfg.D) * 4
         msq = timed(lambda: quant.quantize_q(q, 0.0884, want_gate=True), args.steps, args.warmup, world)
@@ -483,6 +563,20 @@ def main():
                                        "peak_source": peaks["source"] + " copy bandwidth",
                                        "traffic": 794.5e6 / 775.8e6 * dbytes},
                           "device_status": _C.device_status()}
+        # strong decode: the 128 sequences of the ONE global batch, longest-first balanced over the ranks
+        owned = shard.balance_by_length(lens.tolist(), world)[rank]
+        if world > 1:
+            idx = torch.tensor(owned, device=dev)
+            sq, sk8, sks, sv, sl_ = (t.index_select(0, idx).contiguous() for t in (dq, dk8, dks, dv, dlens))
+        else:
+            sq, sk8, sks, sv, sl_ = dq, dk8, dks, dv, dlens
+        msds = timed(lambda: s8.attn_decode_int8_cache(sq, sk8, sks, sv, context_lens=sl_), max(args.steps, 10),
+                     args.warmup, world)
+        gds = dbytes / (msds * 1e-3) / 1e9
+        line["strong"]["decode"] = {"value": gds, "unit": "GB/s", "ms_per_step": msds, "global_sequences": dcfg.B,
+                                    "per_gpu_sequences": len(owned), "split": "shard.balance_by_length (longest first)",
+                                    "efficiency_vs_one_gpu": gds / gd if world > 1 else 1.0}
+        del sq, sk8, sks, sv, sl_
         # ---- the same decode against an int8 V cache (per-channel scales): D + 4 + D bytes per key ----
         dv8, dvs = quant.quantize_v_perchannel(dv)
         dvs = dvs.squeeze(-2).contiguous()
@@ -522,6 +616,7 @@ def main():
                                                     "accumulators in tensor memory)"}}
         del bq, bk, bv, bdo, bout, blse
 
+    line["shard_check"] = shard_check(world, rank, dev)
     if rank == 0 and world == 1:
         try:
             torch.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))

@@ -16,6 +16,33 @@ import torch
 
 from . import _lib
 
+# Two bindings serve the reference's six compiled operators (quantize_i8_rowwise, attn_int8_fwd,
+# attn_int8_fwd_train, attn_fp16_fwd, attn_bwd, attn_int8_decode): the compiled torch extension
+# ``_C_ext`` (csrc/torch_ext, built by ``python -m superl8_b200.build``) when it is present, and
+# ctypes otherwise.  Both end in the same C-ABI calls.  Calls that use an argument the reference's
+# operators do not have (seqlens, backend, out, gate_flag, context_lens) always take ctypes.
+try:
+    from . import _C_ext as _ext
+except ImportError:          # not built: the ctypes binding serves everything
+    _ext = None
+BINDING = "compiled" if _ext is not None else "ctypes"
+
+
+def use_binding(name: str) -> str:
+    """Selects "compiled" or "ctypes" for the six reference operators; returns the previous choice."""
+    global BINDING
+    if name not in ("compiled", "ctypes"):
+        raise ValueError(name)
+    if name == "compiled" and _ext is None:
+        raise RuntimeError("superl8_b200: the compiled extension _C_ext is not built (python -m superl8_b200.build)")
+    prev, BINDING = BINDING, name
+    return prev
+
+
+def _compiled() -> bool:
+    return BINDING == "compiled"
+
+
 _DTYPE = {torch.float16: _lib.SL8_F16, torch.bfloat16: _lib.SL8_BF16, torch.float32: _lib.SL8_F32}
 _status_ws: dict = {}
 _decode_ws: dict = {}
@@ -61,12 +88,18 @@ def device_status(device=None) -> int:
     bws = _bwd_ws.get((device.index, torch.cuda.current_stream(device).cuda_stream))
     if rc == 0 and bws is not None:
         rc = lib.sl8_read_device_status(_ptr(bws), _stream(device))
+    if rc == 0 and _ext is not None:
+        rc = int(_ext.device_status(torch.empty(0, device=device)))
     return rc
 
 
 def quantize_i8_rowwise(x: torch.Tensor):
     """x [M, K] fp16/bf16/fp32 -> (q int8 [M, K], scale fp32 [M]).
     Reference binding: csrc/fni8_api.cpp:286-291; op csrc/kernel/quant_rowwise.cu:84-121."""
+    if _compiled():
+        r = _ext.quantize_i8_rowwise(x)
+        _lib.launches += 1 if x.numel() else 0
+        return r
     _check(x.is_cuda, "superl8_b200 quantize_i8_rowwise: x must be a CUDA tensor")
     _check(x.dim() == 2, "superl8_b200 quantize_i8_rowwise: expect [M, K]")
     _check(x.dtype in _DTYPE, "superl8_b200 quantize_i8_rowwise: x must be float16, bfloat16 or float32")
@@ -140,12 +173,21 @@ def attn_int8_fwd(q, q_scale, k, k_scale, v, causal=False, window_left=-1, *, se
     """Reference binding csrc/fni8_api.cpp:225-229 (op csrc/kernel/attn_int8_fwd.cu:185-190).
     ``out`` (optional) receives the result; ``gate_flag`` (int32 CUDA tensor, optional) makes the
     launch conditional on the device: the kernel works only if (flag != 0) == gate_want."""
+    if (_compiled() and seqlens_q is None and seqlens_k is None and backend == _lib.SL8_BACKEND_AUTO and out is None
+            and gate_flag is None):
+        r = _ext.attn_int8_fwd(q, q_scale, k, k_scale, v, bool(causal), int(window_left))
+        _lib.launches += 1 if r.numel() else 0
+        return r
     return _run_fwd(q, q_scale, k, k_scale, v, causal, False, window_left, seqlens_q, seqlens_k, backend,
                     out, gate_flag, gate_want)[0]
 
 
 def attn_int8_fwd_train(q, q_scale, k, k_scale, v, causal=False, *, backend=_lib.SL8_BACKEND_AUTO):
     """Also returns the natural-log LSE.  Reference binding csrc/fni8_api.cpp:230-233."""
+    if _compiled() and backend == _lib.SL8_BACKEND_AUTO:
+        r = _ext.attn_int8_fwd_train(q, q_scale, k, k_scale, v, bool(causal))
+        _lib.launches += 1 if r[0].numel() else 0
+        return r
     return _run_fwd(q, q_scale, k, k_scale, v, causal, True, -1, None, None, backend)
 
 
@@ -235,6 +277,17 @@ def attn_fp16_fwd(q, k, v, causal=False, scale=None, window_left=-1, mask=None, 
     return the natural-log row sums [B, H, M] (what the backward consumes).  ``out`` / ``gate_flag`` /
     ``gate_want``: as in attn_int8_fwd (conditional launch decided on the device)."""
     what = "superl8_b200 fp16 fwd"
+    if (_compiled() and seqlens_q is None and seqlens_k is None and backend == _lib.SL8_BACKEND_AUTO and out is None
+            and gate_flag is None):
+        sc_ = None if scale is None else float(scale)
+        if want_lse and mask is None and window_left < 0:
+            r = _ext.attn_fp16_fwd_train(q, k, v, bool(causal), sc_)
+            _lib.launches += 1 if r[0].numel() else 0
+            return r
+        if not want_lse:
+            r = _ext.attn_fp16_fwd(q, k, v, bool(causal), sc_, int(window_left), mask)
+            _lib.launches += 1 if r.numel() else 0
+            return r
     _check_cuda(q, k, v)
     _check(q.dtype in (torch.float16, torch.bfloat16), f"{what}: q must be float16 or bfloat16")
     _check(k.dtype == q.dtype and v.dtype == q.dtype, f"{what}: q, k, v must share one dtype")
@@ -293,6 +346,10 @@ def _decode_workspace(device, nbytes: int) -> torch.Tensor:
 def attn_int8_decode(q, q_scale, k, k_scale, v, num_splits=-1, *, context_lens=None):
     """Reference binding csrc/fni8_api.cpp:260-263 (op csrc/kernel/attn_decode.cu:163-240)."""
     what = "superl8_b200 decode"
+    if _compiled() and context_lens is None:
+        r = _ext.attn_int8_decode(q, q_scale, k, k_scale, v, int(num_splits))
+        _lib.launches += 2 if (r.numel() and k.shape[2] > 0) else 0
+        return r
     B, H, Hkv, M, N, D = _fwd_checks(q, q_scale, k, k_scale, v, what)
     _check(v.dtype == torch.float16, f"{what}: v must be float16")
     _check(M == 1, f"{what}: query length M must be 1 (decode)")
@@ -422,6 +479,10 @@ def attn_bwd(q, k, v, o, do_, lse, scale, causal=False, *, backend=_lib.SL8_BACK
     natural-log row sums ``lse`` [B, Hq, M] and the output gradient ``do_``.  q, o, do_
     [B, Hq, M, D]; k, v [B, Hkv, N, D]; dk / dv are summed over the query heads of a KV head."""
     what = "superl8_b200 bwd"
+    if _compiled() and backend == _lib.SL8_BACKEND_AUTO:
+        r = _ext.attn_bwd(q, k, v, o, do_, lse, float(scale), bool(causal))
+        _lib.launches += 3 if (q.numel() and k.numel()) else 0
+        return r
     for t in (q, k, v, o, do_, lse):
         _check(t.is_cuda, f"{what}: all inputs must be CUDA")
         _check(t.device == q.device, f"{what}: all inputs must be on the same device")

@@ -69,5 +69,46 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+EXT_SRC = CSRC / "torch_ext" / "sl8_torch_ext.cpp"
+EXT_NAME = "_C_ext"
+
+
+def ext_path() -> Path:
+    import sysconfig
+    return PKG_DIR / (EXT_NAME + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
+
+
+def build_torch_ext(force: bool = False) -> Path:
+    """Compiles the thin torch extension (csrc/torch_ext) with g++ against the installed torch and
+    links it to libsuperl8_b200.so; the result sits beside the library (in-tree, nothing goes to a
+    JIT cache).  Needs no GPU and no nvcc, only the CUDA headers torch's own headers include."""
+    import sysconfig
+
+    import torch
+    from torch.utils import cpp_extension as ce
+
+    out = ext_path()
+    hdr = PKG_DIR.parent / "include" / "superl8_b200.h"
+    if out.exists() and not force and out.stat().st_mtime > max(EXT_SRC.stat().st_mtime, hdr.stat().st_mtime):
+        return out
+    build()  # the extension links against the library
+    cuda_home = os.environ.get("CUDA_HOME") or "/usr/local/cuda"
+    incs = [*ce.include_paths(), sysconfig.get_paths()["include"], str(Path(cuda_home) / "include")]
+    torch_lib = str(Path(torch.__file__).resolve().parent / "lib")
+    cmd = [os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
+           f"-DTORCH_EXTENSION_NAME={EXT_NAME}", "-DTORCH_API_INCLUDE_EXTENSION_H",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           *[f"-I{i}" for i in incs], str(EXT_SRC), "-o", str(out),
+           f"-L{torch_lib}", f"-L{PKG_DIR}", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
+           f"-L{Path(cuda_home) / 'lib64'}", "-lcudart", "-l:libsuperl8_b200.so",
+           "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{torch_lib}"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("torch extension build failed: " + " ".join(cmd) + "\n" + r.stdout + r.stderr)
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--no-ext" not in sys.argv:
+        print(build_torch_ext(force="--force" in sys.argv))

@@ -111,6 +111,16 @@ def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, 
         return out
     internal_accuracy_gate = bool(internal_accuracy_gate)
     use_gate = internal_accuracy_gate and not _capturing()
+    if (_C._compiled() and not rotate and seqlens_q is None and seqlens_k is None and backend == _lib.SL8_BACKEND_AUTO
+            and q.is_cuda and q.dim() == 4 and q.dtype == k.dtype == v.dtype and q.dtype in (torch.float16, torch.bfloat16)):
+        # the whole step in one call of the compiled extension (same kernels, same order, same gate read)
+        ask_first = last_gate(dev)[0] if expect_demotion is None else expect_demotion
+        out, demoted = _C._ext.attn_int8_prefill(q, k, v, bool(causal), float(s), int(window_left), use_gate,
+                                                 bool(use_gate and ask_first))
+        if out.numel():
+            _lib.launches += 2 if demoted else (6 if (use_gate and ask_first) else 5)
+        _set_gate(dev, bool(demoted) if use_gate else None)
+        return out
     if s < 0 and backend == _lib.SL8_BACKEND_AUTO:
         backend = _lib.SL8_BACKEND_MMA
     if rotate:

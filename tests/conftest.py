@@ -30,6 +30,30 @@ def _seed():
     torch.manual_seed(0)
 
 
+# The reference's six compiled operators have two bindings here (the compiled torch extension and
+# ctypes, superl8_b200/_C.py); the GPU tests of these modules run once through each.
+BOTH_BINDINGS = {"test_fwd_gpu", "test_decode_gpu", "test_bwd_gpu", "test_quant_gpu", "test_reference_cases_gpu"}
+
+
+def pytest_generate_tests(metafunc):
+    if metafunc.module.__name__ in BOTH_BINDINGS and "_sl8_binding" in metafunc.fixturenames:
+        metafunc.parametrize("_sl8_binding", ["compiled", "ctypes"], indirect=True)
+
+
+@pytest.fixture(autouse=True)
+def _sl8_binding(request):
+    name = getattr(request, "param", None)
+    if name is None:
+        yield
+        return
+    from superl8_b200 import _C
+    if name == "compiled" and _C._ext is None:
+        pytest.skip("the compiled extension is not built")
+    prev = _C.use_binding(name)
+    yield
+    _C.use_binding(prev)
+
+
 @pytest.fixture(scope="session")
 def device():
     assert torch.cuda.is_available()
