@@ -100,7 +100,7 @@ def build_torch_ext(force: bool = False) -> Path:
            f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
            *[f"-I{i}" for i in incs], str(EXT_SRC), "-o", str(out),
            f"-L{torch_lib}", f"-L{PKG_DIR}", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
-           f"-L{Path(cuda_home) / 'lib64'}", "-lcudart", "-l:libsuperl8_b200.so",
+           "-l:libsuperl8_b200.so",
            "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{torch_lib}"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:

@@ -11,6 +11,7 @@
 #include <cmath>
 #include <map>
 #include <mutex>
+#include <string>
 #include <tuple>
 #include <utility>
 
@@ -22,6 +23,7 @@ using at::Tensor;
 
 struct PerStream {
   Tensor status;      // 256 bytes: the status word of the bounded device-side waits
+  Tensor gate_flag;   // int32 [1]: the accuracy gate's device flag
   Tensor decode_ws;   // split partials of the decode, grown on demand
 };
 std::mutex g_mu;
@@ -34,12 +36,19 @@ PerStream& per_stream(const Tensor& like) {
   const auto key = std::make_pair(dev, reinterpret_cast<uintptr_t>(stream_of(like)));
   std::lock_guard<std::mutex> lock(g_mu);
   PerStream& ps = g_cache[key];
-  if (!ps.status.defined()) ps.status = at::zeros({64}, like.options().dtype(at::kInt));
+  if (!ps.status.defined()) {
+    ps.status = at::zeros({64}, like.options().dtype(at::kInt));
+    ps.gate_flag = at::zeros({1}, like.options().dtype(at::kInt));
+  }
   return ps;
 }
 
+// Numbers go into messages through std::to_string: streaming an int into c10::str from this module
+// crashed on a GPU box (number formatting through locale facets), strings do not.  The module also
+// calls nothing of the CUDA runtime itself (flags are read and cleared through tensor methods), so
+// it links torch and the library only.
 void check_rc(int rc, const char* what) {
-  TORCH_CHECK(rc == SL8_OK, "superl8_b200 ", what, ": ", sl8_status_string(rc), " (status ", rc, ")");
+  TORCH_CHECK(rc == SL8_OK, "superl8_b200 ", what, ": ", sl8_status_string(rc), " (status ", std::to_string(rc), ")");
 }
 
 int dtype_code(const Tensor& t, const char* what) {
@@ -92,7 +101,7 @@ std::tuple<Tensor, Tensor> run_fwd(const Tensor& q, const Tensor& q_scale, const
   const Dims d = fwd_checks(q, q_scale, k, k_scale, v, what);
   TORCH_CHECK(v.scalar_type() == at::kHalf || v.scalar_type() == at::kBFloat16, what, ": v must be float16 or bfloat16");
   TORCH_CHECK(d.D == 32 || d.D == 64 || d.D == 72 || d.D == 80 || d.D == 128 || d.D == 256, what,
-              ": head dim must be 32/64/72/80/128/256, got ", d.D);
+              ": head dim must be 32/64/72/80/128/256, got ", std::to_string(d.D));
   const c10::cuda::CUDAGuard guard(q.device());
   Tensor out = at::empty({d.B, d.H, d.M, d.D}, v.options());
   Tensor lse = want_lse ? at::empty({d.B, d.H, d.M}, q.options().dtype(at::kFloat)) : at::empty({0}, q.options().dtype(at::kFloat));
@@ -136,7 +145,7 @@ std::tuple<Tensor, Tensor> run_fp16(const Tensor& q_in, const Tensor& k_in, cons
   TORCH_CHECK(Hkv > 0 && H % Hkv == 0, what, ": H_q must be divisible by H_kv (GQA)");
   TORCH_CHECK(k.size(3) == D && v.size(3) == D && v.size(2) == N, what, ": K/V shape mismatch");
   TORCH_CHECK(D == 32 || D == 64 || D == 72 || D == 80 || D == 128 || D == 256, what,
-              ": head dim must be 32/64/72/80/128/256, got ", D);
+              ": head dim must be 32/64/72/80/128/256, got ", std::to_string(D));
   sl8_fp16_fwd_params p{};
   if (mask.has_value() && mask->defined()) {
     const Tensor& m = *mask;
@@ -186,10 +195,10 @@ Tensor attn_int8_decode(const Tensor& q, const Tensor& q_scale, const Tensor& k,
   const Dims d = fwd_checks(q, q_scale, k, k_scale, v, what);
   TORCH_CHECK(v.scalar_type() == at::kHalf, what, ": v must be float16");
   TORCH_CHECK(d.M == 1, what, ": query length M must be 1 (decode)");
-  TORCH_CHECK(d.D == 32 || d.D == 64 || d.D == 128 || d.D == 256, what, ": head dim must be 32/64/128/256, got ", d.D);
+  TORCH_CHECK(d.D == 32 || d.D == 64 || d.D == 128 || d.D == 256, what, ": head dim must be 32/64/128/256, got ", std::to_string(d.D));
   TORCH_CHECK(num_splits != 0, what, ": num_splits=0 is invalid; use -1 for auto or 1..256");
   if (num_splits < 0) num_splits = -1;
-  TORCH_CHECK(num_splits <= 256, what, ": num_splits must be 1..256, got ", num_splits);
+  TORCH_CHECK(num_splits <= 256, what, ": num_splits must be 1..256, got ", std::to_string(num_splits));
   const c10::cuda::CUDAGuard guard(q.device());
   Tensor out = at::empty({d.B, d.H, 1, d.D}, v.options());
   if (out.numel() == 0) return out;
@@ -224,7 +233,7 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(const Tensor& q_in, const Tensor& k_
                dout = do_in.contiguous(), lse = lse_in.contiguous();
   const int B = q.size(0), H = q.size(1), M = q.size(2), D = q.size(3), Hkv = k.size(1), N = k.size(2);
   TORCH_CHECK(Hkv > 0 && H % Hkv == 0, what, ": H_q must be divisible by H_kv (GQA)");
-  TORCH_CHECK(D == 32 || D == 64 || D == 128, what, ": head dim must be 32/64/128, got ", D);
+  TORCH_CHECK(D == 32 || D == 64 || D == 128, what, ": head dim must be 32/64/128, got ", std::to_string(D));
   TORCH_CHECK(k.sizes() == v.sizes() && k.size(0) == B && k.size(3) == D, what, ": K/V shape mismatch");
   TORCH_CHECK(o.sizes() == q.sizes() && dout.sizes() == q.sizes(), what, ": o/do must have q's shape");
   TORCH_CHECK(lse.numel() == (int64_t)B * H * M, what, ": lse must be [B,H,M]");
@@ -263,32 +272,26 @@ std::tuple<Tensor, bool> attn_int8_prefill(const Tensor& q_in, const Tensor& k_i
   TORCH_CHECK(Hkv > 0 && H % Hkv == 0, what, ": H_q must be divisible by H_kv (GQA)");
   TORCH_CHECK(k.size(3) == D && v.size(3) == D && v.size(2) == N, what, ": K/V shape mismatch");
   TORCH_CHECK(D == 32 || D == 64 || D == 72 || D == 80 || D == 128 || D == 256, what,
-              ": head dim must be 32/64/72/80/128/256, got ", D);
+              ": head dim must be 32/64/72/80/128/256, got ", std::to_string(D));
   const int dt = q.scalar_type() == at::kHalf ? SL8_F16 : SL8_BF16;
   const c10::cuda::CUDAGuard guard(q.device());
   void* st = stream_of(q);
-  auto cu_stream = at::cuda::getCurrentCUDAStream(q.get_device());
   PerStream& ps = per_stream(q);
   Tensor out = at::empty({B, H, M, D}, v.options());
   if (out.numel() == 0) return {out, false};
   const int64_t qrows = (int64_t)B * H * M;
   const float fold = (float)(scale * 1.4426950408889634);
-  int32_t* flag = ps.status.data_ptr<int32_t>() + 32;   // a spare word of the per-stream status area
+  int32_t* flag = ps.gate_flag.data_ptr<int32_t>();
   Tensor q_i8, q_scale;
   bool demoted = false;
-  auto read_flag = [&]() {
-    int32_t host = 0;
-    C10_CUDA_CHECK(cudaMemcpyAsync(&host, flag, sizeof(int32_t), cudaMemcpyDeviceToHost, cu_stream.stream()));
-    C10_CUDA_CHECK(cudaStreamSynchronize(cu_stream.stream()));
-    return host != 0;
-  };
+  auto read_flag = [&]() { return ps.gate_flag.item<int32_t>() != 0; };   // the 4-byte device->host read
   auto quantise_q = [&](bool with_gate) {
     q_i8 = at::empty(q.sizes(), q.options().dtype(at::kChar));
     q_scale = at::empty({B, H, M}, q.options().dtype(at::kFloat));
     check_rc(sl8_quant_q_prologue(q.data_ptr(), dt, qrows, D, fold, 12.f, q_i8.data_ptr<int8_t>(), q_scale.data_ptr<float>(),
                                   nullptr, with_gate ? flag : nullptr, st), "quant_q_prologue");
   };
-  if (gate) C10_CUDA_CHECK(cudaMemsetAsync(flag, 0, sizeof(int32_t), cu_stream.stream()));
+  if (gate) ps.gate_flag.zero_();
   if (gate && ask_first) {
     check_rc(sl8_q_outlier_gate(q.data_ptr(), dt, qrows, D, 12.f, flag, st), "q_outlier_gate");
     demoted = read_flag();
