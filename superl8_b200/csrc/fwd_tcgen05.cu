@@ -41,6 +41,7 @@
 // Every mbarrier wait is bounded (sl8_common.cuh); on expiry the block raises the
 // workspace status word, frees tensor memory and exits.
 #include "sl8_common.cuh"
+#include "sl8_fwd_tc2.cuh"
 #include "sl8_softmax.cuh"
 
 #include <type_traits>
@@ -659,10 +660,21 @@ extern "C" int sl8_attn_int8_fwd(const sl8_fwd_params* p, void* workspace, size_
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int backend = p->backend;
   if (backend == SL8_BACKEND_AUTO) backend = (tc_head_dim(p->D) && p->N > 0) ? SL8_BACKEND_TCGEN05 : SL8_BACKEND_MMA;
-  if (p->gate_flag != nullptr && backend != SL8_BACKEND_TCGEN05) return SL8_ERR_UNSUPPORTED;
+  if (p->gate_flag != nullptr && backend != SL8_BACKEND_TCGEN05 && backend != SL8_BACKEND_TCGEN05_N64) return SL8_ERR_UNSUPPORTED;
   if (backend == SL8_BACKEND_MMA) return sl8_fwd_mma_int8(p, s);
-  if (backend != SL8_BACKEND_TCGEN05) return SL8_ERR_UNSUPPORTED;
+  if (backend != SL8_BACKEND_TCGEN05 && backend != SL8_BACKEND_TCGEN05_N64) return SL8_ERR_UNSUPPORTED;
   if (!tc_head_dim(p->D) || p->N == 0) return SL8_ERR_UNSUPPORTED;
+  // a window that reaches past the first key hides nothing: the same call as no window at all
+  const int window_eff = p->window_left >= p->N ? -1 : p->window_left;
+  if (backend == SL8_BACKEND_TCGEN05 && sl8_fwd_tc2_supported(p->D, window_eff, false)) {
+    Tc2Args t{};
+    t.q = p->q; t.k = p->k; t.v = p->v; t.out = p->out; t.q_scale = p->q_scale; t.k_scale = p->k_scale; t.lse = p->lse;
+    t.seqlens_q = p->seqlens_q; t.seqlens_k = p->seqlens_k; t.status = reinterpret_cast<int*>(workspace);
+    t.gate_flag = p->gate_flag; t.gate_want = p->gate_want;
+    t.B = p->B; t.Hq = p->Hq; t.Hkv = p->Hkv; t.M = p->M; t.N = p->N; t.D = p->D; t.causal = p->causal;
+    t.qk8 = 1; t.v_bf16 = p->v_dtype == SL8_BF16;
+    return sl8_fwd_tc2(t, s);
+  }
   TcArgs a{};
   a.q_scale = p->q_scale; a.k_scale = p->k_scale; a.out = p->out; a.lse = p->lse;
   a.seqlens_q = p->seqlens_q; a.seqlens_k = p->seqlens_k; a.status = reinterpret_cast<int*>(workspace);
@@ -708,6 +720,17 @@ extern "C" int sl8_attn_int8_varlen(const sl8_varlen_params* p, void* workspace,
 // by sl8_attn_fp16_fwd (fwd_mma.cu).
 int sl8_fwd_tc_fp16(const sl8_fp16_fwd_params* p, int* status, cudaStream_t s) {
   if (!tc_head_dim(p->D) || p->N == 0) return SL8_ERR_UNSUPPORTED;
+  const int window_eff = p->window_left >= p->N ? -1 : p->window_left;   // such a window hides nothing
+  if (p->backend != SL8_BACKEND_TCGEN05_N64 && sl8_fwd_tc2_supported(p->D, window_eff, false)) {
+    Tc2Args t{};
+    t.q = p->q; t.k = p->k; t.v = p->v; t.out = p->out; t.lse = p->lse;
+    t.seqlens_q = p->seqlens_q; t.seqlens_k = p->seqlens_k; t.status = status;
+    t.gate_flag = p->gate_flag; t.gate_want = p->gate_want;
+    t.B = p->B; t.Hq = p->Hq; t.Hkv = p->Hkv; t.M = p->M; t.N = p->N; t.D = p->D; t.causal = p->causal;
+    t.scale_log2 = p->softmax_scale * 1.4426950408889634f;
+    t.qk8 = 0; t.v_bf16 = p->dtype == SL8_BF16;
+    return sl8_fwd_tc2(t, s);
+  }
   TcArgs a{};
   a.out = p->out; a.lse = p->lse; a.seqlens_q = p->seqlens_q; a.seqlens_k = p->seqlens_k; a.status = status;
   a.gate_flag = p->gate_flag; a.gate_want = p->gate_want;
