@@ -46,11 +46,12 @@ extern "C" {
 
 /* prefill backends (sl8_fwd_params.backend) */
 #define SL8_BACKEND_AUTO 0
-#define SL8_BACKEND_TCGEN05 1 /* TMA + tcgen05 (D = 64, 128, 256): the fastest tensor-memory kernel that serves the call */
+#define SL8_BACKEND_TCGEN05 1 /* TMA + tcgen05 (D = 64, 128, 256): 128 x 64 tiles, two blocks per SM */
 #define SL8_BACKEND_MMA 2     /* warp-level mma.sync path (every supported D) */
-#define SL8_BACKEND_TCGEN05_N64 3 /* TMA + tcgen05, always the 128 x 64-tile kernel (two blocks per SM); BACKEND_TCGEN05
-                                     prefers the one-block-per-SM kernel with two 128-row query tiles and 128-key
-                                     tiles where it applies (D = 128, dense layout, no window) */
+#define SL8_BACKEND_TCGEN05_2Q 3 /* TMA + tcgen05, one block per SM with two 128-row query tiles and 128-key tiles
+                                    (D = 128, dense layout, no window; other calls fall back to BACKEND_TCGEN05).
+                                    Measured equal to BACKEND_TCGEN05 for 16-bit Q/K and 10 % slower for int8 Q/K on
+                                    B16 Hq64 S8192, so BACKEND_AUTO does not pick it. */
 
 int sl8_abi_version(void);
 const char* sl8_status_string(int status);

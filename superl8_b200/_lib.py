@@ -17,7 +17,7 @@ LIB_PATH = Path(os.environ.get("SUPERL8_B200_LIB") or (Path(__file__).resolve().
 
 SL8_OK = 0
 SL8_F16, SL8_BF16, SL8_F32 = 0, 1, 2
-SL8_BACKEND_AUTO, SL8_BACKEND_TCGEN05, SL8_BACKEND_MMA, SL8_BACKEND_TCGEN05_N64 = 0, 1, 2, 3
+SL8_BACKEND_AUTO, SL8_BACKEND_TCGEN05, SL8_BACKEND_MMA, SL8_BACKEND_TCGEN05_2Q = 0, 1, 2, 3
 
 ERR_BAD_HEAD_DIM = -1
 ERR_BAD_DTYPE = -2

@@ -382,7 +382,7 @@ extern "C" int sl8_attn_fp16_fwd(const sl8_fp16_fwd_params* p, void* workspace, 
                      p->softmax_scale >= 0.f;
   int backend = p->backend;
   if (backend == SL8_BACKEND_AUTO) backend = tc_ok ? SL8_BACKEND_TCGEN05 : SL8_BACKEND_MMA;
-  if (backend == SL8_BACKEND_TCGEN05 || backend == SL8_BACKEND_TCGEN05_N64) {
+  if (backend == SL8_BACKEND_TCGEN05 || backend == SL8_BACKEND_TCGEN05_2Q) {
     if (!tc_ok) return SL8_ERR_UNSUPPORTED;
     if (workspace == nullptr || workspace_bytes < 256) return SL8_ERR_WORKSPACE;
     return sl8_fwd_tc_fp16(p, reinterpret_cast<int*>(workspace), static_cast<cudaStream_t>(stream));

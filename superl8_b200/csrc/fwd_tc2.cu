@@ -90,43 +90,23 @@ __device__ __forceinline__ float2 i2f_pair(uint32_t a, uint32_t b) {
 template <bool QK8>
 __device__ __forceinline__ float pass1_plain(uint32_t (&r)[kKT], const float* __restrict__ ksv) {
   const float2* ks2 = reinterpret_cast<const float2*>(ksv);
-#ifdef SL8_EXP_MAX8
-  float mx[8];
-#pragma unroll
-  for (int u = 0; u < 8; ++u) mx[u] = -INFINITY;
-#else
   float mx0 = -INFINITY, mx1 = -INFINITY;
-#endif
 #pragma unroll
   for (int i = 0; i < kKT / 2; i += 2) {
     float2 p0, p1;
     if (QK8) {
-#ifdef SL8_EXP_NO_LDS
-      const float2 k0 = make_float2(0.01f, 0.01f), k1 = k0;
-#else
-      const float2 k0 = ks2[i], k1 = ks2[i + 1];
-#endif
-      p0 = mul2(i2f_pair(r[2 * i], r[2 * i + 1]), k0);
-      p1 = mul2(i2f_pair(r[2 * i + 2], r[2 * i + 3]), k1);
+      p0 = mul2(i2f_pair(r[2 * i], r[2 * i + 1]), ks2[i]);
+      p1 = mul2(i2f_pair(r[2 * i + 2], r[2 * i + 3]), ks2[i + 1]);
       r[2 * i] = __float_as_uint(p0.x); r[2 * i + 1] = __float_as_uint(p0.y);
       r[2 * i + 2] = __float_as_uint(p1.x); r[2 * i + 3] = __float_as_uint(p1.y);
     } else {
       p0 = bits2(r[2 * i], r[2 * i + 1]);
       p1 = bits2(r[2 * i + 2], r[2 * i + 3]);
     }
-#ifdef SL8_EXP_MAX8
-    mx[(i / 2) & 7] = max3f(mx[(i / 2) & 7], p0.x, p0.y);
-    mx[((i / 2) + 4) & 7] = max3f(mx[((i / 2) + 4) & 7], p1.x, p1.y);
-#else
     mx0 = max3f(mx0, p0.x, p0.y);
     mx1 = max3f(mx1, p1.x, p1.y);
-#endif
   }
-#ifdef SL8_EXP_MAX8
-  return fmaxf(max3f(mx[0], mx[1], mx[2]), max3f(max3f(mx[3], mx[4], mx[5]), mx[6], mx[7]));
-#else
   return fmaxf(mx0, mx1);
-#endif
 }
 // pass 1 on a tile that needs masking (diagonal or tail): leaves the finished logits
 // t * qs (int8: float(acc) * k_scale * q_scale), -inf where masked; returns their max.

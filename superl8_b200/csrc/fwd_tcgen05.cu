@@ -660,13 +660,13 @@ extern "C" int sl8_attn_int8_fwd(const sl8_fwd_params* p, void* workspace, size_
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int backend = p->backend;
   if (backend == SL8_BACKEND_AUTO) backend = (tc_head_dim(p->D) && p->N > 0) ? SL8_BACKEND_TCGEN05 : SL8_BACKEND_MMA;
-  if (p->gate_flag != nullptr && backend != SL8_BACKEND_TCGEN05 && backend != SL8_BACKEND_TCGEN05_N64) return SL8_ERR_UNSUPPORTED;
+  if (p->gate_flag != nullptr && backend != SL8_BACKEND_TCGEN05 && backend != SL8_BACKEND_TCGEN05_2Q) return SL8_ERR_UNSUPPORTED;
   if (backend == SL8_BACKEND_MMA) return sl8_fwd_mma_int8(p, s);
-  if (backend != SL8_BACKEND_TCGEN05 && backend != SL8_BACKEND_TCGEN05_N64) return SL8_ERR_UNSUPPORTED;
+  if (backend != SL8_BACKEND_TCGEN05 && backend != SL8_BACKEND_TCGEN05_2Q) return SL8_ERR_UNSUPPORTED;
   if (!tc_head_dim(p->D) || p->N == 0) return SL8_ERR_UNSUPPORTED;
   // a window that reaches past the first key hides nothing: the same call as no window at all
   const int window_eff = p->window_left >= p->N ? -1 : p->window_left;
-  if (backend == SL8_BACKEND_TCGEN05 && sl8_fwd_tc2_supported(p->D, window_eff, false)) {
+  if (backend == SL8_BACKEND_TCGEN05_2Q && sl8_fwd_tc2_supported(p->D, window_eff, false)) {
     Tc2Args t{};
     t.q = p->q; t.k = p->k; t.v = p->v; t.out = p->out; t.q_scale = p->q_scale; t.k_scale = p->k_scale; t.lse = p->lse;
     t.seqlens_q = p->seqlens_q; t.seqlens_k = p->seqlens_k; t.status = reinterpret_cast<int*>(workspace);
@@ -721,7 +721,7 @@ extern "C" int sl8_attn_int8_varlen(const sl8_varlen_params* p, void* workspace,
 int sl8_fwd_tc_fp16(const sl8_fp16_fwd_params* p, int* status, cudaStream_t s) {
   if (!tc_head_dim(p->D) || p->N == 0) return SL8_ERR_UNSUPPORTED;
   const int window_eff = p->window_left >= p->N ? -1 : p->window_left;   // such a window hides nothing
-  if (p->backend != SL8_BACKEND_TCGEN05_N64 && sl8_fwd_tc2_supported(p->D, window_eff, false)) {
+  if (p->backend == SL8_BACKEND_TCGEN05_2Q && sl8_fwd_tc2_supported(p->D, window_eff, false)) {
     Tc2Args t{};
     t.q = p->q; t.k = p->k; t.v = p->v; t.out = p->out; t.lse = p->lse;
     t.seqlens_q = p->seqlens_q; t.seqlens_k = p->seqlens_k; t.status = status;

@@ -1,5 +1,5 @@
-"""GPU parity of the int8-QK prefill forward (every backend: the tensor-memory kernels -- TC picks the
-one-block-per-SM kernel where it applies, TC64 forces the 128 x 64-tile one -- and mma.sync), through the C ABI.
+"""GPU parity of the int8-QK prefill forward (every backend: the two tensor-memory kernels -- TC = 128 x 64
+tiles, two blocks per SM; TC2Q = two 128-row query tiles per block, 128-key tiles -- and mma.sync), through the C ABI.
 
 Bars: int32 logits bit-exact; outputs inside the reference's int8 gate against the fp32
 oracle (cos >= 0.999, rel-L1 <= 0.02, SQNR >= 20 dB; reference tests/tolerances.py:74-88) and,
@@ -16,7 +16,7 @@ from superl8_b200 import _C, _lib
 
 pytestmark = pytest.mark.gpu
 
-TC, MMA, TC64 = _lib.SL8_BACKEND_TCGEN05, _lib.SL8_BACKEND_MMA, _lib.SL8_BACKEND_TCGEN05_N64
+TC, MMA, TC2Q = _lib.SL8_BACKEND_TCGEN05, _lib.SL8_BACKEND_MMA, _lib.SL8_BACKEND_TCGEN05_2Q
 
 # (B, Hq, Hkv, M, N, D, causal)
 SHAPES = [
@@ -44,7 +44,7 @@ def check_against_restatement(out, d, causal, window=-1, rel=3e-3, cos=0.99999):
     assert oracle.rel_l1(out, rest) <= rel, oracle.rel_l1(out, rest)
 
 
-@pytest.mark.parametrize("backend", [TC, MMA, TC64])
+@pytest.mark.parametrize("backend", [TC, MMA, TC2Q])
 @pytest.mark.parametrize("B,Hq,Hkv,M,N,D,causal", SHAPES)
 def test_fwd_shapes(B, Hq, Hkv, M, N, D, causal, backend, device):
     d = quantized_inputs(10 + D, B, Hq, Hkv, M, D, N=N)
@@ -84,7 +84,7 @@ def test_int32_logits_bit_exact(D, device):
     assert _C.device_status() == 0
 
 
-@pytest.mark.parametrize("backend", [TC, MMA, TC64])
+@pytest.mark.parametrize("backend", [TC, MMA, TC2Q])
 def test_bf16_v_and_out(backend, device):
     d = quantized_inputs(31, 1, 4, 2, 300, 128, dtype=torch.bfloat16)
     d["dev"]["v"] = d["dev"]["v"] * 300.0                      # would overflow an fp16 output
@@ -105,7 +105,7 @@ def test_bad_head_dim_raises(device):
         _C.attn_int8_fwd(q, sc, q, sc, v, False, -1)
 
 
-@pytest.mark.parametrize("backend", [TC, MMA, TC64])
+@pytest.mark.parametrize("backend", [TC, MMA, TC2Q])
 def test_lse(backend, device):
     d = quantized_inputs(32, 1, 4, 2, 200, 128, N=260)
     out, lse = run(d, True, backend, want_lse=True)
@@ -114,7 +114,7 @@ def test_lse(backend, device):
     assert torch.equal(out, run(d, True, backend))
 
 
-@pytest.mark.parametrize("backend", [TC, MMA, TC64])
+@pytest.mark.parametrize("backend", [TC, MMA, TC2Q])
 def test_gqa_equals_repeat_interleave_bitwise(backend, device):
     d = quantized_inputs(33, 1, 8, 2, 256, 128)
     out = run(d, True, backend)
@@ -126,7 +126,7 @@ def test_gqa_equals_repeat_interleave_bitwise(backend, device):
     assert torch.equal(out, out2)
 
 
-@pytest.mark.parametrize("backend", [TC, MMA, TC64])
+@pytest.mark.parametrize("backend", [TC, MMA, TC2Q])
 def test_window(backend, device):
     d = quantized_inputs(34, 1, 4, 2, 400, 128)
     full = run(d, True, backend)
@@ -137,7 +137,7 @@ def test_window(backend, device):
     oracle.assert_int8_quality(out, oracle.attention_fp32(d["q"], d["k"], d["v"], window_left=37))
 
 
-@pytest.mark.parametrize("backend", [TC, MMA, TC64])
+@pytest.mark.parametrize("backend", [TC, MMA, TC2Q])
 def test_fully_masked_rows_are_zero(backend, device):
     # causal with N < M: the first M - N query rows see no key (reference: out 0, lse -inf)
     d = quantized_inputs(35, 1, 2, 2, 300, 128, N=40)
@@ -147,7 +147,7 @@ def test_fully_masked_rows_are_zero(backend, device):
     check_against_restatement(out, d, True)
 
 
-@pytest.mark.parametrize("backend", [TC, MMA, TC64])
+@pytest.mark.parametrize("backend", [TC, MMA, TC2Q])
 def test_ragged_seqlens(backend, device):
     B, Hq, Hkv, S, D = 4, 4, 1, 512, 64
     d = quantized_inputs(36, B, Hq, Hkv, S, D)
@@ -192,7 +192,7 @@ def test_python_entry_with_gate_and_smoothing(device):
 
 
 @pytest.mark.parametrize("D,dtype,backend", [(64, torch.float16, TC), (128, torch.bfloat16, TC), (128, torch.float16, TC),
-                                             (256, torch.float16, TC), (128, torch.float16, TC64), (128, torch.bfloat16, TC64), (80, torch.float16, MMA), (128, torch.float16, MMA),
+                                             (256, torch.float16, TC), (128, torch.float16, TC2Q), (128, torch.bfloat16, TC2Q), (80, torch.float16, MMA), (128, torch.float16, MMA),
                                              (64, torch.bfloat16, MMA), (256, torch.float16, MMA)])
 def test_fp16_fwd(D, dtype, backend, device):
     q, k, v = oracle.make_batch(40 + D, 2, 4, 2, 300, D, Sk=333, dtype=dtype)
