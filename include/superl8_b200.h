@@ -114,6 +114,20 @@ int sl8_smooth_quant_k(const void* k, int dtype, int64_t BH, int64_t N, int64_t 
                        const float* mean, int8_t* k_i8, float* k_scale, void* k_smoothed,
                        void* stream);
 
+/*
+ * K prologue in ONE launch: steps 1 and 2 together (reference superl8/quant/core.py:29-44, 70-95, then
+ * :47-62).  A thread-block cluster owns each (batch, kv-head) slab: it forms the fp32 mean (the same
+ * chunked, fixed-order sum as sl8_k_mean: the results are bitwise equal), shares it through distributed
+ * shared memory, and quantises the slab on a second walk that finds the rows in L2, so K crosses HBM once.
+ * mean [BH, D] receives the mean; k_smoothed is nullable.  sl8_k_prologue_fused_ok() says whether the
+ * shape is served (fp16 / bf16, D in {64, 128, 256}, BH <= 65535, N <= about 90 000 at D = 128); otherwise
+ * SL8_ERR_UNSUPPORTED: use the two steps.
+ */
+int sl8_k_prologue_fused_ok(int dtype, int64_t BH, int64_t N, int64_t D);
+int sl8_k_prologue(const void* k, int dtype, int64_t BH, int64_t N, int64_t D,
+                   const int32_t* seqlens, int32_t heads_per_batch, float* mean,
+                   int8_t* k_i8, float* k_scale, void* k_smoothed, void* stream);
+
 /* ---- prefill: int8-QK FlashAttention-2 forward -------------------------- */
 
 typedef struct sl8_fwd_params {

@@ -229,7 +229,8 @@ def attn_int8_fwd_fused(q, k, v, causal=False, scale=None, window_left=-1, *, se
         nbytes = int(lib.sl8_attn_int8_fwd_fused_workspace(C.byref(p)))
         ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
         rc = lib.sl8_attn_int8_fwd_fused(C.byref(p), _ptr(ws), nbytes, _stream(q.device))
-    _lib.check(rc, "attn_int8_fwd_fused", (5 + (1 if gate else 0)) if out.numel() else 0)
+    _lib.check(rc, "attn_int8_fwd_fused",
+               (2 + _lib.k_prologue_launches(_DTYPE[k.dtype], B * Hkv, N, D) + (1 if gate else 0)) if out.numel() else 0)
     return out, flag
 
 

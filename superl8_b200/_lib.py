@@ -130,6 +130,9 @@ SIGNATURES = {
                              C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "sl8_smooth_quant_k": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
                                      C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "sl8_k_prologue_fused_ok": (C.c_int, [C.c_int, C.c_int64, C.c_int64, C.c_int64]),
+    "sl8_k_prologue": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int32,
+                                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "sl8_attn_int8_fwd_workspace": (C.c_size_t, [C.POINTER(FwdParams)]),
     "sl8_attn_int8_fwd": (C.c_int, [C.POINTER(FwdParams), C.c_void_p, C.c_size_t, C.c_void_p]),
     "sl8_qk_logits_i32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
@@ -189,6 +192,11 @@ def load():
         fn.argtypes = args
     _lib = lib
     return lib
+
+
+def k_prologue_launches(dtype_code: int, BH: int, N: int, D: int) -> int:
+    """Kernels the K prologue launches for this shape: 1 (cluster kernel) or 3 (mean partial, finish, quantise)."""
+    return 1 if load().sl8_k_prologue_fused_ok(int(dtype_code), int(BH), int(N), int(D)) else 3
 
 
 def status_string(code: int) -> str:

@@ -68,11 +68,16 @@ extern "C" int sl8_attn_int8_fwd_fused(const sl8_fused_fwd_params* p, void* work
   int rc = sl8_quant_q_prologue(p->q, p->dtype, (int64_t)p->B * p->Hq * p->M, p->D, fold,
                                 gate ? p->ratio_threshold : 12.f, q_i8, q_scale, nullptr, gate ? flag : nullptr, stream);
   if (rc != SL8_OK) return rc;
-  rc = sl8_k_mean(p->k, p->dtype, bhk, p->N, p->D, p->seqlens_k, p->Hkv, mean, ws + l.mean_ws,
-                  l.total - l.mean_ws, stream);
-  if (rc != SL8_OK) return rc;
-  rc = sl8_smooth_quant_k(p->k, p->dtype, bhk, p->N, p->D, mean, k_i8, k_scale, nullptr, stream);
-  if (rc != SL8_OK) return rc;
+  if (sl8_k_prologue_fused_ok(p->dtype, bhk, p->N, p->D)) {   // one launch, K read from HBM once
+    rc = sl8_k_prologue(p->k, p->dtype, bhk, p->N, p->D, p->seqlens_k, p->Hkv, mean, k_i8, k_scale, nullptr, stream);
+    if (rc != SL8_OK) return rc;
+  } else {
+    rc = sl8_k_mean(p->k, p->dtype, bhk, p->N, p->D, p->seqlens_k, p->Hkv, mean, ws + l.mean_ws,
+                    l.total - l.mean_ws, stream);
+    if (rc != SL8_OK) return rc;
+    rc = sl8_smooth_quant_k(p->k, p->dtype, bhk, p->N, p->D, mean, k_i8, k_scale, nullptr, stream);
+    if (rc != SL8_OK) return rc;
+  }
   sl8_fwd_params f{};
   f.q = q_i8; f.q_scale = q_scale; f.k = k_i8; f.k_scale = k_scale; f.v = p->v; f.out = p->out;
   f.seqlens_q = p->seqlens_q; f.seqlens_k = p->seqlens_k;

@@ -12,6 +12,10 @@
 // 8 * (32 / lanes-per-row) rows per step and walks the rows grid-stride.
 #include "sl8_common.cuh"
 
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
+
 namespace sl8 {
 namespace {
 
@@ -106,9 +110,13 @@ __device__ __forceinline__ int half_gate_count(const uint4 (&raw)[NV], const boo
   return (int)(__low2float(cnt2) + __high2float(cnt2));
 }
 
-// LPR lanes own one row; each lane holds NV vectors of 8 elements.
+// LPR lanes own one row; each lane holds NV vectors of 8 elements.  The block walks the row groups
+// base0, base0 + stride, ... below row_end; returns whether one of this thread's rows tripped the gate.
+// mean_local (key mode, nullable): the mean row of every row of the walk, in shared memory (the fused
+// K prologue); otherwise the mean table a.mean is read through the read-only path.
 template <typename T, int LPR, int NV, int MODE>
-__global__ void __launch_bounds__(kQuantThreads) quant_rows_vec_kernel(QuantArgs a) {
+__device__ __forceinline__ int quant_rows_vec_body(const QuantArgs& a, int64_t base0, int64_t stride, int64_t row_end,
+                                                   const float* mean_local) {
   constexpr int ROWS_PER_WARP = 32 / LPR;
   constexpr unsigned FULL = 0xffffffffu;
   const int lane = threadIdx.x & 31;
@@ -116,14 +124,12 @@ __global__ void __launch_bounds__(kQuantThreads) quant_rows_vec_kernel(QuantArgs
   const int sl = lane % LPR;        // lane within the row
   const int warp = threadIdx.x >> 5;
   const int kvec = a.K >> 3;
-  const int64_t rows_per_block = (int64_t)(kQuantThreads / 32) * ROWS_PER_WARP;
   const int rank_need = ((a.K - 1) >> 1) + 1;  // elements <= lower median, counted from the bottom
   int any_outlier = 0;
 
-  for (int64_t base = (int64_t)blockIdx.x * rows_per_block; base < a.rows;
-       base += (int64_t)gridDim.x * rows_per_block) {
+  for (int64_t base = base0; base < row_end; base += stride) {
     const int64_t row = base + (int64_t)warp * ROWS_PER_WARP + sub;
-    const bool live = row < a.rows;
+    const bool live = row < row_end;
     const T* xr = reinterpret_cast<const T*>(a.x) + row * a.K;
     float f[NV][8];
     uint4 raw[NV];
@@ -137,14 +143,20 @@ __global__ void __launch_bounds__(kQuantThreads) quant_rows_vec_kernel(QuantArgs
       Vec8<T>::unpack(raw[v], f[v]);
     }
     if (MODE == kKeySmooth) {
-      const int64_t bh = live ? mean_row(a, row) : 0;
-      const float* mr = a.mean + bh * a.K;
+      const int64_t bh = (live && mean_local == nullptr) ? mean_row(a, row) : 0;
+      const float* mr = mean_local != nullptr ? mean_local : a.mean + bh * a.K;
 #pragma unroll
       for (int v = 0; v < NV; ++v) {
         if (!has[v]) continue;
         const int c0 = (sl + v * LPR) * 8;
-        const float4 m0 = __ldg(reinterpret_cast<const float4*>(mr + c0));
-        const float4 m1 = __ldg(reinterpret_cast<const float4*>(mr + c0 + 4));
+        float4 m0, m1;
+        if (mean_local != nullptr) {   // written by this kernel: plain loads
+          m0 = *reinterpret_cast<const float4*>(mr + c0);
+          m1 = *reinterpret_cast<const float4*>(mr + c0 + 4);
+        } else {
+          m0 = __ldg(reinterpret_cast<const float4*>(mr + c0));
+          m1 = __ldg(reinterpret_cast<const float4*>(mr + c0 + 4));
+        }
         const float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
         T t[8];
 #pragma unroll
@@ -252,6 +264,14 @@ __global__ void __launch_bounds__(kQuantThreads) quant_rows_vec_kernel(QuantArgs
       }
     }
   }
+  return any_outlier;
+}
+
+template <typename T, int LPR, int NV, int MODE>
+__global__ void __launch_bounds__(kQuantThreads) quant_rows_vec_kernel(QuantArgs a) {
+  const int64_t rows_per_block = (int64_t)(kQuantThreads / 32) * (32 / LPR);
+  int any_outlier = quant_rows_vec_body<T, LPR, NV, MODE>(a, (int64_t)blockIdx.x * rows_per_block,
+                                                          (int64_t)gridDim.x * rows_per_block, a.rows, nullptr);
   if ((MODE == kQueryFoldGate || MODE == kGateOnly) && a.flag != nullptr) {
     any_outlier = __syncthreads_or(any_outlier);
     if (threadIdx.x == 0 && any_outlier) atomicOr(a.flag, 1);
@@ -367,25 +387,37 @@ constexpr int kMeanThreads = 256;
 
 // grid (chunks, BH).  Thread (rl, cv) sums rows rl, rl + RL, ... of the chunk for
 // the 8 columns of vector cv; the RL row-lanes are then added in index order.
+// Column sums of rows [r0, r1) of one head (kb = its first row) into out[K] (global or shared memory),
+// by the whole block of kMeanThreads threads, in a fixed order: thread (rl, cv) sums rows
+// r0 + rl, r0 + rl + RL, ... for the 8 columns of vector cv, then the RL row-lanes are added in index
+// order.  red: shared scratch [RL][K].  Ends with a block-wide sync.
 template <typename T>
-__global__ void __launch_bounds__(kMeanThreads) k_mean_partial_kernel(
-    const T* __restrict__ k, int64_t N, int K, const int32_t* __restrict__ seqlens, int heads_per_batch,
-    float* __restrict__ partial, int nchunks) {
-  extern __shared__ float red[];  // [RL][K]
+__device__ __forceinline__ void chunk_column_sums(const T* __restrict__ kb, int64_t r0, int64_t r1, int K, float* red,
+                                                  float* out) {
   const int kvec = K >> 3;
   int cvp = 1;
   while (cvp < kvec) cvp <<= 1;   // column lanes, power of two <= 256
   const int RL = kMeanThreads / cvp;
   const int cv = threadIdx.x % cvp;
   const int rl = threadIdx.x / cvp;
-  const int64_t bh = blockIdx.y;
-  const int64_t len = seqlens ? (int64_t)seqlens[bh / heads_per_batch] : N;
-  const int64_t r0 = (int64_t)blockIdx.x * kMeanChunkRows;
-  const int64_t r1 = min(len < N ? len : N, r0 + kMeanChunkRows);
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (cv < kvec) {
-    const T* kb = k + bh * N * K;
-    for (int64_t r = r0 + rl; r < r1; r += RL) {
+    // four rows in flight per thread; they are added in row order, so the sum does not depend on it
+    constexpr int U = 4;
+    int64_t r = r0 + rl;
+    for (; r + (int64_t)(U - 1) * RL < r1; r += (int64_t)U * RL) {
+      uint4 u[U];
+#pragma unroll
+      for (int x = 0; x < U; ++x) u[x] = __ldg(reinterpret_cast<const uint4*>(kb + (r + (int64_t)x * RL) * K) + cv);
+#pragma unroll
+      for (int x = 0; x < U; ++x) {
+        float f[8];
+        Vec8<T>::unpack(u[x], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      }
+    }
+    for (; r < r1; r += RL) {
       const uint4 u = __ldg(reinterpret_cast<const uint4*>(kb + r * K) + cv);
       float f[8];
       Vec8<T>::unpack(u, f);
@@ -399,7 +431,77 @@ __global__ void __launch_bounds__(kMeanThreads) k_mean_partial_kernel(
   for (int c = threadIdx.x; c < K; c += kMeanThreads) {
     float s = 0.0f;
     for (int r = 0; r < RL; ++r) s += red[r * K + c];
-    partial[(bh * nchunks + blockIdx.x) * K + c] = s;
+    out[c] = s;
+  }
+  __syncthreads();
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kMeanThreads) k_mean_partial_kernel(
+    const T* __restrict__ k, int64_t N, int K, const int32_t* __restrict__ seqlens, int heads_per_batch,
+    float* __restrict__ partial, int nchunks) {
+  extern __shared__ float red[];  // [RL][K]
+  const int64_t bh = blockIdx.y;
+  const int64_t len = seqlens ? (int64_t)seqlens[bh / heads_per_batch] : N;
+  const int64_t r0 = (int64_t)blockIdx.x * kMeanChunkRows;
+  const int64_t r1 = min(len < N ? len : N, r0 + kMeanChunkRows);
+  chunk_column_sums<T>(k + bh * N * K, r0, r1, K, red, partial + (bh * nchunks + blockIdx.x) * K);
+}
+
+// ---- K prologue in one launch ---------------------------------------------------
+// A cluster of kClusterCtas blocks owns one (batch, kv-head) slab [N, K].  Block r takes the 1024-row
+// chunks r, r + 8, ...: (1) their column sums, chunk by chunk, into its own shared memory -- the same
+// thread map and order as k_mean_partial_kernel; (2) after a cluster barrier every block adds ALL chunk
+// sums of the slab in chunk order, reading the other blocks' through distributed shared memory, so
+// every block holds the same mean, bit for bit the one the two-kernel path produces; (3) after a
+// second cluster barrier (nobody reads a neighbour's shared memory any more) it walks its chunks
+// again -- they were read microseconds ago and sit in L2 -- subtracts the mean, rounds to the storage
+// dtype and quantises the rows.  K crosses HBM once.
+constexpr int kClusterCtas = 8;
+static_assert(kMeanThreads == kQuantThreads, "one block shape for both phases");
+
+template <typename T, int LPR, int NV>
+__global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kMeanThreads)
+    k_prologue_cluster_kernel(QuantArgs a, int64_t N, const int32_t* __restrict__ seqlens, int heads_per_batch,
+                              float* __restrict__ mean_out, int nchunks, int chunks_per_cta) {
+  extern __shared__ float sm[];
+  const int K = a.K;
+  float* mean_s = sm;                       // [K]
+  float* part = sm + K;                     // [chunks_per_cta][K]: this block's chunk sums
+  float* red = part + chunks_per_cta * K;   // [RL][K]
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  const int64_t bh = blockIdx.y;
+  int64_t len = seqlens ? (int64_t)seqlens[bh / heads_per_batch] : N;
+  len = len < 0 ? 0 : (len > N ? N : len);
+  const T* kb = reinterpret_cast<const T*>(a.x) + bh * N * K;
+  for (int jj = 0; jj < chunks_per_cta; ++jj) {
+    const int j = rank + jj * kClusterCtas;
+    if (j >= nchunks) break;
+    const int64_t r0 = (int64_t)j * kMeanChunkRows;
+    chunk_column_sums<T>(kb, r0, min(len, r0 + kMeanChunkRows), K, red, part + jj * K);
+  }
+  cluster.sync();
+  const float inv = len > 0 ? __fdiv_rn(1.0f, (float)len) : 0.0f;
+  for (int c = threadIdx.x; c < K; c += kMeanThreads) {
+    float s = 0.0f;
+    for (int j = 0; j < nchunks; ++j) {
+      const float* remote = cluster.map_shared_rank(part, j % kClusterCtas);
+      s += remote[(j / kClusterCtas) * K + c];
+    }
+    const float m = s * inv;
+    mean_s[c] = m;
+    if (rank == 0 && mean_out != nullptr) mean_out[bh * K + c] = m;
+  }
+  cluster.sync();
+  // quantise this block's chunks (all N rows of the slab are quantised, also those past seqlens)
+  const int64_t rows_per_block = (int64_t)(kQuantThreads / 32) * (32 / LPR);
+  for (int jj = 0; jj < chunks_per_cta; ++jj) {
+    const int j = rank + jj * kClusterCtas;
+    if (j >= nchunks) break;
+    const int64_t row0 = bh * N + (int64_t)j * kMeanChunkRows;
+    const int64_t row1 = bh * N + min(N, (int64_t)(j + 1) * kMeanChunkRows);
+    quant_rows_vec_body<T, LPR, NV, kKeySmooth>(a, row0, rows_per_block, row1, mean_s);
   }
 }
 
@@ -679,4 +781,59 @@ extern "C" int sl8_smooth_quant_k(const void* k, int dtype, int64_t BH, int64_t 
   a.x = k; a.q = k_i8; a.scale = k_scale; a.mean = mean; a.smoothed = k_smoothed;
   a.rows = BH * N; a.K = (int)D; a.rows_per_head = N > 0 ? N : 1;
   return dispatch<kKeySmooth>(a, dtype, static_cast<cudaStream_t>(stream));
+}
+
+namespace {
+template <typename T, int LPR, int NV>
+int launch_k_prologue(const QuantArgs& a, int64_t BH, int64_t N, const int32_t* seqlens, int heads_per_batch, float* mean,
+                      int nchunks, int chunks_per_cta, size_t smem, cudaStream_t s) {
+  dim3 grid(kClusterCtas, (unsigned)BH);
+  k_prologue_cluster_kernel<T, LPR, NV><<<grid, kMeanThreads, smem, s>>>(a, N, seqlens, heads_per_batch, mean, nchunks,
+                                                                       chunks_per_cta);
+  return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
+}
+}  // namespace
+
+extern "C" int sl8_k_prologue_fused_ok(int dtype, int64_t BH, int64_t N, int64_t D) {
+  if (dtype != SL8_F16 && dtype != SL8_BF16) return 0;
+  if (D != 64 && D != 128 && D != 256) return 0;
+  if (BH <= 0 || BH > 65535 || N <= 0) return 0;
+  const int64_t nchunks = (N + kMeanChunkRows - 1) / kMeanChunkRows;
+  const int64_t per = (nchunks + kClusterCtas - 1) / kClusterCtas;
+  int cvp = 1;
+  while (cvp < D / 8) cvp <<= 1;
+  const int64_t smem = (D + per * D + (int64_t)(kMeanThreads / cvp) * D) * 4;
+  return smem <= 48 * 1024 ? 1 : 0;
+}
+
+extern "C" int sl8_k_prologue(const void* k, int dtype, int64_t BH, int64_t N, int64_t D, const int32_t* seqlens,
+                              int32_t heads_per_batch, float* mean, int8_t* k_i8, float* k_scale, void* k_smoothed,
+                              void* stream) {
+  if (BH < 0 || N < 0 || D < 0) return SL8_ERR_BAD_SHAPE;
+  if (BH == 0 || D == 0 || N == 0) return SL8_OK;
+  if (k == nullptr || mean == nullptr || k_i8 == nullptr || k_scale == nullptr) return SL8_ERR_NULL;
+  if (seqlens != nullptr && heads_per_batch <= 0) return SL8_ERR_BAD_SHAPE;
+  if (!sl8_k_prologue_fused_ok(dtype, BH, N, D)) return SL8_ERR_UNSUPPORTED;
+  if (!aligned16(k) || !aligned16(mean) || reinterpret_cast<uintptr_t>(k_i8) % 8 != 0 ||
+      (k_smoothed != nullptr && !aligned16(k_smoothed)))
+    return SL8_ERR_MISALIGNED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  QuantArgs a{};
+  a.x = k; a.q = k_i8; a.scale = k_scale; a.mean = mean; a.smoothed = k_smoothed;
+  a.rows = BH * N; a.K = (int)D; a.rows_per_head = N;
+  const int nchunks = (int)((N + kMeanChunkRows - 1) / kMeanChunkRows);
+  const int per = (nchunks + kClusterCtas - 1) / kClusterCtas;
+  int cvp = 1;
+  while (cvp < D / 8) cvp <<= 1;
+  const size_t smem = (size_t)(D + (int64_t)per * D + (int64_t)(kMeanThreads / cvp) * D) * 4;
+  const bool h = dtype == SL8_F16;
+  switch ((int)D) {   // lanes per row x vectors per lane as in launch_2byte
+    case 64: return h ? launch_k_prologue<__half, 2, 4>(a, BH, N, seqlens, heads_per_batch, mean, nchunks, per, smem, s)
+                      : launch_k_prologue<__nv_bfloat16, 2, 4>(a, BH, N, seqlens, heads_per_batch, mean, nchunks, per, smem, s);
+    case 128: return h ? launch_k_prologue<__half, 4, 4>(a, BH, N, seqlens, heads_per_batch, mean, nchunks, per, smem, s)
+                       : launch_k_prologue<__nv_bfloat16, 4, 4>(a, BH, N, seqlens, heads_per_batch, mean, nchunks, per, smem, s);
+    case 256: return h ? launch_k_prologue<__half, 8, 4>(a, BH, N, seqlens, heads_per_batch, mean, nchunks, per, smem, s)
+                       : launch_k_prologue<__nv_bfloat16, 8, 4>(a, BH, N, seqlens, heads_per_batch, mean, nchunks, per, smem, s);
+  }
+  return SL8_ERR_UNSUPPORTED;
 }

@@ -311,7 +311,11 @@ std::tuple<Tensor, bool> attn_int8_prefill(const Tensor& q_in, const Tensor& k_i
   const int64_t bhk = (int64_t)B * Hkv;
   Tensor k_i8 = at::empty(k.sizes(), k.options().dtype(at::kChar));
   Tensor k_scale = at::empty({B, Hkv, N}, k.options().dtype(at::kFloat));
-  if (N > 0) {
+  if (N > 0 && sl8_k_prologue_fused_ok(dt, bhk, N, D)) {   // one launch, K read from HBM once
+    Tensor mean = at::empty({bhk * D}, k.options().dtype(at::kFloat));
+    check_rc(sl8_k_prologue(k.data_ptr(), dt, bhk, N, D, nullptr, 1, mean.data_ptr<float>(), k_i8.data_ptr<int8_t>(),
+                            k_scale.data_ptr<float>(), nullptr, st), "k_prologue");
+  } else if (N > 0) {
     const size_t mws = sl8_k_mean_workspace(bhk, N, D);
     Tensor mean = at::empty({(int64_t)(bhk * D * 4 + mws + 256)}, k.options().dtype(at::kByte));
     float* mean_p = reinterpret_cast<float*>(mean.data_ptr());

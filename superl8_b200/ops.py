@@ -8,7 +8,7 @@ import threading
 import torch
 
 from . import _C, _lib
-from .quant import (_capturing, k_mean, q_outlier_flag, quantize_q, quantize_qk, smooth_quantize_k,
+from .quant import (_capturing, k_mean, k_prologue, q_outlier_flag, quantize_q, quantize_qk, smooth_quantize_k,
                     varlen_smooth_quantize_k)
 
 # The outcome of the accuracy gate of the most recent attn_int8_fwd call, kept per (device, stream):
@@ -118,7 +118,8 @@ def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, 
         out, demoted = _C._ext.attn_int8_prefill(q, k, v, bool(causal), float(s), int(window_left), use_gate,
                                                  bool(use_gate and ask_first))
         if out.numel():
-            _lib.launches += 2 if demoted else (6 if (use_gate and ask_first) else 5)
+            kp = _lib.k_prologue_launches(_C._DTYPE[k.dtype], k.shape[0] * k.shape[1], k.shape[2], k.shape[3])
+            _lib.launches += 2 if demoted else (2 + kp + (1 if (use_gate and ask_first) else 0))
         _set_gate(dev, bool(demoted) if use_gate else None)
         return out
     if s < 0 and backend == _lib.SL8_BACKEND_AUTO:
@@ -143,7 +144,7 @@ def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, 
         if demote:
             _set_gate(dev, True)
             return _demote(q, k, v, causal, s, window_left, seqlens_q, seqlens_k)
-        k_i8, k_scale, _ = smooth_quantize_k(k, k_mean(k, seqlens_k))
+        k_i8, k_scale, _, _ = k_prologue(k, seqlens_k)
     _set_gate(dev, False if use_gate else None)
     return _C.attn_int8_fwd(q_i8, q_scale.squeeze(-1).contiguous(), k_i8, k_scale.squeeze(-1).contiguous(),
                             v.contiguous(), causal, window_left, seqlens_q=seqlens_q, seqlens_k=seqlens_k,
@@ -212,7 +213,8 @@ def attn_int8_fwd_host(q, k, v, out=None, *, chunk_batch: int | None = None, sta
             nbytes = int(lib.sl8_attn_int8_fwd_host_workspace(p))
             ws = _host_workspace(dev, nbytes)
             rc = lib.sl8_attn_int8_fwd_host(p, ws.data_ptr(), ws.numel(), _C._stream(dev))
-        _lib.check(rc, "attn_int8_fwd_host", n_chunks * (5 + (1 if gate else 0)))
+        kp = _lib.k_prologue_launches(_C._DTYPE[k.dtype], max(1, k.shape[1] * B // max(n_chunks, 1)), k.shape[2], k.shape[3])
+        _lib.check(rc, "attn_int8_fwd_host", n_chunks * (2 + kp + (1 if gate else 0)))
         _set_gate(dev, None, None)
         return out
     nb = max(1, B // 16) if chunk_batch is None else max(1, int(chunk_batch))

@@ -92,6 +92,36 @@ def smooth_quantize_k(k: torch.Tensor, mean: torch.Tensor, want_smoothed: bool =
     return k_i8, k_scale, k_s
 
 
+def k_prologue(k: torch.Tensor, seqlens_k: torch.Tensor | None = None, want_smoothed: bool = False):
+    """K prologue: fp32 mean over the keys, k_s = dtype(float(k) - mean), row quantiser.  Returns
+    (k_i8, k_scale [..., N, 1], k_mean [..., 1, D], k_s or None).  One launch (a thread-block cluster
+    per (batch, kv-head) slab, K read from HBM once) where the library serves the shape, otherwise
+    k_mean + smooth_quantize_k; both give the same bits."""
+    _require_cuda(k, "k_prologue")
+    if k.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("superl8_b200 k_prologue: k must be float16 or bfloat16")
+    k = k.contiguous()
+    N, D = k.shape[-2], k.shape[-1]
+    BH = int(math.prod(k.shape[:-2]))
+    lib = _lib.load()
+    if k.numel() == 0 or not lib.sl8_k_prologue_fused_ok(_C._DTYPE[k.dtype], BH, N, D):
+        mean = k_mean(k, seqlens_k)
+        k_i8, k_scale, k_s = smooth_quantize_k(k, mean, want_smoothed)
+        return k_i8, k_scale, mean, k_s
+    mean = torch.empty((*k.shape[:-2], 1, D), dtype=torch.float32, device=k.device)
+    k_i8 = torch.empty(k.shape, dtype=torch.int8, device=k.device)
+    k_scale = torch.empty((*k.shape[:-1], 1), dtype=torch.float32, device=k.device)
+    k_s = torch.empty_like(k) if want_smoothed else None
+    hpb = k.shape[1] if (seqlens_k is not None and k.dim() == 4) else 1
+    with torch.cuda.device(k.device):
+        rc = lib.sl8_k_prologue(k.data_ptr(), _C._DTYPE[k.dtype], BH, N, D,
+                                None if seqlens_k is None else seqlens_k.data_ptr(), hpb, mean.data_ptr(),
+                                k_i8.data_ptr(), k_scale.data_ptr(), None if k_s is None else k_s.data_ptr(),
+                                _C._stream(k.device))
+    _lib.check(rc, "k_prologue", 1)
+    return k_i8, k_scale, mean, k_s
+
+
 def quantize_v_perchannel(v: torch.Tensor):
     """Symmetric int8 per CHANNEL of V, scale over the key axis (reference
     superl8/quant/core.py:98-110): returns (v_i8 [..., N, D], v_scale fp32 [..., 1, D])."""
@@ -225,12 +255,15 @@ def quantize_qk(q, k, *, softmax_scale: float | None = None, rotate: bool = Fals
     instead of computing it (the summation order of a mean is not portable bit for bit)."""
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(q.shape[-1])
-    mean = k_mean(k, seqlens_k) if k_mean_override is None else k_mean_override
     if rotate:
+        mean = k_mean(k, seqlens_k) if k_mean_override is None else k_mean_override
         _ki8, _ks, k_s = smooth_quantize_k(k, mean, want_smoothed=True)
         q = rotate_last(q)
         k_i8, k_scale = quantize_int8_rowwise(rotate_last(k_s))
-    else:
+    elif k_mean_override is not None:
+        mean = k_mean_override
         k_i8, k_scale, _ = smooth_quantize_k(k, mean)
+    else:
+        k_i8, k_scale, mean, _ = k_prologue(k, seqlens_k)
     q_i8, q_scale, _ = quantize_q(q, softmax_scale)
     return q_i8, q_scale, k_i8, k_scale, mean

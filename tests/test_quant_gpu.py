@@ -10,7 +10,7 @@ import superl8_b200 as s8
 from conftest import GOLDEN, from_bits
 from gpu_helpers import ref_lib, ref_quantize
 from oracle import oracle
-from superl8_b200 import quant
+from superl8_b200 import _C, _lib, quant
 
 pytestmark = pytest.mark.gpu
 
@@ -209,3 +209,33 @@ def test_attention_asks_the_gate_first_after_a_demotion(device):
     assert s8.ops.last_gate_decision is False
     b2 = s8.attn_int8_fwd(q, k, v, causal=True)           # fused gate
     assert torch.equal(b1, b2)
+
+
+@pytest.mark.parametrize("D,dtype", [(128, torch.float16), (64, torch.float16), (256, torch.bfloat16), (128, torch.bfloat16)])
+def test_one_launch_k_prologue_equals_the_two_step_path_bitwise(D, dtype, device):
+    # The cluster kernel (mean through distributed shared memory, quantisation on a second walk) keeps the
+    # chunked, fixed-order sum of sl8_k_mean: mean, codes, scales and smoothed keys are the same bits.
+    g = torch.Generator().manual_seed(500 + D)
+    for (B, H, N) in ((1, 2, 1000), (2, 3, 1024), (1, 2, 1025), (1, 1, 5000), (2, 2, 8192), (1, 1, 9217), (1, 2, 7)):
+        k = (torch.randn(B, H, N, D, generator=g) + 0.7 * torch.randn(1, H, 1, D, generator=g)).to(dtype).to(device)
+        assert _lib.load().sl8_k_prologue_fused_ok(_C._DTYPE[dtype], B * H, N, D) == 1
+        mean2 = quant.k_mean(k)
+        i2, s2, ks2 = quant.smooth_quantize_k(k, mean2, want_smoothed=True)
+        i1, s1, mean1, ks1 = quant.k_prologue(k, want_smoothed=True)
+        assert torch.equal(mean1, mean2), (B, H, N)
+        assert torch.equal(i1, i2) and torch.equal(s1, s2) and torch.equal(ks1.view(torch.int16), ks2.view(torch.int16)), (B, H, N)
+        # repeatable
+        j1, t1, m1, _ = quant.k_prologue(k)
+        assert torch.equal(j1, i1) and torch.equal(t1, s1) and torch.equal(m1, mean1)
+    # per-sequence lengths: the mean runs over the first len keys of each sequence, all rows are quantised
+    k = torch.randn(3, 2, 3000, D, generator=g).to(dtype).to(device)
+    lens = torch.tensor([3000, 17, 1500], dtype=torch.int32, device=device)
+    mean2 = quant.k_mean(k, lens)
+    i2, s2, _ = quant.smooth_quantize_k(k, mean2)
+    i1, s1, mean1, _ = quant.k_prologue(k, lens)
+    assert torch.equal(mean1, mean2) and torch.equal(i1, i2) and torch.equal(s1, s2)
+    # shapes the cluster kernel does not serve fall back to the two steps
+    k = torch.randn(1, 2, 300, 80, generator=g).to(dtype).to(device)
+    assert _lib.load().sl8_k_prologue_fused_ok(_C._DTYPE[dtype], 2, 300, 80) == 0
+    i1, s1, mean1, _ = quant.k_prologue(k)
+    assert torch.equal(mean1, quant.k_mean(k)) and torch.equal(i1, quant.smooth_quantize_k(k, mean1)[0])
