@@ -225,7 +225,7 @@ def run_kernel_case(args):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     n = args.warmup + args.steps
-    if args.kernel_case in ("prefill_int8", "prefill_fp16", "quant_q", "quant_k"):
+    if args.kernel_case in ("prefill_int8", "prefill_fp16", "prefill_w8a8", "quant_q", "quant_k", "quant_k_fused"):
         c = workloads.PrefillCfg("cfg3_b2", 2, 64, 8, 8192, 128, True)
         q, k, v = workloads.prefill_inputs(c, dev, outliers=False)
         if args.kernel_case == "prefill_fp16":
@@ -238,6 +238,17 @@ def run_kernel_case(args):
             kk = torch.cat([k] * 8, dim=0)
             for _ in range(n):
                 quant.smooth_quantize_k(kk, quant.k_mean(kk))
+        elif args.kernel_case == "quant_k_fused":       # mean + smoothing + quantisation in one launch
+            kk = torch.cat([k] * 8, dim=0)
+            for _ in range(n):
+                quant.k_prologue(kk)
+        elif args.kernel_case == "prefill_w8a8":
+            q_i8, q_scale, k_i8, k_scale, _ = s8.quantize_qk(q, k)
+            qs, ks = q_scale.squeeze(-1).contiguous(), k_scale.squeeze(-1).contiguous()
+            v_i8, v_scale = quant.quantize_v_perchannel(v)
+            vs = v_scale.squeeze(-2).contiguous()
+            for _ in range(n):
+                _C.attn_w8a8_fwd(q_i8, qs, k_i8, ks, v_i8, vs, True, 0, True)
         else:
             q_i8, q_scale, k_i8, k_scale, _ = s8.quantize_qk(q, k)
             qs, ks = q_scale.squeeze(-1).contiguous(), k_scale.squeeze(-1).contiguous()
@@ -370,7 +381,7 @@ def main():
     ap.add_argument("--skip-extras", action="store_true", help="only the headline workload")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: every GPU owns a full batch; strong: the batch's units are split across the GPUs")
-    ap.add_argument("--kernel-case", default="", choices=["", "prefill_int8", "prefill_fp16", "decode", "decode_kv8", "backward", "quant_q", "quant_k"],
+    ap.add_argument("--kernel-case", default="", choices=["", "prefill_int8", "prefill_fp16", "prefill_w8a8", "quant_k_fused", "decode", "decode_kv8", "backward", "quant_q", "quant_k"],
                     help="launch ONE kernel family on a small case (for profilers): W warm-up + K launches, no JSON")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -506,6 +517,28 @@ def main():
         line["int8_path"] = {"value": total_ops / (ms8 * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms8,
                              "gate": "off", "roofline": r8}
         del out
+        # ---- full W8A8 (P on the int8 grid, int8 V) on a two-element slice of the batch ----
+        wq, wk, wv = (t[:2] for t in (q, k, v))
+        wqi, wqs, wki, wks, _m = s8.quantize_qk(wq, wk)
+        wqs, wks = wqs.squeeze(-1).contiguous(), wks.squeeze(-1).contiguous()
+        wvi, wvs = quant.quantize_v_perchannel(wv)
+        wvs = wvs.squeeze(-2).contiguous()
+        w_ops = cfg.ops * wq.shape[0] / cfg.B
+        ms_w = timed(lambda: _C.attn_w8a8_fwd(wqi, wqs, wki, wks, wvi, wvs, cfg.causal, 0, True), args.steps, args.warmup, world)
+        ms_wm = timed(lambda: _C.attn_w8a8_fwd(wqi, wqs, wki, wks, wvi, wvs, cfg.causal, 0, True, backend=_lib.SL8_BACKEND_MMA),
+                      1, 1, world)
+        line["w8a8"] = {"metric": "attn_w8a8_fwd_tops", "value": world * w_ops / (ms_w * 1e-3) / 1e12, "unit": UNIT,
+                        "ms_per_step": ms_w,
+                        "config": {"workload": f"first {wq.shape[0]} batch elements of {cfg.name}, per GPU; int8 Q, K, V, "
+                                               "P re-quantised per row and 32-key half"},
+                        "kernel": "fwd_tc_kernel W8 (tcgen05 kind::i8 QK; P snapped to the int8 grid, kind::f16 PV on the codes) "
+                                  "+ v_codes_kernel",
+                        "mma_sync_kernel": {"value": world * w_ops / (ms_wm * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_wm},
+                        "roofline": {"bound": "tensor", "achieved": w_ops / (ms_w * 1e-3) / 1e12,
+                                     "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                                     "frac": w_ops / (ms_w * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],
+                                     "peak_source": peaks["source"] + " bf16 dense (sustained)", "traffic": None}}
+        del wq, wk, wv, wqi, wqs, wki, wks, wvi, wvs
         # ---- the experiment the configurations describe: ONE global batch, sharded over the GPUs ----
         b_rng, _h = shard.batch_range(cfg.B, cfg.Hkv, min(world, cfg.B), rank % min(world, cfg.B))
         qs_, ks_, vs_ = (t[b_rng.start:b_rng.stop] for t in (q, k, v))

@@ -283,6 +283,19 @@ typedef struct sl8_w8a8_params {
 } sl8_w8a8_params;
 int sl8_attn_w8a8_fwd(const sl8_w8a8_params* p, void* stream);
 
+/*
+ * The same operator on the tensor-memory kernel of sl8_attn_int8_fwd (TMA tiles, Q.K^T as
+ * tcgen05 kind::i8): P is snapped to the reference's int8 grid (same p_scale, same codes) and
+ * code * p_scale enters a kind::f16 P.V against V's int8 codes held exactly as fp16, so the
+ * result differs from the integer P.V only by the fp16 rounding of code * p_scale (2^-11
+ * relative).  Serves D in {64, 128, 256}, N > 0 and causal_diag == N - M; anything else returns
+ * SL8_ERR_UNSUPPORTED and belongs to sl8_attn_w8a8_fwd.  The workspace
+ * (sl8_attn_w8a8_fwd_tc_workspace bytes, 16-byte aligned) holds the status word of the bounded
+ * device-side waits in its first int32 (zeroed by the call) and V's codes as fp16.
+ */
+size_t sl8_attn_w8a8_fwd_tc_workspace(const sl8_w8a8_params* p);
+int sl8_attn_w8a8_fwd_tc(const sl8_w8a8_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- packed variable-length prefill ------------------------------------------------- */
 
 /*

@@ -378,10 +378,13 @@ def attn_int8_decode(q, q_scale, k, k_scale, v, num_splits=-1, *, context_lens=N
     return out
 
 
-def attn_w8a8_fwd(q, q_scale, k, k_scale, v, v_scale, causal=False, causal_diag=0, per_warp_quant=True):
+def attn_w8a8_fwd(q, q_scale, k, k_scale, v, v_scale, causal=False, causal_diag=0, per_warp_quant=True, *,
+                  backend=None):
     """Full-W8A8 forward (int8 Q.K^T and int8 P.V).  Reference binding csrc/fni8_api.cpp:249-255
     (op csrc/kernel/attn_w8a8_fwd.cu:72-160): v int8 [B, Hkv, N, D], v_scale fp32 [B, Hkv, D];
-    returns fp16 [B, Hq, M, D]."""
+    returns fp16 [B, Hq, M, D].  ``backend`` (an extension): None picks the tensor-memory kernel
+    where it serves the call (D in 64/128/256, N > 0, causal diagonal at the sequence end) and the
+    mma.sync kernel otherwise; SL8_BACKEND_TCGEN05 / SL8_BACKEND_MMA force one."""
     what = "superl8_b200 w8a8"
     _check(v.is_cuda and v.dtype == torch.int8, f"{what}: q/k/v must be int8")
     _check(v_scale.is_cuda and v_scale.dtype == torch.float32, f"{what}: scales must be float32")
@@ -394,8 +397,16 @@ def attn_w8a8_fwd(q, q_scale, k, k_scale, v, v_scale, causal=False, causal_diag=
     p = _lib.W8A8Params(q=q.data_ptr(), q_scale=q_scale.data_ptr(), k=k.data_ptr(), k_scale=k_scale.data_ptr(),
                         v=v.data_ptr(), v_scale=v_scale.data_ptr(), out=out.data_ptr(), B=B, Hq=H, Hkv=Hkv, M=M, N=N,
                         D=D, causal=int(bool(causal)), causal_diag=int(causal_diag), per_warp_quant=int(bool(per_warp_quant)))
+    tc_ok = D in (64, 128, 256) and N > 0 and (not causal or int(causal_diag) == N - M)
+    _check(backend in (None, _lib.SL8_BACKEND_TCGEN05, _lib.SL8_BACKEND_MMA), f"{what}: unknown backend {backend}")
+    _check(tc_ok or backend != _lib.SL8_BACKEND_TCGEN05, f"{what}: the tensor-memory kernel does not serve this call")
+    lib = _lib.load()
     with torch.cuda.device(q.device):
-        rc = _lib.load().sl8_attn_w8a8_fwd(C.byref(p), _stream(q.device))
+        if tc_ok and backend != _lib.SL8_BACKEND_MMA:
+            ws = torch.empty(int(lib.sl8_attn_w8a8_fwd_tc_workspace(C.byref(p))), dtype=torch.uint8, device=q.device)
+            rc = lib.sl8_attn_w8a8_fwd_tc(C.byref(p), _ptr(ws), ws.numel(), _stream(q.device))
+        else:
+            rc = lib.sl8_attn_w8a8_fwd(C.byref(p), _stream(q.device))
     _lib.check(rc, "attn_w8a8_fwd", 1)
     return out
 

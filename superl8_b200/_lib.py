@@ -145,6 +145,8 @@ SIGNATURES = {
     "sl8_attn_int8_fwd_host_chunks": (C.c_int, [C.POINTER(HostFwdParams)]),
     "sl8_attn_int8_fwd_host": (C.c_int, [C.POINTER(HostFwdParams), C.c_void_p, C.c_size_t, C.c_void_p]),
     "sl8_attn_w8a8_fwd": (C.c_int, [C.POINTER(W8A8Params), C.c_void_p]),
+    "sl8_attn_w8a8_fwd_tc_workspace": (C.c_size_t, [C.POINTER(W8A8Params)]),
+    "sl8_attn_w8a8_fwd_tc": (C.c_int, [C.POINTER(W8A8Params), C.c_void_p, C.c_size_t, C.c_void_p]),
     "sl8_attn_int8_varlen": (C.c_int, [C.POINTER(VarlenParams), C.c_void_p, C.c_size_t, C.c_void_p]),
     "sl8_k_mean_packed": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int32, C.c_int64, C.c_void_p, C.c_int32,
                                     C.c_void_p, C.c_void_p]),

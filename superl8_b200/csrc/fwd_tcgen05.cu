@@ -44,6 +44,7 @@
 #include "sl8_fwd_tc2.cuh"
 #include "sl8_softmax.cuh"
 
+#include <algorithm>
 #include <type_traits>
 
 int sl8_fwd_mma_int8(const sl8_fwd_params* p, cudaStream_t s);  // fwd_mma.cu
@@ -80,7 +81,8 @@ struct TcCfg {
   static constexpr int OFF_K = OFF_Q + Q_TILE_BYTES;
   static constexpr int OFF_V = OFF_K + NKS * K_TILE_BYTES;
   static constexpr int OFF_KS = OFF_V + NVS * V_TILE_BYTES;   // kScaleStages x kTN floats
-  static constexpr int OFF_BAR = OFF_KS + kScaleStages * kTN * 4;
+  static constexpr int OFF_VS = OFF_KS + kScaleStages * kTN * 4;  // W8A8 mode: v_scale of the head, D floats
+  static constexpr int OFF_BAR = OFF_VS + 1024;
   static constexpr int NEED = OFF_BAR + 512 + 1024;
   // never more than two blocks per SM: each holds TMEM_COLS columns of the 512
   static constexpr int SMEM = NEED < 78 * 1024 ? 78 * 1024 : NEED;
@@ -107,6 +109,11 @@ struct TcArgs {
   int Hq, Hkv, M, N;
   int causal, window_left;
   float scale_log2;  // 16-bit Q/K mode: softmax_scale * log2(e)
+  // Full-W8A8 mode (kernel template W8): V holds int8 codes as fp16, v_scale fp32 [B, Hkv, D]
+  // multiplies the output channels, P is snapped to the int8 grid per row and tile
+  // (w8_per_half = 0) or per row and 32-key half (w8_per_half != 0).
+  const float* v_scale;
+  int w8_per_half;
 };
 
 enum Bar {
@@ -119,7 +126,7 @@ enum Bar {
 
 SL8_TRACE_DEFINE()
 
-template <int D, typename VT, bool QK8, bool PACKED>
+template <int D, typename VT, bool QK8, bool PACKED, bool W8 = false>
 __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                                                                const __grid_constant__ CUtensorMap k_map,
                                                                const __grid_constant__ CUtensorMap v_map,
@@ -344,6 +351,11 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
     const uint32_t t_row = tmem + ((uint32_t)(32 * lg) << 16);
     const uint32_t t_o = t_row + C::COL_O;
     float m_run = -INFINITY, l_run = 0.f;
+    float* const vs_smem = reinterpret_cast<float*>(smem + C::OFF_VS);
+    if (W8) {   // read back in the epilogue, after many block-wide barriers' worth of mbarrier traffic
+      for (int c = row; c < D; c += 32 * kSoftmaxWarps) vs_smem[c] = __ldg(a.v_scale + (int64_t)kv_bh * D + c);
+      named_sync(1, 32 * kSoftmaxWarps);
+    }
 
     for (int j = 0; j < ntiles; ++j) {
       const int n_block = n_begin + j * kTN;
@@ -371,7 +383,13 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
       // (the first tile, and rarely later) the max moves, O is corrected and P is formed again.
       const float xs = need_mask ? 1.f : qs;      // masked tiles keep finished logits in r, the others t
       float mx, psum;
-      {
+      float mxh[2] = {0.f, 0.f};
+      if (W8) {
+        // W8A8 mode: the tile's maxima come first (P's int8 grid hangs on them), no speculation
+        if (need_mask) w8_logits_pass<QK8, true>(r, ksv, qs, n_block, n_len, a.causal, qpos, a.window_left, mxh);
+        else w8_logits_pass<QK8, false>(r, ksv, qs, n_block, n_len, a.causal, qpos, a.window_left, mxh);
+        mx = fmaxf(mxh[0], mxh[1]);
+      } else {
         const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
         if (need_mask) softmax_pass<QK8, true, true, VT>(r, ksv, qs, xs, neg_m, n_block, n_len, a.causal, qpos, a.window_left, t_s, mx, psum);
         else softmax_pass<QK8, false, true, VT>(r, ksv, qs, xs, neg_m, n_block, n_len, a.causal, qpos, a.window_left, t_s, mx, psum);
@@ -405,11 +423,14 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
             tc_st32(t_o + 32 * c, o);
           }
         }
-        tc_wait_st();   // the speculative P stores are done before P is stored again
-        float unused;
-        softmax_pass<QK8, false, false, VT>(r, ksv, qs, xs, (m_run == -INFINITY) ? 0.f : -m_run, n_block, n_len, a.causal,
-                                            qpos, a.window_left, t_s, unused, psum);
+        if (!W8) {
+          tc_wait_st();   // the speculative P stores are done before P is stored again
+          float unused;
+          softmax_pass<QK8, false, false, VT>(r, ksv, qs, xs, (m_run == -INFINITY) ? 0.f : -m_run, n_block, n_len, a.causal,
+                                              qpos, a.window_left, t_s, unused, psum);
+        }
       }
+      if (W8) w8_exp_pass<VT>(r, xs, (m_run == -INFINITY) ? 0.f : -m_run, mxh, a.w8_per_half != 0, t_s, psum);
       l_run = l_run * resc + psum;
       if (warp == 0 && lane == 0) TR(8 * j + 4);
       tc_wait_st();
@@ -445,6 +466,16 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
           tc_wait_ld();
           tc_regs_ready(o);
           uint8_t* const sub = stage + (c >> 1) * (kTM * 128);
+          if (W8) {   // out = O * v_scale[channel] / l (reference csrc/include/attn_w8a8_fwd.cuh:207-222)
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              const float4 vs4 = *reinterpret_cast<const float4*>(vs_smem + 32 * c + i);
+              o[i] = __float_as_uint(__uint_as_float(o[i]) * vs4.x);
+              o[i + 1] = __float_as_uint(__uint_as_float(o[i + 1]) * vs4.y);
+              o[i + 2] = __float_as_uint(__uint_as_float(o[i + 2]) * vs4.z);
+              o[i + 3] = __float_as_uint(__uint_as_float(o[i + 3]) * vs4.w);
+            }
+          }
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             uint4 w;
@@ -577,7 +608,7 @@ __global__ void __launch_bounds__(128) qk_logits_kernel(const __grid_constant__ 
 
 // Dense call: M, N = rows per head.  Packed call (a.cu_q set): M = longest query sequence (sizes
 // the grid), total_q / total_k = tokens in the packed tensors.
-template <int D, typename VT, bool QK8>
+template <int D, typename VT, bool QK8, bool W8 = false>
 int launch_tc_impl(const void* q, const void* k, const void* v, int B, int Hq, int Hkv, int M, int N, const TcArgs& a,
                    cudaStream_t stream, int64_t total_q = 0, int64_t total_k = 0) {
   using C = TcCfg<D, QK8>;
@@ -604,8 +635,8 @@ int launch_tc_impl(const void* q, const void* k, const void* v, int B, int Hq, i
     SL8_CUDA_TRY(cudaFuncSetAttribute(fwd_tc_kernel<D, VT, QK8, kPk>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
     fwd_tc_kernel<D, VT, QK8, kPk><<<grid, kTcThreads, C::SMEM, stream>>>(q_map, k_map, v_map, o_map, a);
   } else {
-    SL8_CUDA_TRY(cudaFuncSetAttribute(fwd_tc_kernel<D, VT, QK8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-    fwd_tc_kernel<D, VT, QK8, false><<<grid, kTcThreads, C::SMEM, stream>>>(q_map, k_map, v_map, o_map, a);
+    SL8_CUDA_TRY(cudaFuncSetAttribute(fwd_tc_kernel<D, VT, QK8, false, W8>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+    fwd_tc_kernel<D, VT, QK8, false, W8><<<grid, kTcThreads, C::SMEM, stream>>>(q_map, k_map, v_map, o_map, a);
   }
   return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
 }
@@ -619,6 +650,26 @@ int launch_tc_d(int D, const void* q, const void* k, const void* v, int B, int H
     case 256: return launch_tc_impl<256, VT, QK8>(q, k, v, B, Hq, Hkv, M, N, a, s, total_q, total_k);
   }
   return SL8_ERR_UNSUPPORTED;
+}
+
+// int8 codes -> the same integers as fp16 (exact), 16 per thread
+__global__ void __launch_bounds__(256) v_codes_kernel(const int8_t* __restrict__ v, __half* __restrict__ out, int64_t n16) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) {
+    const uint4 w = __ldg(reinterpret_cast<const uint4*>(v) + i);
+    const uint32_t in[4] = {w.x, w.y, w.z, w.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int b0 = (int8_t)(in[j] & 0xff), b1 = (int8_t)((in[j] >> 8) & 0xff), b2 = (int8_t)((in[j] >> 16) & 0xff),
+                b3 = (int8_t)(in[j] >> 24);
+      o[2 * j] = pack2<__half>((float)b0, (float)b1);
+      o[2 * j + 1] = pack2<__half>((float)b2, (float)b3);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out) + 2 * i;
+    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+  }
 }
 
 template <int D>
@@ -683,6 +734,50 @@ extern "C" int sl8_attn_int8_fwd(const sl8_fwd_params* p, void* workspace, size_
   return p->v_dtype == SL8_F16
              ? launch_tc_d<__half, true>(p->D, p->q, p->k, p->v, p->B, p->Hq, p->Hkv, p->M, p->N, a, s)
              : launch_tc_d<__nv_bfloat16, true>(p->D, p->q, p->k, p->v, p->B, p->Hq, p->Hkv, p->M, p->N, a, s);
+}
+
+// ---- full W8A8 on the tensor-memory kernel -------------------------------------------------
+namespace {
+bool w8a8_tc_ok(const sl8_w8a8_params* p) {
+  return tc_head_dim(p->D) && p->N > 0 && (!p->causal || p->causal_diag == p->N - p->M);
+}
+size_t w8a8_codes_bytes(const sl8_w8a8_params* p) { return (size_t)p->B * p->Hkv * p->N * p->D * sizeof(__half); }
+}  // namespace
+
+extern "C" size_t sl8_attn_w8a8_fwd_tc_workspace(const sl8_w8a8_params* p) {
+  if (p == nullptr || p->B < 0 || p->Hkv < 0 || p->N < 0 || p->D < 0) return 256;
+  return 256 + (w8a8_codes_bytes(p) + 255) / 256 * 256;
+}
+
+extern "C" int sl8_attn_w8a8_fwd_tc(const sl8_w8a8_params* p, void* workspace, size_t workspace_bytes, void* stream) {
+  if (p == nullptr) return SL8_ERR_NULL;
+  if (p->B < 0 || p->Hq < 0 || p->Hkv < 0 || p->M < 0 || p->N < 0) return SL8_ERR_BAD_SHAPE;
+  if (p->D != 32 && p->D != 64 && p->D != 128 && p->D != 256) return SL8_ERR_BAD_HEAD_DIM;
+  if (p->Hq > 0 && (p->Hkv <= 0 || p->Hq % p->Hkv != 0)) return SL8_ERR_BAD_SHAPE;
+  if ((int64_t)p->B * p->Hq * p->M == 0) return SL8_OK;   // empty output
+  if (!w8a8_tc_ok(p)) return SL8_ERR_UNSUPPORTED;          // sl8_attn_w8a8_fwd serves these
+  if (!p->q || !p->q_scale || !p->out || !p->k || !p->k_scale || !p->v || !p->v_scale) return SL8_ERR_NULL;
+  if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->out)) return SL8_ERR_MISALIGNED;
+  if ((int64_t)p->B * p->Hq > 65535) return SL8_ERR_TOO_LARGE;
+  if (workspace == nullptr || workspace_bytes < sl8_attn_w8a8_fwd_tc_workspace(p)) return SL8_ERR_WORKSPACE;
+  if (!aligned16(workspace)) return SL8_ERR_MISALIGNED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  __half* codes = reinterpret_cast<__half*>(static_cast<uint8_t*>(workspace) + 256);
+  const int64_t n16 = (int64_t)p->B * p->Hkv * p->N * p->D / 16;   // D is a multiple of 64
+  const int blocks = (int)std::min<int64_t>((n16 + 255) / 256, 148 * 16);
+  SL8_CUDA_TRY(cudaMemsetAsync(workspace, 0, 256, s));   // status word of the bounded waits
+  v_codes_kernel<<<blocks, 256, 0, s>>>(p->v, codes, n16);
+  if (cudaGetLastError() != cudaSuccess) return SL8_ERR_CUDA;
+  TcArgs a{};
+  a.q_scale = p->q_scale; a.k_scale = p->k_scale; a.out = p->out; a.status = reinterpret_cast<int*>(workspace);
+  a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N; a.causal = p->causal; a.window_left = -1;
+  a.v_scale = p->v_scale; a.w8_per_half = p->per_warp_quant != 0;
+  switch (p->D) {
+    case 64: return launch_tc_impl<64, __half, true, true>(p->q, p->k, codes, p->B, p->Hq, p->Hkv, p->M, p->N, a, s);
+    case 128: return launch_tc_impl<128, __half, true, true>(p->q, p->k, codes, p->B, p->Hq, p->Hkv, p->M, p->N, a, s);
+    case 256: return launch_tc_impl<256, __half, true, true>(p->q, p->k, codes, p->B, p->Hq, p->Hkv, p->M, p->N, a, s);
+  }
+  return SL8_ERR_UNSUPPORTED;
 }
 
 extern "C" int sl8_attn_int8_varlen(const sl8_varlen_params* p, void* workspace, size_t workspace_bytes,

@@ -100,5 +100,94 @@ __device__ __forceinline__ void softmax_pass(uint32_t (&r)[kSweepCols], const fl
   mx = fmaxf(mx0, mx1);
 }
 
+// ---- full-W8A8 mode: P re-quantised to the int8 grid before P.V ----------------------------
+// The reference's W8A8 kernel (csrc/include/attn_w8a8_fwd.cuh:150-205) forms, per query row and
+// 64-key tile (or per 32-key half of it), p_scale = max(max(P) / 127, 2e-38) and the codes
+// P8 = rint(P / p_scale), multiplies the codes with the int8 V tile in int32 and adds
+// p_scale * (P8 . V8) to the fp32 output.  Here the same codes are formed, and code * p_scale --
+// a value of the int8 grid -- goes to tensor memory as fp16 for a kind::f16 P.V against V's int8
+// codes held as fp16 (exact): the products are those of the integer MMA up to the fp16 rounding
+// of code * p_scale (2^-11 relative), and no per-tile int32 -> fp32 fold of D columns per row is
+// needed.  The row sum l uses the unquantised P, as the reference does.
+
+// First walk: finished multiplicands in r (as softmax_pass FIRST leaves them) and the maximum of
+// each 32-key half.
+template <bool QK8, bool MASK>
+__device__ __forceinline__ void w8_logits_pass(uint32_t (&r)[kSweepCols], const float* __restrict__ ksv, float qs,
+                                               int n_block, int n_len, int causal, int qpos, int window_left,
+                                               float (&mxh)[2]) {
+  const float2 qs2 = make_float2(qs, qs);
+  const float2* ks2 = reinterpret_cast<const float2*>(ksv);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < kSweepCols / 4; ++u) {
+      const int i = h * (kSweepCols / 4) + u;
+      float2 p = QK8 ? mul2(make_float2((float)(int)r[2 * i], (float)(int)r[2 * i + 1]), ks2[i]) : bits2(r[2 * i], r[2 * i + 1]);
+      if (MASK) {
+        p = mul2(p, qs2);
+        const int gn = n_block + 2 * i;
+        const bool v0 = (gn < n_len) && (!causal || gn <= qpos) && (window_left < 0 || gn > qpos - window_left);
+        const bool v1 = (gn + 1 < n_len) && (!causal || gn + 1 <= qpos) && (window_left < 0 || gn + 1 > qpos - window_left);
+        p.x = v0 ? p.x : -INFINITY;
+        p.y = v1 ? p.y : -INFINITY;
+      }
+      if (u & 1) m1 = max3f(m1, p.x, p.y);
+      else m0 = max3f(m0, p.x, p.y);
+      r[2 * i] = __float_as_uint(p.x);
+      r[2 * i + 1] = __float_as_uint(p.y);
+    }
+    mxh[h] = fmaxf(m0, m1);
+  }
+}
+
+// Second walk: P = 2^(r * xs - m), its fp32 row sum, and code * p_scale packed as 16-bit pairs
+// into tensor memory.  mxh are the half maxima in r's units; per_half selects one scale per
+// 32-key half instead of one per tile.
+template <typename VT>
+__device__ __forceinline__ void w8_exp_pass(const uint32_t (&r)[kSweepCols], float xs, float neg_m, const float (&mxh)[2],
+                                            bool per_half, uint32_t t_p, float& sum) {
+  const float2 xs2 = make_float2(xs, xs), neg_m2 = make_float2(neg_m, neg_m);
+  float pm0 = ex2_issue(fmaf(mxh[0], xs, neg_m)), pm1 = ex2_issue(fmaf(mxh[1], xs, neg_m));
+  if (!per_half) pm0 = pm1 = fmaxf(pm0, pm1);
+  const float inv127 = 1.0f / 127.0f;
+  constexpr float kRint = 12582912.f;        // 1.5 * 2^23: adding and subtracting it rounds to nearest even
+  const float2 rint2 = make_float2(kRint, kRint), nrint2 = make_float2(-kRint, -kRint);
+  float2 sum_a = make_float2(0.f, 0.f), sum_b = sum_a;
+  constexpr int G = 4;
+  uint32_t pk[16];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const float ps = fmaxf((h ? pm1 : pm0) * inv127, 2e-38f);
+    const float ip = __frcp_rn(ps);
+    const float2 ps2 = make_float2(ps, ps), ip2 = make_float2(ip, ip);
+#pragma unroll
+    for (int g = 0; g < kSweepCols / 4 / G; ++g) {
+      float2 e[G];
+#pragma unroll
+      for (int u = 0; u < G; ++u) {
+        const int i = h * (kSweepCols / 4) + g * G + u;
+        const float2 x = __ffma2_rn(bits2(r[2 * i], r[2 * i + 1]), xs2, neg_m2);
+        e[u] = make_float2(ex2_issue(x.x), ex2_issue(x.y));
+      }
+#pragma unroll
+      for (int u = 0; u < G; u += 2) {
+        sum_a = add2(sum_a, e[u]);
+        sum_b = add2(sum_b, e[u + 1]);
+      }
+#pragma unroll
+      for (int u = 0; u < G; ++u) {
+        const int i = h * (kSweepCols / 4) + g * G + u;
+        const float2 code = add2(__ffma2_rn(e[u], ip2, rint2), nrint2);
+        const float2 d = mul2(code, ps2);
+        pk[i & 15] = pack2<VT>(d.x, d.y);
+      }
+    }
+    tc_st16(t_p + 16 * h, pk);
+  }
+  const float2 st = add2(sum_a, sum_b);
+  sum = st.x + st.y;
+}
 
 }  // namespace sl8

@@ -9,7 +9,7 @@ import torch
 import superl8_b200 as s8
 from gpu_helpers import ref_attn_w8a8_fwd, ref_lib
 from oracle import oracle
-from superl8_b200 import _C
+from superl8_b200 import _C, _lib
 
 pytestmark = pytest.mark.gpu
 PV_BARS = dict(min_cos=0.998, max_rel_l1=0.03, min_sqnr_db=18.0)
@@ -20,21 +20,29 @@ CASES = [  # B, Hq, Hkv, M, N, D, causal
 ]
 
 
+BACKENDS = {"tensor-memory": _lib.SL8_BACKEND_TCGEN05, "mma.sync": _lib.SL8_BACKEND_MMA}
+
+
 @pytest.mark.parametrize("case", CASES)
 @pytest.mark.parametrize("per_warp", [True, False])
-def test_w8a8_matches_reference_kernel_and_oracle(device, case, per_warp):
+@pytest.mark.parametrize("backend", list(BACKENDS))
+def test_w8a8_matches_reference_kernel_and_oracle(device, case, per_warp, backend):
     B, Hq, Hkv, M, N, D, causal = case
+    if backend == "tensor-memory" and D == 32:
+        pytest.skip("the tensor-memory kernel serves D = 64, 128, 256")
+    backend = BACKENDS[backend]
     q, k, v = oracle.make_batch(300 + D, B, Hq, Hkv, M, D, Sk=N)
     q_i8, q_scale, k_i8, k_scale, _ = oracle.quantize_qk(q, k)
     v_i8, v_scale = oracle.quantize_v_perchannel(v)
     qs, ks, vs = q_scale.squeeze(-1).contiguous(), k_scale.squeeze(-1).contiguous(), v_scale.squeeze(-2).contiguous()
     diag = (N - M) if causal else 0
     dv = lambda t: t.to(device)
-    out = _C.attn_w8a8_fwd(dv(q_i8), dv(qs), dv(k_i8), dv(ks), dv(v_i8), dv(vs), causal, diag, per_warp)
+    out = _C.attn_w8a8_fwd(dv(q_i8), dv(qs), dv(k_i8), dv(ks), dv(v_i8), dv(vs), causal, diag, per_warp, backend=backend)
     assert out.shape == (B, Hq, M, D) and out.dtype == torch.float16
-    assert torch.equal(out, _C.attn_w8a8_fwd(dv(q_i8), dv(qs), dv(k_i8), dv(ks), dv(v_i8), dv(vs), causal, diag, per_warp))
+    assert torch.equal(out, _C.attn_w8a8_fwd(dv(q_i8), dv(qs), dv(k_i8), dv(ks), dv(v_i8), dv(vs), causal, diag, per_warp, backend=backend))
     ref_o = oracle.attn_w8a8_fwd(q_i8, qs, k_i8, ks, v_i8, vs, causal, diag, per_warp)
-    # same tiles, same scales: only the rounding of an occasional P code (ex2 approximation) differs
+    # same tiles, same scales: only the rounding of an occasional P code (ex2 approximation) differs --
+    # and, on the tensor-memory kernel, the fp16 rounding of code * p_scale (2^-11 relative)
     assert oracle.cos_sim(out, ref_o) >= 0.9999 and oracle.rel_l1(out, ref_o) <= 5e-3
     if ref_lib() is not None and D <= 128:
         ref_k = ref_attn_w8a8_fwd(dv(q_i8), dv(qs), dv(k_i8), dv(ks), dv(v_i8), dv(vs), causal, diag, per_warp)
@@ -76,3 +84,22 @@ def test_int8_pv_is_still_behind_the_accuracy_gate(device):
                             internal_accuracy_gate=False)
     assert s8.ops.last_gate()[0] is None and torch.isfinite(out2.float()).all()
     assert not torch.equal(out2, out)
+
+
+def test_w8a8_backends_agree_and_the_causal_diagonal_picks_the_kernel(device):
+    """Both kernels form the same int8 grid for P; a causal diagonal that is not at the sequence
+    end (only the mma.sync kernel takes one) is routed there and refused by the other."""
+    q, k, v = oracle.make_batch(320, 2, 4, 2, 300, 128)
+    q_i8, q_scale, k_i8, k_scale, _ = oracle.quantize_qk(q, k)
+    v_i8, v_scale = oracle.quantize_v_perchannel(v)
+    args = [t.to(device) for t in (q_i8, q_scale.squeeze(-1).contiguous(), k_i8, k_scale.squeeze(-1).contiguous(), v_i8,
+                                   v_scale.squeeze(-2).contiguous())]
+    tc = _C.attn_w8a8_fwd(*args, True, 0, True, backend=_lib.SL8_BACKEND_TCGEN05)
+    mma = _C.attn_w8a8_fwd(*args, True, 0, True, backend=_lib.SL8_BACKEND_MMA)
+    assert oracle.cos_sim(tc, mma) >= 0.99999 and oracle.rel_l1(tc, mma) <= 2e-3
+    assert torch.equal(_C.attn_w8a8_fwd(*args, True, 0, True), tc)            # the default where it serves
+    shifted = _C.attn_w8a8_fwd(*args, True, 5, True)
+    assert torch.equal(shifted, _C.attn_w8a8_fwd(*args, True, 5, True, backend=_lib.SL8_BACKEND_MMA))
+    with pytest.raises(RuntimeError, match="does not serve"):
+        _C.attn_w8a8_fwd(*args, True, 5, True, backend=_lib.SL8_BACKEND_TCGEN05)
+    assert _C.device_status(device) == 0
