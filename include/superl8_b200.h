@@ -244,7 +244,7 @@ int sl8_attn_int8_fwd_fused(const sl8_fused_fwd_params* p, void* workspace, size
  * workspace: DEVICE memory, sl8_attn_int8_fwd_host_workspace() bytes (status word at + 0, then
  * the staging slots); the call allocates nothing on the device.  The first call on a device
  * creates the two copy streams and the events it keeps (make it before any stream capture).
- * kv_heads_per_chunk: 0 = choose (about 64 chunks per call, every chunk still filling the GPU);
+ * kv_heads_per_chunk: 0 = choose (about 16 chunks per call, every chunk still filling the GPU);
  * slots: 0 = 3.  gate_flags (nullable): host int32 [sl8_attn_int8_fwd_host_chunks()], receives every
  * chunk's gate flag.  Same shape limits as sl8_attn_int8_fwd_fused; no seqlens.
  */

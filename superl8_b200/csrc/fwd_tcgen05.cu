@@ -60,6 +60,18 @@ constexpr int kSoftmaxWarps = 4;                       // warp w owns tensor-mem
 constexpr int kProducerWarp = kSoftmaxWarps, kMmaWarp = kSoftmaxWarps + 1;
 constexpr int kTcThreads = 32 * (kSoftmaxWarps + 2);
 constexpr int kScaleStages = 4;                        // ring of k_scale tiles
+#ifndef SL8_QK_PAIR
+#define SL8_QK_PAIR 0
+#endif
+// Build option, off: Q.K^T issued for two key tiles at once (N = 128 into both S buffers).  An MMA
+// with N = 64 re-reads its 128-row A operand from shared memory for 64 columns of work and runs
+// at 58 % of the tensor pipe's rate (sl8_tensor_peak_probe_n: 1307 of 2222 TFLOP/s for kind::f16,
+// 2578 of 4496 TOPS for kind::i8); with N = 128 it runs at full rate.  Measured on a B = 4 slice of
+// the S = 8192 causal workload the pairing nevertheless LOSES (16-bit 4.10 -> 4.5-4.8 ms, int8
+// 4.12 -> 5.04 ms): the pair can only be issued once both P tiles have been consumed, so the
+// softmax warps wait for P.V + Q.K^T (about 770 cycles) every second tile, and the look-ahead of
+// one finished S tile -- what keeps them busy in the default order -- is gone.
+constexpr bool kQkPair = SL8_QK_PAIR != 0;
 
 template <int D, bool QK8>
 struct TcCfg {
@@ -223,7 +235,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
       mbar_expect_tx(&bars[K_FULL + ks], C::K_TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < C::QSUBS; ++c)
-        tma_load_3d(smem + C::OFF_K + ks * C::K_TILE_BYTES + c * C::K_SUB_BYTES, &k_map, &bars[K_FULL + ks],
+        tma_load_3d(smem + C::OFF_K + (kQkPair ? c * 2 * C::K_SUB_BYTES + ks * C::K_SUB_BYTES : ks * C::K_TILE_BYTES + c * C::K_SUB_BYTES),
+                    &k_map, &bars[K_FULL + ks],
                     c * (C::QROW / (QK8 ? 1 : 2)), SL8_KC1(n_begin + t * kTN), SL8_KC2(n_begin + t * kTN));
       return true;
     };
@@ -308,10 +321,37 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
       __syncwarp();
       return true;
     };
+    // Pair mode: tiles t (even) and t + 1 in one N = 128 instruction per K step; the two key tiles
+    // lie behind one another in shared memory (per 128-byte sub-tile: 128 rows).
+    const uint32_t idesc_qk2 = QK8 ? umma_idesc(2, 1, 1, 0, 0, kTM, 2 * kTN) : umma_idesc(1, vfmt, vfmt, 0, 0, kTM, 2 * kTN);
+    auto issue_qk_pair = [&](int t) -> bool {
+      const bool both = t + 1 < ntiles;
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars[K_FULL + 0], (t >> 1) & 1, a.status))) return false;
+      if (both && !__all_sync(0xffffffffu, mbar_wait(&bars[K_FULL + 1], (t >> 1) & 1, a.status))) return false;
+      tc_fence_after();
+      if (elect_one()) {
+#pragma unroll
+        for (int s = 0; s < C::QK_STEPS; ++s) {
+          const uint32_t sub = 32 * s / C::QROW, within = 32 * s % C::QROW;
+          const uint64_t da = umma_desc_advance(dq, sub * C::Q_SUB_BYTES + within);
+          const uint64_t db = umma_desc_advance(dk, sub * 2 * C::K_SUB_BYTES + within);
+          if (QK8) tc_mma_i8_ss(tmem + C::COL_S, da, db, idesc_qk2, s > 0 ? 1u : 0u);
+          else tc_mma_f16_ss(tmem + C::COL_S, da, db, idesc_qk2, s > 0 ? 1u : 0u);
+        }
+        tc_commit(&bars[S_FULL + 0]);
+        if (both) tc_commit(&bars[S_FULL + 1]);
+      }
+      __syncwarp();
+      return true;
+    };
     static_assert(C::NKS == 2 && C::NVS == 2, "the issuer is unrolled over two stages");
     ok = __all_sync(0xffffffffu, mbar_wait(&bars[Q_FULL], 0, a.status));
-    if (ok) ok = issue_qk(0, 0);
-    if (ok && ntiles > 1) ok = issue_qk(1, 1);
+    if (kQkPair) {
+      if (ok) ok = issue_qk_pair(0);
+    } else {
+      if (ok) ok = issue_qk(0, 0);
+      if (ok && ntiles > 1) ok = issue_qk(1, 1);
+    }
     for (int j0 = 0; j0 < ntiles && ok; j0 += 2) {
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
@@ -334,7 +374,9 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
         }
         __syncwarp();
         TR(4096 + 8 * j + 2);
-        if (j + 2 < ntiles) ok = issue_qk(j + 2, u);
+        if (kQkPair) {
+          if (u == 1 && j + 1 < ntiles) ok = issue_qk_pair(j + 1);
+        } else if (j + 2 < ntiles) ok = issue_qk(j + 2, u);
         TR(4096 + 8 * j + 3);
         if (j == ntiles - 1 && elect_one()) tc_commit(&bars[O_DONE]);
         __syncwarp();

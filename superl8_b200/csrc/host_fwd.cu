@@ -54,7 +54,11 @@ int device_state(DeviceState** out) {
 }
 
 struct Plan {
-  int kv_per_chunk, chunks_per_batch, n_chunks, slots;
+  // Chunks are kv_per_chunk KV heads wide; in the automatic plan the LAST batch element is cut into
+  // narrower ones (kv_tail heads), because what follows the last host->device copy -- the last
+  // chunk's kernels and its copy back -- overlaps with nothing (S = 8192, 64 heads: 2.4 ms of copy
+  // behind a 134 MB chunk, 0.6 ms behind a 34 MB one).
+  int kv_per_chunk, chunks_per_batch, kv_tail, tail_chunks, n_chunks, slots;
   size_t q_bytes, kv_bytes, out_bytes, fused_ws, slot_bytes, total;
   sl8_fused_fwd_params chunk;   // shape of one (full-size) chunk
 };
@@ -68,17 +72,24 @@ Plan plan(const sl8_host_fwd_params* p) {
   const int G = p->Hkv > 0 ? p->Hq / p->Hkv : 1;
   int kvc = p->kv_heads_per_chunk;
   if (kvc <= 0) {
-    // enough chunks to keep fill and drain of the three-stage pipeline short (about 64 per call),
-    // but not so small that a chunk's kernels no longer fill the GPU
+    // enough chunks to keep fill and drain of the three-stage pipeline short (about 16 per call),
+    // but not so small that a chunk's kernels no longer fill the GPU -- and no smaller than that:
+    // on the S = 8192, 64-head workload 16 / 32 / 64 / 128 chunks (134 ... 17 MB of Q per copy) measure
+    // 58.1 / 59.0 / 63.1 / 71.9 ms per call, whatever the number of staging slots
     kvc = p->Hkv;
-    while (kvc > 1 && kvc % 2 == 0 && (int64_t)p->B * (p->Hkv / kvc) < 64 && (int64_t)(kvc / 2) * G * ((p->M + 127) / 128) >= 296) kvc /= 2;
+    while (kvc > 1 && kvc % 2 == 0 && (int64_t)p->B * (p->Hkv / kvc) < 16 && (int64_t)(kvc / 2) * G * ((p->M + 127) / 128) >= 296) kvc /= 2;
   }
   if (kvc > p->Hkv) kvc = p->Hkv;
   while (kvc > 1 && p->Hkv % kvc) --kvc;
   if (kvc < 1) kvc = 1;
   pl.kv_per_chunk = kvc;
   pl.chunks_per_batch = p->Hkv > 0 ? p->Hkv / kvc : 0;
-  pl.n_chunks = p->B * pl.chunks_per_batch;
+  pl.kv_tail = kvc;
+  if (p->kv_heads_per_chunk <= 0)
+    while (pl.kv_tail > 1 && pl.kv_tail % 2 == 0 && pl.kv_tail * 4 > kvc && (int64_t)(pl.kv_tail / 2) * G * ((p->M + 127) / 128) >= 296)
+      pl.kv_tail /= 2;
+  pl.tail_chunks = p->Hkv > 0 ? p->Hkv / pl.kv_tail : 0;
+  pl.n_chunks = p->B > 0 ? (p->B - 1) * pl.chunks_per_batch + pl.tail_chunks : 0;
   pl.slots = p->slots <= 0 ? 3 : (p->slots < 2 ? 2 : (p->slots > kMaxSlots ? kMaxSlots : p->slots));
   pl.q_bytes = (size_t)kvc * G * p->M * p->D * 2;
   pl.kv_bytes = (size_t)kvc * p->N * p->D * 2;
@@ -133,16 +144,25 @@ extern "C" int sl8_attn_int8_fwd_host(const sl8_host_fwd_params* p, void* worksp
   SL8_CUDA_TRY(cudaMemsetAsync(ws, 0, 256, cur));   // the call's status word
 
   auto slot_base = [&](int s) { return ws + 256 + (size_t)s * pl.slot_bytes; };
+  // chunk i = KV heads [h0, h0 + kvc) of batch element b
+  const int body = (p->B - 1) * pl.chunks_per_batch;
+  auto chunk_of = [&](int i, int* b, int* h0, int* kvc) {
+    if (i < body) { *b = i / pl.chunks_per_batch; *h0 = (i % pl.chunks_per_batch) * pl.kv_per_chunk; *kvc = pl.kv_per_chunk; }
+    else { *b = p->B - 1; *h0 = (i - body) * pl.kv_tail; *kvc = pl.kv_tail; }
+  };
   auto upload = [&](int i) -> int {
-    const int s = i % pl.slots, b = i / pl.chunks_per_batch, h0 = (i % pl.chunks_per_batch) * pl.kv_per_chunk;
+    const int s = i % pl.slots;
+    int b, h0, kvc;
+    chunk_of(i, &b, &h0, &kvc);
+    const size_t qb = pl.q_bytes / pl.kv_per_chunk * kvc, kvb = pl.kv_bytes / pl.kv_per_chunk * kvc;
     uint8_t* base = slot_base(s);
     if (i >= pl.slots) SL8_CUDA_TRY(cudaStreamWaitEvent(st->h2d, st->computed[s], 0));   // the slot's previous kernels
     const uint8_t* hq = static_cast<const uint8_t*>(p->q) + (size_t)b * q_batch + (size_t)h0 * G * p->M * p->D * 2;
     const uint8_t* hk = static_cast<const uint8_t*>(p->k) + (size_t)b * kv_batch + (size_t)h0 * p->N * p->D * 2;
     const uint8_t* hv = static_cast<const uint8_t*>(p->v) + (size_t)b * kv_batch + (size_t)h0 * p->N * p->D * 2;
-    SL8_CUDA_TRY(cudaMemcpyAsync(base, hq, pl.q_bytes, cudaMemcpyHostToDevice, st->h2d));
-    SL8_CUDA_TRY(cudaMemcpyAsync(base + up(pl.q_bytes), hk, pl.kv_bytes, cudaMemcpyHostToDevice, st->h2d));
-    SL8_CUDA_TRY(cudaMemcpyAsync(base + up(pl.q_bytes) + up(pl.kv_bytes), hv, pl.kv_bytes, cudaMemcpyHostToDevice, st->h2d));
+    SL8_CUDA_TRY(cudaMemcpyAsync(base, hq, qb, cudaMemcpyHostToDevice, st->h2d));
+    SL8_CUDA_TRY(cudaMemcpyAsync(base + up(pl.q_bytes), hk, kvb, cudaMemcpyHostToDevice, st->h2d));
+    SL8_CUDA_TRY(cudaMemcpyAsync(base + up(pl.q_bytes) + up(pl.kv_bytes), hv, kvb, cudaMemcpyHostToDevice, st->h2d));
     SL8_CUDA_TRY(cudaEventRecord(st->arrived[s], st->h2d));
     return SL8_OK;
   };
@@ -151,7 +171,9 @@ extern "C" int sl8_attn_int8_fwd_host(const sl8_host_fwd_params* p, void* worksp
   for (int i = 0; i < ahead && i < pl.n_chunks; ++i)
     if ((rc = upload(i)) != SL8_OK) return rc;
   for (int i = 0; i < pl.n_chunks; ++i) {
-    const int s = i % pl.slots, b = i / pl.chunks_per_batch, h0 = (i % pl.chunks_per_batch) * pl.kv_per_chunk;
+    const int s = i % pl.slots;
+    int b, h0, kvc;
+    chunk_of(i, &b, &h0, &kvc);
     uint8_t* base = slot_base(s);
     uint8_t* d_out = base + up(pl.q_bytes) + 2 * up(pl.kv_bytes);
     uint8_t* fused_ws = d_out + up(pl.out_bytes);
@@ -159,6 +181,7 @@ extern "C" int sl8_attn_int8_fwd_host(const sl8_host_fwd_params* p, void* worksp
     SL8_CUDA_TRY(cudaStreamWaitEvent(cur, st->arrived[s], 0));
     if (i >= pl.slots) SL8_CUDA_TRY(cudaStreamWaitEvent(cur, st->drained[s], 0));   // the slot's previous output has left
     sl8_fused_fwd_params c = pl.chunk;
+    c.Hq = kvc * G; c.Hkv = kvc;
     c.q = base; c.k = base + up(pl.q_bytes); c.v = base + up(pl.q_bytes) + up(pl.kv_bytes); c.out = d_out;
     c.gate_flag = flag; c.device_status = ws;
     if ((rc = sl8_attn_int8_fwd_fused(&c, fused_ws, pl.fused_ws, stream)) != SL8_OK) return rc;
@@ -166,7 +189,7 @@ extern "C" int sl8_attn_int8_fwd_host(const sl8_host_fwd_params* p, void* worksp
     if (i + ahead < pl.n_chunks && (rc = upload(i + ahead)) != SL8_OK) return rc;
     SL8_CUDA_TRY(cudaStreamWaitEvent(st->d2h, st->computed[s], 0));
     uint8_t* ho = static_cast<uint8_t*>(p->out) + (size_t)b * q_batch + (size_t)h0 * G * p->M * p->D * 2;
-    SL8_CUDA_TRY(cudaMemcpyAsync(ho, d_out, pl.out_bytes, cudaMemcpyDeviceToHost, st->d2h));
+    SL8_CUDA_TRY(cudaMemcpyAsync(ho, d_out, pl.out_bytes / pl.kv_per_chunk * kvc, cudaMemcpyDeviceToHost, st->d2h));
     if (p->gate_flags != nullptr)
       SL8_CUDA_TRY(cudaMemcpyAsync(p->gate_flags + i, flag, sizeof(int32_t), cudaMemcpyDeviceToHost, st->d2h));
     SL8_CUDA_TRY(cudaEventRecord(st->drained[s], st->d2h));
