@@ -434,8 +434,7 @@ int sl8_quantize_v_perchannel(const void* v, int dtype, int64_t BH, int64_t N, i
  *    SL8_ERR_TOO_LARGE and launches nothing.
  *  - This function calls no cudaMalloc / cudaFree and no allocating library routine.
  *  - The first call on each device looks up the array's device address (once per
- *    device, with that device current, under a host lock); make that first call before
- *    any stream capture.
+ *    device, with that device current, under a host lock).
  *  - All calls on a device share the one array, and it keeps the previous call's
  *    contents (every value a call reads it has written itself first, so nothing needs
  *    clearing between calls).  Two calls that overlap on the GPU -- different streams,
