@@ -165,7 +165,13 @@ typedef struct sl8_fwd_params {
  * status word the kernel sets non-zero when a bounded wait expires (read it
  * with sl8_read_device_status after synchronising).
  * With seqlens_*, sequence b is computed as if the reference had been called on
- * its [:, :, :len] slices; padded output rows are written as zeros.
+ * its [:, :, :len] slices; padded output rows are written as zeros.  One difference
+ * from a slice: K and V rows between seqlens_k[b] and N are still LOADED with the tile
+ * that holds the last valid key (their P is exactly 0), so they must hold finite
+ * numbers -- 0 * NaN in the P.V contraction would poison the row.  Zero-initialised or
+ * previously used cache memory is fine; memory that may hold NaN / Inf bit patterns
+ * (a fresh allocation that was never written) is not.  The same holds for the keys
+ * past context_lens in the decode entries.
  */
 size_t sl8_attn_int8_fwd_workspace(const sl8_fwd_params* p);
 int sl8_attn_int8_fwd(const sl8_fwd_params* p, void* workspace, size_t workspace_bytes,

@@ -4,6 +4,13 @@
 ``sm_100a`` and links one C-ABI shared library next to this file.  nvcc
 cross-compiles, so no GPU is needed to build.  Objects are rebuilt only when a
 source or header is newer than the object.
+
+``python -m superl8_b200.build --trace [-DSL8_TRACE_BASE=n -DSL8_TRACE_STRIDE=m ...]`` builds a SECOND
+library, ``libsuperl8_b200_trace.so`` (objects under ``csrc/build_trace``), with ``-DSL8_TRACE``: the
+forward and backward tensor-memory kernels then stamp ``clock64()`` at the points marked ``TR(slot)``
+in their sources for eight blocks of a launch (csrc/sl8_common.cuh), and the library exports
+``sl8_dbg_read_trace`` / ``sl8_dbg_read_trace2`` / ``sl8_dbg_read_trace_bwd``.  ``superl8_b200.trace``
+loads that library and reads the stamps back.  The shipped library never carries any of it.
 """
 
 from __future__ import annotations
@@ -37,18 +44,27 @@ def _newest_header_mtime() -> float:
     return max(h.stat().st_mtime for h in hdrs if h.exists())
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    BUILD_DIR.mkdir(parents=True, exist_ok=True)
+TRACE_BUILD_DIR = PKG_DIR / "csrc" / "build_trace"
+TRACE_LIB_PATH = PKG_DIR / "libsuperl8_b200_trace.so"
+
+
+def build(force: bool = False, verbose: bool = False, trace: bool = False, defines=()) -> Path:
+    """Compiles and links the library; ``trace=True`` builds the clock-stamp variant (always from
+    scratch: its defines are not part of the staleness check) beside it."""
+    build_dir, lib_path = (TRACE_BUILD_DIR, TRACE_LIB_PATH) if trace else (BUILD_DIR, LIB_PATH)
+    extra = ["-DSL8_TRACE", *defines] if trace else list(defines)
+    force = force or trace
+    build_dir.mkdir(parents=True, exist_ok=True)
     sources = sorted(CSRC.glob("*.cu"))
     hdr_m = _newest_header_mtime()
     jobs = []
     objs = []
     for src in sources:
-        obj = BUILD_DIR / (src.stem + ".o")
+        obj = build_dir / (src.stem + ".o")
         objs.append(obj)
         stale = force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_m)
         if stale:
-            cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+            cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-c", str(src), "-o", str(obj)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append(cmd)
@@ -63,10 +79,10 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as ex:
         list(ex.map(run, jobs))
 
-    relink = force or jobs or not LIB_PATH.exists() or any(o.stat().st_mtime > LIB_PATH.stat().st_mtime for o in objs)
+    relink = force or jobs or not lib_path.exists() or any(o.stat().st_mtime > lib_path.stat().st_mtime for o in objs)
     if relink:
-        run([_nvcc(), "-shared", "-o", str(LIB_PATH), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"])
-    return LIB_PATH
+        run([_nvcc(), "-shared", "-o", str(lib_path), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"])
+    return lib_path
 
 
 EXT_SRC = CSRC / "torch_ext" / "sl8_torch_ext.cpp"
@@ -109,6 +125,9 @@ def build_torch_ext(force: bool = False) -> Path:
 
 
 if __name__ == "__main__":
+    if "--trace" in sys.argv:
+        print(build(trace=True, verbose="-v" in sys.argv, defines=[a for a in sys.argv[1:] if a.startswith("-D")]))
+        sys.exit(0)
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
     if "--no-ext" not in sys.argv:
         print(build_torch_ext(force="--force" in sys.argv))

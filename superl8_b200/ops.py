@@ -80,7 +80,8 @@ def attn_int8_fwd(q, k, v, *, causal: bool = False, scale: float | None = None, 
     (the reference skips its gate under capture); ``last_gate()`` then returns (None, flag).
     Head dims 64/128/256 with one dtype for q, k, v; other cases take the host-side gate.
     ``seqlens_q`` / ``seqlens_k`` (int32 [B], not in the reference) give per-sequence
-    lengths for padded ragged batches.  A negative ``scale`` is served by the warp-level
+    lengths for padded ragged batches; the padding of k and v must hold finite numbers (rows of the
+    last tile past a sequence's length are loaded and multiplied by a P of exactly 0).  A negative ``scale`` is served by the warp-level
     backend (the tensor-memory kernel takes row maxima before scaling and wants scale >= 0).
     """
     s = (1.0 / math.sqrt(q.shape[-1])) if scale is None else scale
