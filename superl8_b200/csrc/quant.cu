@@ -75,6 +75,14 @@ template <> struct Vec8<__half> {
       f[2 * i + 1] = t.y;
     }
   }
+  // round to nearest even, two elements per conversion instruction
+  __device__ static uint4 pack(const float (&f)[8]) {
+    uint4 u;
+    __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    return u;
+  }
 };
 template <> struct Vec8<__nv_bfloat16> {
   __device__ static void unpack(const uint4& u, float (&f)[8]) {
@@ -85,6 +93,13 @@ template <> struct Vec8<__nv_bfloat16> {
       f[2 * i] = t.x;
       f[2 * i + 1] = t.y;
     }
+  }
+  __device__ static uint4 pack(const float (&f)[8]) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return u;
   }
 };
 
@@ -158,15 +173,11 @@ __device__ __forceinline__ int quant_rows_vec_body(const QuantArgs& a, int64_t b
           m1 = __ldg(reinterpret_cast<const float4*>(mr + c0 + 4));
         }
         const float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
-        T t[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          t[i] = from_f32<T>(f[v][i] - mm[i]);  // rounded to the storage dtype, as torch.sub(out=)
-          f[v][i] = to_f32<T>(t[i]);
-        }
-        if (a.smoothed != nullptr)
-          *reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.smoothed) + row * a.K + c0) =
-              *reinterpret_cast<const uint4*>(t);
+        for (int i = 0; i < 8; ++i) f[v][i] -= mm[i];
+        const uint4 t = Vec8<T>::pack(f[v]);   // rounded to the storage dtype, as torch.sub(out=)
+        Vec8<T>::unpack(t, f[v]);
+        if (a.smoothed != nullptr) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.smoothed) + row * a.K + c0) = t;
       }
     }
     float amax = 0.0f;
@@ -383,7 +394,7 @@ int dispatch(const QuantArgs& a, int dtype, cudaStream_t s) {
 
 // ---- K mean -------------------------------------------------------------------
 constexpr int kMeanChunkRows = 1024;
-constexpr int kMeanThreads = 256;
+constexpr int kMeanThreads = 512;
 
 // grid (chunks, BH).  Thread (rl, cv) sums rows rl, rl + RL, ... of the chunk for
 // the 8 columns of vector cv; the RL row-lanes are then added in index order.
@@ -462,7 +473,6 @@ __global__ void __launch_bounds__(kMeanThreads) k_mean_partial_kernel(
 // the three-launch path because it is bound by latency, not by bytes: fewer resident blocks, which
 // would keep the slabs in L2, measure slower (3 / 2 blocks per SM: 179 / 198 us against 155).
 constexpr int kClusterCtas = 8;
-static_assert(kMeanThreads == kQuantThreads, "one block shape for both phases");
 
 template <typename T, int LPR, int NV>
 __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kMeanThreads)
@@ -499,7 +509,7 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kMeanThre
   }
   cluster.sync();
   // quantise this block's chunks (all N rows of the slab are quantised, also those past seqlens)
-  const int64_t rows_per_block = (int64_t)(kQuantThreads / 32) * (32 / LPR);
+  const int64_t rows_per_block = (int64_t)(kMeanThreads / 32) * (32 / LPR);
   for (int jj = 0; jj < chunks_per_cta; ++jj) {
     const int j = rank + jj * kClusterCtas;
     if (j >= nchunks) break;
