@@ -115,6 +115,23 @@ int sl8_smooth_quant_k(const void* k, int dtype, int64_t BH, int64_t N, int64_t 
                        void* stream);
 
 /*
+ * The rotate=True prologue (reference superl8/quant/core.py:186-194 with
+ * superl8/quant/rotation.py:28-51): every row of x [rows, D] is, in one pass and in registers,
+ *   [mean != NULL]  smoothed:  x - mean[row / rows_per_head, :], rounded to x's dtype;
+ *   rotated:        y = x @ (H_D / sqrt(D)), H_D the Sylvester-Hadamard matrix, computed in fp32 as a
+ *                   Walsh-Hadamard butterfly and rounded to x's dtype (the reference's matmul adds in
+ *                   another order: results agree to fp32 rounding before that cast);
+ *   [rotated != NULL]  stored as x's dtype;
+ *   [q != NULL]        quantised per row: codes to q, scale * fold to scale (fold = softmax_scale *
+ *                      log2(e) for Q, 1 for K).
+ * Q: mean = NULL.  K: mean = the slab means of sl8_k_mean, rows_per_head = N.  The rotation alone
+ * (`rotate_last`): q = NULL.  fp16 / bf16, D a power of two in [32, 1024], 16-byte aligned rows.
+ */
+int sl8_hadamard_quant_rows(const void* x, int dtype, int64_t rows, int64_t D, const float* mean,
+                            int64_t rows_per_head, float fold, int8_t* q, float* scale, void* rotated,
+                            void* stream);
+
+/*
  * K prologue in ONE launch: steps 1 and 2 together (reference superl8/quant/core.py:29-44, 70-95, then
  * :47-62).  A thread-block cluster owns each (batch, kv-head) slab: it forms the fp32 mean (the same
  * chunked, fixed-order sum as sl8_k_mean: the results are bitwise equal), shares it through distributed

@@ -86,11 +86,29 @@ def fold_scale(scale: torch.Tensor, softmax_scale: float) -> torch.Tensor:
     return scale * (softmax_scale * LOG2E)
 
 
-def quantize_qk(q, k, softmax_scale=None, rule: str = "cuda", k_mean=None):
-    """Reference superl8/quant/core.py:164-196 (rotate=False)."""
+def hadamard_matrix(d: int) -> torch.Tensor:
+    """Reference superl8/quant/rotation.py:28-38: the Sylvester-Hadamard matrix over sqrt(d), fp32."""
+    assert d > 0 and d & (d - 1) == 0
+    h = torch.ones(1, 1, dtype=torch.float32)
+    while h.shape[0] < d:
+        h = torch.cat([torch.cat([h, h], dim=1), torch.cat([h, -h], dim=1)], dim=0)
+    return h / (d ** 0.5)
+
+
+def rotate_last(x: torch.Tensor) -> torch.Tensor:
+    """Reference superl8/quant/rotation.py:41-51: (x.float() @ M) cast back to x's dtype."""
+    x = x.detach().cpu()
+    return (x.float() @ hadamard_matrix(x.shape[-1])).to(x.dtype)
+
+
+def quantize_qk(q, k, softmax_scale=None, rule: str = "cuda", k_mean=None, rotate: bool = False):
+    """Reference superl8/quant/core.py:164-196; rotate: lines 186-190 (Q and the smoothed K rotated
+    by the same Hadamard matrix before the row quantiser)."""
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(q.shape[-1])
     k_s, mean = smooth_k(k, k_mean)
+    if rotate:
+        q, k_s = rotate_last(q), rotate_last(k_s)
     q_i8, q_scale = quantize_rowwise(q, rule)
     k_i8, k_scale = quantize_rowwise(k_s, rule)
     return q_i8, fold_scale(q_scale, softmax_scale), k_i8, k_scale, mean

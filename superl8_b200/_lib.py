@@ -130,6 +130,8 @@ SIGNATURES = {
                              C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "sl8_smooth_quant_k": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
                                      C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "sl8_hadamard_quant_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_float,
+                                          C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "sl8_k_prologue_fused_ok": (C.c_int, [C.c_int, C.c_int64, C.c_int64, C.c_int64]),
     "sl8_k_prologue": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int32,
                                  C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),

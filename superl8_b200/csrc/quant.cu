@@ -12,6 +12,8 @@
 // 8 * (32 / lanes-per-row) rows per step and walks the rows grid-stride.
 #include "sl8_common.cuh"
 
+#include <cmath>
+
 #include <cooperative_groups.h>
 
 namespace cg = cooperative_groups;
@@ -25,7 +27,11 @@ constexpr float kQMaxInv = 1.0f / 127.0f;
 
 // kGateOnly: the outlier statistic of the query mode alone -- rows are read, nothing is written
 // but the flag (the reference runs its gate before it quantises, superl8/ops.py:118-130)
-enum QuantMode { kPlain = 0, kQueryFoldGate = 1, kKeySmooth = 2, kGateOnly = 3 };
+// kRotate: [subtract the mean if one is given, round] -> normalised Hadamard rotation of the row in
+// fp32 -> round to the storage dtype -> [store the rotated row] -> [quantise, scale * fold]: the
+// rotate=True prologue of the reference (superl8/quant/core.py:186-194, superl8/quant/rotation.py:41-51)
+// in the registers of the row quantiser, no extra trip through HBM
+enum QuantMode { kPlain = 0, kQueryFoldGate = 1, kKeySmooth = 2, kGateOnly = 3, kRotate = 4 };
 
 struct QuantArgs {
   const void* x;
@@ -34,6 +40,7 @@ struct QuantArgs {
   float* plain_scale;   // query mode only (nullable)
   const float* mean;    // key mode: [BH, K]
   void* smoothed;       // key mode (nullable): k - mean in x's dtype
+  void* rotated;        // rotate mode (nullable): the rotated row in x's dtype
   int32_t* flag;        // query mode (nullable): OR-ed with 1 if any row is outlier dominated
   int64_t rows;
   int64_t rows_per_head;
@@ -45,6 +52,7 @@ struct QuantArgs {
   int K;
   float fold;
   float ratio_threshold;
+  float rot_norm;       // rotate mode: 1 / sqrt(K)
 };
 
 // Row of the mean table for a row of the key tensor (see QuantArgs).
@@ -125,6 +133,49 @@ __device__ __forceinline__ int half_gate_count(const uint4 (&raw)[NV], const boo
   return (int)(__low2float(cnt2) + __high2float(cnt2));
 }
 
+// Unnormalised Walsh-Hadamard transform (Sylvester order: y[k] = sum_j x[j] (-1)^popcount(j & k)) of a
+// row of 8 * LPR * NV elements held by LPR lanes: lane sl keeps element i + 8 * (sl + LPR * v) in
+// f[v][i], so the index bits are i (in the vector), sl (across lanes: one shuffle per value and
+// stage) and v (across the lane's vectors).  One butterfly stage per index bit, any order.
+template <int LPR, int NV>
+__device__ __forceinline__ void wht_row(float (&f)[NV][8], int sl) {
+  static_assert((NV & (NV - 1)) == 0 && (LPR & (LPR - 1)) == 0, "power-of-two row");
+#pragma unroll
+  for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+    for (int v = 0; v < NV; ++v)
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if ((i & h) == 0) {
+          const float a = f[v][i], b = f[v][i + h];
+          f[v][i] = a + b;
+          f[v][i + h] = a - b;
+        }
+#pragma unroll
+  for (int h = 1; h < NV; h <<= 1)
+#pragma unroll
+    for (int v = 0; v < NV; ++v)
+      if ((v & h) == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float a = f[v][i], b = f[v + h][i];
+          f[v][i] = a + b;
+          f[v + h][i] = a - b;
+        }
+      }
+#pragma unroll
+  for (int h = 1; h < LPR; h <<= 1) {
+    const bool upper = (sl & h) != 0;
+#pragma unroll
+    for (int v = 0; v < NV; ++v)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float other = __shfl_xor_sync(0xffffffffu, f[v][i], h);
+        f[v][i] = upper ? other - f[v][i] : f[v][i] + other;
+      }
+  }
+}
+
 // LPR lanes own one row; each lane holds NV vectors of 8 elements.  The block walks the row groups
 // base0, base0 + stride, ... below row_end; returns whether one of this thread's rows tripped the gate.
 // mean_local (key mode, nullable): the mean row of every row of the walk, in shared memory (the fused
@@ -157,7 +208,7 @@ __device__ __forceinline__ int quant_rows_vec_body(const QuantArgs& a, int64_t b
       if (has[v]) raw[v] = __ldg(reinterpret_cast<const uint4*>(xr) + vi);
       Vec8<T>::unpack(raw[v], f[v]);
     }
-    if (MODE == kKeySmooth) {
+    if (MODE == kKeySmooth || (MODE == kRotate && a.mean != nullptr)) {
       const int64_t bh = (live && mean_local == nullptr) ? mean_row(a, row) : 0;
       const float* mr = mean_local != nullptr ? mean_local : a.mean + bh * a.K;
 #pragma unroll
@@ -179,6 +230,20 @@ __device__ __forceinline__ int quant_rows_vec_body(const QuantArgs& a, int64_t b
         Vec8<T>::unpack(t, f[v]);
         if (a.smoothed != nullptr) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.smoothed) + row * a.K + c0) = t;
       }
+    }
+    if (MODE == kRotate) {
+      // every lane of the warp takes part in the shuffles (rows past the end carry zeros)
+      if constexpr (MODE == kRotate && (NV & (NV - 1)) == 0) wht_row<LPR, NV>(f, sl);
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[v][i] *= a.rot_norm;
+        const uint4 t = Vec8<T>::pack(f[v]);     // the reference casts the rotated row back to the input dtype
+        Vec8<T>::unpack(t, f[v]);
+        if (has[v] && a.rotated != nullptr)
+          *reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.rotated) + row * a.K + (sl + v * LPR) * 8) = t;
+      }
+      if (a.q == nullptr) continue;   // rotation alone
     }
     float amax = 0.0f;
 #pragma unroll
@@ -270,6 +335,8 @@ __device__ __forceinline__ int quant_rows_vec_body(const QuantArgs& a, int64_t b
       if (MODE == kQueryFoldGate) {
         a.scale[row] = s * a.fold;
         if (a.plain_scale != nullptr) a.plain_scale[row] = s;
+      } else if (MODE == kRotate) {
+        a.scale[row] = s * a.fold;
       } else {
         a.scale[row] = s;
       }
@@ -362,6 +429,7 @@ int launch_2byte(const QuantArgs& a, cudaStream_t s) {
   const int kvec = a.K / 8;
   const bool vec_ok = (a.K % 8 == 0) && aligned16(a.x) && (MODE == kGateOnly || reinterpret_cast<uintptr_t>(a.q) % 8 == 0) &&
                       (MODE != kKeySmooth || (aligned16(a.mean) && (a.smoothed == nullptr || aligned16(a.smoothed))));
+  if (MODE == kRotate && !vec_ok) return SL8_ERR_MISALIGNED;   // the rotation lives in the vector kernel only
   // lanes per row x vectors per lane: four 16-byte vectors per lane amortise the per-row work
   // (reductions, scale, reciprocal, threshold) over 32 elements
   if (vec_ok && kvec <= 4) launch_vec<T, MODE, 2, 2>(a, s);
@@ -795,6 +863,27 @@ extern "C" int sl8_smooth_quant_k(const void* k, int dtype, int64_t BH, int64_t 
   a.x = k; a.q = k_i8; a.scale = k_scale; a.mean = mean; a.smoothed = k_smoothed;
   a.rows = BH * N; a.K = (int)D; a.rows_per_head = N > 0 ? N : 1;
   return dispatch<kKeySmooth>(a, dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int sl8_hadamard_quant_rows(const void* x, int dtype, int64_t rows, int64_t D, const float* mean,
+                                       int64_t rows_per_head, float fold, int8_t* q, float* scale, void* rotated,
+                                       void* stream) {
+  if (rows < 0 || D < 0) return SL8_ERR_BAD_SHAPE;
+  if (dtype != SL8_F16 && dtype != SL8_BF16) return SL8_ERR_BAD_DTYPE;
+  if (D < 32 || D > 1024 || (D & (D - 1)) != 0) return SL8_ERR_UNSUPPORTED;   // Sylvester order: power of two
+  if (rows == 0) return SL8_OK;
+  if (x == nullptr || (q == nullptr && rotated == nullptr) || (q != nullptr && scale == nullptr)) return SL8_ERR_NULL;
+  if (mean != nullptr && rows_per_head <= 0) return SL8_ERR_BAD_SHAPE;
+  if (!aligned16(x) || (rotated != nullptr && !aligned16(rotated)) || reinterpret_cast<uintptr_t>(q) % 8 != 0 ||
+      (mean != nullptr && !aligned16(mean)))
+    return SL8_ERR_MISALIGNED;
+  QuantArgs a{};
+  a.x = x; a.q = q; a.scale = scale; a.mean = mean; a.rotated = rotated;
+  a.rows = rows; a.K = (int)D; a.rows_per_head = mean != nullptr ? rows_per_head : 1; a.fold = fold;
+  a.rot_norm = (float)(1.0 / sqrt((double)D));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // (dispatch<> insists on code and scale pointers; the rotation alone has none)
+  return dtype == SL8_F16 ? launch_2byte<__half, kRotate>(a, s) : launch_2byte<__nv_bfloat16, kRotate>(a, s);
 }
 
 namespace {

@@ -331,10 +331,13 @@ def quantize_kv_cache(k, v, *, v_quant: str = "per_channel", rotate: bool = Fals
         raise ValueError(f"v_quant must be 'per_channel' or 'per_token', got {v_quant!r}")
     if v_quant == "per_token":
         raise NotImplementedError("superl8_b200: per-token V scales are served by the reference's paged decode only")
-    from .quant import quantize_v_perchannel, rotate_last
+    from .quant import _rotation_kernel_ok, hadamard_quantize_rows, quantize_v_perchannel, rotate_last
 
     mean = k_mean(k)
-    if rotate:
+    if rotate and _rotation_kernel_ok(k):   # smoothing, rotation and quantisation of a row in one pass
+        k_i8, k_scale, _ = hadamard_quantize_rows(k, mean=mean.reshape(*k.shape[:-2], k.shape[-1]))
+        k_scale = k_scale.squeeze(-1)
+    elif rotate:
         _, _, k_s = smooth_quantize_k(k, mean, want_smoothed=True)
         k_i8, k_scale = _C.quantize_i8_rowwise(rotate_last(k_s).reshape(-1, k.shape[-1]).contiguous())
         k_i8, k_scale = k_i8.reshape(k.shape), k_scale.reshape(*k.shape[:-1])
@@ -356,9 +359,13 @@ def attn_decode_cached(q, k_i8, k_scale, v_i8, v_scale, *, scale: float | None =
                            "per-channel V scales [B,H,D]")
     s = (1.0 / math.sqrt(q.shape[-1])) if scale is None else scale
     if rotate:
-        from .quant import rotate_last
-        q = rotate_last(q)
-    q_i8, q_scale, _ = quantize_q(q, s)
+        from .quant import LOG2E, _rotation_kernel_ok, hadamard_quantize_rows, rotate_last
+        if _rotation_kernel_ok(q):
+            q_i8, q_scale, _ = hadamard_quantize_rows(q, fold=s * LOG2E)
+        else:
+            q_i8, q_scale, _ = quantize_q(rotate_last(q), s)
+    else:
+        q_i8, q_scale, _ = quantize_q(q, s)
     ns = -1 if num_splits is None else int(num_splits)
     return _C.attn_int8_decode_kv8(q_i8, q_scale.reshape(q.shape[0], q.shape[1], 1).contiguous(), k_i8.contiguous(),
                                    k_scale.contiguous(), v_i8, v_scale, ns, context_lens=context_lens)

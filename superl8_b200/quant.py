@@ -236,12 +236,48 @@ def detect_q_outlier_domination(q: torch.Tensor, *, ratio_threshold: float = OUT
     return bool(q_outlier_flag(q, ratio_threshold).item())
 
 
+def _rotation_kernel_ok(x: torch.Tensor) -> bool:
+    d = x.shape[-1]
+    return x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and 32 <= d <= 1024 and d & (d - 1) == 0
+
+
+def hadamard_quantize_rows(x: torch.Tensor, *, mean: torch.Tensor | None = None, fold: float = 1.0,
+                           want_codes: bool = True, want_rotated: bool = False):
+    """[smooth] -> Hadamard rotation -> [quantise] of the rows of x [..., N, D] in one kernel pass
+    (sl8_hadamard_quant_rows): the rotate=True prologue of the reference (superl8/quant/core.py:186-194).
+    ``mean`` fp32 [..., D] per slab of N rows (K), None for Q.  Returns (codes or None,
+    scale [..., N, 1] * fold or None, rotated rows in x's dtype or None)."""
+    _require_cuda(x, "hadamard_quantize_rows")
+    if not _rotation_kernel_ok(x):
+        raise RuntimeError("superl8_b200 hadamard_quantize_rows: float16 or bfloat16, power-of-two last dim in [32, 1024]")
+    x = x.contiguous()
+    D = x.shape[-1]
+    rows = x.numel() // D
+    q = torch.empty(x.shape, dtype=torch.int8, device=x.device) if want_codes else None
+    scale = torch.empty((*x.shape[:-1], 1), dtype=torch.float32, device=x.device) if want_codes else None
+    rot = torch.empty_like(x) if want_rotated else None
+    if mean is not None:
+        mean = mean.to(device=x.device, dtype=torch.float32).contiguous()
+    if rows:
+        with torch.cuda.device(x.device):
+            rc = _lib.load().sl8_hadamard_quant_rows(
+                x.data_ptr(), _C._DTYPE[x.dtype], rows, D, None if mean is None else mean.data_ptr(),
+                x.shape[-2] if x.dim() >= 2 else 1, C.c_float(fold), None if q is None else q.data_ptr(),
+                None if scale is None else scale.data_ptr(), None if rot is None else rot.data_ptr(), _C._stream(x.device))
+        _lib.check(rc, "hadamard_quant_rows", 1)
+    return q, scale, rot
+
+
 def rotate_last(x: torch.Tensor) -> torch.Tensor:
     """Normalised Sylvester-Hadamard rotation of the last dim in fp32, cast back
-    (reference superl8/quant/rotation.py:28-51).  Off the measured path (default off)."""
+    (reference superl8/quant/rotation.py:28-51): a Walsh-Hadamard butterfly in the row quantiser's
+    registers for 16-bit CUDA tensors with a power-of-two last dim in [32, 1024], the reference's
+    own matmul formula in torch otherwise (fp32 input, other sizes)."""
     d = x.shape[-1]
     if d & (d - 1):
         raise ValueError(f"Hadamard rotation needs a power-of-two last dim, got {d}")
+    if _rotation_kernel_ok(x):
+        return hadamard_quantize_rows(x, want_codes=False, want_rotated=True)[2]
     h = torch.ones(1, 1, device=x.device, dtype=torch.float32)
     while h.shape[0] < d:
         h = torch.cat([torch.cat([h, h], 1), torch.cat([h, -h], 1)], 0)
@@ -255,6 +291,12 @@ def quantize_qk(q, k, *, softmax_scale: float | None = None, rotate: bool = Fals
     instead of computing it (the summation order of a mean is not portable bit for bit)."""
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(q.shape[-1])
+    if rotate and _rotation_kernel_ok(q) and _rotation_kernel_ok(k):
+        # smoothing, rotation and quantisation of a row in one pass each for Q and K
+        mean = k_mean(k, seqlens_k) if k_mean_override is None else k_mean_override
+        k_i8, k_scale, _ = hadamard_quantize_rows(k, mean=mean.reshape(*k.shape[:-2], k.shape[-1]))
+        q_i8, q_scale, _ = hadamard_quantize_rows(q, fold=softmax_scale * LOG2E)
+        return q_i8, q_scale, k_i8, k_scale, mean
     if rotate:
         mean = k_mean(k, seqlens_k) if k_mean_override is None else k_mean_override
         _ki8, _ks, k_s = smooth_quantize_k(k, mean, want_smoothed=True)

@@ -1,7 +1,7 @@
 """Generates tests/golden/*.npz by running the REFERENCE's own Python code on CPU.
 
 Run in a container that has the reference checkout (it cannot travel to a GPU box):
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [group ...]
 Inputs are seeded; inputs and the reference's outputs are both stored so the tests
 never need the reference.  16-bit floats are stored as raw bit patterns.
 """
@@ -219,16 +219,32 @@ def v_cache_cases():
         out[f"{name}__v_i8"], out[f"{name}__v_scale"] = v_i8.numpy(), v_scale.numpy()
     np.savez_compressed(OUT / "v_perchannel.npz", **out)
 
+def rotation_cases():
+    """rotate=True prologue: the Hadamard rotation alone and quantize_qk with it."""
+    from superl8.quant.rotation import rotate_last
+
+    out = {}
+    for name, x in {"f16_128": torch.randn(9, 128, generator=gen(61)).half() * 2.0,
+                    "bf16_64": torch.randn(7, 64, generator=gen(62)).bfloat16(),
+                    "f16_32": torch.randn(5, 32, generator=gen(63)).half()}.items():
+        out[f"{name}__x"] = bits(x)
+        out[f"{name}__rot"] = bits(rotate_last(x))
+    q = torch.randn(1, 4, 70, 128, generator=gen(64)).half()
+    k = torch.randn(1, 2, 90, 128, generator=gen(65)).half() + 0.5
+    k[..., 5] *= 12.0                              # an outlier channel: what the rotation is for
+    q_i8, q_scale, k_i8, k_scale, k_mean = quantize_qk(q, k, rotate=True)
+    out.update(q=bits(q), k=bits(k), q_i8=q_i8.numpy(), q_scale=q_scale.numpy(), k_i8=k_i8.numpy(),
+               k_scale=k_scale.numpy(), k_mean=k_mean.numpy())
+    np.savez_compressed(OUT / "rotation.npz", **out)
+
 
 if __name__ == "__main__":
     torch.set_num_threads(1)
-    quant_cases()
-    smooth_cases()
-    gate_cases()
-    qk_cases()
-    attention_cases()
-    backward_cases()
-    varlen_cases()
-    v_cache_cases()
+    cases = dict(quant=quant_cases, smooth=smooth_cases, gate=gate_cases, qk=qk_cases, attention=attention_cases,
+                 backward=backward_cases, varlen=varlen_cases, v_cache=v_cache_cases, rotation=rotation_cases)
+    only = sys.argv[2:]                            # optional: names of the case groups to regenerate
+    for name, fn in cases.items():
+        if not only or name in only:
+            fn()
     for f in sorted(OUT.glob("*.npz")):
         print(f.name, f.stat().st_size)

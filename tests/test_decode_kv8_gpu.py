@@ -82,3 +82,29 @@ def test_decode_kv8_context_lens_and_errors(device):
         _C.attn_int8_decode_kv8(k_i8[:, :, :1], k_scale[:, :, :1], k_i8, k_scale, v, v_scale, -1)
     with pytest.raises(NotImplementedError):
         s8.quantize_kv_cache(k, v, v_quant="per_token")
+
+
+def test_rotated_cache_keeps_the_logits_and_tightens_an_outlier_channel(device):
+    """rotate=True on both sides (cache built once, every query rotated the same way) leaves q.k
+    unchanged (reference superl8/ops.py:671-727 with superl8/quant/rotation.py): decode against the
+    rotated int8 cache meets the int8-V bar, and with an outlier channel in K it is closer to fp32
+    attention than the unrotated cache."""
+    gen = torch.Generator().manual_seed(81)
+    B, Hq, Hkv, N, D = 2, 8, 2, 1500, 128
+    q = torch.randn(B, Hq, 1, D, generator=gen).half()
+    k = torch.randn(B, Hkv, N, D, generator=gen).half()
+    k[..., 9] *= 25.0
+    v = torch.randn(B, Hkv, N, D, generator=gen).half()
+    ref = oracle.attention_fp32(q, k, v)
+    errs = {}
+    for rotate in (False, True):
+        k8, ks, v8, vs = s8.quantize_kv_cache(k.to(device), v.to(device), rotate=rotate)
+        out = s8.attn_decode_cached(q.to(device), k8, ks, v8, vs, rotate=rotate)
+        errs[rotate] = oracle.rel_l1(out, ref)
+        assert torch.isfinite(out.float()).all()
+    assert errs[True] <= 0.03 and errs[True] < errs[False]
+    # the one-pass cache quantiser equals its pieces: smooth, rotate, plain quantiser
+    k8, ks, _, _ = s8.quantize_kv_cache(k.to(device), v.to(device), rotate=True)
+    k_s = quant.smooth_quantize_k(k.to(device), quant.k_mean(k.to(device)), want_smoothed=True)[2]
+    r8, rs = quant.quantize_int8_rowwise(quant.rotate_last(k_s))
+    assert torch.equal(k8, r8) and torch.equal(ks, rs.squeeze(-1))

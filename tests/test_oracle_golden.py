@@ -71,6 +71,17 @@ def test_quantize_qk_matches_reference_cpu_branch():
         assert np.array_equal(k_mean.numpy(), g[f"{name}__k_mean"])
 
 
+def test_hadamard_rotation_and_rotated_quantize_qk_match_the_reference():
+    g = np.load(GOLDEN / "rotation.npz")
+    for name, dt in (("f16_128", "float16"), ("bf16_64", "bfloat16"), ("f16_32", "float16")):
+        x = from_bits(g[f"{name}__x"], dt)
+        assert torch.equal(oracle.rotate_last(x), from_bits(g[f"{name}__rot"], dt))
+    q, k = from_bits(g["q"], "float16"), from_bits(g["k"], "float16")
+    q_i8, q_scale, k_i8, k_scale, k_mean = oracle.quantize_qk(q, k, rule="cpu", rotate=True)
+    for got, key in ((q_i8, "q_i8"), (q_scale, "q_scale"), (k_i8, "k_i8"), (k_scale, "k_scale"), (k_mean, "k_mean")):
+        assert np.array_equal(got.numpy(), g[key]), key
+
+
 def test_fp32_attention_oracles():
     g = np.load(GOLDEN / "attention_fp32.npz")
     q, k, v = (from_bits(g[n], "float16") for n in ("q", "k", "v"))

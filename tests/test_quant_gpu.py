@@ -239,3 +239,76 @@ def test_one_launch_k_prologue_equals_the_two_step_path_bitwise(D, dtype, device
     assert _lib.load().sl8_k_prologue_fused_ok(_C._DTYPE[dtype], 2, 300, 80) == 0
     i1, s1, mean1, _ = quant.k_prologue(k)
     assert torch.equal(mean1, quant.k_mean(k)) and torch.equal(i1, quant.smooth_quantize_k(k, mean1)[0])
+
+
+# ---- rotate=True prologue: Hadamard rotation in the row quantiser's registers ----------------
+
+def _ulp_close(a: torch.Tensor, b: torch.Tensor, x: torch.Tensor, frac_exact: float) -> None:
+    """a and b are roundings of the same rotation of x computed in two summation orders: equal but for
+    a few elements that sat on a rounding boundary; those differ by one unit in the last place plus the
+    fp32 error of a sum of the row's terms (which counts where the terms cancel to something small)."""
+    a, b = a.cpu(), b.cpu()
+    assert a.dtype == b.dtype and a.shape == b.shape
+    same = (a == b).float().mean().item()
+    assert same >= frac_exact, same
+    step = torch.maximum(a.float().abs(), b.float().abs()) * (2.0 ** -10 if a.dtype == torch.float16 else 2.0 ** -7)
+    sum_err = x.float().abs().sum(-1, keepdim=True) / x.shape[-1] ** 0.5 * 2.0 ** -20
+    assert bool(((a.float() - b.float()).abs() <= step + sum_err + 1e-7).all())
+
+
+@pytest.mark.parametrize("D", [32, 64, 128, 256, 512])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_hadamard_rotation_kernel_against_the_matmul_formula(D, dtype, device):
+    x = (torch.randn(3, 5, 77, D, generator=torch.Generator().manual_seed(D)) * 2.0).to(dtype)
+    x[0, 0, 3] = 0
+    x[1, 2, 5, 7] = 300.0
+    got = quant.rotate_last(x.to(device))
+    assert got.dtype == dtype and got.shape == x.shape
+    _ulp_close(got, oracle.rotate_last(x), x, 0.97)
+    # orthonormal: rotating twice gives the input back (to the rounding of the two casts)
+    back = quant.rotate_last(got)
+    tol = 2e-3 if dtype == torch.float16 else 2e-2
+    assert torch.allclose(back.float().cpu(), x.float(), atol=tol * float(x.float().abs().max()), rtol=tol)
+    assert torch.equal(got, quant.rotate_last(x.to(device)))           # bitwise repeatable
+
+
+def test_hadamard_rotation_golden_vectors(device):
+    g = np.load(GOLDEN / "rotation.npz")
+    for name, dt in (("f16_128", "float16"), ("bf16_64", "bfloat16"), ("f16_32", "float16")):
+        x = from_bits(g[f"{name}__x"], dt)
+        _ulp_close(quant.rotate_last(x.to(device)), from_bits(g[f"{name}__rot"], dt), x, 0.97)
+
+
+@pytest.mark.parametrize("D", [64, 128, 256])
+def test_rotated_quantize_qk_is_the_oracles_up_to_the_rotation_order(D, device):
+    gen = torch.Generator().manual_seed(700 + D)
+    q = torch.randn(2, 4, 150, D, generator=gen).half()
+    k = torch.randn(2, 2, 190, D, generator=gen).half() + 0.5
+    k[..., 5] *= 12.0
+    oq_i8, oq_s, ok_i8, ok_s, omean = oracle.quantize_qk(q, k, rotate=True)
+    q_i8, q_s, k_i8, k_s, mean = quant.quantize_qk(q.to(device), k.to(device), rotate=True, k_mean_override=omean.to(device))
+    assert q_i8.shape == oq_i8.shape and q_s.shape == oq_s.shape and k_i8.shape == ok_i8.shape and k_s.shape == ok_s.shape
+    # a rotated value that rounds the other way moves its code by at most one and the row scale by one fp16 step
+    for got, ref in ((q_i8, oq_i8), (k_i8, ok_i8)):
+        d = (got.cpu().int() - ref.int()).abs()
+        assert int(d.max()) <= 1 and float((d != 0).float().mean()) < 0.02
+    for got, ref in ((q_s, oq_s), (k_s, ok_s)):
+        assert torch.allclose(got.cpu(), ref, rtol=1.1e-3, atol=0)
+    # the kernel's own pieces agree with each other bit for bit: rotation alone, then the plain quantiser
+    k_sm = quant.smooth_quantize_k(k.to(device), omean.to(device), want_smoothed=True)[2]
+    r_i8, r_s = quant.quantize_int8_rowwise(quant.rotate_last(k_sm))
+    assert torch.equal(r_i8, k_i8) and torch.equal(r_s, k_s)
+    # and attention through the rotated prologue keeps the int8 quality bar
+    v = torch.randn(2, 2, 190, D, generator=gen).half()
+    out = s8.attn_int8_fwd(q.to(device), k.to(device), v.to(device), rotate=True, internal_accuracy_gate=False)
+    oracle.assert_int8_quality(out, oracle.attention_fp32(q, k, v), what=f"rotated prologue D={D}")
+
+
+def test_hadamard_entry_rejects_what_it_cannot_rotate(device):
+    x = torch.randn(4, 96, device=device).half()
+    with pytest.raises(RuntimeError, match="power-of-two"):
+        quant.hadamard_quantize_rows(x)
+    with pytest.raises(ValueError, match="power-of-two"):
+        quant.rotate_last(x)
+    f = torch.randn(4, 64, device=device)                  # fp32: the matmul formula in torch
+    assert torch.allclose(quant.rotate_last(f).cpu(), oracle.rotate_last(f.cpu()), atol=1e-5)
