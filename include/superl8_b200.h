@@ -216,8 +216,10 @@ typedef struct sl8_fp16_fwd_params {
   float softmax_scale;
   int32_t backend;        /* SL8_BACKEND_* (tcgen05 for D = 64/128/256, else mma.sync) */
   /* optional additive bias [B|1, H|1, M, N] in natural-log units, element type = dtype, indexed in
-   * place through element strides (0 on broadcast axes); served by the mma.sync kernel
-   * (reference csrc/kernel/attn_fp16_fwd.cu:146-168) */
+   * place through element strides (0 on broadcast axes); served by both kernels -- on the
+   * tensor-memory kernel (D = 64/128/256) every thread adds its own query row's values to the
+   * finished logits, eight contiguous 16-byte aligned values per load, any other layout element
+   * by element (reference csrc/kernel/attn_fp16_fwd.cu:146-168, csrc/include/attn_fp16_fwd.cuh:176-178) */
   const void* mask;
   int64_t mask_stride_b, mask_stride_h, mask_stride_m, mask_stride_n;
   const int32_t* gate_flag;   /* device-side dispatch, as in sl8_fwd_params (nullable; tcgen05 backend, no mask) */

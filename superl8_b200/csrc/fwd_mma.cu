@@ -378,8 +378,8 @@ extern "C" int sl8_attn_fp16_fwd(const sl8_fp16_fwd_params* p, void* workspace, 
   if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->out)) return SL8_ERR_MISALIGNED;
   if ((int64_t)p->B * p->Hq > 65535) return SL8_ERR_TOO_LARGE;
   // the tensor-memory kernel takes the row maximum before scaling, so it wants a scale >= 0
-  const bool tc_ok = (p->D == 64 || p->D == 128 || p->D == 256) && p->N > 0 && p->mask == nullptr &&
-                     p->softmax_scale >= 0.f;
+  const bool tc_ok = (p->D == 64 || p->D == 128 || p->D == 256) && p->N > 0 && p->softmax_scale >= 0.f &&
+                     (p->mask == nullptr || p->gate_flag == nullptr);
   int backend = p->backend;
   if (backend == SL8_BACKEND_AUTO) backend = tc_ok ? SL8_BACKEND_TCGEN05 : SL8_BACKEND_MMA;
   if (backend == SL8_BACKEND_TCGEN05 || backend == SL8_BACKEND_TCGEN05_2Q) {

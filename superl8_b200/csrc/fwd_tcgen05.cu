@@ -126,6 +126,10 @@ struct TcArgs {
   // (w8_per_half = 0) or per row and 32-key half (w8_per_half != 0).
   const float* v_scale;
   int w8_per_half;
+  // 16-bit mode with an additive bias (kernel template BIAS): natural-log units, V's element type,
+  // strides in elements, 0 on broadcast axes (reference csrc/include/attn_fp16_fwd.cuh:176-178)
+  const void* mask;
+  int64_t mask_sb, mask_sh, mask_sm, mask_sn;
 };
 
 enum Bar {
@@ -138,7 +142,7 @@ enum Bar {
 
 SL8_TRACE_DEFINE()
 
-template <int D, typename VT, bool QK8, bool PACKED, bool W8 = false>
+template <int D, typename VT, bool QK8, bool PACKED, bool W8 = false, bool BIAS = false>
 __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                                                                const __grid_constant__ CUtensorMap k_map,
                                                                const __grid_constant__ CUtensorMap v_map,
@@ -394,6 +398,10 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
     const uint32_t t_o = t_row + C::COL_O;
     float m_run = -INFINITY, l_run = 0.f;
     float* const vs_smem = reinterpret_cast<float*>(smem + C::OFF_VS);
+    // this row of the additive bias (null for rows past the end: nothing is read for them)
+    const VT* const bias_row = (BIAS && m < m_len)
+                                   ? reinterpret_cast<const VT*>(a.mask) + (int64_t)b * a.mask_sb + (int64_t)hq * a.mask_sh + (int64_t)m * a.mask_sm
+                                   : nullptr;
     if (W8) {   // read back in the epilogue, after many block-wide barriers' worth of mbarrier traffic
       for (int c = row; c < D; c += 32 * kSoftmaxWarps) vs_smem[c] = __ldg(a.v_scale + (int64_t)kv_bh * D + c);
       named_sync(1, 32 * kSoftmaxWarps);
@@ -416,7 +424,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
       for (int c = 0; c < kTN / 32; ++c) tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
       if (warp == 0 && lane == 0) TR(8 * j + 2);
       const float* ksv = ks_smem + ss * kTN;
-      const bool need_mask = (n_block + kTN > n_len) || (a.causal && n_block + kTN - 1 > m_block + causal_diag) ||
+      const bool need_mask = BIAS || (n_block + kTN > n_len) || (a.causal && n_block + kTN - 1 > m_block + causal_diag) ||
                              (a.window_left >= 0 && n_block <= m_block + kTM - 1 + causal_diag - a.window_left);
       // Speculative single sweep: P is formed against the running max while the tile's own max is
       // still being collected.  Lazy rescale makes that the final answer whenever no row of the
@@ -433,7 +441,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
         mx = fmaxf(mxh[0], mxh[1]);
       } else {
         const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
-        if (need_mask) softmax_pass<QK8, true, true, VT>(r, ksv, qs, xs, neg_m, n_block, n_len, a.causal, qpos, a.window_left, t_s, mx, psum);
+        if constexpr (BIAS) softmax_pass<QK8, true, true, VT, true>(r, ksv, qs, xs, neg_m, n_block, n_len, a.causal, qpos, a.window_left, t_s, mx, psum, bias_row, a.mask_sn);
+        else if (need_mask) softmax_pass<QK8, true, true, VT>(r, ksv, qs, xs, neg_m, n_block, n_len, a.causal, qpos, a.window_left, t_s, mx, psum);
         else softmax_pass<QK8, false, true, VT>(r, ksv, qs, xs, neg_m, n_block, n_len, a.causal, qpos, a.window_left, t_s, mx, psum);
       }
       const float tmax = need_mask ? mx : mx * qs;
@@ -650,7 +659,7 @@ __global__ void __launch_bounds__(128) qk_logits_kernel(const __grid_constant__ 
 
 // Dense call: M, N = rows per head.  Packed call (a.cu_q set): M = longest query sequence (sizes
 // the grid), total_q / total_k = tokens in the packed tensors.
-template <int D, typename VT, bool QK8, bool W8 = false>
+template <int D, typename VT, bool QK8, bool W8 = false, bool BIAS = false>
 int launch_tc_impl(const void* q, const void* k, const void* v, int B, int Hq, int Hkv, int M, int N, const TcArgs& a,
                    cudaStream_t stream, int64_t total_q = 0, int64_t total_k = 0) {
   using C = TcCfg<D, QK8>;
@@ -677,8 +686,8 @@ int launch_tc_impl(const void* q, const void* k, const void* v, int B, int Hq, i
     SL8_CUDA_TRY(cudaFuncSetAttribute(fwd_tc_kernel<D, VT, QK8, kPk>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
     fwd_tc_kernel<D, VT, QK8, kPk><<<grid, kTcThreads, C::SMEM, stream>>>(q_map, k_map, v_map, o_map, a);
   } else {
-    SL8_CUDA_TRY(cudaFuncSetAttribute(fwd_tc_kernel<D, VT, QK8, false, W8>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-    fwd_tc_kernel<D, VT, QK8, false, W8><<<grid, kTcThreads, C::SMEM, stream>>>(q_map, k_map, v_map, o_map, a);
+    SL8_CUDA_TRY(cudaFuncSetAttribute(fwd_tc_kernel<D, VT, QK8, false, W8, BIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+    fwd_tc_kernel<D, VT, QK8, false, W8, BIAS><<<grid, kTcThreads, C::SMEM, stream>>>(q_map, k_map, v_map, o_map, a);
   }
   return cudaGetLastError() == cudaSuccess ? SL8_OK : SL8_ERR_CUDA;
 }
@@ -858,7 +867,7 @@ extern "C" int sl8_attn_int8_varlen(const sl8_varlen_params* p, void* workspace,
 int sl8_fwd_tc_fp16(const sl8_fp16_fwd_params* p, int* status, cudaStream_t s) {
   if (!tc_head_dim(p->D) || p->N == 0) return SL8_ERR_UNSUPPORTED;
   const int window_eff = p->window_left >= p->N ? -1 : p->window_left;   // such a window hides nothing
-  if (p->backend == SL8_BACKEND_TCGEN05_2Q && sl8_fwd_tc2_supported(p->D, window_eff, false)) {
+  if (p->backend == SL8_BACKEND_TCGEN05_2Q && p->mask == nullptr && sl8_fwd_tc2_supported(p->D, window_eff, false)) {
     Tc2Args t{};
     t.q = p->q; t.k = p->k; t.v = p->v; t.out = p->out; t.lse = p->lse;
     t.seqlens_q = p->seqlens_q; t.seqlens_k = p->seqlens_k; t.status = status;
@@ -873,6 +882,20 @@ int sl8_fwd_tc_fp16(const sl8_fp16_fwd_params* p, int* status, cudaStream_t s) {
   a.gate_flag = p->gate_flag; a.gate_want = p->gate_want;
   a.Hq = p->Hq; a.Hkv = p->Hkv; a.M = p->M; a.N = p->N; a.causal = p->causal; a.window_left = p->window_left;
   a.scale_log2 = p->softmax_scale * 1.4426950408889634f;
+  if (p->mask != nullptr) {   // the additive-bias instantiations
+    a.mask = p->mask; a.mask_sb = p->mask_stride_b; a.mask_sh = p->mask_stride_h;
+    a.mask_sm = p->mask_stride_m; a.mask_sn = p->mask_stride_n;
+    const bool h = p->dtype == SL8_F16;
+    switch (p->D) {
+      case 64: return h ? launch_tc_impl<64, __half, false, false, true>(p->q, p->k, p->v, p->B, p->Hq, p->Hkv, p->M, p->N, a, s)
+                        : launch_tc_impl<64, __nv_bfloat16, false, false, true>(p->q, p->k, p->v, p->B, p->Hq, p->Hkv, p->M, p->N, a, s);
+      case 128: return h ? launch_tc_impl<128, __half, false, false, true>(p->q, p->k, p->v, p->B, p->Hq, p->Hkv, p->M, p->N, a, s)
+                         : launch_tc_impl<128, __nv_bfloat16, false, false, true>(p->q, p->k, p->v, p->B, p->Hq, p->Hkv, p->M, p->N, a, s);
+      case 256: return h ? launch_tc_impl<256, __half, false, false, true>(p->q, p->k, p->v, p->B, p->Hq, p->Hkv, p->M, p->N, a, s)
+                         : launch_tc_impl<256, __nv_bfloat16, false, false, true>(p->q, p->k, p->v, p->B, p->Hq, p->Hkv, p->M, p->N, a, s);
+    }
+    return SL8_ERR_UNSUPPORTED;
+  }
   return p->dtype == SL8_F16
              ? launch_tc_d<__half, false>(p->D, p->q, p->k, p->v, p->B, p->Hq, p->Hkv, p->M, p->N, a, s)
              : launch_tc_d<__nv_bfloat16, false>(p->D, p->q, p->k, p->v, p->B, p->Hq, p->Hkv, p->M, p->N, a, s);

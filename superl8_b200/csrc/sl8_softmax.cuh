@@ -63,10 +63,17 @@ __host__ __device__ constexpr bool pair_uses_poly(int u) {
 // then the conversion / scaling / max of group g + 1 (work for the FMA and ALU pipes that does
 // not depend on them), and only then the sums and the packing of group g.  A warp issues in
 // order, so this is what lets the special-function unit run while the other pipes work.
-template <bool QK8, bool MASK, bool FIRST, typename VT>
+// BIAS (16-bit mode, with MASK and FIRST): an additive bias row in natural-log units (element type
+// VT, bias[n * bias_sn] for key n of this thread's query row; null for rows past the end) is added
+// to the finished logits as bias * log2(e) -- the mask argument of the reference's full-precision
+// forward (csrc/include/attn_fp16_fwd.cuh:176-178).  Eight contiguous, 16-byte aligned values are
+// one load; anything else is read element by element.
+template <bool QK8, bool MASK, bool FIRST, typename VT, bool BIAS = false>
 __device__ __forceinline__ void softmax_pass(uint32_t (&r)[kSweepCols], const float* __restrict__ ksv, float qs, float xs,
                                              float neg_m, int n_block, int n_len, int causal, int qpos,
-                                             int window_left, uint32_t t_p, float& mx, float& sum) {
+                                             int window_left, uint32_t t_p, float& mx, float& sum,
+                                             const VT* __restrict__ bias = nullptr, int64_t bias_sn = 0) {
+  static_assert(!BIAS || (MASK && FIRST && !QK8), "the bias joins the finished logits of the 16-bit mode");
   const float2 qs2 = make_float2(qs, qs), xs2 = make_float2(xs, xs), neg_m2 = make_float2(neg_m, neg_m);
   const float2* ks2 = reinterpret_cast<const float2*>(ksv);
   float mx0 = -INFINITY, mx1 = -INFINITY;
@@ -84,10 +91,35 @@ __device__ __forceinline__ void softmax_pass(uint32_t (&r)[kSweepCols], const fl
       if (FIRST && QK8) p[u] = mul2(make_float2((float)(int)r[2 * i], (float)(int)r[2 * i + 1]), ks2[i]);
       else p[u] = bits2(r[2 * i], r[2 * i + 1]);
     }
+    float bv[2 * G];
+    if (BIAS) {
+      const int gn0 = n_block + 2 * g * G;      // first key of the group (2 * G = 8 keys)
+#pragma unroll
+      for (int e = 0; e < 2 * G; ++e) bv[e] = 0.f;
+      if (bias != nullptr) {
+        const VT* bp = bias + (int64_t)gn0 * bias_sn;
+        if (bias_sn == 1 && gn0 + 2 * G <= n_len && (reinterpret_cast<uintptr_t>(bp) & 15) == 0) {
+          static_assert(G == 4, "one 16-byte load = the 8 keys of a group");
+          const uint4 w = __ldg(reinterpret_cast<const uint4*>(bp));
+          const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 t = unpack2<VT>(ww[e]);
+            bv[2 * e] = t.x;
+            bv[2 * e + 1] = t.y;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 2 * G; ++e)
+            if (gn0 + e < n_len) bv[e] = to_f32<VT>(__ldg(bp + (int64_t)e * bias_sn));
+        }
+      }
+    }
     if (FIRST && MASK) {
 #pragma unroll
       for (int u = 0; u < G; ++u) {
         p[u] = mul2(p[u], qs2);
+        if (BIAS) p[u] = __ffma2_rn(make_float2(bv[2 * u], bv[2 * u + 1]), make_float2(1.4426950408889634f, 1.4426950408889634f), p[u]);
         const int gn = n_block + 2 * (g * G + u);
         const bool v0 = (gn < n_len) && (!causal || gn <= qpos) && (window_left < 0 || gn > qpos - window_left);
         const bool v1 = (gn + 1 < n_len) && (!causal || gn + 1 <= qpos) && (window_left < 0 || gn + 1 > qpos - window_left);

@@ -257,6 +257,50 @@ def test_tensor_peak_probe_runs(device):
     assert i8 > f16 > 100.0          # int8 issues at twice the fp16 rate; both far above any CUDA-core figure
 
 
+@pytest.mark.parametrize("D,dtype", [(128, torch.float16), (64, torch.bfloat16), (256, torch.float16)])
+def test_additive_mask_on_the_tensor_memory_kernel(D, dtype, device):
+    """The bias is added by the tensor-memory kernel itself (not a detour through the mma.sync kernel):
+    both kernels against the fp32 oracle and against each other, for the layouts a caller can hand
+    over -- contiguous (one 16-byte load per eight keys), a row pitch that breaks the alignment, a
+    transposed view (element by element), broadcast axes -- and with seqlens."""
+    B, Hq, Hkv, M, N = 2, 4, 2, 200, 333
+    q, k, v = (t.to(device) for t in oracle.make_batch(148, B, Hq, Hkv, M, D, Sk=N, dtype=dtype))
+    g = torch.Generator().manual_seed(19)
+    tol = 5e-3 if dtype == torch.float16 else 2e-2
+    base = (torch.randn(B, Hq, M, N + 3, generator=g) * 2.0).to(dtype)
+    base[..., ::7, 3::11] = float("-inf")
+    base[0, 1, 5, :] = float("-inf")                         # a row that sees nothing
+    layouts = {
+        "contiguous": base[..., :N].contiguous().to(device),
+        "pitched (rows not 16-byte aligned)": base.to(device)[..., 1:N + 1],
+        "transposed": base[..., :N].transpose(2, 3).contiguous().to(device).transpose(2, 3),
+        "broadcast over heads": base[:, :1, :, :N].contiguous().to(device),
+        "broadcast over batch and heads": base[:1, :1, :, :N].contiguous().to(device),
+    }
+    for name, bias in layouts.items():
+        for causal in (False, True):
+            ref = oracle.attention_fp32(q.cpu(), k.cpu(), v.cpu(), causal=causal, mask=bias.cpu().expand(B, Hq, M, N))
+            ref = torch.nan_to_num(ref, nan=0.0)     # torch's softmax of a row of -inf is NaN; the kernels write 0 (l == 0)
+            tc = _C.attn_fp16_fwd(q, k, v, causal, None, -1, bias, backend=_lib.SL8_BACKEND_TCGEN05)
+            mma = _C.attn_fp16_fwd(q, k, v, causal, None, -1, bias, backend=_lib.SL8_BACKEND_MMA)
+            assert oracle.cos_sim(tc, ref) >= 0.9999 and oracle.rel_l1(tc, ref) <= tol, (name, causal)
+            assert oracle.cos_sim(tc, mma) >= 0.99999 and oracle.rel_l1(tc, mma) <= tol / 2, (name, causal)
+            assert torch.equal(tc, _C.attn_fp16_fwd(q, k, v, causal, None, -1, bias)), "the default backend where it serves"
+    # the row whose bias is -inf everywhere comes out as zeros
+    assert float(_C.attn_fp16_fwd(q, k, v, False, None, -1, layouts["contiguous"])[0, 1, 5].float().abs().max()) == 0.0
+    # ragged lengths: the bias of padded keys is never read into a valid row
+    sq = torch.tensor([150, 200], dtype=torch.int32, device=device)
+    sk = torch.tensor([333, 97], dtype=torch.int32, device=device)
+    bias = layouts["contiguous"]
+    out = _C.attn_fp16_fwd(q, k, v, False, None, -1, bias, seqlens_q=sq, seqlens_k=sk, backend=_lib.SL8_BACKEND_TCGEN05)
+    for bi in range(B):
+        mq, nk = int(sq[bi]), int(sk[bi])
+        ref = oracle.attention_fp32(q[bi:bi + 1, :, :mq].cpu(), k[bi:bi + 1, :, :nk].cpu(), v[bi:bi + 1, :, :nk].cpu(),
+                                    mask=bias[bi:bi + 1, :, :mq, :nk].cpu())
+        assert oracle.cos_sim(out[bi:bi + 1, :, :mq], torch.nan_to_num(ref, nan=0.0)) >= 0.9999
+    assert _C.device_status(device) == 0
+
+
 @pytest.mark.parametrize("D,dtype", [(128, torch.float16), (64, torch.bfloat16), (80, torch.float16)])
 def test_fp16_fwd_additive_mask(D, dtype, device):
     B, Hq, Hkv, M, N = 2, 4, 2, 150, 200
