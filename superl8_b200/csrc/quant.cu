@@ -346,7 +346,7 @@ __device__ __forceinline__ int quant_rows_vec_body(const QuantArgs& a, int64_t b
 }
 
 template <typename T, int LPR, int NV, int MODE>
-__global__ void __launch_bounds__(kQuantThreads) quant_rows_vec_kernel(QuantArgs a) {
+__global__ void __launch_bounds__(kQuantThreads, 4) quant_rows_vec_kernel(QuantArgs a) {
   const int64_t rows_per_block = (int64_t)(kQuantThreads / 32) * (32 / LPR);
   int any_outlier = quant_rows_vec_body<T, LPR, NV, MODE>(a, (int64_t)blockIdx.x * rows_per_block,
                                                           (int64_t)gridDim.x * rows_per_block, a.rows, nullptr);
