@@ -9,10 +9,16 @@ prologue and attention kernel -- on the 64-head causal S=8192 configuration ("cf
 B16 Hq64 Hkv8 S8192 D128, fp16 ~N(0,1), a seeded 1 % of Q and K channels x20).  With the
 gate on (default, the reference's behaviour) those outlier channels demote the call to the
 full-precision kernel; the same line also carries the pure int8 path (gate off), the
-split-KV decode (cfg5) and the quantiser, each with its own roofline figures.
+full-W8A8 route on a slice of the batch, the split-KV decode (cfg5, fp16 and int8 V), the
+backward pair and the quantiser, each with its own roofline figures; ``e2e`` -- the same step
+through ``attn_int8_fwd_host`` with Q, K, V and the output in pinned host memory, plus the
+PCIe bandwidth measured on those buffers alone; ``strong`` -- ONE cfg3 batch / cfg5's 128
+sequences split over the ranks; and ``shard_check`` -- a small batch computed sharded,
+all-gathered over NCCL and compared bitwise with the unsharded result.
 Every rank owns a full cfg3 batch (weak scaling over (batch, kv-head) units, no collective
 in the timed region).  ``--impl reference`` times the CPU restatement of the reference's
-path (oracle/) on the host cores instead.
+path (oracle/) on the host cores instead.  ``--kernel-case NAME`` launches one kernel family
+on a small case and prints nothing on stdout (for profilers).
 """
 
 from __future__ import annotations
