@@ -79,6 +79,55 @@ def test_host_side_validation_needs_no_device():
     assert lib.sl8_attn_int8_fwd(C.byref(f), C.c_void_p(16), 256, None) == _lib.ERR_UNSUPPORTED
 
 
+def test_host_side_plans_of_the_round_two_entries_need_no_device():
+    """Chunk plan of the host-buffer entry, eligibility of the one-launch K prologue, workspace of the
+    tensor-memory W8A8 route and the validation of the Hadamard entry: pure host code."""
+    lib = _lib.load()
+    cfg3 = dict(B=16, Hq=64, Hkv=8, M=8192, N=8192, D=128, dtype=0, causal=1, window_left=-1, ratio_threshold=12.0,
+                softmax_scale=0.0884)
+    # automatic plan: one chunk per batch element, the last element in quarters (short drain)
+    assert lib.sl8_attn_int8_fwd_host_chunks(C.byref(_lib.HostFwdParams(**cfg3))) == 15 + 4
+    for kvc, chunks in ((8, 16), (4, 32), (2, 64), (1, 128), (3, 64), (100, 16)):   # explicit width: uniform chunks (rounded down to a divisor of Hkv)
+        assert lib.sl8_attn_int8_fwd_host_chunks(C.byref(_lib.HostFwdParams(kv_heads_per_chunk=kvc, **cfg3))) == chunks, kvc
+    small = dict(cfg3, B=1, Hq=8, Hkv=2, M=1024, N=1024)                             # too small to cut: one chunk
+    assert lib.sl8_attn_int8_fwd_host_chunks(C.byref(_lib.HostFwdParams(**small))) == 1
+    assert lib.sl8_attn_int8_fwd_host_chunks(C.byref(_lib.HostFwdParams(**dict(cfg3, Hkv=3)))) == 0   # Hq % Hkv != 0
+    ws3 = lib.sl8_attn_int8_fwd_host_workspace(C.byref(_lib.HostFwdParams(slots=3, **cfg3)))
+    ws4 = lib.sl8_attn_int8_fwd_host_workspace(C.byref(_lib.HostFwdParams(slots=4, **cfg3)))
+    one = 8 * 8 * 8192 * 128 * 2                                                      # Q bytes of a batch element
+    assert ws3 % 256 == 0 and ws4 - ws3 == (ws3 - 256) // 3 and (ws3 - 256) // 3 >= 2 * one + 2 * one // 8
+    h = _lib.HostFwdParams(q=16, k=16, v=16, out=16, **cfg3)
+    assert lib.sl8_attn_int8_fwd_host(C.byref(h), None, 0, None) == _lib.ERR_WORKSPACE
+    assert lib.sl8_attn_int8_fwd_host(C.byref(_lib.HostFwdParams(**cfg3)), None, 0, None) == _lib.ERR_NULL
+    assert lib.sl8_attn_int8_fwd_host(C.byref(_lib.HostFwdParams(**dict(cfg3, D=80))), None, 0, None) == _lib.ERR_UNSUPPORTED
+    assert lib.sl8_attn_int8_fwd_host(C.byref(_lib.HostFwdParams(**dict(cfg3, M=0))), None, 0, None) == 0
+    # K prologue in one launch: 16-bit, the tensor-memory head dims, a slab short enough for the cluster's shared memory
+    ok = lib.sl8_k_prologue_fused_ok
+    assert ok(0, 128, 8192, 128) == 1 and ok(1, 8, 4096, 64) == 1 and ok(0, 1, 100, 256) == 1
+    assert ok(2, 128, 8192, 128) == 0 and ok(0, 128, 8192, 80) == 0 and ok(0, 70000, 8192, 128) == 0 and ok(0, 0, 8, 128) == 0
+    assert ok(0, 8, 1 << 20, 128) == 0            # 1024 chunks: their sums no longer fit the cluster's shared memory
+    assert lib.sl8_k_prologue(None, 0, 0, 8, 128, None, 1, None, None, None, None, None) == 0     # empty
+    assert lib.sl8_k_prologue(None, 0, 4, 8, 128, None, 1, None, None, None, None, None) == _lib.ERR_NULL
+    assert lib.sl8_k_prologue(16, 2, 4, 8, 128, None, 1, 16, 16, 16, None, None) == _lib.ERR_UNSUPPORTED
+    # W8A8 on the tensor-memory kernel: workspace = status area + V's codes as fp16
+    w = _lib.W8A8Params(B=2, Hq=8, Hkv=2, M=300, N=500, D=128, causal=1, causal_diag=200, per_warp_quant=1)
+    assert lib.sl8_attn_w8a8_fwd_tc_workspace(C.byref(w)) == 256 + 2 * 2 * 500 * 128 * 2
+    assert lib.sl8_attn_w8a8_fwd_tc(C.byref(w), None, 0, None) == _lib.ERR_NULL
+    for bad in (dict(D=32), dict(causal_diag=5), dict(N=0)):
+        wb = _lib.W8A8Params(**{**dict(B=2, Hq=8, Hkv=2, M=300, N=500, D=128, causal=1, causal_diag=200, per_warp_quant=1), **bad})
+        assert lib.sl8_attn_w8a8_fwd_tc(C.byref(wb), None, 0, None) == _lib.ERR_UNSUPPORTED, bad
+    assert lib.sl8_attn_w8a8_fwd_tc(C.byref(_lib.W8A8Params(B=2, Hq=8, Hkv=2, M=0, N=500, D=128)), None, 0, None) == 0
+    # Hadamard entry: 16-bit, power-of-two rows of 32 ... 1024 elements
+    hq = lib.sl8_hadamard_quant_rows
+    assert hq(None, 0, 0, 128, None, 1, 1.0, None, None, None, None) == 0
+    assert hq(16, 2, 4, 128, None, 1, 1.0, 16, 16, None, None) == _lib.ERR_BAD_DTYPE
+    for d in (96, 16, 2048):
+        assert hq(16, 0, 4, d, None, 1, 1.0, 16, 16, None, None) == _lib.ERR_UNSUPPORTED, d
+    assert hq(16, 0, 4, 128, None, 1, 1.0, None, None, None, None) == _lib.ERR_NULL            # nothing to write
+    assert hq(16, 0, 4, 128, None, 1, 1.0, 16, None, None, None) == _lib.ERR_NULL              # codes without scales
+    assert hq(24, 0, 4, 128, None, 1, 1.0, 16, 16, None, None) == _lib.ERR_MISALIGNED
+
+
 def test_split_heuristic_properties():
     lib = _lib.load()
     assert lib.sl8_choose_n_splits(0, 8) == 1
