@@ -40,6 +40,16 @@
 // Two blocks share an SM, so one block's softmax overlaps the other's MMAs.
 // Every mbarrier wait is bounded (sl8_common.cuh); on expiry the block raises the
 // workspace status word, frees tensor memory and exits.
+//
+// Template modes of the same kernel:
+//   PACKED  token-major packed tensors [tokens, heads, D] with cu_seqlens (the variable-length
+//           prefill, reference csrc/include/attn_varlen_fwd.cuh:25-190);
+//   W8      full W8A8 (reference csrc/include/attn_w8a8_fwd.cuh:93-222): V holds int8 codes as
+//           fp16, P is snapped to the reference's int8 grid per row and tile (or 32-key half)
+//           before it is packed, v_scale multiplies the output channels in the epilogue;
+//   BIAS    16-bit mode with the additive mask of the full-precision forward (reference
+//           csrc/include/attn_fp16_fwd.cuh:176-178): every tile takes the finished-logits sweep
+//           and each thread adds its own query row's bias values.
 #include "sl8_common.cuh"
 #include "sl8_fwd_tc2.cuh"
 #include "sl8_softmax.cuh"
