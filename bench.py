@@ -346,6 +346,37 @@ def copy_bandwidth(hin, din, dout, hout, world, reps=3):
     return res
 
 
+def host_placement(local: int) -> dict:
+    """Where this rank's host side sits relative to its GPU: the NUMA node of the GPU's PCIe slot, the
+    NUMA nodes of the CPUs the process may run on (pinned buffers are first touched there) and how
+    many CPUs that is.  Explains an end-to-end figure that does not scale with the GPUs: all ranks
+    of a box share one host memory system."""
+    out = {"cpus_allowed": len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else os.cpu_count()}
+    try:
+        bus = torch.cuda.get_device_properties(local).pci_bus_id
+        dom = torch.cuda.get_device_properties(local).pci_domain_id
+        dev = torch.cuda.get_device_properties(local).pci_device_id
+        path = Path(f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0/numa_node")
+        out["gpu_numa_node"] = int(path.read_text().strip()) if path.exists() else None
+    except Exception:
+        out["gpu_numa_node"] = None
+    try:
+        allowed = os.sched_getaffinity(0)
+        nodes = []
+        for node in sorted(Path("/sys/devices/system/node").glob("node[0-9]*")):
+            cpus = set()
+            for part in (node / "cpulist").read_text().strip().split(","):
+                if part:
+                    lo, _, hi = part.partition("-")
+                    cpus.update(range(int(lo), int(hi or lo) + 1))
+            if cpus & allowed:
+                nodes.append(int(node.name[4:]))
+        out["cpu_numa_nodes"] = nodes
+    except Exception:
+        out["cpu_numa_nodes"] = None
+    return out
+
+
 def workload_config(cfg, args, world):
     return {"workload": f"{cfg.name}: attn_int8_fwd causal B{cfg.B} Hq{cfg.Hq} Hkv{cfg.Hkv} S{cfg.S} D{cfg.D} fp16 "
                         f"~N(0,1), 1% of Q/K channels x20, per GPU",
@@ -483,6 +514,7 @@ def main():
     if not args.skip_extras:
         # what the PCIe link gives this step's buffers: Q alone in (2.1 GB), the output alone out, both at once
         e2e["copy_bandwidth"] = copy_bandwidth(hq, q, out, hout, world)
+        e2e["host"] = host_placement(local)
 
     # DRAM traffic per launch from the ncu captures summarised under profiles/ (a B = 2 slice of
     # cfg3 for prefill, 1 M rows for the quantiser, 16 sequences for decode), scaled to this launch
