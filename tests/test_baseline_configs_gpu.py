@@ -177,3 +177,39 @@ def test_cfg5_geometry_ragged_decode(device):
         o2 = _C.attn_int8_decode(q_i8, qs3, dk, dks, dv, ns, context_lens=dl)
         _same_int8_inputs(o2, out, what=f"cfg5 num_splits={ns}")
     assert _C.device_status() == 0
+
+
+def test_cfg3_full_size_properties_and_the_host_entry(device):
+    """The whole cfg3 batch (B16 Hq64 Hkv8 S8192 D128 causal, the bench's own tensors) through
+    size-independent properties: rows of P sum to one (V = 1 gives out = 1) on both precisions; a
+    (batch, kv-head) unit computed alone equals its slice of the batch bit for bit (units are
+    independent: what sharding and the host entry's chunks rely on); the host-buffer entry returns the
+    bits of the device-side call on the same tensors."""
+    cfg = workloads.PREFILL["cfg3"]
+    q, k, v = workloads.prefill_inputs(cfg, device)
+    g = cfg.Hq // cfg.Hkv
+    # rows of P sum to one, int8 path and its full-precision sibling
+    ones = torch.ones_like(v)
+    for gate in (False, True):                      # gate off: int8 kernel; gate on: the outliers demote
+        out = s8.attn_int8_fwd(q, k, ones, causal=True, internal_accuracy_gate=gate)
+        assert s8.ops.last_gate()[0] is (True if gate else None)
+        assert float((out.float() - 1.0).abs().max()) <= 2e-3, gate
+        del out
+    del ones
+    whole = s8.attn_int8_fwd(q, k, v, causal=True, internal_accuracy_gate="device")
+    assert torch.isfinite(whole.float()).all()
+    # units are independent, bit for bit
+    for b, h in ((0, 0), (7, 3), (15, 7)):
+        unit = s8.attn_int8_fwd(q[b:b + 1, h * g:(h + 1) * g].contiguous(), k[b:b + 1, h:h + 1].contiguous(),
+                                v[b:b + 1, h:h + 1].contiguous(), causal=True, internal_accuracy_gate="device")
+        assert torch.equal(unit, whole[b:b + 1, h * g:(h + 1) * g]), (b, h)
+    # the end-to-end entry: pinned host tensors in and out, 19 chunks on three streams
+    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+    del q, k, v
+    hout = torch.empty(whole.shape, dtype=torch.float16).pin_memory()
+    flags = torch.full((64,), -1, dtype=torch.int32).pin_memory()
+    s8.attn_int8_fwd_host(hq, hk, hv, hout, causal=True, gate_flags=flags)
+    torch.cuda.synchronize()
+    assert torch.equal(hout, whole.cpu())
+    assert all(int(f) == 1 for f in flags[:19]) and int(flags[19]) == -1      # every chunk demoted, 19 chunks
+    assert _C.device_status(device) == 0
