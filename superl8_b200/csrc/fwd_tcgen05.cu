@@ -70,6 +70,16 @@ constexpr int kSoftmaxWarps = 4;                       // warp w owns tensor-mem
 constexpr int kProducerWarp = kSoftmaxWarps, kMmaWarp = kSoftmaxWarps + 1;
 constexpr int kTcThreads = 32 * (kSoftmaxWarps + 2);
 constexpr int kScaleStages = 4;                        // ring of k_scale tiles
+// 16-bit mode loads the next tile's logits at the end of a tile (see EARLY in the kernel): measured
+// + 4 % on the S = 8192 causal workload, burst and sustained alike (18.37 -> 17.67 ms for the full
+// batch).  In int8 mode the same change LOSES (SL8_EARLY_LOAD=2 builds it: B = 4 slice 4.05 -> 4.49 ms
+// with all 64 accumulators carried, 4.05 -> 4.75 ms with the first 32): that instantiation sits at the
+// register limit of two blocks per SM and spills what it carries across the loop's back edge.
+// SL8_EARLY_LOAD=0 builds without any of it.
+#ifndef SL8_EARLY_LOAD
+#define SL8_EARLY_LOAD 1
+#endif
+constexpr bool kEarlyLoad = SL8_EARLY_LOAD != 0;
 #ifndef SL8_QK_PAIR
 #define SL8_QK_PAIR 0
 #endif
@@ -151,6 +161,13 @@ enum Bar {
 };
 
 SL8_TRACE_DEFINE()
+
+// One of two register arrays, chosen at compile time (the other has one element and disappears).
+template <bool FIRST, int NA, int NB>
+__device__ __forceinline__ auto& pick_regs(uint32_t (&a)[NA], uint32_t (&b)[NB]) {
+  if constexpr (FIRST) return a;
+  else return b;
+}
 
 template <int D, typename VT, bool QK8, bool PACKED, bool W8 = false, bool BIAS = false>
 __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_constant__ CUtensorMap q_map,
@@ -417,18 +434,34 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
       named_sync(1, 32 * kSoftmaxWarps);
     }
 
+    // EARLY (16-bit mode): the tile's 64 accumulator registers live across the loop's back edge, so
+    // that the next tile's logits can be loaded into them at the end of this tile.  The other
+    // modes keep them local to an iteration (the int8 instantiation sits at the register limit
+    // and spills when they are carried).
+    constexpr bool EARLY = kEarlyLoad && (!QK8 || SL8_EARLY_LOAD == 2);
+    constexpr int EARLY_CHUNKS = QK8 ? 1 : kTN / 32;   // 32-column pieces loaded early (experiment: int8 carries half)
+    uint32_t r_carried[EARLY ? kTN : 1];
+    bool loaded = false;   // the load of this tile's logits was issued at the end of the previous tile
     for (int j = 0; j < ntiles; ++j) {
+      uint32_t r_local[EARLY ? 1 : kTN];
+      uint32_t(&r)[kTN] = pick_regs<EARLY>(r_carried, r_local);
       const int n_block = n_begin + j * kTN;
       const int ss = j % kScaleStages;
       const uint32_t t_s = t_row + C::COL_S + kTN * (j & 1);
       if (warp == 0 && lane == 0) TR(8 * j + 0);
-      ok = mbar_wait(&bars[S_FULL + (j & 1)], (j >> 1) & 1, a.status);
-      if (!ok) break;
-      tc_fence_after();
+      if (!EARLY || !loaded) {
+        ok = mbar_wait(&bars[S_FULL + (j & 1)], (j >> 1) & 1, a.status);
+        if (!ok) break;
+        tc_fence_after();
+      }
       if (warp == 0 && lane == 0) TR(8 * j + 1);
-      uint32_t r[kTN];
+      if (!EARLY || !loaded) {
 #pragma unroll
-      for (int c = 0; c < kTN / 32; ++c) tc_ld32(t_s + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
+        for (int c = 0; c < kTN / 32; ++c) tc_ld32(t_s + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
+      } else {
+#pragma unroll
+        for (int c = EARLY_CHUNKS; c < kTN / 32; ++c) tc_ld32(t_s + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
+      }
       tc_wait_ld();
 #pragma unroll
       for (int c = 0; c < kTN / 32; ++c) tc_regs_ready(*reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
@@ -494,6 +527,19 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
       if (W8) w8_exp_pass<VT>(r, xs, (m_run == -INFINITY) ? 0.f : -m_run, mxh, a.w8_per_half != 0, t_s, psum);
       l_run = l_run * resc + psum;
       if (warp == 0 && lane == 0) TR(8 * j + 4);
+      // The tile's logits are dead (P is final): when the next tile's are already in tensor memory --
+      // its Q.K^T was queued a whole sweep ago -- start loading them now, so that the latency of the
+      // load runs under this tile's store wait, fence and arrival instead of in front of the sweep.
+      if constexpr (EARLY) {
+        loaded = false;
+        if (j + 1 < ntiles && __all_sync(0xffffffffu, mbar_test(&bars[S_FULL + ((j + 1) & 1)], ((j + 1) >> 1) & 1))) {
+          tc_fence_after();
+          const uint32_t t_n = t_row + C::COL_S + kTN * ((j + 1) & 1);
+#pragma unroll
+          for (int c = 0; c < EARLY_CHUNKS; ++c) tc_ld32(t_n + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
+          loaded = true;
+        }
+      }
       tc_wait_st();
       tc_fence_before();
       __syncwarp();

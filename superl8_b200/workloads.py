@@ -57,7 +57,9 @@ def outlier_channels(H: int, D: int, seed: int, frac: float = 0.01) -> torch.Ten
 
 
 def _cfg_index(cfg: PrefillCfg) -> int:
-    return int("".join(ch for ch in cfg.name if ch.isdigit())[:1])
+    """Seed base of a configuration: the first digit of its name ("cfg3" -> 3), 0 for a name without one."""
+    digits = "".join(ch for ch in cfg.name if ch.isdigit())
+    return int(digits[:1]) if digits else 0
 
 
 def _apply_outliers(cfg: PrefillCfg, q, k):
