@@ -68,7 +68,24 @@ constexpr int kTN = 64;                                // keys per tile
 static_assert(kTN == kSweepCols, "one softmax sweep per key tile");
 constexpr int kSoftmaxWarps = 4;                       // warp w owns tensor-memory lanes [32 w, 32 w + 32)
 constexpr int kProducerWarp = kSoftmaxWarps, kMmaWarp = kSoftmaxWarps + 1;
-constexpr int kTcThreads = 32 * (kSoftmaxWarps + 2);
+// Build option, off: a block of two full warpgroups (two idle warps behind the producer and the
+// issuer) whose second warpgroup hands registers to the softmax warpgroup after launch
+// (setmaxnreg: 128 per thread at launch, then 192 / 64 -- the producer and issuer code does not
+// fit in 56; the instruction has to sit INSIDE each role's branch, or ptxas allocates every role
+// within the launch bound and spills kilobytes), so that the softmax threads of the int8
+// instantiation can carry accumulators across tiles without spilling.  Measured on the B = 4 slice
+// of the S = 8192 causal workload: int8 with the early load 4.00-4.04 -> 4.18 ms (the early load
+// does not pay in int8 mode even with the registers for it), 16-bit 4.08-4.15 -> 3.96-4.08 ms
+// (inside the run-to-run spread).
+#ifndef SL8_WG_REGS
+#define SL8_WG_REGS 0
+#endif
+constexpr bool kWgRegs = SL8_WG_REGS != 0;
+constexpr int kTcThreads = kWgRegs ? 256 : 32 * (kSoftmaxWarps + 2);
+constexpr int kRegsSoftmax = 192, kRegsOther = 64;
+static_assert(!kWgRegs || 128 * kRegsSoftmax + 128 * kRegsOther <= 256 * 128, "the block's register pool");
+template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 constexpr int kScaleStages = 4;                        // ring of k_scale tiles
 // 16-bit mode loads the next tile's logits at the end of a tile (see EARLY in the kernel): measured
 // + 4 % on the S = 8192 causal workload, burst and sustained alike (18.37 -> 17.67 ms for the full
@@ -248,8 +265,11 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
   bool ok = true;
   if (threadIdx.x == 0) TR(8189);
 
-  if (warp == kProducerWarp) {
+  if (kWgRegs && warp > kMmaWarp) {
+    reg_dec<kRegsOther>();   // idle warps of the second warpgroup: they only lend their registers
+  } else if (warp == kProducerWarp) {
     // ======================= producer =======================
+    if (kWgRegs) reg_dec<kRegsOther>();
     if (lane == 0) {
       tma_prefetch_desc(&q_map);
       tma_prefetch_desc(&k_map);
@@ -323,6 +343,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
     }
   } else if (warp == kMmaWarp) {
     // ======================= MMA issuer =======================
+    if (kWgRegs) reg_dec<kRegsOther>();
     // Order of issue: QK_0, QK_1, then for every tile j: P.V_j, QK_{j+2}.  S has two buffers, so
     // the next tile's logits are already in tensor memory while the softmax warps work on
     // this one; QK_{j+2} reuses the buffer whose P the (earlier issued) P.V_j reads.
@@ -415,6 +436,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
     }
   } else {
     // ======================= softmax / correction / epilogue =======================
+    if (kWgRegs) reg_inc<kRegsSoftmax>();
     // Thread = query row: warp w reads and writes tensor-memory lanes [32 w, 32 w + 32).
     const int lg = warp;
     const int row = 32 * lg + lane;
@@ -438,8 +460,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) fwd_tc_kernel(const __grid_cons
     // that the next tile's logits can be loaded into them at the end of this tile.  The other
     // modes keep them local to an iteration (the int8 instantiation sits at the register limit
     // and spills when they are carried).
-    constexpr bool EARLY = kEarlyLoad && (!QK8 || SL8_EARLY_LOAD == 2);
-    constexpr int EARLY_CHUNKS = QK8 ? 1 : kTN / 32;   // 32-column pieces loaded early (experiment: int8 carries half)
+    constexpr bool EARLY = kEarlyLoad && (!QK8 || SL8_EARLY_LOAD == 2 || kWgRegs);
+    constexpr int EARLY_CHUNKS = (QK8 && !kWgRegs) ? 1 : kTN / 32;   // 32-column pieces loaded early (experiment: int8 carries half)
     uint32_t r_carried[EARLY ? kTN : 1];
     bool loaded = false;   // the load of this tile's logits was issued at the end of the previous tile
     for (int j = 0; j < ntiles; ++j) {
