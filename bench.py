@@ -529,6 +529,12 @@ def main():
                 "frac_of_burst_bf16": ach / peaks["bf16_tflops"], "frac_of_nominal_int8": ach / NOMINAL_INT8_TOPS,
                 "frac_of_probed_int8": ach / probe_i8, "frac_of_probed_f16": ach / probe_f16,
                 "frac_of_probed_mixed_ceiling": ach / (1.0 / (0.5 / probe_i8 + 0.5 / probe_f16)),
+                # one exponential per logit on a unit that delivers 16 per clock and SM: 4 * D operations ride on
+                # each, so softmax without exponentials elsewhere cannot pass 16 * 4 * D * SMs * clock
+                "exp_unit_ceiling": {"at_max_clock": 16 * 4 * cfg.D * 148 * (clocks.get("sm_max_mhz") or 1965.0) * 1e6 / 1e12,
+                                     "at_sampled_clock": 16 * 4 * cfg.D * 148 * (clocks.get("sm_mhz") or 1965.0) * 1e6 / 1e12,
+                                     "unit": "T(FL)OP/s",
+                                     "frac_at_sampled_clock": ach / (16 * 4 * cfg.D * 148 * (clocks.get("sm_mhz") or 1965.0) * 1e6 / 1e12)},
                 "traffic": NCU_TRAFFIC[key] * cfg.B, "ms_per_launch": kernel_ms}
 
     roofline = tensor_roofline(kern_ms, dominant + (" (gate demoted the call)" if demoted else ""), dominant)
