@@ -79,7 +79,7 @@ def test_host_side_validation_needs_no_device():
     assert lib.sl8_attn_int8_fwd(C.byref(f), C.c_void_p(16), 256, None) == _lib.ERR_UNSUPPORTED
 
 
-def test_host_side_plans_of_the_round_two_entries_need_no_device():
+def test_host_side_plans_and_argument_checks_need_no_device():
     """Chunk plan of the host-buffer entry, eligibility of the one-launch K prologue, workspace of the
     tensor-memory W8A8 route and the validation of the Hadamard entry: pure host code."""
     lib = _lib.load()
